@@ -1,0 +1,371 @@
+"""Block-table paged KV cache: page pool, free list, append, gather, release.
+
+The reference's layer gives every (sequence, head) a private run of
+``max_blocks`` adjacent pages (``python/barqtrain/kv_cache.py:66-70,84-89``) -
+a block table fixed at ``table[b][j] = j``.  This module is the general form
+its roadmap describes: one pool of pages per layer shared by all sequences, an
+explicit ``[slot, logical page] -> physical page`` table, a free list pages are
+drawn from and returned to, and a gather that turns a sequence's scattered
+pages back into contiguous K/V.  Logical content is defined by the reference:
+logical page ``j`` of a sequence equals the reference's ``keys[b, :, j]`` and a
+gathered sequence equals its ``current_tensors()`` slice.
+
+Layout in device memory, per layer: ``K`` and ``V`` pools of shape
+``[kv_heads, num_pages, page_size, head_dim]`` (a page of one head is
+contiguous - 4 KiB at page 16, head_dim 128, 2-byte elements - and a KV-head
+shard is a contiguous slice).  All layers share one block table and one set of
+lengths; the host owns both and mirrors them to the device.
+
+All device work goes through ``libbarqkv.so``; there is no CPU path.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, Iterable, List, Optional, Sequence, Tuple
+
+import torch
+
+from . import _ffi
+
+
+class PagePoolExhausted(RuntimeError):
+    """The free list cannot satisfy an allocation; nothing was changed."""
+
+
+class PageAllocator:
+    """Host-side free list with resident/peak accounting.
+
+    ``order`` fixes the initial free list (e.g. a seeded permutation, so tests
+    and benchmarks get fragmented but reproducible tables); pages are handed
+    out from its front and released pages go to its back.
+    """
+
+    def __init__(self, num_pages: int, order: Optional[Sequence[int]] = None, seed: Optional[int] = None):
+        if order is None:
+            if seed is None:
+                order = range(num_pages)
+            else:
+                g = torch.Generator().manual_seed(seed)
+                order = torch.randperm(num_pages, generator=g).tolist()
+        order = [int(p) for p in order]
+        if sorted(order) != list(range(num_pages)):
+            raise ValueError("free-list order must be a permutation of range(num_pages)")
+        self.num_pages = num_pages
+        self._free: List[int] = order
+        self._head = 0
+        self._owned = bytearray(num_pages)
+        self.pages_resident = 0
+        self.pages_peak = 0
+        self.alloc_calls = 0
+        self.release_calls = 0
+
+    @property
+    def pages_free(self) -> int:
+        return len(self._free) - self._head
+
+    def take(self, count: int) -> List[int]:
+        if count > self.pages_free:
+            raise PagePoolExhausted(f"need {count} pages, {self.pages_free} free of {self.num_pages}")
+        pages = self._free[self._head:self._head + count]
+        self._head += count
+        if self._head > 4096 and self._head * 2 > len(self._free):
+            del self._free[:self._head]
+            self._head = 0
+        for p in pages:
+            if self._owned[p]:
+                raise AssertionError(f"page {p} handed out twice")
+            self._owned[p] = 1
+        self.pages_resident += count
+        self.pages_peak = max(self.pages_peak, self.pages_resident)
+        self.alloc_calls += 1
+        return pages
+
+    def give_back(self, pages: Iterable[int]) -> None:
+        pages = list(pages)
+        for p in pages:
+            if not self._owned[p]:
+                raise AssertionError(f"page {p} released but not owned")
+            self._owned[p] = 0
+        self._free.extend(pages)
+        self.pages_resident -= len(pages)
+        self.release_calls += 1
+
+
+@dataclass(frozen=True)
+class PoolStats:
+    pages_total: int
+    pages_resident: int
+    pages_peak: int
+    bytes_per_page: int          # all layers, K and V, all local heads
+    bytes_resident: int
+    bytes_peak: int
+    sequences_live: int
+
+
+class _Descriptor:
+    """Per-step int32 batch description on the device:
+    ``[slots(n) | first(n) | cu(n + 1)]`` where ``first`` is the start position
+    (append) or the length (gather) and ``cu`` the packed row offsets."""
+
+    def __init__(self, n: int, dev: torch.Tensor, total: int, host_first: List[int], host_cu: List[int],
+                 slots: List[int]):
+        self.n = n
+        self.dev = dev
+        self.total = total
+        self.first = host_first
+        self.cu = host_cu
+        self.slots = slots
+        base = dev.data_ptr()
+        self.p_slots = base
+        self.p_first = base + 4 * n
+        self.p_cu = base + 8 * n
+
+
+class BlockTableKVCache:
+    """Paged K/V for ``num_layers`` layers over a shared block table.
+
+    ``num_kv_heads`` is the number of heads THIS device holds (the full count
+    divided by the tensor-parallel size when the cache is sharded by KV head).
+    """
+
+    def __init__(self, num_layers: int, num_kv_heads: int, head_dim: int, *, page_size: int = 16, num_pages: int,
+                 max_seqs: int, max_blocks_per_seq: int, dtype: torch.dtype = torch.bfloat16,
+                 device="cuda", free_order: Optional[Sequence[int]] = None, seed: Optional[int] = None,
+                 zero_pages: bool = True, gather_mode: str = "auto"):
+        self.backend = _ffi.require_cuda_backend()
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise RuntimeError("BlockTableKVCache needs a CUDA device: this build has no CPU path")
+        if self.device.index is None:
+            self.device = torch.device("cuda", torch.cuda.current_device())
+        self.num_layers, self.num_kv_heads, self.head_dim = num_layers, num_kv_heads, head_dim
+        self.page_size, self.num_pages = page_size, num_pages
+        self.max_seqs, self.max_blocks = max_seqs, max_blocks_per_seq
+        self.dtype = dtype
+        self.gather_mode = gather_mode
+        self.allocator = PageAllocator(num_pages, order=free_order, seed=seed)
+
+        shape = (num_layers, 2, num_kv_heads, num_pages, page_size, head_dim)
+        self.pools = (torch.zeros if zero_pages else torch.empty)(shape, dtype=dtype, device=self.device)
+        self.elem = self.pools.element_size()
+        page_elems = page_size * head_dim
+        self._pool_layout = _ffi.PoolLayout(num_kv_heads, head_dim, page_size, self.elem, num_pages, 0,
+                                            num_pages * page_elems, page_elems)
+        self._k_ptr = [self.pools[l, 0].data_ptr() for l in range(num_layers)]
+        self._v_ptr = [self.pools[l, 1].data_ptr() for l in range(num_layers)]
+
+        # block table: pinned host copy is authoritative, device copy follows
+        self.table_host = torch.full((max_seqs, max_blocks_per_seq), -1, dtype=torch.int32).pin_memory()
+        self.table_dev = torch.full((max_seqs, max_blocks_per_seq), -1, dtype=torch.int32, device=self.device)
+        self._table_np = self.table_host.numpy()
+        self._dirty_lo, self._dirty_hi = max_seqs, 0
+        self._table = _ffi.BlockTable(self.table_dev.data_ptr(), None, max_seqs, max_blocks_per_seq, 0, 0)
+
+        self.lengths: List[int] = [0] * max_seqs       # tokens held, per slot
+        self.pages_of: List[List[int]] = [[] for _ in range(max_seqs)]
+        self._free_slots: List[int] = list(range(max_seqs - 1, -1, -1))
+        self._slot_of: Dict[object, int] = {}
+
+        # staging ring for descriptors and table uploads (pinned; reuse guarded by events)
+        self._ring: List[Tuple[torch.Tensor, Optional[torch.cuda.Event]]] = []
+        self._ring_pos = 0
+        self._ring_words = 0
+        self._desc_dev: Dict[str, torch.Tensor] = {}
+        self._status = self.backend.status_word(self.device)
+
+    # -- sequences and pages ----------------------------------------------------
+    def open(self, seq_id=None) -> int:
+        """Claim a table row for a new sequence; returns its slot."""
+        if not self._free_slots:
+            raise RuntimeError(f"all {self.max_seqs} sequence slots are in use")
+        slot = self._free_slots.pop()
+        self._slot_of[slot if seq_id is None else seq_id] = slot
+        self.lengths[slot] = 0
+        return slot
+
+    def slot(self, seq_id) -> int:
+        return self._slot_of[seq_id]
+
+    def release(self, seq_id) -> None:
+        """Return a sequence's pages to the free list and free its slot (data stays in the pages)."""
+        slot = self._slot_of.pop(seq_id)
+        self.allocator.give_back(self.pages_of[slot])
+        used = len(self.pages_of[slot])
+        self.pages_of[slot] = []
+        self._table_np[slot, :used] = -1
+        self._mark_dirty(slot)
+        self.lengths[slot] = 0
+        self._free_slots.append(slot)
+
+    def reserve(self, slot: int, new_length: int) -> None:
+        """Make sure the slot owns pages for ``new_length`` tokens."""
+        need = -(-new_length // self.page_size)
+        have = len(self.pages_of[slot])
+        if need <= have:
+            return
+        if need > self.max_blocks:
+            raise ValueError(
+                f"paged KV cache capacity exceeded: requested {new_length}, "
+                f"max_cache_len={self.max_blocks * self.page_size}"
+            )
+        pages = self.allocator.take(need - have)
+        self.pages_of[slot].extend(pages)
+        self._table_np[slot, have:need] = pages
+        self._mark_dirty(slot)
+
+    def _mark_dirty(self, slot: int) -> None:
+        self._dirty_lo = min(self._dirty_lo, slot)
+        self._dirty_hi = max(self._dirty_hi, slot + 1)
+
+    # -- host -> device staging ---------------------------------------------------
+    def _stage(self, words: int) -> torch.Tensor:
+        """A pinned int32 buffer nobody is reading any more."""
+        if words > self._ring_words:
+            self._ring_words = max(2 * words, 1 << 16)
+            self._ring = [(torch.empty(self._ring_words, dtype=torch.int32).pin_memory(), None) for _ in range(8)]
+            self._ring_pos = 0
+        buf, event = self._ring[self._ring_pos]
+        if event is not None:
+            event.synchronize()
+        return buf
+
+    def _stage_done(self) -> None:
+        buf, _ = self._ring[self._ring_pos]
+        event = torch.cuda.Event()
+        event.record(torch.cuda.current_stream(self.device))
+        self._ring[self._ring_pos] = (buf, event)
+        self._ring_pos = (self._ring_pos + 1) % len(self._ring)
+
+    def _flush_table(self) -> None:
+        lo, hi = self._dirty_lo, self._dirty_hi
+        if lo >= hi:
+            return
+        words = (hi - lo) * self.max_blocks
+        buf = self._stage(words)
+        buf[:words].view(hi - lo, self.max_blocks).copy_(self.table_host[lo:hi])
+        self.table_dev[lo:hi].copy_(buf[:words].view(hi - lo, self.max_blocks), non_blocking=True)
+        self._stage_done()
+        self._dirty_lo, self._dirty_hi = self.max_seqs, 0
+
+    def _describe(self, kind: str, slots: Sequence[int], first: List[int], counts: List[int]) -> _Descriptor:
+        n = len(slots)
+        cu = [0] * (n + 1)
+        for i, c in enumerate(counts):
+            cu[i + 1] = cu[i] + c
+        words = 3 * n + 1
+        dev = self._desc_dev.get(kind)
+        if dev is None or dev.numel() < words:
+            dev = torch.empty(max(words, 3 * self.max_seqs + 1), dtype=torch.int32, device=self.device)
+            self._desc_dev[kind] = dev
+        buf = self._stage(words)
+        buf[:words] = torch.tensor(list(slots) + first + cu, dtype=torch.int32)
+        # the device buffer is laid out for this n: [slots | first | cu]
+        dev[:words].copy_(buf[:words], non_blocking=True)
+        self._stage_done()
+        return _Descriptor(n, dev, cu[n], first, cu, list(slots))
+
+    # -- append -------------------------------------------------------------------
+    def begin_append(self, slots: Sequence[int], counts: Sequence[int]) -> _Descriptor:
+        """Reserve pages for ``counts[i]`` new tokens of ``slots[i]`` and upload the step description.
+
+        Use the returned batch for every layer's ``append`` of this step, then ``end_append``.
+        """
+        counts = [int(c) for c in counts]
+        first = [self.lengths[s] for s in slots]
+        for s, c in zip(slots, counts):
+            self.reserve(s, self.lengths[s] + c)
+        self._flush_table()
+        return self._describe("append", slots, first, counts)
+
+    def append(self, layer: int, batch: _Descriptor, k_new: torch.Tensor, v_new: torch.Tensor) -> None:
+        """Scatter packed new rows ``[total_tokens, kv_heads, head_dim]`` (any strides with a
+        contiguous last dimension; ``[H, T, D].transpose(0, 1)`` works) into the layer's pages."""
+        if batch.total == 0:
+            return
+        if k_new.shape != v_new.shape or k_new.dim() != 3:
+            raise ValueError("k_new and v_new must both be [total_tokens, kv_heads, head_dim]")
+        if k_new.shape != (batch.total, self.num_kv_heads, self.head_dim):
+            raise ValueError(f"new rows have shape {tuple(k_new.shape)}, expected "
+                             f"{(batch.total, self.num_kv_heads, self.head_dim)}")
+        if k_new.dtype != self.dtype or v_new.dtype != self.dtype:
+            raise ValueError("new rows must be in the cache dtype")
+        if k_new.device != self.device or v_new.device != self.device:
+            raise ValueError("new rows must be on the cache device")
+        if k_new.stride(2) != 1 or v_new.stride() != k_new.stride():
+            k_new, v_new = k_new.contiguous(), v_new.contiguous()
+        rows = _ffi.RowsLayout(0, k_new.stride(0), k_new.stride(1), 1, 0)
+        self._table.slots = batch.p_slots
+        self.backend.append_raw(self._pool_layout, self._k_ptr[layer], self._v_ptr[layer], self._table,
+                                batch.p_first, batch.p_cu, batch.n, 0, batch.total,
+                                k_new.data_ptr(), v_new.data_ptr(), rows, self._status.data_ptr(),
+                                torch.cuda.current_stream(self.device).cuda_stream)
+
+    def end_append(self, batch: _Descriptor) -> None:
+        for i, s in enumerate(batch.slots):
+            self.lengths[s] = batch.first[i] + (batch.cu[i + 1] - batch.cu[i])
+
+    def append_step(self, slots: Sequence[int], counts: Sequence[int], k_layers, v_layers) -> None:
+        """All layers of one step: ``k_layers[l]`` / ``v_layers[l]`` are that layer's packed rows."""
+        batch = self.begin_append(slots, counts)
+        for layer in range(self.num_layers):
+            self.append(layer, batch, k_layers[layer], v_layers[layer])
+        self.end_append(batch)
+
+    # -- gather -------------------------------------------------------------------
+    def begin_gather(self, slots: Sequence[int]) -> _Descriptor:
+        lens = [self.lengths[s] for s in slots]
+        self._flush_table()
+        return self._describe("gather", slots, lens, lens)
+
+    def gather(self, layer: int, batch: _Descriptor, layout: str = "HND",
+               out: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
+               mode: Optional[str] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Materialise the batch's sequences back to back.
+
+        ``layout="HND"``: ``[kv_heads, total_tokens, head_dim]`` (sequence ``i`` is
+        ``[:, cu[i]:cu[i+1]]``, each head's rows contiguous: the SDPA operand).
+        ``layout="NHD"``: ``[total_tokens, kv_heads, head_dim]`` (the varlen
+        flash-attention operand).  ``batch.cu`` holds the offsets.
+        """
+        total, H, D = batch.total, self.num_kv_heads, self.head_dim
+        shape = (H, total, D) if layout == "HND" else (total, H, D)
+        if layout not in ("HND", "NHD"):
+            raise ValueError("layout must be 'HND' or 'NHD'")
+        if out is None:
+            k_out = torch.empty(shape, dtype=self.dtype, device=self.device)
+            v_out = torch.empty(shape, dtype=self.dtype, device=self.device)
+        else:
+            k_out, v_out = out
+            if tuple(k_out.shape) != shape or tuple(v_out.shape) != shape or not k_out.is_contiguous() \
+                    or not v_out.is_contiguous() or k_out.dtype != self.dtype or k_out.device != self.device:
+                raise ValueError(f"out tensors must be contiguous {shape} in the cache dtype on the cache device")
+        if total == 0:
+            return k_out, v_out
+        rows = _ffi.RowsLayout(0, D, total * D, 1, 0) if layout == "HND" else _ffi.RowsLayout(0, H * D, D, 1, 0)
+        self._table.slots = batch.p_slots
+        self.backend.gather_raw(self._pool_layout, self._k_ptr[layer], self._v_ptr[layer], self._table,
+                                batch.p_first, batch.p_cu, batch.n, total, k_out.data_ptr(), v_out.data_ptr(),
+                                rows, _ffi.MODES[mode or self.gather_mode], self._status.data_ptr(),
+                                torch.cuda.current_stream(self.device).cuda_stream)
+        return k_out, v_out
+
+    def gather_sequence(self, layer: int, seq_id, layout: str = "HND") -> Tuple[torch.Tensor, torch.Tensor]:
+        """One sequence as contiguous ``[H, len, D]`` (or ``[len, H, D]``)."""
+        return self.gather(layer, self.begin_gather([self.slot(seq_id)]), layout)
+
+    # -- inspection ---------------------------------------------------------------
+    def logical_page(self, layer: int, seq_id, j: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        """``[kv_heads, page_size, head_dim]`` views of logical page ``j`` of a sequence."""
+        page = self.pages_of[self.slot(seq_id)][j]
+        return self.pools[layer, 0, :, page], self.pools[layer, 1, :, page]
+
+    def check_device_status(self) -> None:
+        """Synchronise and raise if any kernel guard fired since the last check."""
+        self.backend.raise_on_status(self.device)
+
+    def stats(self) -> PoolStats:
+        per_page = self.num_layers * 2 * self.num_kv_heads * self.page_size * self.head_dim * self.elem
+        a = self.allocator
+        return PoolStats(a.num_pages, a.pages_resident, a.pages_peak, per_page, a.pages_resident * per_page,
+                         a.pages_peak * per_page, len(self._slot_of))

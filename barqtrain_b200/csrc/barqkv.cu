@@ -1,0 +1,851 @@
+// barqkv: paged KV-cache append and gather kernels for NVIDIA B200 (sm_100a)
+// and the C ABI declared in include/barqkv.h.
+//
+// The path is integer-indexed byte movement, so there is no arithmetic on the
+// payload and no tensor-core use: the roofline is HBM bandwidth.  Three kernels:
+//
+//   append_rows_kernel   new K/V rows -> page slots through the block table.
+//                        A CTA takes a tile of consecutive new tokens, resolves
+//                        each token's (entry, position, page) once into shared
+//                        memory, then all threads stream (token, head, K|V)
+//                        rows with the widest vector the alignment allows
+//                        (16 B for every real configuration: a head_dim row is
+//                        256 B, i.e. 16 lanes, so one warp moves the K row and
+//                        the V row of a (token, head) pair per instruction).
+//   gather_vector_kernel pages -> contiguous rows with 16-byte ld/st through
+//                        registers; serves every alignment and layout.
+//   gather_bulk_kernel   pages -> contiguous rows with cp.async.bulk:
+//                        global -> shared (mbarrier complete_tx) -> global
+//                        (bulk_group), a ring of stages per one-warp CTA, whole
+//                        (page, head) tiles of K and V per stage.  No multicast,
+//                        no tensor map, no peer memory.
+//
+// Both gathers share one work decomposition: every CTA scans the batch's page
+// counts into shared memory (the batch is small: <= kMaxEntries sequences),
+// takes an equal contiguous share of the flat (sequence, page) list, and
+// resolves block-table entries in groups of 32 into shared memory before the
+// copies that use them are issued.
+//
+// Device-side guards never trap and never spin without a bound.
+
+#include <cuda_runtime.h>
+#include <initializer_list>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "barqkv.h"
+
+namespace {
+
+constexpr int kMaxEntries = 8192;      // sequences per launch (shared-memory scan)
+constexpr int kAppendThreads = 256;
+constexpr int kAppendMaxTile = 64;     // new tokens resolved per CTA
+constexpr int kGatherThreads = 256;
+constexpr int kGroup = 32;             // (sequence, page) tiles resolved at a time
+constexpr int kUnroll = 4;
+constexpr int kBulkMaxStage = 32 * 1024;   // K page + V page of one head
+constexpr long long kWaitCycles = 2000000000LL;  // ~1 s: bound of any mbarrier wait
+
+thread_local char g_err[256] = "";
+
+int fail(int code, const char* msg) {
+    snprintf(g_err, sizeof(g_err), "%s", msg);
+    return code;
+}
+
+int fail_cuda(const char* what, cudaError_t e) {
+    snprintf(g_err, sizeof(g_err), "%s: %s", what, cudaGetErrorString(e));
+    return BARQKV_E_LAUNCH;
+}
+
+// --------------------------------------------------------------------------
+// kernel arguments (byte units everywhere)
+// --------------------------------------------------------------------------
+struct Table {
+    const int32_t* table;
+    const int32_t* slots;
+    int rows;
+    int stride;
+    int implicit;
+    int num_pages;
+};
+
+struct RowsB {            // barqkv_rows_layout in bytes
+    long long seq, tok, head;
+    int packed;
+};
+
+struct AppendArgs {
+    unsigned char* k_pool;
+    unsigned char* v_pool;
+    const unsigned char* k_new;
+    const unsigned char* v_new;
+    Table tb;
+    const int32_t* seq_start;
+    const int32_t* cu_new;
+    int n, tokens_per_entry, total_tokens, tile;
+    int heads, page_size, row_bytes;
+    long long pool_head, pool_page;   // bytes
+    RowsB nr;
+    // reference-layout extras
+    int32_t* seq_lens_rw;
+    int32_t* ticket;
+    int capacity;
+    int32_t* status;
+};
+
+struct GatherArgs {
+    const unsigned char* k_pool;
+    const unsigned char* v_pool;
+    unsigned char* k_out;
+    unsigned char* v_out;
+    Table tb;
+    const int32_t* seq_lens;
+    const int32_t* cu_out;
+    int n;
+    int heads, page_size, row_bytes;
+    long long pool_head, pool_page;
+    RowsB orow;
+    int stages;            // bulk kernel only
+    int32_t* status;
+};
+
+__device__ __forceinline__ void raise(int32_t* status, int bit) {
+    if (status) atomicOr(status, bit);
+}
+
+// Physical page of logical page j of batch entry i; -1 (and a status bit) if out of range.
+__device__ __forceinline__ long long resolve_page(const Table& tb, int i, int j, int32_t* status) {
+    const int row = tb.slots ? tb.slots[i] : i;
+    if (row < 0 || row >= tb.rows || j < 0 || j >= tb.stride) {
+        raise(status, BARQKV_S_BAD_SLOT);
+        return -1;
+    }
+    long long page;
+    if (tb.table) {
+        page = tb.table[(long long)row * tb.stride + j];
+    } else {
+        page = (long long)row * tb.implicit + j;
+    }
+    if (page < 0 || page >= tb.num_pages) {
+        raise(status, BARQKV_S_BAD_PAGE);
+        return -1;
+    }
+    return page;
+}
+
+// --------------------------------------------------------------------------
+// append
+// --------------------------------------------------------------------------
+template <typename V, bool LEGACY>
+__global__ void __launch_bounds__(kAppendThreads)
+append_rows_kernel(const AppendArgs a) {
+    __shared__ long long s_dst[kAppendMaxTile];   // byte offset of the token's slot in head 0's pool, -1 = skip
+    __shared__ long long s_src[kAppendMaxTile];   // byte offset of the token's head-0 row in the new rows
+    __shared__ int s_flag;
+
+    const int tid = threadIdx.x;
+    const int first_tok = blockIdx.x * a.tile;
+    const int ntok = min(a.tile, a.total_tokens - first_tok);
+
+    bool refuse = false;
+    if (LEGACY) {
+        // All-or-nothing capacity rule of the reference launcher: the longest
+        // sequence plus the new tokens must fit.
+        if (tid == 0) s_flag = 0;
+        __syncthreads();
+        int longest = 0;
+        for (int i = tid; i < a.n; i += blockDim.x) longest = max(longest, a.seq_start[i]);
+        if (longest + a.tokens_per_entry > a.capacity) s_flag = 1;
+        __syncthreads();
+        refuse = s_flag != 0;
+    }
+
+    if (tid < ntok && !refuse) {
+        const int r = first_tok + tid;
+        int i, t;
+        if (a.cu_new) {
+            int lo = 0, hi = a.n - 1;             // largest i with cu_new[i] <= r
+            while (lo < hi) {
+                const int mid = (lo + hi + 1) >> 1;
+                if (a.cu_new[mid] <= r) lo = mid; else hi = mid - 1;
+            }
+            i = lo;
+            t = r - a.cu_new[i];
+        } else {
+            i = r / a.tokens_per_entry;
+            t = r - i * a.tokens_per_entry;
+        }
+        const int pos = a.seq_start[i] + t;
+        const int j = pos / a.page_size;
+        const int slot = pos - j * a.page_size;
+        const long long page = pos < 0 ? -1 : resolve_page(a.tb, i, j, a.status);
+        s_dst[tid] = page < 0 ? -1 : page * a.pool_page + (long long)slot * a.row_bytes;
+        s_src[tid] = (long long)i * a.nr.seq + (long long)(a.nr.packed ? r : t) * a.nr.tok;
+    }
+    __syncthreads();
+
+    if (!refuse) {
+        const int vpr = a.row_bytes / (int)sizeof(V);      // vectors per row
+        const int per_tok = a.heads * 2 * vpr;             // order inside a token: head, K|V, vector
+        const int items = ntok * per_tok;
+        for (int base = tid; base < items; base += blockDim.x * kUnroll) {
+            V val[kUnroll];
+            V* out[kUnroll];
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                const int idx = base + u * blockDim.x;
+                out[u] = nullptr;
+                if (idx < items) {
+                    const int t = idx / per_tok;
+                    const int rem = idx - t * per_tok;
+                    const int hk = rem / vpr;
+                    const int vec = rem - hk * vpr;
+                    const int h = hk >> 1;
+                    const bool is_v = hk & 1;
+                    const long long d = s_dst[t];
+                    if (d >= 0) {
+                        const unsigned char* src = (is_v ? a.v_new : a.k_new) + s_src[t] + h * a.nr.head;
+                        unsigned char* dst = (is_v ? a.v_pool : a.k_pool) + d + h * a.pool_head;
+                        val[u] = __ldcs(reinterpret_cast<const V*>(src) + vec);
+                        out[u] = reinterpret_cast<V*>(dst) + vec;
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                if (out[u]) *out[u] = val[u];
+            }
+        }
+    }
+
+    if (LEGACY) {
+        // The launch also advances seq_lens (the reference does it with a
+        // second kernel).  Every CTA has read the lengths it needs above; the
+        // last one to take a ticket performs the update and re-arms the ticket.
+        __syncthreads();
+        if (tid == 0) {
+            __threadfence();
+            const int t = atomicAdd(a.ticket, 1);
+            s_flag = (t == (int)gridDim.x - 1) ? (refuse ? 2 : 1) : 0;
+        }
+        __syncthreads();
+        if (s_flag) {
+            if (s_flag == 1) {
+                for (int i = tid; i < a.n; i += blockDim.x) a.seq_lens_rw[i] += a.tokens_per_entry;
+            } else if (tid == 0) {
+                raise(a.status, BARQKV_S_CAPACITY);
+            }
+            if (tid == 0) *a.ticket = 0;
+        }
+    }
+}
+
+// --------------------------------------------------------------------------
+// gather: shared work decomposition
+// --------------------------------------------------------------------------
+// Exclusive prefix sum of per-entry page counts into s_cu[0..n]; returns nothing,
+// callers read s_cu[n] for the total after the trailing barrier.
+__device__ void scan_pages(const int32_t* lens, int n, int page_size, int* s_cu, int* s_part) {
+    const int tid = threadIdx.x;
+    const int nthr = blockDim.x;
+    const int chunk = (n + nthr - 1) / nthr;
+    const int lo = min(n, tid * chunk);
+    const int hi = min(n, lo + chunk);
+    int sum = 0;
+    for (int i = lo; i < hi; ++i) {
+        const int len = max(lens[i], 0);
+        sum += (len + page_size - 1) / page_size;
+    }
+    // inclusive scan inside the warp
+    const int lane = tid & 31;
+    int incl = sum;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += up;
+    }
+    if (lane == 31) s_part[tid >> 5] = incl;
+    __syncthreads();
+    int before = 0;
+    for (int w = 0; w < (tid >> 5); ++w) before += s_part[w];
+    int run = before + incl - sum;
+    for (int i = lo; i < hi; ++i) {
+        s_cu[i] = run;
+        const int len = max(lens[i], 0);
+        run += (len + page_size - 1) / page_size;
+    }
+    if (lo < hi && hi == n) s_cu[n] = run;      // the thread that owns the last entry
+    if (n == 0 && tid == 0) s_cu[0] = 0;
+    __syncthreads();
+}
+
+struct TileInfo {
+    long long src;   // byte offset of the physical page within head 0's pool
+    long long dst;   // byte offset of the page's first row (head 0) in the output
+    int rows;        // valid rows in this page, 0 = skip
+};
+
+// Resolve flat tile q (a (sequence, page) pair) using the scanned page counts.
+__device__ __forceinline__ TileInfo resolve_tile(const GatherArgs& a, const int* s_cu, int q) {
+    int lo = 0, hi = a.n - 1;                 // largest i with s_cu[i] <= q
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (s_cu[mid] <= q) lo = mid; else hi = mid - 1;
+    }
+    const int i = lo;
+    const int j = q - s_cu[i];
+    const int len = a.seq_lens[i];
+    TileInfo t;
+    t.rows = min(a.page_size, len - j * a.page_size);
+    const long long page = resolve_page(a.tb, i, j, a.status);
+    if (page < 0) t.rows = 0;
+    t.src = page * a.pool_page;
+    const long long base_tok = (a.orow.packed ? (long long)a.cu_out[i] : 0) + (long long)j * a.page_size;
+    t.dst = (long long)i * a.orow.seq + base_tok * a.orow.tok;
+    return t;
+}
+
+template <typename V>
+__global__ void __launch_bounds__(kGatherThreads)
+gather_vector_kernel(const GatherArgs a) {
+    extern __shared__ int s_dyn[];            // s_cu[n + 1]
+    __shared__ int s_part[kGatherThreads / 32];
+    __shared__ long long s_src[kGroup];
+    __shared__ long long s_dst[kGroup];
+    __shared__ int s_rows[kGroup];
+
+    int* s_cu = s_dyn;
+    scan_pages(a.seq_lens, a.n, a.page_size, s_cu, s_part);
+    const int total = s_cu[a.n];
+    const int per = (total + (int)gridDim.x - 1) / (int)gridDim.x;
+    const int lo = min(total, (int)blockIdx.x * per);
+    const int hi = min(total, lo + per);
+
+    const int tid = threadIdx.x;
+    const int vpr = a.row_bytes / (int)sizeof(V);
+    const int page_vecs = a.page_size * vpr;
+    const int per_tile = a.heads * 2 * page_vecs;          // order inside a tile: head, K|V, row, vector
+
+    for (int g0 = lo; g0 < hi; g0 += kGroup) {
+        const int nt = min(kGroup, hi - g0);
+        __syncthreads();
+        if (tid < nt) {
+            const TileInfo t = resolve_tile(a, s_cu, g0 + tid);
+            s_src[tid] = t.src;
+            s_dst[tid] = t.dst;
+            s_rows[tid] = t.rows;
+        }
+        __syncthreads();
+        const int items = nt * per_tile;
+        for (int base = tid; base < items; base += blockDim.x * kUnroll) {
+            V val[kUnroll];
+            V* out[kUnroll];
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                const int idx = base + u * blockDim.x;
+                out[u] = nullptr;
+                if (idx < items) {
+                    const int t = idx / per_tile;
+                    const int rem = idx - t * per_tile;
+                    const int hk = rem / page_vecs;
+                    const int pv = rem - hk * page_vecs;
+                    const int row = pv / vpr;
+                    const int vec = pv - row * vpr;
+                    if (row < s_rows[t]) {
+                        const int h = hk >> 1;
+                        const bool is_v = hk & 1;
+                        const unsigned char* src = (is_v ? a.v_pool : a.k_pool) + s_src[t] + h * a.pool_head;
+                        unsigned char* dst = (is_v ? a.v_out : a.k_out) + s_dst[t] + h * a.orow.head +
+                                             (long long)row * a.orow.tok;
+                        val[u] = __ldcs(reinterpret_cast<const V*>(src) + pv);
+                        out[u] = reinterpret_cast<V*>(dst) + vec;
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                if (out[u]) __stcs(out[u], val[u]);
+            }
+        }
+    }
+}
+
+// --------------------------------------------------------------------------
+// gather with bulk asynchronous copies
+// --------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_addr(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src_gmem, uint32_t bytes, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem),
+        "l"(__cvta_generic_to_global(src_gmem)), "r"(bytes), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* dst_gmem, uint32_t src_smem, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(__cvta_generic_to_global(dst_gmem)),
+                 "r"(src_smem), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// One warp per CTA.  A "unit" is one (page, head): the K page and the V page of
+// that head travel together through one ring stage.  Unit g is loaded at loop
+// step g and stored at step g + lag (lag = stages - 2), so `lag` loads are in
+// flight while at most two stores are still reading shared memory.
+__global__ void __launch_bounds__(32)
+gather_bulk_kernel(const GatherArgs a) {
+    extern __shared__ __align__(128) unsigned char s_raw[];
+    const int lane = threadIdx.x;
+    const int S = a.stages;
+    const int lag = S - 2;
+    const int page_bytes = a.page_size * a.row_bytes;
+
+    unsigned char* s_data = s_raw;                                          // [S][2][page_bytes]
+    unsigned long long* s_bar = reinterpret_cast<unsigned long long*>(s_data + (size_t)S * 2 * page_bytes);
+    long long* s_slot_dst = reinterpret_cast<long long*>(s_bar + S);        // [S] output offset incl. head
+    long long* s_src = s_slot_dst + S;                                      // [kGroup]
+    long long* s_dst = s_src + kGroup;                                      // [kGroup]
+    int* s_rows = reinterpret_cast<int*>(s_dst + kGroup);                   // [kGroup]
+    int* s_slot_rows = s_rows + kGroup;                                     // [S]
+    int* s_part = s_slot_rows + S;                                          // [1]
+    int* s_cu = s_part + 1;                                                 // [n + 1]
+
+    if (lane == 0) {
+        for (int s = 0; s < S; ++s) mbar_init(smem_addr(&s_bar[s]), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    scan_pages(a.seq_lens, a.n, a.page_size, s_cu, s_part);   // ends with a CTA barrier
+
+    const int total = s_cu[a.n];
+    const int per = (total + (int)gridDim.x - 1) / (int)gridDim.x;
+    const int lo = min(total, (int)blockIdx.x * per);
+    const int hi = min(total, lo + per);
+    const long long units = (long long)(hi - lo) * a.heads;
+    const bool contiguous_rows = a.orow.tok == a.row_bytes;   // a page's rows are adjacent in the output
+
+    int group_base = lo - kGroup;          // first tile of the resolved group
+    int tile = lo, head = 0;               // issue cursor
+    int islot = 0;                         // issue ring position
+    int cslot = 0;                         // consume ring position
+    uint32_t cphase = 0;
+    bool dead = false;
+
+    for (long long g = 0; g < units + lag; ++g) {
+        if (g < units && !dead) {
+            if (tile >= group_base + kGroup) {
+                group_base = tile;
+                __syncwarp();
+                if (group_base + lane < hi) {
+                    const TileInfo t = resolve_tile(a, s_cu, group_base + lane);
+                    s_src[lane] = t.src;
+                    s_dst[lane] = t.dst;
+                    s_rows[lane] = t.rows;
+                }
+                __syncwarp();
+            }
+            if (g >= S) {
+                bulk_wait_read<1>();       // the stores that read this stage two rounds ago are done with it
+                __syncwarp();
+            }
+            const int ti = tile - group_base;
+            const int rows = s_rows[ti];
+            const uint32_t bytes = (uint32_t)(rows * a.row_bytes);
+            const uint32_t bar = smem_addr(&s_bar[islot]);
+            if (lane == 0) {
+                s_slot_rows[islot] = rows;
+                s_slot_dst[islot] = s_dst[ti] + head * a.orow.head;
+                if (bytes) mbar_arrive_expect(bar, 2 * bytes); else mbar_arrive(bar);
+            }
+            __syncwarp();
+            if (lane < 2 && bytes) {
+                const unsigned char* src = (lane ? a.v_pool : a.k_pool) + s_src[ti] + head * a.pool_head;
+                bulk_load(smem_addr(s_data + ((size_t)islot * 2 + lane) * page_bytes), src, bytes, bar);
+            }
+            if (++head == a.heads) { head = 0; ++tile; }
+            if (++islot == S) islot = 0;
+        }
+        if (g >= lag && !dead) {
+            const uint32_t bar = smem_addr(&s_bar[cslot]);
+            const long long t0 = clock64();
+            while (!mbar_try_wait(bar, cphase)) {
+                if (clock64() - t0 > kWaitCycles) { dead = true; break; }
+            }
+            dead = __any_sync(0xffffffffu, dead);
+            if (!dead) {
+                const int rows = s_slot_rows[cslot];
+                const long long dst = s_slot_dst[cslot];
+                if (rows) {
+                    fence_async_smem();
+                    const uint32_t sk = smem_addr(s_data + (size_t)cslot * 2 * page_bytes);
+                    if (contiguous_rows) {
+                        if (lane < 2) {
+                            bulk_store((lane ? a.v_out : a.k_out) + dst, sk + lane * page_bytes,
+                                       (uint32_t)(rows * a.row_bytes));
+                        }
+                    } else {
+                        for (int op = lane; op < 2 * rows; op += 32) {
+                            const int r = op >> 1, kv = op & 1;
+                            bulk_store((kv ? a.v_out : a.k_out) + dst + (long long)r * a.orow.tok,
+                                       sk + kv * page_bytes + r * a.row_bytes, (uint32_t)a.row_bytes);
+                        }
+                    }
+                }
+                bulk_commit();
+                if (++cslot == S) { cslot = 0; cphase ^= 1; }
+            }
+        }
+    }
+    bulk_wait_read<0>();
+    if (dead && lane == 0) raise(a.status, BARQKV_S_TIMEOUT);
+}
+
+// --------------------------------------------------------------------------
+// host side
+// --------------------------------------------------------------------------
+struct DeviceInfo {
+    int sms = 0;
+    int smem_optin = 0;
+    bool bulk_attr_set = false;
+};
+DeviceInfo g_dev[64];
+
+DeviceInfo* device_info() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    DeviceInfo* d = &g_dev[dev];
+    if (d->sms == 0) {
+        int sms = 0, optin = 0;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return nullptr;
+        if (cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) return nullptr;
+        d->smem_optin = optin;
+        d->sms = sms;
+    }
+    return d;
+}
+
+inline bool aligned(const void* p, int a) { return (reinterpret_cast<uintptr_t>(p) % (uintptr_t)a) == 0; }
+inline bool multiple(long long v, int a) { return (v % a) == 0; }
+
+int check_pool(const barqkv_pool_layout* p) {
+    if (!p) return fail(BARQKV_E_INVALID, "pool layout is null");
+    if (p->num_heads <= 0 || p->head_dim <= 0 || p->page_size <= 0 || p->num_pages <= 0)
+        return fail(BARQKV_E_INVALID, "pool layout: num_heads, head_dim, page_size, num_pages must be positive");
+    if (p->elem_bytes != 1 && p->elem_bytes != 2 && p->elem_bytes != 4 && p->elem_bytes != 8)
+        return fail(BARQKV_E_INVALID, "pool layout: elem_bytes must be 1, 2, 4 or 8");
+    if (p->page_stride < (int64_t)p->page_size * p->head_dim)
+        return fail(BARQKV_E_INVALID, "pool layout: page_stride is smaller than one page");
+    if (p->head_stride < 0) return fail(BARQKV_E_INVALID, "pool layout: negative head_stride");
+    return 0;
+}
+
+int check_table(const barqkv_block_table* t, int n) {
+    if (!t) return fail(BARQKV_E_INVALID, "block table descriptor is null");
+    if (t->table_rows <= 0 || t->table_stride <= 0)
+        return fail(BARQKV_E_INVALID, "block table: table_rows and table_stride must be positive");
+    if (!t->table && t->implicit_pages_per_slot <= 0)
+        return fail(BARQKV_E_INVALID, "block table: implicit paging needs implicit_pages_per_slot > 0");
+    if (!t->slots && n > t->table_rows)
+        return fail(BARQKV_E_INVALID, "block table: more batch entries than table rows");
+    return 0;
+}
+
+Table make_table(const barqkv_block_table* t, int num_pages) {
+    Table tb;
+    tb.table = t->table;
+    tb.slots = t->slots;
+    tb.rows = t->table_rows;
+    tb.stride = t->table_stride;
+    tb.implicit = t->implicit_pages_per_slot;
+    tb.num_pages = num_pages;
+    return tb;
+}
+
+// Widest power-of-two vector (bytes) that divides every offset the kernels form.
+int vector_bytes(int row_bytes, std::initializer_list<long long> strides, std::initializer_list<const void*> ptrs) {
+    for (int v = 16; v >= 2; v >>= 1) {
+        bool ok = multiple(row_bytes, v);
+        for (long long s : strides) ok = ok && multiple(s, v);
+        for (const void* p : ptrs) ok = ok && aligned(p, v);
+        if (ok) return v;
+    }
+    return 1;
+}
+
+template <bool LEGACY>
+int launch_append(const AppendArgs& a, int vec, int grid, int threads, cudaStream_t st) {
+    switch (vec) {
+        case 16: append_rows_kernel<uint4, LEGACY><<<grid, threads, 0, st>>>(a); break;
+        case 8: append_rows_kernel<uint2, LEGACY><<<grid, threads, 0, st>>>(a); break;
+        case 4: append_rows_kernel<uint32_t, LEGACY><<<grid, threads, 0, st>>>(a); break;
+        case 2: append_rows_kernel<uint16_t, LEGACY><<<grid, threads, 0, st>>>(a); break;
+        default: append_rows_kernel<uint8_t, LEGACY><<<grid, threads, 0, st>>>(a); break;
+    }
+    const cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : fail_cuda("append launch", e);
+}
+
+// Tokens per CTA and threads per CTA: enough CTAs to cover the machine for small
+// (decode) batches, ~32 KiB of payload per CTA for bulk (prefill) batches.
+void append_shape(const DeviceInfo* d, int total_tokens, int heads, int row_bytes, int vec, int* tile, int* threads) {
+    const long long tok_bytes = 2LL * heads * row_bytes;
+    int t = (int)((32 * 1024 + tok_bytes - 1) / tok_bytes);
+    if (t > kAppendMaxTile) t = kAppendMaxTile;
+    const int want_ctas = 4 * d->sms;
+    while (t > 1 && (total_tokens + t - 1) / t < want_ctas) t >>= 1;
+    if (t < 1) t = 1;
+    const long long items = (long long)t * heads * 2 * (row_bytes / vec);
+    int th = kAppendThreads;
+    while (th > 32 && th / 2 >= items && th / 2 >= t) th >>= 1;
+    if (th < t) th = kAppendThreads;
+    *tile = t;
+    *threads = th;
+}
+
+}  // namespace
+
+extern "C" {
+
+int barqkv_version(void) { return BARQKV_VERSION; }
+
+const char* barqkv_last_error(void) { return g_err; }
+
+int barqkv_sm_count(void) {
+    DeviceInfo* d = device_info();
+    if (!d) return fail(BARQKV_E_LAUNCH, "no CUDA device is current");
+    return d->sms;
+}
+
+int barqkv_append(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,
+                  const barqkv_block_table* table,
+                  const int32_t* seq_start, const int32_t* cu_new,
+                  int32_t n, int32_t tokens_per_entry, int32_t total_tokens,
+                  const void* k_new, const void* v_new, const barqkv_rows_layout* new_rows,
+                  int32_t* status, barqkv_stream_t stream) {
+    if (int rc = check_pool(pool)) return rc;
+    if (n < 0 || total_tokens < 0) return fail(BARQKV_E_INVALID, "append: negative batch size or token count");
+    if (n == 0 || total_tokens == 0) return 0;
+    if (int rc = check_table(table, n)) return rc;
+    if (!k_pool || !v_pool || !k_new || !v_new || !seq_start || !new_rows)
+        return fail(BARQKV_E_INVALID, "append: null pointer argument");
+    if (!cu_new && (tokens_per_entry <= 0 || (long long)tokens_per_entry * n != total_tokens))
+        return fail(BARQKV_E_INVALID, "append: without cu_new, total_tokens must equal n * tokens_per_entry");
+    if (new_rows->packed && !cu_new && tokens_per_entry != 1)
+        return fail(BARQKV_E_INVALID, "append: packed rows with more than one token per entry need cu_new");
+    DeviceInfo* d = device_info();
+    if (!d) return fail(BARQKV_E_LAUNCH, "no CUDA device is current");
+
+    const long long e = pool->elem_bytes;
+    AppendArgs a;
+    memset(&a, 0, sizeof(a));
+    a.k_pool = static_cast<unsigned char*>(k_pool);
+    a.v_pool = static_cast<unsigned char*>(v_pool);
+    a.k_new = static_cast<const unsigned char*>(k_new);
+    a.v_new = static_cast<const unsigned char*>(v_new);
+    a.tb = make_table(table, pool->num_pages);
+    a.seq_start = seq_start;
+    a.cu_new = cu_new;
+    a.n = n;
+    a.tokens_per_entry = tokens_per_entry;
+    a.total_tokens = total_tokens;
+    a.heads = pool->num_heads;
+    a.page_size = pool->page_size;
+    a.row_bytes = (int)(pool->head_dim * e);
+    a.pool_head = pool->head_stride * e;
+    a.pool_page = pool->page_stride * e;
+    a.nr.seq = new_rows->seq_stride * e;
+    a.nr.tok = new_rows->tok_stride * e;
+    a.nr.head = new_rows->head_stride * e;
+    a.nr.packed = new_rows->packed;
+    a.status = status;
+
+    const int vec = vector_bytes(a.row_bytes, {a.pool_head, a.pool_page, a.nr.seq, a.nr.tok, a.nr.head},
+                                 {k_pool, v_pool, k_new, v_new});
+    int threads;
+    append_shape(d, total_tokens, a.heads, a.row_bytes, vec, &a.tile, &threads);
+    const int grid = (total_tokens + a.tile - 1) / a.tile;
+    return launch_append<false>(a, vec, grid, threads, static_cast<cudaStream_t>(stream));
+}
+
+int barqkv_append_legacy(void* key_cache, void* value_cache, int32_t* seq_lens,
+                         const void* k_new, const void* v_new, const barqkv_rows_layout* new_rows,
+                         int32_t batch, int32_t max_batch, int32_t heads, int32_t tokens,
+                         int32_t head_dim, int32_t max_blocks, int32_t page_size, int32_t elem_bytes,
+                         int32_t* ticket, int32_t* status, barqkv_stream_t stream) {
+    if (!key_cache || !value_cache || !seq_lens || !k_new || !v_new || !new_rows || !ticket)
+        return fail(BARQKV_E_INVALID, "append_legacy: null pointer argument");
+    if (batch < 0 || tokens < 0 || max_batch <= 0 || heads <= 0 || head_dim <= 0 || max_blocks <= 0 || page_size <= 0)
+        return fail(BARQKV_E_INVALID, "append_legacy: sizes must be positive");
+    if (batch > max_batch) return fail(BARQKV_E_INVALID, "key_cache batch dimension is too small");
+    if (elem_bytes != 1 && elem_bytes != 2 && elem_bytes != 4 && elem_bytes != 8)
+        return fail(BARQKV_E_INVALID, "append_legacy: elem_bytes must be 1, 2, 4 or 8");
+    if (new_rows->packed) return fail(BARQKV_E_INVALID, "append_legacy: new rows must be batched, not packed");
+    if ((long long)max_batch * heads * max_blocks > 0x7fffffffLL || (long long)batch * tokens > 0x7fffffffLL)
+        return fail(BARQKV_E_LIMIT, "append_legacy: cache has more than 2^31 pages or the call more than 2^31 tokens");
+    if (batch == 0 || tokens == 0) return 0;
+    DeviceInfo* d = device_info();
+    if (!d) return fail(BARQKV_E_LAUNCH, "no CUDA device is current");
+
+    const long long e = elem_bytes;
+    AppendArgs a;
+    memset(&a, 0, sizeof(a));
+    a.k_pool = static_cast<unsigned char*>(key_cache);
+    a.v_pool = static_cast<unsigned char*>(value_cache);
+    a.k_new = static_cast<const unsigned char*>(k_new);
+    a.v_new = static_cast<const unsigned char*>(v_new);
+    a.tb.table = nullptr;
+    a.tb.slots = nullptr;
+    a.tb.rows = max_batch;
+    a.tb.stride = max_blocks;
+    a.tb.implicit = heads * max_blocks;
+    a.tb.num_pages = max_batch * heads * max_blocks;
+    a.seq_start = seq_lens;
+    a.cu_new = nullptr;
+    a.n = batch;
+    a.tokens_per_entry = tokens;
+    a.total_tokens = batch * tokens;
+    a.heads = heads;
+    a.page_size = page_size;
+    a.row_bytes = (int)(head_dim * e);
+    a.pool_page = (long long)page_size * head_dim * e;
+    a.pool_head = (long long)max_blocks * a.pool_page;
+    a.nr.seq = new_rows->seq_stride * e;
+    a.nr.tok = new_rows->tok_stride * e;
+    a.nr.head = new_rows->head_stride * e;
+    a.nr.packed = 0;
+    a.seq_lens_rw = seq_lens;
+    a.ticket = ticket;
+    a.capacity = max_blocks * page_size;
+    a.status = status;
+
+    const int vec = vector_bytes(a.row_bytes, {a.pool_head, a.pool_page, a.nr.seq, a.nr.tok, a.nr.head},
+                                 {key_cache, value_cache, k_new, v_new});
+    int threads;
+    append_shape(d, a.total_tokens, heads, a.row_bytes, vec, &a.tile, &threads);
+    const int grid = (a.total_tokens + a.tile - 1) / a.tile;
+    return launch_append<true>(a, vec, grid, threads, static_cast<cudaStream_t>(stream));
+}
+
+int barqkv_gather(const barqkv_pool_layout* pool, const void* k_pool, const void* v_pool,
+                  const barqkv_block_table* table,
+                  const int32_t* seq_lens, const int32_t* cu_out, int32_t n,
+                  int64_t total_tokens_hint,
+                  void* k_out, void* v_out, const barqkv_rows_layout* out_rows,
+                  int32_t mode, int32_t* status, barqkv_stream_t stream) {
+    if (int rc = check_pool(pool)) return rc;
+    if (n < 0) return fail(BARQKV_E_INVALID, "gather: negative batch size");
+    if (n == 0) return 0;
+    if (n > kMaxEntries) return fail(BARQKV_E_LIMIT, "gather: more than 8192 sequences in one call; split the batch");
+    if (int rc = check_table(table, n)) return rc;
+    if (!k_pool || !v_pool || !k_out || !v_out || !seq_lens || !out_rows)
+        return fail(BARQKV_E_INVALID, "gather: null pointer argument");
+    if (out_rows->packed && !cu_out) return fail(BARQKV_E_INVALID, "gather: packed output needs cu_out");
+    if (mode < BARQKV_MODE_AUTO || mode > BARQKV_MODE_BULK) return fail(BARQKV_E_INVALID, "gather: unknown mode");
+    DeviceInfo* d = device_info();
+    if (!d) return fail(BARQKV_E_LAUNCH, "no CUDA device is current");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+    const long long e = pool->elem_bytes;
+    GatherArgs a;
+    memset(&a, 0, sizeof(a));
+    a.k_pool = static_cast<const unsigned char*>(k_pool);
+    a.v_pool = static_cast<const unsigned char*>(v_pool);
+    a.k_out = static_cast<unsigned char*>(k_out);
+    a.v_out = static_cast<unsigned char*>(v_out);
+    a.tb = make_table(table, pool->num_pages);
+    a.seq_lens = seq_lens;
+    a.cu_out = cu_out;
+    a.n = n;
+    a.heads = pool->num_heads;
+    a.page_size = pool->page_size;
+    a.row_bytes = (int)(pool->head_dim * e);
+    a.pool_head = pool->head_stride * e;
+    a.pool_page = pool->page_stride * e;
+    a.orow.seq = out_rows->seq_stride * e;
+    a.orow.tok = out_rows->tok_stride * e;
+    a.orow.head = out_rows->head_stride * e;
+    a.orow.packed = out_rows->packed;
+    a.status = status;
+
+    const int vec = vector_bytes(a.row_bytes, {a.pool_head, a.pool_page, a.orow.seq, a.orow.tok, a.orow.head},
+                                 {k_pool, v_pool, k_out, v_out});
+    const long long page_bytes = (long long)a.page_size * a.row_bytes;
+    const bool bulk_ok = vec == 16 && 2 * page_bytes <= kBulkMaxStage;
+    if (mode == BARQKV_MODE_BULK && !bulk_ok)
+        return fail(BARQKV_E_INVALID, "gather: bulk mode needs 16-byte aligned rows and strides and pages of at most 16 KiB");
+    const bool use_bulk = mode == BARQKV_MODE_BULK || (mode == BARQKV_MODE_AUTO && bulk_ok);
+
+    // Upper bound of (sequence, page) tiles, to keep tiny gathers from launching a full machine.
+    long long tiles_bound = 0x7fffffffLL;
+    if (total_tokens_hint > 0) tiles_bound = (total_tokens_hint + a.page_size - 1) / a.page_size + n;
+
+    if (use_bulk) {
+        int S = (int)(64 * 1024 / (2 * page_bytes));
+        if (S > 8) S = 8;
+        if (S < 3) S = 3;
+        a.stages = S;
+        const size_t smem = (size_t)S * 2 * page_bytes + (size_t)S * 8 /*bar*/ + (size_t)S * 8 /*slot dst*/ +
+                            2 * kGroup * 8 + kGroup * 4 + (size_t)S * 4 + 4 + (size_t)(n + 1) * 4;
+        if ((long long)smem > d->smem_optin)
+            return fail(BARQKV_E_LIMIT, "gather: bulk pipeline does not fit in shared memory");
+        if (!d->bulk_attr_set) {
+            const cudaError_t ce = cudaFuncSetAttribute(gather_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                        d->smem_optin);
+            if (ce != cudaSuccess) return fail_cuda("gather: cudaFuncSetAttribute", ce);
+            d->bulk_attr_set = true;
+        }
+        int per_sm = (int)((220 * 1024) / (smem + 1024));
+        if (per_sm < 1) per_sm = 1;
+        if (per_sm > 8) per_sm = 8;
+        long long grid = (long long)d->sms * per_sm;
+        const long long units_bound = tiles_bound * a.heads;
+        const long long want = (units_bound + 2 * S - 1) / (2 * S);   // at least two ring rounds per CTA
+        if (want < grid) grid = want < 1 ? 1 : want;
+        gather_bulk_kernel<<<(int)grid, 32, smem, st>>>(a);
+    } else {
+        const size_t smem = (size_t)(n + 1) * 4;
+        long long grid = (long long)d->sms * 8;
+        const long long want = (tiles_bound + 3) / 4;
+        if (want < grid) grid = want < 1 ? 1 : want;
+        switch (vec) {
+            case 16: gather_vector_kernel<uint4><<<(int)grid, kGatherThreads, smem, st>>>(a); break;
+            case 8: gather_vector_kernel<uint2><<<(int)grid, kGatherThreads, smem, st>>>(a); break;
+            case 4: gather_vector_kernel<uint32_t><<<(int)grid, kGatherThreads, smem, st>>>(a); break;
+            case 2: gather_vector_kernel<uint16_t><<<(int)grid, kGatherThreads, smem, st>>>(a); break;
+            default: gather_vector_kernel<uint8_t><<<(int)grid, kGatherThreads, smem, st>>>(a); break;
+        }
+    }
+    const cudaError_t ce = cudaGetLastError();
+    return ce == cudaSuccess ? 0 : fail_cuda("gather launch", ce);
+}
+
+}  // extern "C"

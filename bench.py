@@ -1,0 +1,488 @@
+"""Benchmark of the paged KV-cache hot path (append + gather) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl barqkv|reference]
+
+Workload (the Llama-3-8B-shaped decode configuration): 32 layers, 8 KV heads
+(sharded N ways by KV head), head_dim 128, bf16, page size 16; 64 sequences
+with seeded prompt lengths uniform in [512, 4096] prefilled into a pool whose
+free list is a seeded permutation; then decode steps.  One STEP is one pass of
+the hot path over the batch: for every layer, append one new token per
+sequence through the block table, then gather every sequence's pages into
+contiguous ``[H, sum_len, D]`` K and V (the attention operand).
+
+The printed JSON line follows the driver's contract; ``value`` is whole-job
+GB/s of ALGORITHMIC bytes (append 4*N_tok*H*D*e + gather 4*sum_len*H*D*e per
+layer, K and V, read + write; index traffic excluded) with inputs resident in
+HBM; ``e2e`` is the same metric through the public Python API with the step's
+new K/V rows coming from pinned host memory and the status word read back.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+METRIC = "paged KV append+gather HBM GB/s"
+UNIT = "GB/s"
+NOMINAL_PEAK_GBS = 8000.0
+FALLBACK_PEAK_GBS = 6650.0
+
+CFG = dict(name="llama3-8b-decode", layers=32, kv_heads=8, head_dim=128, dtype="bf16", page_size=16, batch=64,
+           prompt_lo=512, prompt_hi=4096, seed=1236)
+
+
+def measured_peak():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+        except Exception:  # noqa: BLE001
+            pass
+    return FALLBACK_PEAK_GBS, "fallback"
+
+
+def seeded_lengths():
+    g = torch.Generator().manual_seed(CFG["seed"])
+    lens = torch.randint(CFG["prompt_lo"], CFG["prompt_hi"] + 1, (CFG["batch"],), generator=g).tolist()
+    return g, lens
+
+
+# ---------------------------------------------------------------------------
+# clocks
+# ---------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            time.sleep(0.3)
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        self.summary = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out = ""
+        sm, mx, reasons = [], [], set()
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, flag in zip(self.NAMES, parts[3:7]):
+                if flag.lower() == "active":
+                    reasons.add(name)
+        if sm:
+            self.summary = {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                            "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------
+# the GPU arm
+# ---------------------------------------------------------------------------
+class DecodeWorkload:
+    def __init__(self, world: int, rank: int, device: torch.device, total_steps: int):
+        from barqtrain_b200 import BlockTableKVCache
+
+        self.L, self.D, self.ps, self.B = CFG["layers"], CFG["head_dim"], CFG["page_size"], CFG["batch"]
+        if CFG["kv_heads"] % world:
+            raise SystemExit(f"--gpus must divide the {CFG['kv_heads']} KV heads")
+        self.H = CFG["kv_heads"] // world                   # KV-head shard of this rank
+        self.dtype = torch.bfloat16
+        self.device = device
+        g, self.prompts = seeded_lengths()
+        final = [n + total_steps for n in self.prompts]
+        num_pages = sum(-(-n // self.ps) for n in final)
+        order = torch.randperm(num_pages, generator=g).tolist()
+        self.cache = BlockTableKVCache(self.L, self.H, self.D, page_size=self.ps, num_pages=num_pages,
+                                       max_seqs=self.B, max_blocks_per_seq=-(-max(final) // self.ps),
+                                       dtype=self.dtype, device=device, free_order=order, zero_pages=False)
+        self.slots = [self.cache.open(i) for i in range(self.B)]
+        self.row_bytes = self.D * 2
+
+        # prefill (untimed set-up): the prompts' K/V through the same append kernel, 2048-token chunks
+        gen = torch.Generator(device=device).manual_seed(CFG["seed"] + rank)
+        chunk = 2048
+        done = [0] * self.B
+        while any(d < n for d, n in zip(done, self.prompts)):
+            counts = [min(chunk, n - d) for d, n in zip(done, self.prompts)]
+            total = sum(counts)
+            k = torch.randn(total, self.H, self.D, generator=gen, device=device, dtype=torch.float32).to(self.dtype)
+            v = torch.randn(total, self.H, self.D, generator=gen, device=device, dtype=torch.float32).to(self.dtype)
+            batch = self.cache.begin_append(self.slots, counts)
+            for layer in range(self.L):
+                self.cache.append(layer, batch, k, v)
+            self.cache.end_append(batch)
+            done = [d + c for d, c in zip(done, counts)]
+        # per-step new rows, [L, B, H, D]; a few distinct sets cycled
+        self.new_k = [torch.randn(self.L, self.B, self.H, self.D, generator=gen, device=device,
+                                  dtype=torch.float32).to(self.dtype) for _ in range(4)]
+        self.new_v = [torch.randn(self.L, self.B, self.H, self.D, generator=gen, device=device,
+                                  dtype=torch.float32).to(self.dtype) for _ in range(4)]
+        max_total = sum(final)
+        self.out = [(torch.empty(self.H, max_total, self.D, dtype=self.dtype, device=device),
+                     torch.empty(self.H, max_total, self.D, dtype=self.dtype, device=device)) for _ in range(2)]
+        self.host_k = torch.empty(self.L, self.B, self.H, self.D, dtype=self.dtype).pin_memory()
+        self.host_v = torch.empty(self.L, self.B, self.H, self.D, dtype=self.dtype).pin_memory()
+        self.host_k.copy_(self.new_k[0])
+        self.host_v.copy_(self.new_v[0])
+        self.stage_k = torch.empty_like(self.new_k[0])
+        self.stage_v = torch.empty_like(self.new_v[0])
+        self.host_status = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self.step_no = 0
+        torch.cuda.synchronize(device)
+
+    def sum_len(self) -> int:
+        return sum(self.cache.lengths[s] for s in self.slots)
+
+    def step_bytes(self, sum_len_after: int):
+        """Algorithmic bytes of one step on THIS rank: (append, gather)."""
+        per_tok = 4 * self.H * self.row_bytes
+        return self.B * per_tok * self.L, sum_len_after * per_tok * self.L
+
+    def step(self, k_all: torch.Tensor, v_all: torch.Tensor, events=None):
+        """One pass of the hot path: per layer, append B tokens then gather all sequences."""
+        cache = self.cache
+        ab = cache.begin_append(self.slots, [1] * self.B)
+        cache.end_append(ab)                       # lengths now include this step's token
+        gb = cache.begin_gather(self.slots)
+        total = gb.total
+        for layer in range(self.L):
+            cache.append(layer, ab, k_all[layer], v_all[layer])
+            if events is not None:
+                e0 = torch.cuda.Event(enable_timing=True)
+                e1 = torch.cuda.Event(enable_timing=True)
+                e0.record()
+            self._gather_into(layer, gb, total)
+            if events is not None:
+                e1.record()
+                events.append((e0, e1, total))
+        self.step_no += 1
+        return total
+
+    def _gather_into(self, layer: int, gb, total: int):
+        # write into a preallocated [H, total, D] prefix of the reusable output buffers
+        ko, vo = self.out[layer & 1]
+        k_view = ko.view(-1)[: self.H * total * self.D].view(self.H, total, self.D)
+        v_view = vo.view(-1)[: self.H * total * self.D].view(self.H, total, self.D)
+        self.cache.gather(layer, gb, "HND", out=(k_view, v_view))
+
+    def resident_step(self, events=None):
+        i = self.step_no % 4
+        return self.step(self.new_k[i], self.new_v[i], events)
+
+    def e2e_step(self):
+        """Public-API step with host inputs: H2D of the step's new K/V, the hot path, D2H of the status word."""
+        self.stage_k.copy_(self.host_k, non_blocking=True)
+        self.stage_v.copy_(self.host_v, non_blocking=True)
+        total = self.step(self.stage_k, self.stage_v)
+        self.host_status.copy_(self.cache._status, non_blocking=True)
+        torch.cuda.current_stream(self.device).synchronize()
+        if int(self.host_status[0]) != 0:
+            raise RuntimeError(f"device guard fired: status {int(self.host_status[0])}")
+        return total
+
+
+def run_barqkv(args):
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torchrun --nproc-per-node N for --gpus N > 1")
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+
+    from barqtrain_b200 import _ffi
+
+    backend = _ffi.require_cuda_backend()
+    K, W = args.steps, max(args.warmup, 3)
+    e2e_steps = max(3, min(K, 10))
+    total_steps = W + K + 3 + e2e_steps + 4
+    wl = DecodeWorkload(world, rank, device, total_steps)
+
+    def barrier():
+        torch.cuda.synchronize(device)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- resident leg: `value` -------------------------------------------------
+    for _ in range(W):
+        wl.resident_step()
+    barrier()
+    launches0 = backend.launches
+    events = []
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    app_bytes = gat_bytes = 0
+    with ClockSampler(local) as clocks:
+        barrier()
+        start.record()
+        for _ in range(K):
+            total = wl.resident_step(events)
+            a, g = wl.step_bytes(total)
+            app_bytes += a
+            gat_bytes += g
+        stop.record()
+        barrier()
+    launches = backend.launches - launches0
+    ms = max_over_ranks(start.elapsed_time(stop))
+    job_bytes = (app_bytes + gat_bytes) * world
+    value = job_bytes / (ms * 1e-3) / 1e9
+    status = backend.read_status(device)
+    if status:
+        raise SystemExit(f"device guard fired during the timed region: status {status}")
+
+    # ---- roofline of the dominant kernel (gather), per launch ---------------------
+    peak, peak_kind = measured_peak()
+    per_tok = 4 * wl.H * wl.row_bytes
+    durs = [e0.elapsed_time(e1) * 1e-3 for e0, e1, _ in events]
+    gbytes = [t * per_tok for _, _, t in events]
+    avg_dur = sum(durs) / len(durs)
+    achieved = (sum(gbytes) / len(gbytes)) / avg_dur / 1e9
+    roofline = {"bound": "hbm", "kernel": "gather_bulk_kernel", "achieved": round(achieved, 1), "peak": peak,
+                "peak_kind": peak_kind, "unit": "GB/s", "frac": round(achieved / peak, 4),
+                "frac_of_nominal_8TBs": round(achieved / NOMINAL_PEAK_GBS, 4),
+                "avg_launch_us": round(avg_dur * 1e6, 2), "bytes_per_launch": int(sum(gbytes) / len(gbytes)),
+                "traffic": None}
+    tpath = ROOT / "profiles" / "gather_bulk_traffic.json"
+    if tpath.exists():
+        try:
+            t = json.loads(tpath.read_text())
+            # DRAM bytes per algorithmic byte measured by ncu on a smaller case, scaled to this launch
+            roofline["traffic"] = int(t["dram_bytes_per_algorithmic_byte"] * roofline["bytes_per_launch"])
+        except Exception:  # noqa: BLE001
+            pass
+
+    # ---- end-to-end leg ---------------------------------------------------------
+    for _ in range(3):
+        wl.e2e_step()
+    barrier()
+    e2e_bytes = 0
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        total = wl.e2e_step()
+        a, g = wl.step_bytes(total)
+        e2e_bytes += a + g
+    barrier()
+    e2e_s = max_over_ranks(time.perf_counter() - t0)
+    e2e_value = e2e_bytes * world / e2e_s / 1e9
+    h2d = 2 * wl.host_k.numel() * wl.host_k.element_size()
+
+    line = {
+        "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": round(ms / K, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": CFG["name"], "layers": wl.L, "kv_heads": CFG["kv_heads"], "kv_heads_per_gpu": wl.H,
+                   "head_dim": wl.D, "page_size": wl.ps, "batch": wl.B, "prompt_lengths": "uniform[512,4096] seeded",
+                   "sum_len_tokens": wl.sum_len(), "sharding": f"kv-head x{world}",
+                   "step": "per layer: append 1 token/seq, gather all sequences to [H,sum_len,D]",
+                   "l2": "inputs larger than L2: each step reads ~%.1f GB of pool per GPU" % (gat_bytes / K / 2 / 1e9)},
+        "pct_of_nominal_8TBs": round(100 * value / world / NOMINAL_PEAK_GBS, 2),
+        "pct_of_measured_copy": round(100 * value / world / peak, 2),
+        "decode_tokens_per_s": round(wl.B * K / (ms * 1e-3), 1),
+        "append_gb_per_step": round(app_bytes * world / K / 1e9, 4),
+        "gather_gb_per_step": round(gat_bytes * world / K / 1e9, 3),
+        "roofline": roofline,
+        "e2e": {"value": round(e2e_value, 1), "unit": UNIT, "h2d_bytes_per_step": h2d * world,
+                "d2h_bytes_per_step": 4 * world, "steps": e2e_steps,
+                "ms_per_step": round(e2e_s * 1e3 / e2e_steps, 4)},
+        "gpu_launches": launches,
+        "clocks": clocks.summary,
+    }
+
+    # ---- CPU baseline beside it (rank 0, N = 1 only) ------------------------------
+    if world == 1:
+        line["cpu_baseline"] = cpu_baseline(budget_s=args.cpu_seconds)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# ---------------------------------------------------------------------------
+# the CPU arm: the oracle's port of the reference's CPU path
+# ---------------------------------------------------------------------------
+def cpu_baseline(budget_s: float = 15.0, want_native: bool = True, steps_max: int = 60, warmup: int = 1):
+    """Time the reference's CPU algorithm (per-token strided assignment loop for append,
+    flattened view + ``.contiguous()`` for gather) on ONE layer of the workload, all 64
+    sequences at their prompt lengths, for whole decode steps until ``budget_s`` is used."""
+    from oracle.paged_kv_oracle import OracleLayer
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    g, prompts = seeded_lengths()
+    H, D, ps, B = CFG["kv_heads"], CFG["head_dim"], CFG["page_size"], CFG["batch"]
+    dtype = torch.bfloat16
+    layers = []
+    for n in prompts:                                   # set-up (untimed): caches already holding the prompts
+        lay = OracleLayer(1, -(-(n + steps_max + warmup + 1) // ps) * ps, ps)
+        lay._allocate(torch.empty(1, H, 1, D, dtype=dtype))
+        flat = lay.keys.view(1, H, -1, D)
+        flat[0, :, :n] = torch.randn(H, n, D, generator=g).to(dtype)
+        lay.values.view(1, H, -1, D)[0, :, :n] = flat[0, :, :n]
+        lay.seq_lens[0] = n
+        layers.append(lay)
+    k_new = torch.randn(B, 1, H, 1, D, generator=g).to(dtype)
+    per_tok = 4 * H * D * 2
+
+    def one_step():
+        for b, lay in enumerate(layers):
+            lay.append(k_new[b], k_new[b])
+        for lay in layers:
+            ks, vs = lay.current_tensors()
+            ks.contiguous()
+            vs.contiguous()
+
+    for _ in range(warmup):
+        one_step()
+    steps, moved = 0, 0
+    t0 = time.perf_counter()
+    while True:
+        one_step()
+        steps += 1
+        moved += (B + sum(int(l.seq_lens[0]) for l in layers)) * per_tok
+        if time.perf_counter() - t0 > budget_s or steps >= steps_max:
+            break
+    dt = time.perf_counter() - t0
+    out = {"value": round(moved / dt / 1e9, 3), "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+           "host_cpus": os.cpu_count(), "steps": steps, "ms_per_step": round(dt * 1e3 / steps, 3),
+           "sample": f"1 of {CFG['layers']} layers, all {B} sequences, {steps} decode steps "
+                     f"(append loop + view.contiguous() gather), {dt:.1f} s; GB/s is per-layer work / time, "
+                     f"so it compares directly with the GPU figure",
+           "decode_tokens_per_s": round(B * steps / dt / CFG["layers"], 2)}
+    if want_native:
+        try:
+            out["native_c_openmp"] = cpu_baseline_native(prompts, budget_s=min(5.0, budget_s))
+        except Exception as exc:  # noqa: BLE001
+            out["native_c_openmp"] = {"unavailable": str(exc)[:120]}
+    return out
+
+
+def cpu_baseline_native(prompts, budget_s: float = 5.0):
+    """The same layer-sample through the C/OpenMP restatement with a shuffled block table."""
+    from oracle import c_oracle
+
+    H, D, ps, B = CFG["kv_heads"], CFG["head_dim"], CFG["page_size"], CFG["batch"]
+    g = torch.Generator().manual_seed(1)
+    lens = list(prompts)
+    blocks = [-(-(n + 64) // ps) for n in lens]
+    P = sum(blocks)
+    perm = torch.randperm(P, generator=g).to(torch.int32)
+    table = torch.full((B, max(blocks)), -1, dtype=torch.int32)
+    at = 0
+    for b, nb in enumerate(blocks):
+        table[b, :nb] = perm[at:at + nb]
+        at += nb
+    k_pool = torch.zeros(H, P, ps, D, dtype=torch.bfloat16)
+    v_pool = torch.zeros_like(k_pool)
+    k_new = torch.randn(B, H, D, generator=g).to(torch.bfloat16)
+    cu_new = torch.arange(B + 1, dtype=torch.int32)
+    total_cap = sum(lens) + 64 * B
+    k_out = torch.empty(total_cap, H, D, dtype=torch.bfloat16)
+    v_out = torch.empty_like(k_out)
+    per_tok = 4 * H * D * 2
+    steps, moved = 0, 0
+    t0 = time.perf_counter()
+    while steps < 60:
+        start = torch.tensor(lens, dtype=torch.int32)
+        c_oracle.append_paged(k_pool, v_pool, table, None, start, cu_new, k_new, k_new)
+        lens = [n + 1 for n in lens]
+        lt = torch.tensor(lens, dtype=torch.int32)
+        cu = torch.zeros(B, dtype=torch.int32)
+        cu[1:] = torch.cumsum(lt, 0)[:-1]
+        total = sum(lens)
+        # head-major output [H, total, D] addressed as [token, head, dim]
+        ko = k_out.view(-1)[: H * total * D].view(H, total, D).transpose(0, 1)
+        vo = v_out.view(-1)[: H * total * D].view(H, total, D).transpose(0, 1)
+        c_oracle.gather_paged(k_pool, v_pool, table, None, lt, cu, ko, vo)
+        steps += 1
+        moved += (B + total) * per_tok
+        if time.perf_counter() - t0 > budget_s:
+            break
+    dt = time.perf_counter() - t0
+    return {"value": round(moved / dt / 1e9, 3), "unit": UNIT, "cores": c_oracle.threads(), "steps": steps}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    K, W = args.steps, args.warmup
+    base = cpu_baseline(budget_s=max(args.cpu_seconds, 30.0), steps_max=K, warmup=W)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
+        "steps": base["steps"], "warmup": W, "ms_per_step": base["ms_per_step"], "higher_is_better": True,
+        "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": CFG["name"], "layers": CFG["layers"], "kv_heads": CFG["kv_heads"],
+                   "head_dim": CFG["head_dim"], "page_size": CFG["page_size"], "batch": CFG["batch"]},
+        "cpu_baseline": base,
+        "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "reference's CPU PyTorch path (oracle port of _python_append + current_tensors().contiguous()) on the "
+                "host cores; each step is a bounded sample (one layer) of the workload",
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="barqkv", choices=["barqkv", "reference"])
+    ap.add_argument("--cpu-seconds", type=float, default=15.0, help="budget of the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_barqkv(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,170 @@
+/*
+ * barqkv - paged KV-cache append and gather for NVIDIA B200 (sm_100a).
+ *
+ * C ABI of libbarqkv.so.  Every entry point takes raw device pointers, plain
+ * integers and a CUDA stream; nothing here allocates device memory, takes a
+ * lock, or synchronises with the device.  All functions return 0 on success
+ * or a negative BARQKV_E_* code; barqkv_last_error() then holds a message for
+ * the calling thread.  Work is enqueued on the given stream and runs
+ * asynchronously; device-side guards (bad block-table entry, capacity) never
+ * trap: they skip the access and OR a BARQKV_S_* bit into the caller's
+ * optional status word.
+ *
+ * The reference interfaces these replace are cited per function as
+ * <file in the BarqTrain tree>:<lines>.
+ */
+#ifndef BARQKV_H
+#define BARQKV_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BARQKV_VERSION 100 /* major*100 + minor */
+
+/* host-side return codes */
+#define BARQKV_OK 0
+#define BARQKV_E_INVALID (-1) /* bad argument (null pointer, size, alignment) */
+#define BARQKV_E_LAUNCH (-2)  /* the CUDA runtime refused the launch */
+#define BARQKV_E_LIMIT (-3)   /* a size is beyond a documented maximum */
+
+/* bits a kernel may OR into *status (device int32, optional) */
+#define BARQKV_S_BAD_PAGE 1   /* block-table entry outside [0, num_pages): row skipped */
+#define BARQKV_S_CAPACITY 2   /* reference-layout append would pass the cache capacity: nothing written */
+#define BARQKV_S_TIMEOUT 4    /* a bounded wait on a bulk copy gave up: remaining pages skipped */
+#define BARQKV_S_BAD_SLOT 8   /* sequence slot outside the block table: sequence skipped */
+
+/* gather implementations (argument `mode`) */
+#define BARQKV_MODE_AUTO 0
+#define BARQKV_MODE_VECTOR 1  /* 16-byte ld/st through registers */
+#define BARQKV_MODE_BULK 2    /* cp.async.bulk global->shared->global, mbarrier pipelined */
+
+typedef void* barqkv_stream_t; /* a cudaStream_t */
+
+/*
+ * One layer's page pools.  The K pool and the V pool share this geometry.
+ * Page p of head h starts at element h*head_stride + p*page_stride and holds
+ * page_size rows of head_dim elements, contiguous (row r at +r*head_dim).
+ *   [H, P, ps, D] pool:               head_stride = P*ps*D, page_stride = ps*D
+ *   reference [B, H, max_blocks, ps, D] (python/barqtrain/kv_cache.py:66-70):
+ *     head_stride = max_blocks*ps*D, page_stride = ps*D,
+ *     page of (b, j) = b*H*max_blocks + j   (see implicit_pages_per_slot)
+ */
+typedef struct barqkv_pool_layout {
+    int32_t num_heads;   /* KV heads held by this GPU */
+    int32_t head_dim;
+    int32_t page_size;   /* tokens per page */
+    int32_t elem_bytes;  /* 1, 2, 4 or 8; payload is copied bit for bit */
+    int32_t num_pages;   /* valid physical page ids are [0, num_pages) */
+    int32_t reserved;
+    int64_t head_stride; /* elements */
+    int64_t page_stride; /* elements */
+} barqkv_pool_layout;
+
+/*
+ * Which pages a batch entry's sequence owns.  Entry i uses row
+ * slots[i] (i when slots is NULL) of the table; logical page j of that row is
+ * physical page table[row*table_stride + j].  With table == NULL the page is
+ * row*implicit_pages_per_slot + j (the reference's arithmetic paging,
+ * python/barqtrain/kv_cache.py:84-87) and table_stride bounds j.
+ */
+typedef struct barqkv_block_table {
+    const int32_t* table; /* device, int32 [table_rows, table_stride] or NULL */
+    const int32_t* slots; /* device, int32 [n] or NULL */
+    int32_t table_rows;
+    int32_t table_stride;
+    int32_t implicit_pages_per_slot;
+    int32_t reserved;
+} barqkv_block_table;
+
+/*
+ * Addressing of per-token rows outside the pool (new K/V rows for append,
+ * gathered rows for gather).  Row (entry i, token t of that entry, head h)
+ * starts at element  i*seq_stride + (base_i + t)*tok_stride + h*head_stride,
+ * base_i = cu[i] when `packed` is non-zero, else 0.  head_dim elements
+ * contiguous.
+ *   packed [N_tok, H, D]:  seq_stride 0,      tok_stride H*D, head_stride D,   packed 1
+ *   packed [H, N_tok, D]:  seq_stride 0,      tok_stride D,   head_stride N*D, packed 1
+ *   batched [B, H, T, D]:  seq_stride H*T*D,  tok_stride D,   head_stride T*D, packed 0
+ *   view of [B, T, H, D]:  seq_stride T*H*D,  tok_stride H*D, head_stride D,   packed 0
+ */
+typedef struct barqkv_rows_layout {
+    int64_t seq_stride;  /* elements */
+    int64_t tok_stride;  /* elements */
+    int64_t head_stride; /* elements */
+    int32_t packed;
+    int32_t reserved;
+} barqkv_rows_layout;
+
+int barqkv_version(void);
+const char* barqkv_last_error(void);
+
+/* Number of SMs of the current device (cached); used by callers that size work. */
+int barqkv_sm_count(void);
+
+/*
+ * Append new K/V rows through the block table.
+ * Replaces: the scatter of paged_kv_append_kernel
+ *           (csrc/kernels/paged_kv_cache.cu:15-54) and the CPU loop
+ *           _python_append (python/barqtrain/kv_cache.py:75-91), generalised
+ *           from "block j of sequence b" to "page table[b][j]" and from one
+ *           T for all sequences to a ragged batch.
+ * Entry i appends cu_new[i+1]-cu_new[i] tokens (tokens_per_entry each when
+ * cu_new is NULL) to its sequence, the first one landing at position
+ * seq_start[i].  total_tokens = cu_new[n] (n*tokens_per_entry), known to the
+ * host.  Pages must already be in the table; lengths are kept by the caller.
+ */
+int barqkv_append(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,
+                  const barqkv_block_table* table,
+                  const int32_t* seq_start, const int32_t* cu_new,
+                  int32_t n, int32_t tokens_per_entry, int32_t total_tokens,
+                  const void* k_new, const void* v_new, const barqkv_rows_layout* new_rows,
+                  int32_t* status, barqkv_stream_t stream);
+
+/*
+ * The reference's native entry point, same semantics:
+ *   void paged_kv_append_(key_cache, value_cache, seq_lens, key_states, value_states)
+ *   csrc/src/bindings.cpp:43-49,74-75 -> paged_kv_append_cuda
+ *   (csrc/kernels/paged_kv_cache.cu:58-128).
+ * key_cache/value_cache: [max_batch, heads, max_blocks, page_size, head_dim]
+ * contiguous; seq_lens: int32 [>= batch]; new rows [batch, heads, tokens,
+ * head_dim] addressed by new_rows (packed must be 0), so a transposed view
+ * needs no copy.  Writes rows at positions seq_lens[b] .. +tokens-1 and then
+ * adds `tokens` to seq_lens[0..batch) in the same launch.  If any sequence
+ * would pass max_blocks*page_size nothing is written, seq_lens stay, and
+ * BARQKV_S_CAPACITY is set (the reference checks the same bound on the host
+ * after a device sync, paged_kv_cache.cu:92-99).
+ * ticket: device int32 scratch word, zero before its first use; the kernel
+ * leaves it zero.  Concurrent launches must not share a ticket.
+ */
+int barqkv_append_legacy(void* key_cache, void* value_cache, int32_t* seq_lens,
+                         const void* k_new, const void* v_new, const barqkv_rows_layout* new_rows,
+                         int32_t batch, int32_t max_batch, int32_t heads, int32_t tokens,
+                         int32_t head_dim, int32_t max_blocks, int32_t page_size, int32_t elem_bytes,
+                         int32_t* ticket, int32_t* status, barqkv_stream_t stream);
+
+/*
+ * Gather sequences' pages into contiguous rows.
+ * Replaces: _flatten_pages + current_tensors (python/barqtrain/kv_cache.py:
+ *           120-133), which can be a zero-copy view only because the
+ *           reference's pages of one sequence are adjacent; with a block
+ *           table the pages are scattered and this copy materialises them.
+ * Entry i (length seq_lens[i]) is written to rows addressed by out_rows with
+ * base_i = cu_out[i] (packed) - e.g. [sum_len, H, D] or [H, sum_len, D] - or
+ * into a padded [n, H, max_len, D] batch (packed 0).  Rows at and beyond a
+ * sequence's length are not touched.  total_tokens_hint: an upper bound of
+ * sum(seq_lens) used only to size the grid (0 = unknown).
+ */
+int barqkv_gather(const barqkv_pool_layout* pool, const void* k_pool, const void* v_pool,
+                  const barqkv_block_table* table,
+                  const int32_t* seq_lens, const int32_t* cu_out, int32_t n,
+                  int64_t total_tokens_hint,
+                  void* k_out, void* v_out, const barqkv_rows_layout* out_rows,
+                  int32_t mode, int32_t* status, barqkv_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BARQKV_H */

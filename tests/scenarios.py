@@ -23,6 +23,11 @@ def bits(t: torch.Tensor) -> torch.Tensor:
     return t.detach().cpu().contiguous().view(_INT_VIEW[t.element_size()])
 
 
+def bits_dev(t: torch.Tensor) -> torch.Tensor:
+    """Integer view on the tensor's own device (no host copy), for large comparisons."""
+    return t.contiguous().view(_INT_VIEW[t.element_size()])
+
+
 def digest(*tensors: torch.Tensor) -> str:
     """sha256 over shapes and raw bytes of the given tensors."""
     h = hashlib.sha256()

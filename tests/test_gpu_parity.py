@@ -1,0 +1,435 @@
+"""Parity of the CUDA path (through the C ABI) with the oracle and the reference's golden vectors.
+
+Everything here is bit-exact: the path copies bit patterns, so there is no tolerance.
+"""
+
+import numpy as np
+import pytest
+import torch
+
+from tests import scenarios as S
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def _np(t):
+    return S.bits(t).numpy()
+
+
+@pytest.fixture(scope="module")
+def backend():
+    from barqtrain_b200 import _ffi
+
+    be = _ffi.require_cuda_backend()
+    assert be.read_status(DEV) == 0
+    yield be
+    assert be.read_status(DEV) == 0, "a kernel guard fired during the module"
+
+
+# ---------------------------------------------------------------------------
+# reference layout (identity block table)
+# ---------------------------------------------------------------------------
+def test_reference_known_answer_on_gpu(backend, golden_dir):
+    """The reference's own test (tests/test_kv_cache.py:24-47) with the append on the GPU."""
+    from barqtrain_b200 import BarqPagedKVCacheLayer
+
+    gold = np.load(golden_dir / "ref_known_answer.npz")
+    ctor, steps = S.ref_known_answer()
+    layer = BarqPagedKVCacheLayer(**ctor)
+    launches = backend.launches
+    for i, (k, v) in enumerate(steps):
+        ks, vs = layer.update(k.to(DEV), v.to(DEV))
+        assert np.array_equal(_np(ks), gold[f"ret_k_{i}"])
+        assert np.array_equal(_np(vs), gold[f"ret_v_{i}"])
+        assert np.array_equal(_np(layer.keys), gold[f"keys_{i}"])
+        assert np.array_equal(_np(layer.values), gold[f"values_{i}"])
+        assert np.array_equal(layer.seq_lens.cpu().numpy(), gold[f"lens_{i}"])
+        assert layer.get_seq_length() == int(gold[f"seq_length_{i}"])
+    assert ks.shape == (1, 2, 5, 4) and vs.shape == (1, 2, 5, 4)
+    assert torch.equal(ks[:, :, :3].cpu(), steps[0][0]) and torch.equal(ks[:, :, 3:].cpu(), steps[1][0])
+    assert torch.equal(vs[:, :, :3].cpu(), steps[0][1]) and torch.equal(vs[:, :, 3:].cpu(), steps[1][1])
+    assert backend.launches == launches + 2, "the native kernel must have been launched once per append"
+    gk, gv = layer.gather_contiguous()
+    assert gk.is_contiguous() and torch.equal(gk, ks) and torch.equal(gv, vs)
+
+
+@pytest.mark.parametrize("dtype_name", ["fp32", "fp64", "fp16", "bf16"])
+def test_legacy_script_against_reference(backend, golden_dir, dtype_name):
+    from barqtrain_b200 import BarqPagedKVCacheLayer
+
+    gold = np.load(golden_dir / f"legacy_{dtype_name}.npz")
+    ctor, ops = S.legacy_script(dtype_name)
+    ops = [tuple(x.to(DEV) if isinstance(x, torch.Tensor) and x.is_floating_point() else x for x in op) for op in ops]
+    layer = BarqPagedKVCacheLayer(**ctor)
+
+    def check(lay, i, op):
+        assert np.array_equal(_np(lay.keys), gold[f"keys_{i}"]), (i, op[0])
+        assert np.array_equal(_np(lay.values), gold[f"values_{i}"]), (i, op[0])
+        assert np.array_equal(lay.seq_lens.cpu().numpy(), gold[f"lens_{i}"]), (i, op[0])
+        assert lay.current_batch_size == int(gold[f"batch_{i}"])
+        assert lay.get_seq_length() == int(gold[f"seq_length_{i}"])
+        if lay.current_batch_size:
+            ks, vs = lay.current_tensors()
+            assert np.array_equal(_np(ks), gold[f"cur_k_{i}"])
+            assert np.array_equal(_np(vs), gold[f"cur_v_{i}"])
+            for mode in ("vector", "bulk"):
+                gk, gv = lay.gather_contiguous(mode=mode)
+                lens = lay.seq_lens.cpu().tolist()
+                for b in range(lay.current_batch_size):
+                    assert torch.equal(S.bits(gk[b, :, :lens[b]]), S.bits(ks[b, :, :lens[b]])), (i, mode, b)
+                    assert torch.equal(S.bits(gv[b, :, :lens[b]]), S.bits(vs[b, :, :lens[b]])), (i, mode, b)
+                    assert not gk[b, :, lens[b]:].any() and not gv[b, :, lens[b]:].any()
+
+    S.run_legacy_script(layer, ops, check)
+
+
+def test_legacy_capacity_is_all_or_nothing(backend, golden_dir):
+    """The reference's CUDA launcher refuses the whole call (paged_kv_cache.cu:92-99);
+    so does this path, on the host and - when the host check is bypassed - on the device."""
+    from barqtrain_b200 import BarqPagedKVCacheLayer
+
+    ctor, ops = S.legacy_overflow_script()
+    ops = [tuple(x.to(DEV) if isinstance(x, torch.Tensor) and x.is_floating_point() else x for x in op) for op in ops]
+    layer = BarqPagedKVCacheLayer(**ctor)
+    S.run_legacy_script(layer, ops[:3], lambda *a: None)
+    before = (layer.keys.clone(), layer.values.clone(), layer.seq_lens.clone())
+    with pytest.raises(RuntimeError, match="paged KV cache capacity exceeded: requested 9 tokens, max_cache_len=8"):
+        layer.append(ops[3][1], ops[3][2])
+    assert torch.equal(layer.keys, before[0]) and torch.equal(layer.seq_lens, before[2])
+    # without the host-side hint the call reads the lengths back, as the reference does
+    with pytest.raises(RuntimeError, match="capacity exceeded"):
+        backend.paged_kv_append_(layer.keys, layer.values, layer.seq_lens, ops[3][1], ops[3][2])
+    # a wrong hint reaches the kernel: it must write nothing, keep seq_lens and flag the call
+    backend.paged_kv_append_(layer.keys, layer.values, layer.seq_lens, ops[3][1], ops[3][2], max_start=0)
+    assert backend.read_status(DEV) == 2
+    assert torch.equal(layer.keys, before[0]) and torch.equal(layer.values, before[1])
+    assert torch.equal(layer.seq_lens, before[2])
+    # and the ticket was re-armed: the next valid call works
+    ok_k, ok_v = ops[3][1][:, :, :3], ops[3][2][:, :, :3]
+    backend.paged_kv_append_(layer.keys, layer.values, layer.seq_lens, ok_k, ok_v)
+    assert layer.seq_lens.cpu().tolist() == [5, 8, 8]
+    assert backend.read_status(DEV) == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_legacy_append_reads_transposed_views_without_copy(backend, dtype):
+    """[B, T, H, D].transpose(1, 2) - what HF attention passes - gives the same cache as a contiguous copy."""
+    from barqtrain_b200 import BarqPagedKVCacheLayer
+    from oracle.paged_kv_oracle import OracleLayer
+
+    g = torch.Generator().manual_seed(5)
+    B, T, H, D = 3, 37, 4, 64
+    a, b = BarqPagedKVCacheLayer(B, 64, 16), OracleLayer(B, 64, 16)
+    for T_i in (T, 1, 1, 20):
+        k = S.randn(g, (B, T_i, H, D), dtype)
+        v = S.randn(g, (B, T_i, H, D), dtype)
+        a.append(k.to(DEV).transpose(1, 2), v.to(DEV).transpose(1, 2))
+        b.append(k.transpose(1, 2), v.transpose(1, 2))
+        assert torch.equal(S.bits(a.keys), S.bits(b.keys)) and torch.equal(S.bits(a.values), S.bits(b.values))
+        assert a.seq_lens.cpu().tolist() == b.seq_lens.tolist()
+
+
+@pytest.mark.parametrize("shape", [(2, 3, 5, 3, torch.float32), (1, 2, 9, 5, torch.float16), (2, 1, 4, 4, torch.float64),
+                                   (2, 2, 7, 1, torch.float32)])
+def test_legacy_odd_row_sizes_take_narrow_vectors(backend, shape):
+    """Rows of 12, 10, 32 and 4 bytes: the kernel drops to 4-, 2-, 16- and 4-byte accesses."""
+    from barqtrain_b200 import BarqPagedKVCacheLayer
+    from oracle.paged_kv_oracle import OracleLayer
+
+    B, H, T, D, dtype = shape
+    g = torch.Generator().manual_seed(11)
+    a, b = BarqPagedKVCacheLayer(B, 24, 4), OracleLayer(B, 24, 4)
+    for T_i in (T, 1, T):
+        k, v = S.randn(g, (B, H, T_i, D), dtype), S.randn(g, (B, H, T_i, D), dtype)
+        a.append(k.to(DEV), v.to(DEV))
+        b.append(k, v)
+    assert torch.equal(S.bits(a.keys), S.bits(b.keys)) and torch.equal(S.bits(a.values), S.bits(b.values))
+    for mode in ("vector", "auto"):
+        gk, gv = a.gather_contiguous(mode=mode)
+        rk, rv = b.current_tensors()
+        assert torch.equal(S.bits(gk), S.bits(rk)) and torch.equal(S.bits(gv), S.bits(rv))
+
+
+# ---------------------------------------------------------------------------
+# block table
+# ---------------------------------------------------------------------------
+SMALL = {
+    "small_paged_fp32": {},
+    "small_paged_bf16": dict(dtype=torch.bfloat16, kv_heads=2, head_dim=128, prefill=(21, 64, 90),
+                             decode_steps=5, num_pages=40, seed=2001),
+    "small_paged_fp16_ps32": dict(dtype=torch.float16, kv_heads=8, head_dim=128, page_size=32,
+                                  prefill=(100, 33), decode_steps=3, num_pages=16, seed=2002, num_layers=1),
+}
+
+
+@pytest.mark.parametrize("mode", ["vector", "bulk"])
+@pytest.mark.parametrize("name", sorted(SMALL))
+def test_small_paged_against_reference(backend, golden_dir, name, mode):
+    """Prefill + decode through a shuffled free list; every step's gather and the final pages
+    must equal what the unmodified reference produced (tests/golden)."""
+    from barqtrain_b200 import BlockTableKVCache
+
+    gold = np.load(golden_dir / f"{name}.npz")
+    sc = S.small_paged(**SMALL[name])
+    finals = sc.final_lengths()
+    nseq = len(finals)
+    cache = BlockTableKVCache(sc.num_layers, sc.kv_heads, sc.head_dim, page_size=sc.page_size,
+                              num_pages=sc.num_pages, max_seqs=nseq + 1, max_blocks_per_seq=8, dtype=sc.dtype,
+                              device=DEV, free_order=gold["free_list"].tolist(), gather_mode=mode)
+    slots = [cache.open(s) for s in range(nseq)]
+    for i, step in enumerate(sc.steps):
+        counts = [step[0][s][0].shape[1] for s in range(nseq)]
+        # packed [total, H, D] rows per layer: sequences back to back
+        k_layers = [torch.cat([kv[0].transpose(0, 1) for kv in step[l]], 0).to(DEV) for l in range(sc.num_layers)]
+        v_layers = [torch.cat([kv[1].transpose(0, 1) for kv in step[l]], 0).to(DEV) for l in range(sc.num_layers)]
+        cache.append_step(slots, counts, k_layers, v_layers)
+        gb = cache.begin_gather(slots)
+        col = 0
+        for l in range(sc.num_layers):
+            kh, vh = cache.gather(l, gb, "HND")
+            kn, vn = cache.gather(l, gb, "NHD")
+            assert torch.equal(kh, kn.transpose(0, 1)) and torch.equal(vh, vn.transpose(0, 1))
+            for s in range(nseq):
+                a, b = gb.cu[s], gb.cu[s + 1]
+                assert S.digest(kh[:, a:b], vh[:, a:b]) == str(gold["gather_digests"][i][col]), (i, l, s)
+                col += 1
+    for l in range(sc.num_layers):
+        for s, n in enumerate(finals):
+            pages = -(-n // sc.page_size)
+            k_all = torch.stack([cache.logical_page(l, s, j)[0] for j in range(pages)], dim=1)
+            v_all = torch.stack([cache.logical_page(l, s, j)[1] for j in range(pages)], dim=1)
+            assert np.array_equal(_np(k_all), gold[f"keys_l{l}_s{s}"])     # zero tails included
+            assert np.array_equal(_np(v_all), gold[f"values_l{l}_s{s}"])
+            gk, gv = cache.gather_sequence(l, s, "NHD")
+            assert gk.shape == (n, sc.kv_heads, sc.head_dim)
+    # pages nobody owns were never written
+    owned = sorted(p for s in slots for p in cache.pages_of[s])
+    free = [p for p in range(sc.num_pages) if p not in owned]
+    assert not cache.pools[:, :, :, free].any()
+    cache.check_device_status()
+    st = cache.stats()
+    assert st.pages_resident == len(owned) == sum(-(-n // sc.page_size) for n in finals) == st.pages_peak
+
+
+def _ragged_case(seed, nseq, lo, hi, H, D, ps, dtype, layers, chunk, decode):
+    g = torch.Generator().manual_seed(seed)
+    lens = S.ragged_lengths(g, nseq, lo, hi)
+    max_len = max(lens) + decode
+    pages = sum(-(-(n + decode) // ps) for n in lens) + 7
+    order = torch.randperm(pages, generator=g).tolist()
+    return g, lens, max_len, pages, order
+
+
+@pytest.mark.parametrize("mode", ["vector", "bulk"])
+@pytest.mark.parametrize("cfg", [
+    dict(seed=31, nseq=24, lo=1, hi=700, H=8, D=128, ps=16, dtype=torch.bfloat16, layers=2, chunk=256, decode=3),
+    dict(seed=32, nseq=5, lo=300, hi=2100, H=8, D=128, ps=32, dtype=torch.float16, layers=1, chunk=512, decode=2),
+    dict(seed=33, nseq=40, lo=0, hi=90, H=1, D=128, ps=16, dtype=torch.bfloat16, layers=1, chunk=64, decode=4),
+    dict(seed=34, nseq=7, lo=1, hi=150, H=3, D=80, ps=8, dtype=torch.float32, layers=1, chunk=50, decode=2),
+])
+def test_ragged_chunked_prefill_and_decode_against_c_oracle(backend, cfg, mode):
+    """Scaled-down shapes of the large configurations: chunked prefill of a ragged batch into a
+    shuffled pool, then decode steps; whole pools and all gathers equal the C oracle's."""
+    from barqtrain_b200 import BlockTableKVCache
+    from oracle import c_oracle
+
+    g, lens, max_len, pages, order = _ragged_case(**cfg)
+    H, D, ps, dtype, L = cfg["H"], cfg["D"], cfg["ps"], cfg["dtype"], cfg["layers"]
+    nseq = len(lens)
+    cache = BlockTableKVCache(L, H, D, page_size=ps, num_pages=pages, max_seqs=nseq,
+                              max_blocks_per_seq=-(-max_len // ps), dtype=dtype, device=DEV, free_order=order,
+                              gather_mode=mode)
+    slots = [cache.open(s) for s in range(nseq)]
+    ref_k = [torch.zeros(H, pages, ps, D, dtype=dtype) for _ in range(L)]
+    ref_v = [torch.zeros(H, pages, ps, D, dtype=dtype) for _ in range(L)]
+    done = [0] * nseq
+
+    def step(counts):
+        total = sum(counts)
+        batch = cache.begin_append(slots, counts)
+        table = cache.table_host.clone()
+        start = torch.tensor(done, dtype=torch.int32)
+        cu = torch.tensor(batch.cu, dtype=torch.int32)
+        for l in range(L):
+            k = S.randn(g, (total, H, D), dtype)
+            v = S.randn(g, (total, H, D), dtype)
+            cache.append(l, batch, k.to(DEV), v.to(DEV))
+            assert c_oracle.append_paged(ref_k[l], ref_v[l], table, None, start, cu, k, v) == 0
+        cache.end_append(batch)
+        for s, c in enumerate(counts):
+            done[s] += c
+
+    while any(d < n for d, n in zip(done, lens)):
+        step([min(cfg["chunk"], n - d) for d, n in zip(done, lens)])
+    for _ in range(cfg["decode"]):
+        step([1] * nseq)
+
+    for l in range(L):
+        assert torch.equal(S.bits(cache.pools[l, 0]), S.bits(ref_k[l])), "K pool differs"
+        assert torch.equal(S.bits(cache.pools[l, 1]), S.bits(ref_v[l])), "V pool differs"
+    gb = cache.begin_gather(slots)
+    total = gb.total
+    lens_t = torch.tensor(done, dtype=torch.int32)
+    cu_t = torch.tensor(gb.cu[:-1], dtype=torch.int32)
+    table = cache.table_host.clone()
+    for l in range(L):
+        want_k = torch.zeros(total, H, D, dtype=dtype)
+        want_v = torch.zeros(total, H, D, dtype=dtype)
+        assert c_oracle.gather_paged(ref_k[l], ref_v[l], table, None, lens_t, cu_t, want_k, want_v) == 0
+        kn, vn = cache.gather(l, gb, "NHD")
+        kh, vh = cache.gather(l, gb, "HND")
+        assert torch.equal(S.bits(kn), S.bits(want_k)) and torch.equal(S.bits(vn), S.bits(want_v))
+        assert torch.equal(S.bits(kh.transpose(0, 1)), S.bits(want_k))
+        assert torch.equal(S.bits(vh.transpose(0, 1)), S.bits(want_v))
+    cache.check_device_status()
+
+
+def test_release_recycles_pages_and_keeps_live_sequences_intact(backend):
+    """Continuous-batching churn in small: sequences finish, their pages go back to the free
+    list and are handed to new sequences; live sequences always gather to what was appended."""
+    from barqtrain_b200 import BlockTableKVCache
+
+    g = torch.Generator().manual_seed(77)
+    H, D, ps, dtype, L = 2, 64, 16, torch.float16, 2
+    live_max, pages = 6, 40
+    cache = BlockTableKVCache(L, H, D, page_size=ps, num_pages=pages, max_seqs=live_max, max_blocks_per_seq=8,
+                              dtype=dtype, device=DEV, seed=3)
+    truth = {}          # seq_id -> per-layer (k [len, H, D], v)
+    next_id = 0
+
+    def admit(n_tokens):
+        nonlocal next_id
+        sid = next_id
+        next_id += 1
+        slot = cache.open(sid)
+        batch = cache.begin_append([slot], [n_tokens])
+        per_layer = []
+        for l in range(L):
+            k, v = S.randn(g, (n_tokens, H, D), dtype), S.randn(g, (n_tokens, H, D), dtype)
+            cache.append(l, batch, k.to(DEV), v.to(DEV))
+            per_layer.append((k, v))
+        cache.end_append(batch)
+        truth[sid] = per_layer
+
+    for n in (30, 17, 64, 5):
+        admit(n)
+    for step in range(40):
+        ids = sorted(truth)
+        slots = [cache.slot(i) for i in ids]
+        batch = cache.begin_append(slots, [1] * len(ids))
+        for l in range(L):
+            k, v = S.randn(g, (len(ids), H, D), dtype), S.randn(g, (len(ids), H, D), dtype)
+            cache.append(l, batch, k.to(DEV), v.to(DEV))
+            for row, i in enumerate(ids):
+                tk, tv = truth[i][l]
+                truth[i][l] = (torch.cat([tk, k[row:row + 1]]), torch.cat([tv, v[row:row + 1]]))
+        cache.end_append(batch)
+        if step % 5 == 4:                       # one sequence finishes, a new one is admitted
+            victim = ids[(step // 5) % len(ids)]
+            cache.release(victim)
+            del truth[victim]
+            admit(20 + step)
+        ids = sorted(truth)
+        gb = cache.begin_gather([cache.slot(i) for i in ids])
+        for l in range(L):
+            kn, vn = cache.gather(l, gb, "NHD")
+            for row, i in enumerate(ids):
+                a, b = gb.cu[row], gb.cu[row + 1]
+                assert torch.equal(S.bits(kn[a:b]), S.bits(truth[i][l][0])), (step, l, i)
+                assert torch.equal(S.bits(vn[a:b]), S.bits(truth[i][l][1])), (step, l, i)
+    st = cache.stats()
+    assert st.pages_resident == sum(len(cache.pages_of[cache.slot(i)]) for i in truth)
+    assert st.pages_peak >= st.pages_resident and st.sequences_live == len(truth)
+    assert cache.allocator.release_calls == 8
+    cache.check_device_status()
+
+
+def test_corrupt_table_entry_is_skipped_and_flagged(backend):
+    """A page id outside the pool never reaches memory: the rows are skipped, a status bit is set,
+    the other sequences are unaffected and the context stays usable."""
+    from barqtrain_b200 import BlockTableKVCache
+
+    H, D, ps = 2, 64, 16
+    cache = BlockTableKVCache(1, H, D, page_size=ps, num_pages=8, max_seqs=2, max_blocks_per_seq=2,
+                              dtype=torch.float16, device=DEV)
+    s0, s1 = cache.open("a"), cache.open("b")
+    batch = cache.begin_append([s0, s1], [20, 20])
+    cache.table_dev[s1, 1] = 1000                       # corrupt the device copy only
+    k = torch.ones(40, H, D, dtype=torch.float16, device=DEV)
+    cache.append(0, batch, k, k * 2)
+    cache.end_append(batch)
+    assert backend.read_status(DEV) == 1
+    for mode in ("vector", "bulk"):
+        gb = cache.begin_gather([s0, s1])
+        kn, vn = cache.gather(0, gb, "NHD", out=(torch.zeros(40, H, D, dtype=torch.float16, device=DEV),
+                                                  torch.zeros(40, H, D, dtype=torch.float16, device=DEV)), mode=mode)
+        assert backend.read_status(DEV) == 1
+        assert bool((kn[:36] == 1).all()) and bool((vn[:36] == 2).all())
+        assert not kn[36:].any()                         # the skipped page's rows were left alone
+    torch.cuda.synchronize()
+
+
+def test_empty_and_degenerate_batches(backend):
+    from barqtrain_b200 import BlockTableKVCache
+
+    H, D = 2, 32
+    cache = BlockTableKVCache(1, H, D, page_size=4, num_pages=8, max_seqs=3, max_blocks_per_seq=4,
+                              dtype=torch.float32, device=DEV)
+    slots = [cache.open(i) for i in range(3)]
+    launches = backend.launches
+    cache.append_step([], [], [torch.zeros(0, H, D, device=DEV)], [torch.zeros(0, H, D, device=DEV)])
+    cache.append_step(slots, [0, 0, 0], [torch.zeros(0, H, D, device=DEV)], [torch.zeros(0, H, D, device=DEV)])
+    assert backend.launches == launches
+    k = torch.arange(5 * H * D, dtype=torch.float32, device=DEV).view(5, H, D)
+    cache.append_step(slots, [0, 5, 0], [k], [k + 0.5])            # empty neighbours on both sides
+    gb = cache.begin_gather(slots)
+    assert gb.cu == [0, 0, 5, 5]
+    kn, vn = cache.gather(0, gb, "NHD")
+    assert torch.equal(kn, k) and torch.equal(vn, k + 0.5)
+    gb = cache.begin_gather([slots[0], slots[2]])
+    kn, vn = cache.gather(0, gb, "HND")
+    assert kn.shape == (H, 0, D)
+    with pytest.raises(ValueError, match="capacity exceeded"):
+        cache.begin_append([slots[1]], [12])
+    cache.check_device_status()
+
+
+# ---------------------------------------------------------------------------
+# full-size shapes: size-independent properties
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("ps,dtype", [(16, torch.float16), (32, torch.float16), (16, torch.bfloat16)])
+def test_full_size_chunk_round_trip(backend, ps, dtype):
+    """One layer of the chunked-prefill configuration at full width (16 sequences x 2048-token
+    chunks, 8 heads, head_dim 128): append -> gather returns the appended rows, pages outside the
+    table stay zero, and the vector and bulk gathers agree bit for bit."""
+    from barqtrain_b200 import BlockTableKVCache
+
+    nseq, chunk, chunks, H, D = 16, 2048, 2, 8, 128
+    g = torch.Generator(device=DEV).manual_seed(9)
+    pages = nseq * chunk * chunks // ps + 64
+    cache = BlockTableKVCache(1, H, D, page_size=ps, num_pages=pages, max_seqs=nseq,
+                              max_blocks_per_seq=chunk * chunks // ps, dtype=dtype, device=DEV, seed=12)
+    slots = [cache.open(i) for i in range(nseq)]
+    sent_k, sent_v = [], []
+    for _ in range(chunks):
+        k = torch.randn(nseq * chunk, H, D, generator=g, device=DEV, dtype=torch.float32).to(dtype)
+        v = torch.randn(nseq * chunk, H, D, generator=g, device=DEV, dtype=torch.float32).to(dtype)
+        cache.append_step(slots, [chunk] * nseq, [k], [v])
+        sent_k.append(k.view(nseq, chunk, H, D))
+        sent_v.append(v.view(nseq, chunk, H, D))
+    want_k = torch.cat(sent_k, 1).reshape(nseq * chunk * chunks, H, D)
+    want_v = torch.cat(sent_v, 1).reshape(nseq * chunk * chunks, H, D)
+    gb = cache.begin_gather(slots)
+    kv, vv = cache.gather(0, gb, "NHD", mode="vector")
+    kb, vb = cache.gather(0, gb, "NHD", mode="bulk")
+    assert torch.equal(S.bits_dev(kv), S.bits_dev(want_k)) and torch.equal(S.bits_dev(vv), S.bits_dev(want_v))
+    assert torch.equal(S.bits_dev(kb), S.bits_dev(want_k)) and torch.equal(S.bits_dev(vb), S.bits_dev(want_v))
+    kh, vh = cache.gather(0, gb, "HND", mode="bulk")
+    assert torch.equal(S.bits_dev(kh.transpose(0, 1)), S.bits_dev(want_k))
+    assert torch.equal(S.bits_dev(vh.transpose(0, 1)), S.bits_dev(want_v))
+    owned = torch.zeros(pages, dtype=torch.bool, device=DEV)
+    owned[torch.tensor([p for s in slots for p in cache.pages_of[s]], device=DEV)] = True
+    assert not cache.pools[0][:, :, ~owned].any()
+    cache.check_device_status()
