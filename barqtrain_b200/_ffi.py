@@ -57,8 +57,9 @@ class RowsLayout(ctypes.Structure):
     _fields_ = [("seq_stride", _i64), ("tok_stride", _i64), ("head_stride", _i64), ("packed", _i32), ("reserved", _i32)]
 
 
-EXPORTS = ("barqkv_version", "barqkv_last_error", "barqkv_sm_count", "barqkv_append", "barqkv_append_legacy",
-           "barqkv_gather")
+EXPORTS = ("barqkv_version", "barqkv_last_error", "barqkv_sm_count", "barqkv_set_tuning", "barqkv_append",
+           "barqkv_append_legacy", "barqkv_gather")
+KNOBS = {"stages": 1, "ctas": 2, "vctas": 3, "interleave": 4, "group": 5, "static": 6}
 
 
 def _env_enabled(name: str, default: str = "1") -> bool:
@@ -91,6 +92,8 @@ class CudaBackend:
         lib.barqkv_version.restype = _i32
         lib.barqkv_last_error.restype = ctypes.c_char_p
         lib.barqkv_sm_count.restype = _i32
+        lib.barqkv_set_tuning.restype = _i32
+        lib.barqkv_set_tuning.argtypes = [_i32, _i32]
         P = ctypes.POINTER
         lib.barqkv_append.restype = _i32
         lib.barqkv_append.argtypes = [P(PoolLayout), _ptr, _ptr, P(BlockTable), _ptr, _ptr, _i32, _i32, _i32,
@@ -100,11 +103,12 @@ class CudaBackend:
                                              _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _ptr, _ptr, _ptr]
         lib.barqkv_gather.restype = _i32
         lib.barqkv_gather.argtypes = [P(PoolLayout), _ptr, _ptr, P(BlockTable), _ptr, _ptr, _i32, _i64,
-                                      _ptr, _ptr, P(RowsLayout), _i32, _ptr, _ptr]
+                                      _ptr, _ptr, P(RowsLayout), _i32, _ptr, _ptr, _ptr]
         self.version = int(lib.barqkv_version())
         self.launches = 0                      # kernels enqueued through this object
         self._status: Dict[int, "object"] = {}
         self._tickets: Dict[Tuple[int, int], "object"] = {}
+        self._work: Dict[Tuple[int, int], "object"] = {}
 
     # -- plumbing -----------------------------------------------------------
     def _check(self, rc: int) -> None:
@@ -148,8 +152,27 @@ class CudaBackend:
                                     (S_BAD_SLOT, "sequence slot out of range")) if bits & b]
             raise BarqKVError("device-side guard: " + ", ".join(names))
 
+    def work_words(self, device):
+        """Device int32[2] scratch of the bulk gather's page hand-out, one per (device, current stream)."""
+        import torch
+
+        device = torch.device(device)
+        index = device.index if device.index is not None else torch.cuda.current_device()
+        key = (index, self._stream(torch.device("cuda", index)))
+        words = self._work.get(key)
+        if words is None:
+            words = torch.zeros(2, dtype=torch.int32, device=torch.device("cuda", index))
+            self._work[key] = words
+        return words
+
     def sm_count(self) -> int:
         return int(self.lib.barqkv_sm_count())
+
+    def set_tuning(self, **knobs: int) -> None:
+        """Experiment knobs of the gather kernels (0 = default): ``stages``, ``ctas``, ``vctas``,
+        ``interleave``, ``group``, ``static``."""
+        for name, value in knobs.items():
+            self._check(self.lib.barqkv_set_tuning(KNOBS[name], int(value)))
 
     # -- raw calls (pointers as ints) -----------------------------------------
     def append_raw(self, pool: PoolLayout, k_pool: int, v_pool: int, table: BlockTable, seq_start: int,
@@ -163,10 +186,10 @@ class CudaBackend:
 
     def gather_raw(self, pool: PoolLayout, k_pool: int, v_pool: int, table: BlockTable, seq_lens: int,
                    cu_out: Optional[int], n: int, total_tokens_hint: int, k_out: int, v_out: int,
-                   rows: RowsLayout, mode: int, status: Optional[int], stream: int) -> None:
+                   rows: RowsLayout, mode: int, status: Optional[int], work: Optional[int], stream: int) -> None:
         self._check(self.lib.barqkv_gather(ctypes.byref(pool), k_pool, v_pool, ctypes.byref(table), seq_lens, cu_out,
                                            n, total_tokens_hint, k_out, v_out, ctypes.byref(rows), mode,
-                                           status, stream))
+                                           status, work, stream))
         if n:
             self.launches += 1
 

@@ -347,6 +347,7 @@ class BlockTableKVCache:
         self.backend.gather_raw(self._pool_layout, self._k_ptr[layer], self._v_ptr[layer], self._table,
                                 batch.p_first, batch.p_cu, batch.n, total, k_out.data_ptr(), v_out.data_ptr(),
                                 rows, _ffi.MODES[mode or self.gather_mode], self._status.data_ptr(),
+                                self.backend.work_words(self.device).data_ptr(),
                                 torch.cuda.current_stream(self.device).cuda_stream)
         return k_out, v_out
 

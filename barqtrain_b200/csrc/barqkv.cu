@@ -108,6 +108,9 @@ struct GatherArgs {
     long long pool_head, pool_page;
     RowsB orow;
     int stages;            // bulk kernel only
+    int interleave;        // 1: CTAs take every gridDim-th group of tiles instead of one contiguous share
+    int32_t* work;         // bulk kernel: [0] next group to hand out, [1] CTAs finished; null = static shares
+    int group_tiles;       // bulk kernel, dynamic hand-out: (sequence, page) tiles per group
     int32_t* status;
 };
 
@@ -319,16 +322,24 @@ gather_vector_kernel(const GatherArgs a) {
     int* s_cu = s_dyn;
     scan_pages(a.seq_lens, a.n, a.page_size, s_cu, s_part);
     const int total = s_cu[a.n];
-    const int per = (total + (int)gridDim.x - 1) / (int)gridDim.x;
-    const int lo = min(total, (int)blockIdx.x * per);
-    const int hi = min(total, lo + per);
+    int lo, hi, group_step;
+    if (a.interleave) {
+        lo = (int)blockIdx.x * kGroup;
+        hi = total;
+        group_step = (int)gridDim.x * kGroup;
+    } else {
+        const int per = (total + (int)gridDim.x - 1) / (int)gridDim.x;
+        lo = min(total, (int)blockIdx.x * per);
+        hi = min(total, lo + per);
+        group_step = kGroup;
+    }
 
     const int tid = threadIdx.x;
     const int vpr = a.row_bytes / (int)sizeof(V);
     const int page_vecs = a.page_size * vpr;
     const int per_tile = a.heads * 2 * page_vecs;          // order inside a tile: head, K|V, row, vector
 
-    for (int g0 = lo; g0 < hi; g0 += kGroup) {
+    for (int g0 = lo; g0 < hi; g0 += group_step) {
         const int nt = min(kGroup, hi - g0);
         __syncthreads();
         if (tid < nt) {
@@ -419,9 +430,9 @@ __device__ __forceinline__ void bulk_wait_read() {
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // One warp per CTA.  A "unit" is one (page, head): the K page and the V page of
-// that head travel together through one ring stage.  Unit g is loaded at loop
-// step g and stored at step g + lag (lag = stages - 2), so `lag` loads are in
-// flight while at most two stores are still reading shared memory.
+// that head travel together through one ring stage.  The store of unit g is
+// issued once unit g + lag has been loaded (lag = stages - 2), so `lag` loads
+// are in flight while at most two stores are still reading shared memory.
 __global__ void __launch_bounds__(32)
 gather_bulk_kernel(const GatherArgs a) {
     extern __shared__ __align__(128) unsigned char s_raw[];
@@ -446,38 +457,57 @@ gather_bulk_kernel(const GatherArgs a) {
     }
     scan_pages(a.seq_lens, a.n, a.page_size, s_cu, s_part);   // ends with a CTA barrier
 
+    // This CTA's tiles come in groups of consecutive tiles of the flat list:
+    //  - dynamic (a.work != null): groups of a.group_tiles handed out by an atomic
+    //    counter, so SMs that reach memory faster simply take more groups;
+    //  - static: one contiguous share (interleave == 0) or every gridDim-th group.
     const int total = s_cu[a.n];
-    const int per = (total + (int)gridDim.x - 1) / (int)gridDim.x;
-    const int lo = min(total, (int)blockIdx.x * per);
-    const int hi = min(total, lo + per);
-    const long long units = (long long)(hi - lo) * a.heads;
+    const bool dynamic = a.work != nullptr;
+    const int gt = dynamic ? a.group_tiles : kGroup;
+    const int ngroups = (total + gt - 1) / gt;
+    int group_base, group_step = 0, end = total;
+    int pending = 0;                       // lane 0: group index fetched ahead of need
+    if (dynamic) {
+        if (lane == 0) pending = atomicAdd(a.work, 1);
+        const int first = __shfl_sync(0xffffffffu, pending, 0);
+        group_base = first >= ngroups ? end : first * gt;
+        if (lane == 0 && group_base < end) pending = atomicAdd(a.work, 1);
+    } else if (a.interleave) {
+        group_base = (int)blockIdx.x * kGroup;
+        group_step = (int)gridDim.x * kGroup;
+    } else {
+        const int per = (total + (int)gridDim.x - 1) / (int)gridDim.x;
+        group_base = min(total, (int)blockIdx.x * per);
+        group_step = kGroup;
+        end = min(total, group_base + per);
+    }
     const bool contiguous_rows = a.orow.tok == a.row_bytes;   // a page's rows are adjacent in the output
 
-    int group_base = lo - kGroup;          // first tile of the resolved group
-    int tile = lo, head = 0;               // issue cursor
-    int islot = 0;                         // issue ring position
-    int cslot = 0;                         // consume ring position
+    bool more = group_base < end;          // issue side still has units
+    bool staged = false;                   // current group resolved into shared memory
+    int ti = 0, head = 0;                  // issue cursor inside the group
+    int islot = 0, cslot = 0;              // ring positions
     uint32_t cphase = 0;
+    long long issued = 0, consumed = 0;
     bool dead = false;
 
-    for (long long g = 0; g < units + lag; ++g) {
-        if (g < units && !dead) {
-            if (tile >= group_base + kGroup) {
-                group_base = tile;
+    while ((more || consumed < issued) && !dead) {
+        if (more) {
+            if (!staged) {
                 __syncwarp();
-                if (group_base + lane < hi) {
+                if (lane < gt && group_base + lane < end) {
                     const TileInfo t = resolve_tile(a, s_cu, group_base + lane);
                     s_src[lane] = t.src;
                     s_dst[lane] = t.dst;
                     s_rows[lane] = t.rows;
                 }
                 __syncwarp();
+                staged = true;
             }
-            if (g >= S) {
-                bulk_wait_read<1>();       // the stores that read this stage two rounds ago are done with it
+            if (issued >= S) {
+                bulk_wait_read<1>();       // the stores that read this stage one ring round ago are done with it
                 __syncwarp();
             }
-            const int ti = tile - group_base;
             const int rows = s_rows[ti];
             const uint32_t bytes = (uint32_t)(rows * a.row_bytes);
             const uint32_t bar = smem_addr(&s_bar[islot]);
@@ -491,10 +521,25 @@ gather_bulk_kernel(const GatherArgs a) {
                 const unsigned char* src = (lane ? a.v_pool : a.k_pool) + s_src[ti] + head * a.pool_head;
                 bulk_load(smem_addr(s_data + ((size_t)islot * 2 + lane) * page_bytes), src, bytes, bar);
             }
-            if (++head == a.heads) { head = 0; ++tile; }
+            ++issued;
             if (++islot == S) islot = 0;
+            if (++head == a.heads) {
+                head = 0;
+                if (++ti == gt || group_base + ti >= end) {
+                    ti = 0;
+                    staged = false;
+                    if (dynamic) {
+                        const int next = __shfl_sync(0xffffffffu, pending, 0);
+                        group_base = next >= ngroups ? end : next * gt;
+                        if (lane == 0 && group_base < end) pending = atomicAdd(a.work, 1);
+                    } else {
+                        group_base += group_step;
+                    }
+                    more = group_base < end;
+                }
+            }
         }
-        if (g >= lag && !dead) {
+        if (issued - consumed > lag || (!more && consumed < issued)) {
             const uint32_t bar = smem_addr(&s_bar[cslot]);
             const long long t0 = clock64();
             while (!mbar_try_wait(bar, cphase)) {
@@ -521,17 +566,36 @@ gather_bulk_kernel(const GatherArgs a) {
                     }
                 }
                 bulk_commit();
+                ++consumed;
                 if (++cslot == S) { cslot = 0; cphase ^= 1; }
             }
         }
     }
     bulk_wait_read<0>();
     if (dead && lane == 0) raise(a.status, BARQKV_S_TIMEOUT);
+    if (dynamic && lane == 0) {
+        // The last CTA to finish re-arms the counters for the next launch.
+        __threadfence();
+        const int finished = atomicAdd(a.work + 1, 1);
+        if (finished == (int)gridDim.x - 1) {
+            __threadfence();
+            a.work[0] = 0;
+            a.work[1] = 0;
+        }
+    }
 }
 
 // --------------------------------------------------------------------------
 // host side
 // --------------------------------------------------------------------------
+// Tuning knobs (barqkv_set_tuning); 0 = automatic.
+int g_knob_stages = 0;
+int g_knob_bulk_ctas_per_sm = 0;
+int g_knob_vector_ctas_per_sm = 0;
+int g_knob_interleave = -1;
+int g_knob_group_tiles = 0;
+int g_knob_static = 0;
+
 struct DeviceInfo {
     int sms = 0;
     int smem_optin = 0;
@@ -643,6 +707,18 @@ int barqkv_sm_count(void) {
     DeviceInfo* d = device_info();
     if (!d) return fail(BARQKV_E_LAUNCH, "no CUDA device is current");
     return d->sms;
+}
+
+int barqkv_set_tuning(int32_t knob, int32_t value) {
+    switch (knob) {
+        case BARQKV_KNOB_BULK_STAGES: g_knob_stages = value; return 0;
+        case BARQKV_KNOB_BULK_CTAS_PER_SM: g_knob_bulk_ctas_per_sm = value; return 0;
+        case BARQKV_KNOB_VECTOR_CTAS_PER_SM: g_knob_vector_ctas_per_sm = value; return 0;
+        case BARQKV_KNOB_INTERLEAVE: g_knob_interleave = value; return 0;
+        case BARQKV_KNOB_GROUP_TILES: g_knob_group_tiles = value; return 0;
+        case BARQKV_KNOB_STATIC_SHARES: g_knob_static = value; return 0;
+        default: return fail(BARQKV_E_INVALID, "set_tuning: unknown knob");
+    }
 }
 
 int barqkv_append(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,
@@ -760,7 +836,7 @@ int barqkv_gather(const barqkv_pool_layout* pool, const void* k_pool, const void
                   const int32_t* seq_lens, const int32_t* cu_out, int32_t n,
                   int64_t total_tokens_hint,
                   void* k_out, void* v_out, const barqkv_rows_layout* out_rows,
-                  int32_t mode, int32_t* status, barqkv_stream_t stream) {
+                  int32_t mode, int32_t* status, int32_t* work, barqkv_stream_t stream) {
     if (int rc = check_pool(pool)) return rc;
     if (n < 0) return fail(BARQKV_E_INVALID, "gather: negative batch size");
     if (n == 0) return 0;
@@ -795,6 +871,11 @@ int barqkv_gather(const barqkv_pool_layout* pool, const void* k_pool, const void
     a.orow.head = out_rows->head_stride * e;
     a.orow.packed = out_rows->packed;
     a.status = status;
+    a.interleave = g_knob_interleave < 0 ? 0 : g_knob_interleave;
+    a.work = g_knob_static ? nullptr : work;
+    a.group_tiles = g_knob_group_tiles ? g_knob_group_tiles : (a.heads >= 8 ? 1 : 8 / a.heads);
+    if (a.group_tiles > kGroup) a.group_tiles = kGroup;
+    if (a.group_tiles < 1) a.group_tiles = 1;
 
     const int vec = vector_bytes(a.row_bytes, {a.pool_head, a.pool_page, a.orow.seq, a.orow.tok, a.orow.head},
                                  {k_pool, v_pool, k_out, v_out});
@@ -811,7 +892,9 @@ int barqkv_gather(const barqkv_pool_layout* pool, const void* k_pool, const void
     if (use_bulk) {
         int S = (int)(64 * 1024 / (2 * page_bytes));
         if (S > 8) S = 8;
+        if (g_knob_stages) S = g_knob_stages;
         if (S < 3) S = 3;
+        if (S > 32) S = 32;
         a.stages = S;
         const size_t smem = (size_t)S * 2 * page_bytes + (size_t)S * 8 /*bar*/ + (size_t)S * 8 /*slot dst*/ +
                             2 * kGroup * 8 + kGroup * 4 + (size_t)S * 4 + 4 + (size_t)(n + 1) * 4;
@@ -826,6 +909,7 @@ int barqkv_gather(const barqkv_pool_layout* pool, const void* k_pool, const void
         int per_sm = (int)((220 * 1024) / (smem + 1024));
         if (per_sm < 1) per_sm = 1;
         if (per_sm > 8) per_sm = 8;
+        if (g_knob_bulk_ctas_per_sm) per_sm = g_knob_bulk_ctas_per_sm;
         long long grid = (long long)d->sms * per_sm;
         const long long units_bound = tiles_bound * a.heads;
         const long long want = (units_bound + 2 * S - 1) / (2 * S);   // at least two ring rounds per CTA
@@ -833,7 +917,7 @@ int barqkv_gather(const barqkv_pool_layout* pool, const void* k_pool, const void
         gather_bulk_kernel<<<(int)grid, 32, smem, st>>>(a);
     } else {
         const size_t smem = (size_t)(n + 1) * 4;
-        long long grid = (long long)d->sms * 8;
+        long long grid = (long long)d->sms * (g_knob_vector_ctas_per_sm ? g_knob_vector_ctas_per_sm : 8);
         const long long want = (tiles_bound + 3) / 4;
         if (want < grid) grid = want < 1 ? 1 : want;
         switch (vec) {

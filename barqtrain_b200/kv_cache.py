@@ -154,7 +154,7 @@ class BarqPagedKVCacheLayer(CacheLayerMixin):
         backend.gather_raw(pool, self.keys.data_ptr(), self.values.data_ptr(), table, self.seq_lens.data_ptr(), None,
                            rows, sum(self._host_lens[:rows]), k_out.data_ptr(), v_out.data_ptr(), out_rows,
                            _ffi.MODES[mode], backend.status_word(self.device).data_ptr(),
-                           backend._stream(self.device))
+                           backend.work_words(self.device).data_ptr(), backend._stream(self.device))
         return k_out, v_out
 
     def update(self, key_states: torch.Tensor, value_states: torch.Tensor,

@@ -349,7 +349,7 @@ def run_barqkv(args):
 # ---------------------------------------------------------------------------
 # the CPU arm: the oracle's port of the reference's CPU path
 # ---------------------------------------------------------------------------
-def cpu_baseline(budget_s: float = 15.0, want_native: bool = True, steps_max: int = 60, warmup: int = 1):
+def cpu_baseline(budget_s: float = 15.0, want_native: bool = True, steps_max: int = 2000, warmup: int = 1):
     """Time the reference's CPU algorithm (per-token strided assignment loop for append,
     flattened view + ``.contiguous()`` for gather) on ONE layer of the workload, all 64
     sequences at their prompt lengths, for whole decode steps until ``budget_s`` is used."""
@@ -449,6 +449,111 @@ def cpu_baseline_native(prompts, budget_s: float = 5.0):
     return {"value": round(moved / dt / 1e9, 3), "unit": UNIT, "cores": c_oracle.threads(), "steps": steps}
 
 
+# ---------------------------------------------------------------------------
+# single-kernel cases (the commands the ncu summaries under profiles/ were made with)
+# ---------------------------------------------------------------------------
+def run_micro(args):
+    """One kernel alone on a small case of the workload's shape: per-launch CUDA-event times."""
+    from barqtrain_b200 import BlockTableKVCache, _ffi
+
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(device)
+    backend = _ffi.require_cuda_backend()
+    if args.tune:
+        backend.set_tuning(**{k: int(v) for k, v in (kv.split("=") for kv in args.tune.split(","))})
+    H, D, ps = args.heads, CFG["head_dim"], args.page_size
+    dtype = torch.bfloat16
+    gen = torch.Generator(device=device).manual_seed(7)
+    g = torch.Generator().manual_seed(CFG["seed"])
+    if args.micro == "gather":
+        if args.lengths == "loguniform":          # the 70B-shaped gather configuration: 32 sequences in [1k, 32k]
+            import math
+            u = torch.rand(32, generator=g, dtype=torch.float64)
+            lens = [int(round(math.exp(math.log(1024) + float(x) * (math.log(32768) - math.log(1024))))) for x in u]
+        else:
+            lens = torch.randint(CFG["prompt_lo"], CFG["prompt_hi"] + 1, (CFG["batch"],), generator=g).tolist()
+    elif args.micro == "append-prefill":
+        lens = [args.chunk * 4] * 16
+    else:
+        lens = [1024] * CFG["batch"]
+    B = len(lens)
+    pages = sum(-(-(n + 64) // ps) for n in lens)
+    cache = BlockTableKVCache(1, H, D, page_size=ps, num_pages=pages, max_seqs=B,
+                              max_blocks_per_seq=-(-(max(lens) + 64) // ps), dtype=dtype, device=device,
+                              free_order=torch.randperm(pages, generator=g).tolist(), zero_pages=False)
+    slots = [cache.open(i) for i in range(B)]
+    per_tok = 4 * H * D * 2
+    times, nbytes = [], 0
+
+    def timed(fn):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        return e0, e1
+
+    reps = 1
+    if args.micro == "gather":
+        total = sum(lens)
+        k = torch.randn(total, H, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
+        cache.append_step(slots, lens, [k], [k])
+        gb = cache.begin_gather(slots)
+        shape = (H, total, D) if args.layout == "HND" else (total, H, D)
+        out = (torch.empty(shape, dtype=dtype, device=device), torch.empty(shape, dtype=dtype, device=device))
+
+        def launch():
+            cache.gather(0, gb, args.layout, out=out, mode=args.mode)
+        nbytes = total * per_tok
+    elif args.micro == "append-prefill":
+        total = args.chunk * B
+        k = torch.randn(total, H, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
+        v = torch.randn(total, H, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
+        batch = cache.begin_append(slots, [args.chunk] * B)    # the same chunk lands on the same pages every launch
+
+        def launch():
+            cache.append(0, batch, k, v)
+        nbytes = total * per_tok
+    else:  # append-decode: `layers` back-to-back single-token appends form one timed group
+        k = torch.randn(B, H, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
+        fill = k.repeat(1024, 1, 1)[: sum(lens)]
+        cache.append_step(slots, lens, [fill], [fill])
+        batch = cache.begin_append(slots, [1] * B)
+        reps = args.layers
+
+        def launch():
+            for _ in range(args.layers):
+                cache.append(0, batch, k, k)
+        nbytes = B * per_tok * args.layers
+
+    for _ in range(args.warmup):
+        launch()
+    torch.cuda.synchronize(device)
+    if args.graph:
+        # the launches recorded into a CUDA graph: what the kernels take without the host's call overhead
+        side = torch.cuda.Stream(device)
+        with torch.cuda.stream(side):
+            launch()
+            torch.cuda.synchronize(device)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                launch()
+        evs = [timed(graph.replay) for _ in range(args.steps)]
+    else:
+        evs = [timed(launch) for _ in range(args.steps)]
+    args.warmup = 0
+    torch.cuda.synchronize(device)
+    times = sorted(e0.elapsed_time(e1) * 1e-3 for e0, e1 in evs[args.warmup:])
+    med = times[len(times) // 2]
+    peak, kind = measured_peak()
+    status = backend.read_status(device)
+    print(json.dumps({"micro": args.micro, "tune": args.tune, "graph": bool(args.graph), "launches_per_sample": reps,
+                      "us_per_launch": round(med * 1e6 / reps, 2), "mode": args.mode, "layout": args.layout, "heads": H, "page_size": ps,
+                      "sequences": B, "tokens": sum(lens) if args.micro == "gather" else None,
+                      "bytes_per_launch": nbytes, "us_median": round(med * 1e6, 2), "us_min": round(times[0] * 1e6, 2),
+                      "gbs_median": round(nbytes / med / 1e9, 1), "gbs_best": round(nbytes / times[0] / 1e9, 1),
+                      "frac_of_%s_peak" % kind: round(nbytes / med / 1e9 / peak, 4), "status": status}), flush=True)
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -477,8 +582,21 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="barqkv", choices=["barqkv", "reference"])
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="budget of the CPU baseline leg")
+    ap.add_argument("--micro", choices=["gather", "append-prefill", "append-decode"],
+                    help="time one kernel alone on a one-layer case instead of the full step")
+    ap.add_argument("--mode", default="auto", choices=["auto", "vector", "bulk"])
+    ap.add_argument("--layout", default="HND", choices=["HND", "NHD"])
+    ap.add_argument("--heads", type=int, default=8, help="KV heads on this GPU (micro cases)")
+    ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--chunk", type=int, default=2048, help="tokens per sequence per append (append-prefill)")
+    ap.add_argument("--layers", type=int, default=32, help="appends per timed group (append-decode)")
+    ap.add_argument("--lengths", default="uniform", choices=["uniform", "loguniform"])
+    ap.add_argument("--graph", action="store_true", help="micro cases: time a CUDA-graph replay of the launches")
+    ap.add_argument("--tune", default="", help="gather knobs, e.g. stages=8,ctas=3,interleave=1 (micro cases)")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.micro:
+        run_micro(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_barqkv(args)

@@ -98,11 +98,22 @@ typedef struct barqkv_rows_layout {
     int32_t reserved;
 } barqkv_rows_layout;
 
+/* tuning knobs for experiments (process-wide, not thread-safe); value 0 restores the default */
+#define BARQKV_KNOB_BULK_STAGES 1        /* ring stages of the bulk gather (3..32) */
+#define BARQKV_KNOB_BULK_CTAS_PER_SM 2   /* persistent one-warp CTAs per SM of the bulk gather */
+#define BARQKV_KNOB_VECTOR_CTAS_PER_SM 3 /* CTAs per SM of the vector gather */
+#define BARQKV_KNOB_INTERLEAVE 4         /* static shares only. 1: every gridDim-th group of 32 pages; 0: contiguous */
+#define BARQKV_KNOB_GROUP_TILES 5        /* pages handed out per atomic fetch by the bulk gather (1..32) */
+#define BARQKV_KNOB_STATIC_SHARES 6      /* 1: ignore `work` and split pages statically among CTAs */
+
 int barqkv_version(void);
 const char* barqkv_last_error(void);
 
 /* Number of SMs of the current device (cached); used by callers that size work. */
 int barqkv_sm_count(void);
+
+/* Set a BARQKV_KNOB_* value.  No counterpart in the reference, which has no tunables. */
+int barqkv_set_tuning(int32_t knob, int32_t value);
 
 /*
  * Append new K/V rows through the block table.
@@ -156,13 +167,19 @@ int barqkv_append_legacy(void* key_cache, void* value_cache, int32_t* seq_lens,
  * into a padded [n, H, max_len, D] batch (packed 0).  Rows at and beyond a
  * sequence's length are not touched.  total_tokens_hint: an upper bound of
  * sum(seq_lens) used only to size the grid (0 = unknown).
+ * work: device int32[2] scratch, zero before its first use, or NULL.  With it
+ * the bulk gather hands pages to its persistent CTAs through an atomic counter
+ * (SMs differ in how fast they reach memory; equal static shares leave the
+ * fast ones idle at the end).  The kernel leaves both words zero.  Launches
+ * that may overlap on the device must not share a work buffer.  NULL selects
+ * equal static shares.
  */
 int barqkv_gather(const barqkv_pool_layout* pool, const void* k_pool, const void* v_pool,
                   const barqkv_block_table* table,
                   const int32_t* seq_lens, const int32_t* cu_out, int32_t n,
                   int64_t total_tokens_hint,
                   void* k_out, void* v_out, const barqkv_rows_layout* out_rows,
-                  int32_t mode, int32_t* status, barqkv_stream_t stream);
+                  int32_t mode, int32_t* status, int32_t* work, barqkv_stream_t stream);
 
 #ifdef __cplusplus
 }
