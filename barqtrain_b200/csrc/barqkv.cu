@@ -932,4 +932,51 @@ int barqkv_gather(const barqkv_pool_layout* pool, const void* k_pool, const void
     return ce == cudaSuccess ? 0 : fail_cuda("gather launch", ce);
 }
 
+// --------------------------------------------------------------------------
+// gather for callers that cannot allocate device memory
+// --------------------------------------------------------------------------
+// The hand-out counters of the bulk gather normally live in a caller-owned
+// device buffer (`work`).  Some callers have no way to own one: an inference
+// server that gave every free byte of HBM to its own arena at start-up (a later
+// cudaMalloc fails, or stalls the device while the driver makes room), or an
+// operator plugin whose host forbids allocation inside a call.  For them the
+// counters live in this array, which is part of the library image: every GPU
+// that loads the library holds these 4 KiB until the process exits.
+//
+// BARQKV_STATIC_WORK_SLOTS pairs of counters, one 128-byte line apart so that
+// launches using different slots do not contend on a line.
+constexpr int kStaticWorkStride = 32;   // int32 words between slots
+static __device__ __align__(256) int32_t g_static_work[BARQKV_STATIC_WORK_SLOTS * kStaticWorkStride];
+
+// Device address of g_static_work per device.  In host code the array's name is
+// only a handle for the runtime, not an address a kernel can use, so it is
+// translated once per device with that device current.
+static int32_t* g_static_work_addr[64];
+
+int barqkv_gather_noalloc(const barqkv_pool_layout* pool, const void* k_pool, const void* v_pool,
+                          const barqkv_block_table* table,
+                          const int32_t* seq_lens, const int32_t* cu_out, int32_t n,
+                          int64_t total_tokens_hint,
+                          void* k_out, void* v_out, const barqkv_rows_layout* out_rows,
+                          int32_t mode, int32_t* status, int32_t work_slot, barqkv_stream_t stream) {
+    if (work_slot < 0 || work_slot >= BARQKV_STATIC_WORK_SLOTS)
+        return fail(BARQKV_E_LIMIT, "gather_noalloc: work_slot is outside the built-in scratch (32 slots: 0..31)");
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail_cuda("gather_noalloc: cudaGetDevice", e);
+    if (dev < 0 || dev >= 64) return fail(BARQKV_E_LIMIT, "gather_noalloc: device ordinal above 63");
+    if (!g_static_work_addr[dev]) {
+        void* addr = nullptr;
+        e = cudaGetSymbolAddress(&addr, g_static_work);
+        if (e != cudaSuccess || !addr) return fail_cuda("gather_noalloc: cudaGetSymbolAddress", e);
+        g_static_work_addr[dev] = static_cast<int32_t*>(addr);
+    }
+    int32_t* work = g_static_work_addr[dev] + (size_t)work_slot * kStaticWorkStride;
+    // The slot keeps whatever its previous user left; the counters must start at zero.
+    e = cudaMemsetAsync(work, 0, 2 * sizeof(int32_t), static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail_cuda("gather_noalloc: cudaMemsetAsync", e);
+    return barqkv_gather(pool, k_pool, v_pool, table, seq_lens, cu_out, n, total_tokens_hint, k_out, v_out, out_rows,
+                         mode, status, work, stream);
+}
+
 }  // extern "C"

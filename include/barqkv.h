@@ -181,6 +181,35 @@ int barqkv_gather(const barqkv_pool_layout* pool, const void* k_pool, const void
                   void* k_out, void* v_out, const barqkv_rows_layout* out_rows,
                   int32_t mode, int32_t* status, int32_t* work, barqkv_stream_t stream);
 
+/*
+ * barqkv_gather for callers that cannot allocate device memory.
+ * No counterpart in the reference (it never needs scratch memory).
+ *
+ * Same arguments and results as barqkv_gather, except that the two hand-out
+ * counters come from a 4 KiB array built into the library instead of a
+ * caller-owned `work` buffer.  Meant for callers such as a server that has
+ * already given all free device memory to its own arena, or a plugin host that
+ * forbids allocation inside an operator call.  This function and everything it
+ * calls allocate nothing, on the host or on the device.
+ *
+ * work_slot selects one of BARQKV_STATIC_WORK_SLOTS counter pairs; a value
+ * outside [0, BARQKV_STATIC_WORK_SLOTS) is refused with BARQKV_E_LIMIT.  All
+ * calls on a device share the array, and a slot still holds what its last
+ * user left: each call first clears its slot on `stream`.  Two calls that can
+ * be in flight on the GPU at the same time (different streams) must use
+ * different slots, or they corrupt each other's page hand-out.
+ *
+ * The first call on each device looks up the array's device address (with
+ * that device current).  Make that first call outside any stream capture.
+ */
+#define BARQKV_STATIC_WORK_SLOTS 32
+int barqkv_gather_noalloc(const barqkv_pool_layout* pool, const void* k_pool, const void* v_pool,
+                          const barqkv_block_table* table,
+                          const int32_t* seq_lens, const int32_t* cu_out, int32_t n,
+                          int64_t total_tokens_hint,
+                          void* k_out, void* v_out, const barqkv_rows_layout* out_rows,
+                          int32_t mode, int32_t* status, int32_t work_slot, barqkv_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
