@@ -21,6 +21,7 @@ All device work goes through ``libbarqkv.so``; there is no CPU path.
 
 from __future__ import annotations
 
+import ctypes
 from dataclasses import dataclass
 from typing import Dict, Iterable, List, Optional, Sequence, Tuple
 
@@ -109,7 +110,10 @@ class _Descriptor:
     (append) or the length (gather) and ``cu`` the packed row offsets."""
 
     def __init__(self, n: int, dev: torch.Tensor, total: int, host_first: List[int], host_cu: List[int],
-                 slots: List[int]):
+                 slots: List[int], table_ref=None, stream: int = 0, work: int = 0):
+        self.table_ref = table_ref      # ctypes reference to a barqkv_block_table whose `slots` points into `dev`
+        self.stream = stream            # the CUDA stream the description was uploaded on
+        self.work = work                # gather only: the stream's hand-out counters
         self.n = n
         self.dev = dev
         self.total = total
@@ -172,7 +176,15 @@ class BlockTableKVCache:
         self._ring_pos = 0
         self._ring_words = 0
         self._desc_dev: Dict[str, torch.Tensor] = {}
+        self._tables: Dict[str, _ffi.BlockTable] = {}
         self._status = self.backend.status_word(self.device)
+        # per-call constants of the native calls, resolved once
+        self._status_ptr = self._status.data_ptr()
+        self._pool_ref = ctypes.byref(self._pool_layout)
+        self._c_append = self.backend.lib.barqkv_append
+        self._c_gather = self.backend.lib.barqkv_gather
+        self._rows: Dict[Tuple[int, ...], object] = {}
+        self._new_shape = (0, num_kv_heads, head_dim)
 
     # -- sequences and pages ----------------------------------------------------
     def open(self, seq_id=None) -> int:
@@ -263,7 +275,14 @@ class BlockTableKVCache:
         # the device buffer is laid out for this n: [slots | first | cu]
         dev[:words].copy_(buf[:words], non_blocking=True)
         self._stage_done()
-        return _Descriptor(n, dev, cu[n], first, cu, list(slots))
+        table = self._tables.get(kind)
+        if table is None:
+            table = _ffi.BlockTable(self.table_dev.data_ptr(), None, self.max_seqs, self.max_blocks, 0, 0)
+            self._tables[kind] = table
+        table.slots = dev.data_ptr()
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        work = self.backend.work_words(self.device).data_ptr() if kind == "gather" else 0
+        return _Descriptor(n, dev, cu[n], first, cu, list(slots), ctypes.byref(table), stream, work)
 
     # -- append -------------------------------------------------------------------
     def begin_append(self, slots: Sequence[int], counts: Sequence[int]) -> _Descriptor:
@@ -281,25 +300,39 @@ class BlockTableKVCache:
     def append(self, layer: int, batch: _Descriptor, k_new: torch.Tensor, v_new: torch.Tensor) -> None:
         """Scatter packed new rows ``[total_tokens, kv_heads, head_dim]`` (any strides with a
         contiguous last dimension; ``[H, T, D].transpose(0, 1)`` works) into the layer's pages."""
-        if batch.total == 0:
+        total = batch.total
+        if total == 0:
             return
-        if k_new.shape != v_new.shape or k_new.dim() != 3:
+        shape = k_new.shape
+        if shape != v_new.shape or len(shape) != 3:
             raise ValueError("k_new and v_new must both be [total_tokens, kv_heads, head_dim]")
-        if k_new.shape != (batch.total, self.num_kv_heads, self.head_dim):
-            raise ValueError(f"new rows have shape {tuple(k_new.shape)}, expected "
-                             f"{(batch.total, self.num_kv_heads, self.head_dim)}")
+        if shape[0] != total or shape[1] != self.num_kv_heads or shape[2] != self.head_dim:
+            raise ValueError(f"new rows have shape {tuple(shape)}, expected "
+                             f"{(total, self.num_kv_heads, self.head_dim)}")
         if k_new.dtype != self.dtype or v_new.dtype != self.dtype:
             raise ValueError("new rows must be in the cache dtype")
         if k_new.device != self.device or v_new.device != self.device:
             raise ValueError("new rows must be on the cache device")
-        if k_new.stride(2) != 1 or v_new.stride() != k_new.stride():
+        strides = k_new.stride()
+        if strides[2] != 1 or v_new.stride() != strides:
             k_new, v_new = k_new.contiguous(), v_new.contiguous()
-        rows = _ffi.RowsLayout(0, k_new.stride(0), k_new.stride(1), 1, 0)
-        self._table.slots = batch.p_slots
-        self.backend.append_raw(self._pool_layout, self._k_ptr[layer], self._v_ptr[layer], self._table,
-                                batch.p_first, batch.p_cu, batch.n, 0, batch.total,
-                                k_new.data_ptr(), v_new.data_ptr(), rows, self._status.data_ptr(),
-                                torch.cuda.current_stream(self.device).cuda_stream)
+            strides = k_new.stride()
+        rows_ref = self._rows.get(strides)
+        if rows_ref is None:
+            rows_ref = self._rows[strides] = self._rows_ref(0, strides[0], strides[1])
+        rc = self._c_append(self._pool_ref, self._k_ptr[layer], self._v_ptr[layer], batch.table_ref,
+                            batch.p_first, batch.p_cu, batch.n, 0, total, k_new.data_ptr(), v_new.data_ptr(),
+                            rows_ref, self._status_ptr, batch.stream)
+        if rc:
+            self.backend._check(rc)
+        self.backend.launches += 1
+
+    def _rows_ref(self, seq_stride: int, tok_stride: int, head_stride: int):
+        """A cached ctypes reference to a packed ``barqkv_rows_layout``."""
+        layout = _ffi.RowsLayout(seq_stride, tok_stride, head_stride, 1, 0)
+        self._keep = getattr(self, "_keep", [])
+        self._keep.append(layout)               # byref() does not own the structure
+        return ctypes.byref(layout)
 
     def end_append(self, batch: _Descriptor) -> None:
         for i, s in enumerate(batch.slots):
@@ -337,18 +370,26 @@ class BlockTableKVCache:
             v_out = torch.empty(shape, dtype=self.dtype, device=self.device)
         else:
             k_out, v_out = out
-            if tuple(k_out.shape) != shape or tuple(v_out.shape) != shape or not k_out.is_contiguous() \
+            if k_out.shape != shape or v_out.shape != shape or not k_out.is_contiguous() \
                     or not v_out.is_contiguous() or k_out.dtype != self.dtype or k_out.device != self.device:
                 raise ValueError(f"out tensors must be contiguous {shape} in the cache dtype on the cache device")
         if total == 0:
             return k_out, v_out
-        rows = _ffi.RowsLayout(0, D, total * D, 1, 0) if layout == "HND" else _ffi.RowsLayout(0, H * D, D, 1, 0)
-        self._table.slots = batch.p_slots
-        self.backend.gather_raw(self._pool_layout, self._k_ptr[layer], self._v_ptr[layer], self._table,
-                                batch.p_first, batch.p_cu, batch.n, total, k_out.data_ptr(), v_out.data_ptr(),
-                                rows, _ffi.MODES[mode or self.gather_mode], self._status.data_ptr(),
-                                self.backend.work_words(self.device).data_ptr(),
-                                torch.cuda.current_stream(self.device).cuda_stream)
+        key = (layout, total)
+        rows_ref = self._rows.get(key)
+        if rows_ref is None:
+            if len(self._rows) > 4096:
+                self._rows.clear()
+                self._keep = []
+            rows_ref = self._rows[key] = (self._rows_ref(0, D, total * D) if layout == "HND"
+                                          else self._rows_ref(0, H * D, D))
+        rc = self._c_gather(self._pool_ref, self._k_ptr[layer], self._v_ptr[layer], batch.table_ref,
+                            batch.p_first, batch.p_cu, batch.n, total, k_out.data_ptr(), v_out.data_ptr(),
+                            rows_ref, _ffi.MODES[mode or self.gather_mode], self._status_ptr, batch.work,
+                            batch.stream)
+        if rc:
+            self.backend._check(rc)
+        self.backend.launches += 1
         return k_out, v_out
 
     def gather_sequence(self, layer: int, seq_id, layout: str = "HND") -> Tuple[torch.Tensor, torch.Tensor]:

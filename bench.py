@@ -117,11 +117,12 @@ class ClockSampler:
 class DecodeWorkload:
     def __init__(self, world: int, rank: int, device: torch.device, total_steps: int):
         from barqtrain_b200 import BlockTableKVCache
+        from barqtrain_b200.sharding import kv_head_shard
 
         self.L, self.D, self.ps, self.B = CFG["layers"], CFG["head_dim"], CFG["page_size"], CFG["batch"]
         if CFG["kv_heads"] % world:
             raise SystemExit(f"--gpus must divide the {CFG['kv_heads']} KV heads")
-        self.H = CFG["kv_heads"] // world                   # KV-head shard of this rank
+        self.first_head, self.H = kv_head_shard(CFG["kv_heads"], world, rank)   # this rank's KV heads
         self.dtype = torch.bfloat16
         self.device = device
         g, self.prompts = seeded_lengths()
@@ -181,25 +182,23 @@ class DecodeWorkload:
         cache.end_append(ab)                       # lengths now include this step's token
         gb = cache.begin_gather(self.slots)
         total = gb.total
+        # [H, total, D] prefixes of the two reusable output buffers (layers alternate between them)
+        n = self.H * total * self.D
+        outs = [(ko.view(-1)[:n].view(self.H, total, self.D), vo.view(-1)[:n].view(self.H, total, self.D))
+                for ko, vo in self.out]
+        k_rows, v_rows = k_all.unbind(0), v_all.unbind(0)
         for layer in range(self.L):
-            cache.append(layer, ab, k_all[layer], v_all[layer])
+            cache.append(layer, ab, k_rows[layer], v_rows[layer])
             if events is not None:
                 e0 = torch.cuda.Event(enable_timing=True)
                 e1 = torch.cuda.Event(enable_timing=True)
                 e0.record()
-            self._gather_into(layer, gb, total)
+            cache.gather(layer, gb, "HND", out=outs[layer & 1])
             if events is not None:
                 e1.record()
                 events.append((e0, e1, total))
         self.step_no += 1
         return total
-
-    def _gather_into(self, layer: int, gb, total: int):
-        # write into a preallocated [H, total, D] prefix of the reusable output buffers
-        ko, vo = self.out[layer & 1]
-        k_view = ko.view(-1)[: self.H * total * self.D].view(self.H, total, self.D)
-        v_view = vo.view(-1)[: self.H * total * self.D].view(self.H, total, self.D)
-        self.cache.gather(layer, gb, "HND", out=(k_view, v_view))
 
     def resident_step(self, events=None):
         i = self.step_no % 4
