@@ -57,8 +57,8 @@ class RowsLayout(ctypes.Structure):
     _fields_ = [("seq_stride", _i64), ("tok_stride", _i64), ("head_stride", _i64), ("packed", _i32), ("reserved", _i32)]
 
 
-EXPORTS = ("barqkv_version", "barqkv_last_error", "barqkv_sm_count", "barqkv_set_tuning", "barqkv_append",
-           "barqkv_append_legacy", "barqkv_gather")
+EXPORTS = ("barqkv_version", "barqkv_last_error", "barqkv_sm_count", "barqkv_launch_count", "barqkv_set_tuning", "barqkv_append",
+           "barqkv_append_legacy", "barqkv_gather", "barqkv_update")
 KNOBS = {"stages": 1, "ctas": 2, "vctas": 3, "interleave": 4, "group": 5, "static": 6}
 
 
@@ -104,11 +104,20 @@ class CudaBackend:
         lib.barqkv_gather.restype = _i32
         lib.barqkv_gather.argtypes = [P(PoolLayout), _ptr, _ptr, P(BlockTable), _ptr, _ptr, _i32, _i64,
                                       _ptr, _ptr, P(RowsLayout), _i32, _ptr, _ptr, _ptr]
+        lib.barqkv_update.restype = _i32
+        lib.barqkv_update.argtypes = [P(PoolLayout), _ptr, _ptr, P(BlockTable), _ptr, _ptr, _i32, _i32, _i32,
+                                      _ptr, _ptr, P(RowsLayout), _ptr, _i64, _ptr, _ptr, P(RowsLayout),
+                                      _i32, _ptr, _ptr, _ptr, _ptr]
         self.version = int(lib.barqkv_version())
-        self.launches = 0                      # kernels enqueued through this object
+        lib.barqkv_launch_count.restype = _i64
         self._status: Dict[int, "object"] = {}
         self._tickets: Dict[Tuple[int, int], "object"] = {}
         self._work: Dict[Tuple[int, int], "object"] = {}
+
+    @property
+    def launches(self) -> int:
+        """Kernels the library has enqueued in this process (counted in C at every launch)."""
+        return int(self.lib.barqkv_launch_count())
 
     # -- plumbing -----------------------------------------------------------
     def _check(self, rc: int) -> None:
@@ -181,8 +190,6 @@ class CudaBackend:
         self._check(self.lib.barqkv_append(ctypes.byref(pool), k_pool, v_pool, ctypes.byref(table), seq_start, cu_new,
                                            n, tokens_per_entry, total_tokens, k_new, v_new, ctypes.byref(rows),
                                            status, stream))
-        if n and total_tokens:
-            self.launches += 1
 
     def gather_raw(self, pool: PoolLayout, k_pool: int, v_pool: int, table: BlockTable, seq_lens: int,
                    cu_out: Optional[int], n: int, total_tokens_hint: int, k_out: int, v_out: int,
@@ -190,8 +197,6 @@ class CudaBackend:
         self._check(self.lib.barqkv_gather(ctypes.byref(pool), k_pool, v_pool, ctypes.byref(table), seq_lens, cu_out,
                                            n, total_tokens_hint, k_out, v_out, ctypes.byref(rows), mode,
                                            status, work, stream))
-        if n:
-            self.launches += 1
 
     # -- the reference's native entry point -----------------------------------
     def paged_kv_append_(self, key_cache, value_cache, seq_lens, key_states, value_states, *,
@@ -267,7 +272,6 @@ class CudaBackend:
             key_cache.data_ptr(), value_cache.data_ptr(), lens.data_ptr(), k_new.data_ptr(), v_new.data_ptr(),
             ctypes.byref(rows), batch, max_batch, heads, tokens, head_dim, max_blocks, page_size,
             key_cache.element_size(), ticket.data_ptr(), status.data_ptr(), stream))
-        self.launches += 1
         if lens is not seq_lens:
             seq_lens[:batch].add_(tokens)
 

@@ -183,6 +183,7 @@ class BlockTableKVCache:
         self._pool_ref = ctypes.byref(self._pool_layout)
         self._c_append = self.backend.lib.barqkv_append
         self._c_gather = self.backend.lib.barqkv_gather
+        self._c_update = self.backend.lib.barqkv_update
         self._rows: Dict[Tuple[int, ...], object] = {}
         self._new_shape = (0, num_kv_heads, head_dim)
 
@@ -325,7 +326,6 @@ class BlockTableKVCache:
                             rows_ref, self._status_ptr, batch.stream)
         if rc:
             self.backend._check(rc)
-        self.backend.launches += 1
 
     def _rows_ref(self, seq_stride: int, tok_stride: int, head_stride: int):
         """A cached ctypes reference to a packed ``barqkv_rows_layout``."""
@@ -389,7 +389,63 @@ class BlockTableKVCache:
                             batch.stream)
         if rc:
             self.backend._check(rc)
-        self.backend.launches += 1
+        return k_out, v_out
+
+    # -- append + gather in one call ------------------------------------------------
+    def update(self, layer: int, new: _Descriptor, full: _Descriptor, k_new: torch.Tensor, v_new: torch.Tensor,
+               layout: str = "HND", out: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
+               mode: Optional[str] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Append this step's rows and return every sequence gathered, new rows included - the
+        block-table form of the reference layer's ``update`` (``kv_cache.py:135-142``).
+
+        ``new`` comes from ``begin_append`` (followed by ``end_append``) and ``full`` from a
+        ``begin_gather`` of the same slots made after it.  For decode-sized appends this is one
+        kernel launch instead of two.
+        """
+        if full.slots != new.slots:
+            raise ValueError("update: the append and gather descriptions must list the same slots")
+        total, H, D = full.total, self.num_kv_heads, self.head_dim
+        if layout not in ("HND", "NHD"):
+            raise ValueError("layout must be 'HND' or 'NHD'")
+        shape = (H, total, D) if layout == "HND" else (total, H, D)
+        if out is None:
+            out = (torch.empty(shape, dtype=self.dtype, device=self.device),
+                   torch.empty(shape, dtype=self.dtype, device=self.device))
+        k_out, v_out = out
+        if k_out.shape != shape or v_out.shape != shape or not k_out.is_contiguous() \
+                or not v_out.is_contiguous() or k_out.dtype != self.dtype or k_out.device != self.device:
+            raise ValueError(f"out tensors must be contiguous {shape} in the cache dtype on the cache device")
+        if new.total:
+            nshape = k_new.shape
+            if nshape != v_new.shape or len(nshape) != 3 or nshape[0] != new.total or nshape[1] != H or nshape[2] != D:
+                raise ValueError(f"new rows must both be {(new.total, H, D)}")
+            if k_new.dtype != self.dtype or v_new.dtype != self.dtype or k_new.device != self.device \
+                    or v_new.device != self.device:
+                raise ValueError("new rows must be in the cache dtype on the cache device")
+            strides = k_new.stride()
+            if strides[2] != 1 or v_new.stride() != strides:
+                k_new, v_new = k_new.contiguous(), v_new.contiguous()
+                strides = k_new.stride()
+            new_ref = self._rows.get(strides)
+            if new_ref is None:
+                new_ref = self._rows[strides] = self._rows_ref(0, strides[0], strides[1])
+            k_ptr, v_ptr = k_new.data_ptr(), v_new.data_ptr()
+        else:
+            new_ref, k_ptr, v_ptr = self._rows_ref(0, H * D, D), None, None
+        if total == 0:
+            return k_out, v_out
+        key = (layout, total)
+        out_ref = self._rows.get(key)
+        if out_ref is None:
+            out_ref = self._rows[key] = (self._rows_ref(0, D, total * D) if layout == "HND"
+                                         else self._rows_ref(0, H * D, D))
+        rc = self._c_update(self._pool_ref, self._k_ptr[layer], self._v_ptr[layer], new.table_ref,
+                            new.p_first, new.p_cu, new.n, 0, new.total, k_ptr, v_ptr, new_ref,
+                            full.p_cu, total, k_out.data_ptr(), v_out.data_ptr(), out_ref,
+                            _ffi.MODES[mode or self.gather_mode], self._status_ptr, full.work, full.p_first,
+                            full.stream)
+        if rc:
+            self.backend._check(rc)
         return k_out, v_out
 
     def gather_sequence(self, layer: int, seq_id, layout: str = "HND") -> Tuple[torch.Tensor, torch.Tensor]:

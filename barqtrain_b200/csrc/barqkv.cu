@@ -29,6 +29,7 @@
 // Device-side guards never trap and never spin without a bound.
 
 #include <cuda_runtime.h>
+#include <atomic>
 #include <initializer_list>
 #include <stdint.h>
 #include <stdio.h>
@@ -48,6 +49,7 @@ constexpr int kBulkMaxStage = 32 * 1024;   // K page + V page of one head
 constexpr long long kWaitCycles = 2000000000LL;  // ~1 s: bound of any mbarrier wait
 
 thread_local char g_err[256] = "";
+std::atomic<long long> g_launches{0};   // kernels enqueued by this library, process-wide
 
 int fail(int code, const char* msg) {
     snprintf(g_err, sizeof(g_err), "%s", msg);
@@ -112,6 +114,16 @@ struct GatherArgs {
     int32_t* work;         // bulk kernel: [0] next group to hand out, [1] CTAs finished; null = static shares
     int group_tiles;       // bulk kernel, dynamic hand-out: (sequence, page) tiles per group
     int32_t* status;
+    // Fused append ("update", bulk kernel only; k_new == null means plain gather): seq_lens then holds
+    // the lengths BEFORE the append, entry i brings cu_new[i+1]-cu_new[i] (or tokens_per_entry) new rows,
+    // which are written to the output AND into their page slots of the pool.
+    const unsigned char* k_new;
+    const unsigned char* v_new;
+    unsigned char* k_pool_w;
+    unsigned char* v_pool_w;
+    const int32_t* cu_new;
+    int tokens_per_entry;
+    RowsB nr;
 };
 
 __device__ __forceinline__ void raise(int32_t* status, int bit) {
@@ -250,17 +262,24 @@ append_rows_kernel(const AppendArgs a) {
 // --------------------------------------------------------------------------
 // Exclusive prefix sum of per-entry page counts into s_cu[0..n]; returns nothing,
 // callers read s_cu[n] for the total after the trailing barrier.
-__device__ void scan_pages(const int32_t* lens, int n, int page_size, int* s_cu, int* s_part) {
+// Tokens entry i holds once the call is done (old length plus, when an append is fused in, its new rows).
+__device__ __forceinline__ int entry_new_rows(const GatherArgs& a, int i) {
+    if (!a.k_new) return 0;
+    return a.cu_new ? a.cu_new[i + 1] - a.cu_new[i] : a.tokens_per_entry;
+}
+__device__ __forceinline__ int entry_len(const GatherArgs& a, int i) {
+    return max(a.seq_lens[i], 0) + entry_new_rows(a, i);
+}
+
+__device__ void scan_pages(const GatherArgs& a, int* s_cu, int* s_part) {
+    const int n = a.n, page_size = a.page_size;
     const int tid = threadIdx.x;
     const int nthr = blockDim.x;
     const int chunk = (n + nthr - 1) / nthr;
     const int lo = min(n, tid * chunk);
     const int hi = min(n, lo + chunk);
     int sum = 0;
-    for (int i = lo; i < hi; ++i) {
-        const int len = max(lens[i], 0);
-        sum += (len + page_size - 1) / page_size;
-    }
+    for (int i = lo; i < hi; ++i) sum += (entry_len(a, i) + page_size - 1) / page_size;
     // inclusive scan inside the warp
     const int lane = tid & 31;
     int incl = sum;
@@ -276,8 +295,7 @@ __device__ void scan_pages(const int32_t* lens, int n, int page_size, int* s_cu,
     int run = before + incl - sum;
     for (int i = lo; i < hi; ++i) {
         s_cu[i] = run;
-        const int len = max(lens[i], 0);
-        run += (len + page_size - 1) / page_size;
+        run += (entry_len(a, i) + page_size - 1) / page_size;
     }
     if (lo < hi && hi == n) s_cu[n] = run;      // the thread that owns the last entry
     if (n == 0 && tid == 0) s_cu[0] = 0;
@@ -288,6 +306,8 @@ struct TileInfo {
     long long src;   // byte offset of the physical page within head 0's pool
     long long dst;   // byte offset of the page's first row (head 0) in the output
     int rows;        // valid rows in this page, 0 = skip
+    int rows_old;    // of those, rows already in the pool; the rest come from the new rows (fused append)
+    long long new_src;  // byte offset of the page's first new row (head 0) in the new rows
 };
 
 // Resolve flat tile q (a (sequence, page) pair) using the scanned page counts.
@@ -299,11 +319,19 @@ __device__ __forceinline__ TileInfo resolve_tile(const GatherArgs& a, const int*
     }
     const int i = lo;
     const int j = q - s_cu[i];
-    const int len = a.seq_lens[i];
+    const int len_old = max(a.seq_lens[i], 0);
+    const int len = len_old + entry_new_rows(a, i);
     TileInfo t;
     t.rows = min(a.page_size, len - j * a.page_size);
+    t.rows_old = min(t.rows, max(len_old - j * a.page_size, 0));
+    t.new_src = 0;
+    if (t.rows_old < t.rows) {
+        const long long tok = (long long)j * a.page_size + t.rows_old - len_old;      // index among the entry's new rows
+        const long long base = a.nr.packed ? (a.cu_new ? (long long)a.cu_new[i] : (long long)i * a.tokens_per_entry) : 0;
+        t.new_src = (long long)i * a.nr.seq + (base + tok) * a.nr.tok;
+    }
     const long long page = resolve_page(a.tb, i, j, a.status);
-    if (page < 0) t.rows = 0;
+    if (page < 0) t.rows = t.rows_old = 0;
     t.src = page * a.pool_page;
     const long long base_tok = (a.orow.packed ? (long long)a.cu_out[i] : 0) + (long long)j * a.page_size;
     t.dst = (long long)i * a.orow.seq + base_tok * a.orow.tok;
@@ -320,7 +348,7 @@ gather_vector_kernel(const GatherArgs a) {
     __shared__ int s_rows[kGroup];
 
     int* s_cu = s_dyn;
-    scan_pages(a.seq_lens, a.n, a.page_size, s_cu, s_part);
+    scan_pages(a, s_cu, s_part);
     const int total = s_cu[a.n];
     int lo, hi, group_step;
     if (a.interleave) {
@@ -444,18 +472,22 @@ gather_bulk_kernel(const GatherArgs a) {
     unsigned char* s_data = s_raw;                                          // [S][2][page_bytes]
     unsigned long long* s_bar = reinterpret_cast<unsigned long long*>(s_data + (size_t)S * 2 * page_bytes);
     long long* s_slot_dst = reinterpret_cast<long long*>(s_bar + S);        // [S] output offset incl. head
-    long long* s_src = s_slot_dst + S;                                      // [kGroup]
+    long long* s_slot_pool = s_slot_dst + S;                                // [S] pool offset incl. head
+    long long* s_src = s_slot_pool + S;                                     // [kGroup]
     long long* s_dst = s_src + kGroup;                                      // [kGroup]
-    int* s_rows = reinterpret_cast<int*>(s_dst + kGroup);                   // [kGroup]
-    int* s_slot_rows = s_rows + kGroup;                                     // [S]
-    int* s_part = s_slot_rows + S;                                          // [1]
+    long long* s_new = s_dst + kGroup;                                      // [kGroup] first new row (fused append)
+    int* s_rows = reinterpret_cast<int*>(s_new + kGroup);                   // [kGroup]
+    int* s_rows_old = s_rows + kGroup;                                      // [kGroup]
+    int* s_slot_rows = s_rows_old + kGroup;                                 // [S]
+    int* s_slot_rows_old = s_slot_rows + S;                                 // [S]
+    int* s_part = s_slot_rows_old + S;                                      // [1]
     int* s_cu = s_part + 1;                                                 // [n + 1]
 
     if (lane == 0) {
         for (int s = 0; s < S; ++s) mbar_init(smem_addr(&s_bar[s]), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    scan_pages(a.seq_lens, a.n, a.page_size, s_cu, s_part);   // ends with a CTA barrier
+    scan_pages(a, s_cu, s_part);   // ends with a CTA barrier
 
     // This CTA's tiles come in groups of consecutive tiles of the flat list:
     //  - dynamic (a.work != null): groups of a.group_tiles handed out by an atomic
@@ -499,7 +531,9 @@ gather_bulk_kernel(const GatherArgs a) {
                     const TileInfo t = resolve_tile(a, s_cu, group_base + lane);
                     s_src[lane] = t.src;
                     s_dst[lane] = t.dst;
+                    s_new[lane] = t.new_src;
                     s_rows[lane] = t.rows;
+                    s_rows_old[lane] = t.rows_old;
                 }
                 __syncwarp();
                 staged = true;
@@ -509,17 +543,31 @@ gather_bulk_kernel(const GatherArgs a) {
                 __syncwarp();
             }
             const int rows = s_rows[ti];
+            const int rows_old = s_rows_old[ti];
             const uint32_t bytes = (uint32_t)(rows * a.row_bytes);
             const uint32_t bar = smem_addr(&s_bar[islot]);
+            const long long pool_off = s_src[ti] + head * a.pool_head;
             if (lane == 0) {
                 s_slot_rows[islot] = rows;
+                s_slot_rows_old[islot] = rows_old;
                 s_slot_dst[islot] = s_dst[ti] + head * a.orow.head;
+                s_slot_pool[islot] = pool_off;
                 if (bytes) mbar_arrive_expect(bar, 2 * bytes); else mbar_arrive(bar);
             }
             __syncwarp();
-            if (lane < 2 && bytes) {
-                const unsigned char* src = (lane ? a.v_pool : a.k_pool) + s_src[ti] + head * a.pool_head;
-                bulk_load(smem_addr(s_data + ((size_t)islot * 2 + lane) * page_bytes), src, bytes, bar);
+            unsigned char* stage = s_data + (size_t)islot * 2 * page_bytes;
+            if (lane < 2 && rows_old) {
+                bulk_load(smem_addr(stage + lane * page_bytes), (lane ? a.v_pool : a.k_pool) + pool_off,
+                          (uint32_t)(rows_old * a.row_bytes), bar);
+            }
+            if (rows_old < rows) {
+                // rows this call appends: one small copy each, straight from the new rows into the stage
+                const long long src0 = s_new[ti] + head * a.nr.head;
+                for (int op = lane; op < 2 * (rows - rows_old); op += 32) {
+                    const int r = op >> 1, kv = op & 1;
+                    bulk_load(smem_addr(stage + kv * page_bytes + (rows_old + r) * a.row_bytes),
+                              (kv ? a.v_new : a.k_new) + src0 + (long long)r * a.nr.tok, (uint32_t)a.row_bytes, bar);
+                }
             }
             ++issued;
             if (++islot == S) islot = 0;
@@ -548,10 +596,17 @@ gather_bulk_kernel(const GatherArgs a) {
             dead = __any_sync(0xffffffffu, dead);
             if (!dead) {
                 const int rows = s_slot_rows[cslot];
+                const int rows_old = s_slot_rows_old[cslot];
                 const long long dst = s_slot_dst[cslot];
                 if (rows) {
                     fence_async_smem();
                     const uint32_t sk = smem_addr(s_data + (size_t)cslot * 2 * page_bytes);
+                    if (rows_old < rows && lane < 2) {
+                        // fused append: the new rows also go to their slots of the page
+                        bulk_store((lane ? a.v_pool_w : a.k_pool_w) + s_slot_pool[cslot] + (long long)rows_old * a.row_bytes,
+                                   sk + lane * page_bytes + rows_old * a.row_bytes,
+                                   (uint32_t)((rows - rows_old) * a.row_bytes));
+                    }
                     if (contiguous_rows) {
                         if (lane < 2) {
                             bulk_store((lane ? a.v_out : a.k_out) + dst, sk + lane * page_bytes,
@@ -675,6 +730,7 @@ int launch_append(const AppendArgs& a, int vec, int grid, int threads, cudaStrea
         default: append_rows_kernel<uint8_t, LEGACY><<<grid, threads, 0, st>>>(a); break;
     }
     const cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) g_launches.fetch_add(1, std::memory_order_relaxed);
     return e == cudaSuccess ? 0 : fail_cuda("append launch", e);
 }
 
@@ -702,6 +758,8 @@ extern "C" {
 int barqkv_version(void) { return BARQKV_VERSION; }
 
 const char* barqkv_last_error(void) { return g_err; }
+
+int64_t barqkv_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 int barqkv_sm_count(void) {
     DeviceInfo* d = device_info();
@@ -831,12 +889,23 @@ int barqkv_append_legacy(void* key_cache, void* value_cache, int32_t* seq_lens,
     return launch_append<true>(a, vec, grid, threads, static_cast<cudaStream_t>(stream));
 }
 
-int barqkv_gather(const barqkv_pool_layout* pool, const void* k_pool, const void* v_pool,
-                  const barqkv_block_table* table,
-                  const int32_t* seq_lens, const int32_t* cu_out, int32_t n,
-                  int64_t total_tokens_hint,
-                  void* k_out, void* v_out, const barqkv_rows_layout* out_rows,
-                  int32_t mode, int32_t* status, int32_t* work, barqkv_stream_t stream) {
+// New rows joining a gather (barqkv_update); null k_new = plain gather.
+struct FusedRows {
+    const void* k_new;
+    const void* v_new;
+    const barqkv_rows_layout* rows;
+    const int32_t* cu_new;
+    int tokens_per_entry;
+};
+constexpr int kNotFusable = 1;   // gather_common: the fused form cannot run on these arguments
+
+static int gather_common(const barqkv_pool_layout* pool, const void* k_pool, const void* v_pool,
+                         const barqkv_block_table* table,
+                         const int32_t* seq_lens, const int32_t* cu_out, int32_t n,
+                         int64_t total_tokens_hint,
+                         void* k_out, void* v_out, const barqkv_rows_layout* out_rows,
+                         int32_t mode, int32_t* status, int32_t* work, barqkv_stream_t stream,
+                         const FusedRows* fused) {
     if (int rc = check_pool(pool)) return rc;
     if (n < 0) return fail(BARQKV_E_INVALID, "gather: negative batch size");
     if (n == 0) return 0;
@@ -877,10 +946,25 @@ int barqkv_gather(const barqkv_pool_layout* pool, const void* k_pool, const void
     if (a.group_tiles > kGroup) a.group_tiles = kGroup;
     if (a.group_tiles < 1) a.group_tiles = 1;
 
-    const int vec = vector_bytes(a.row_bytes, {a.pool_head, a.pool_page, a.orow.seq, a.orow.tok, a.orow.head},
-                                 {k_pool, v_pool, k_out, v_out});
+    int vec = vector_bytes(a.row_bytes, {a.pool_head, a.pool_page, a.orow.seq, a.orow.tok, a.orow.head},
+                           {k_pool, v_pool, k_out, v_out});
+    if (fused) {
+        a.k_new = static_cast<const unsigned char*>(fused->k_new);
+        a.v_new = static_cast<const unsigned char*>(fused->v_new);
+        a.k_pool_w = const_cast<unsigned char*>(a.k_pool);
+        a.v_pool_w = const_cast<unsigned char*>(a.v_pool);
+        a.cu_new = fused->cu_new;
+        a.tokens_per_entry = fused->tokens_per_entry;
+        a.nr.seq = fused->rows->seq_stride * e;
+        a.nr.tok = fused->rows->tok_stride * e;
+        a.nr.head = fused->rows->head_stride * e;
+        a.nr.packed = fused->rows->packed;
+        const int vec_new = vector_bytes(a.row_bytes, {a.nr.seq, a.nr.tok, a.nr.head}, {fused->k_new, fused->v_new});
+        if (vec_new < vec) vec = vec_new;
+    }
     const long long page_bytes = (long long)a.page_size * a.row_bytes;
     const bool bulk_ok = vec == 16 && 2 * page_bytes <= kBulkMaxStage;
+    if (fused && (!bulk_ok || mode == BARQKV_MODE_VECTOR)) return kNotFusable;
     if (mode == BARQKV_MODE_BULK && !bulk_ok)
         return fail(BARQKV_E_INVALID, "gather: bulk mode needs 16-byte aligned rows and strides and pages of at most 16 KiB");
     const bool use_bulk = mode == BARQKV_MODE_BULK || (mode == BARQKV_MODE_AUTO && bulk_ok);
@@ -896,8 +980,8 @@ int barqkv_gather(const barqkv_pool_layout* pool, const void* k_pool, const void
         if (S < 3) S = 3;
         if (S > 32) S = 32;
         a.stages = S;
-        const size_t smem = (size_t)S * 2 * page_bytes + (size_t)S * 8 /*bar*/ + (size_t)S * 8 /*slot dst*/ +
-                            2 * kGroup * 8 + kGroup * 4 + (size_t)S * 4 + 4 + (size_t)(n + 1) * 4;
+        const size_t smem = (size_t)S * 2 * page_bytes + (size_t)S * 8 /*bar*/ + (size_t)S * 16 /*slot dst, pool*/ +
+                            3 * kGroup * 8 + 2 * kGroup * 4 + (size_t)S * 8 + 4 + (size_t)(n + 1) * 4;
         if ((long long)smem > d->smem_optin)
             return fail(BARQKV_E_LIMIT, "gather: bulk pipeline does not fit in shared memory");
         if (!d->bulk_attr_set) {
@@ -929,7 +1013,56 @@ int barqkv_gather(const barqkv_pool_layout* pool, const void* k_pool, const void
         }
     }
     const cudaError_t ce = cudaGetLastError();
+    if (ce == cudaSuccess) g_launches.fetch_add(1, std::memory_order_relaxed);
     return ce == cudaSuccess ? 0 : fail_cuda("gather launch", ce);
+}
+
+int barqkv_gather(const barqkv_pool_layout* pool, const void* k_pool, const void* v_pool,
+                  const barqkv_block_table* table,
+                  const int32_t* seq_lens, const int32_t* cu_out, int32_t n,
+                  int64_t total_tokens_hint,
+                  void* k_out, void* v_out, const barqkv_rows_layout* out_rows,
+                  int32_t mode, int32_t* status, int32_t* work, barqkv_stream_t stream) {
+    return gather_common(pool, k_pool, v_pool, table, seq_lens, cu_out, n, total_tokens_hint, k_out, v_out, out_rows,
+                         mode, status, work, stream, nullptr);
+}
+
+int barqkv_update(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,
+                  const barqkv_block_table* table,
+                  const int32_t* seq_start, const int32_t* cu_new,
+                  int32_t n, int32_t tokens_per_entry, int32_t total_new_tokens,
+                  const void* k_new, const void* v_new, const barqkv_rows_layout* new_rows,
+                  const int32_t* cu_out, int64_t total_tokens_hint,
+                  void* k_out, void* v_out, const barqkv_rows_layout* out_rows,
+                  int32_t mode, int32_t* status, int32_t* work, const int32_t* seq_lens_after,
+                  barqkv_stream_t stream) {
+    if (n < 0 || total_new_tokens < 0) return fail(BARQKV_E_INVALID, "update: negative batch size or token count");
+    if (n == 0) return 0;
+    if (int rc = check_pool(pool)) return rc;
+    if (!seq_start || !new_rows || (total_new_tokens && (!k_new || !v_new)))
+        return fail(BARQKV_E_INVALID, "update: null pointer argument");
+    if (!cu_new && (tokens_per_entry < 0 || (long long)tokens_per_entry * n != total_new_tokens))
+        return fail(BARQKV_E_INVALID, "update: without cu_new, total_new_tokens must equal n * tokens_per_entry");
+    if (new_rows->packed && !cu_new && tokens_per_entry > 1)
+        return fail(BARQKV_E_INVALID, "update: packed rows with more than one token per entry need cu_new");
+    // One launch when the copy engine path applies and the append is small next to the gather
+    // (decode, short chunks); otherwise the two kernels run back to back with the same result.
+    if (pool && total_new_tokens > 0 && total_new_tokens <= (long long)n * pool->page_size) {
+        const FusedRows fused = {k_new, v_new, new_rows, cu_new, tokens_per_entry};
+        const int rc = gather_common(pool, k_pool, v_pool, table, seq_start, cu_out, n, total_tokens_hint, k_out, v_out,
+                                     out_rows, mode, status, work, stream, &fused);
+        if (rc != kNotFusable) return rc;
+    }
+    if (!seq_lens_after)
+        return fail(BARQKV_E_INVALID, "update: this call cannot run as one launch; pass seq_lens_after (lengths after "
+                                      "the append, device int32[n]) so that it can run as append + gather");
+    if (total_new_tokens) {
+        if (int rc = barqkv_append(pool, k_pool, v_pool, table, seq_start, cu_new, n, tokens_per_entry, total_new_tokens,
+                                   k_new, v_new, new_rows, status, stream))
+            return rc;
+    }
+    return barqkv_gather(pool, k_pool, v_pool, table, seq_lens_after, cu_out, n, total_tokens_hint, k_out, v_out,
+                         out_rows, mode, status, work, stream);
 }
 
 // --------------------------------------------------------------------------

@@ -112,6 +112,9 @@ const char* barqkv_last_error(void);
 /* Number of SMs of the current device (cached); used by callers that size work. */
 int barqkv_sm_count(void);
 
+/* Kernels this library has enqueued so far in this process (every entry point counts its launches). */
+int64_t barqkv_launch_count(void);
+
 /* Set a BARQKV_KNOB_* value.  No counterpart in the reference, which has no tunables. */
 int barqkv_set_tuning(int32_t knob, int32_t value);
 
@@ -180,6 +183,31 @@ int barqkv_gather(const barqkv_pool_layout* pool, const void* k_pool, const void
                   int64_t total_tokens_hint,
                   void* k_out, void* v_out, const barqkv_rows_layout* out_rows,
                   int32_t mode, int32_t* status, int32_t* work, barqkv_stream_t stream);
+
+/*
+ * Append and gather in one call - what the reference's layer does per attention call:
+ *   update(key_states, value_states) = append(...) then current_tensors()
+ *   (python/barqtrain/kv_cache.py:135-142).
+ * Arguments are those of barqkv_append (seq_start = lengths BEFORE the append, cu_new /
+ * tokens_per_entry, new rows) followed by those of barqkv_gather, where cu_out and
+ * total_tokens_hint refer to the lengths AFTER the append, and seq_lens_after holds those
+ * lengths (device int32[n]).  On return (stream order) the pool holds the new rows and the
+ * output holds every sequence including them.
+ * When the bulk gather applies (16-byte aligned rows and strides, pages <= 16 KiB, mode not
+ * VECTOR) and the call brings at most page_size new tokens per entry on average (decode,
+ * short chunks), ONE kernel does both: the new rows are read once, joined with the page's
+ * old rows in shared memory, and stored to the output and to their page slots.  Otherwise
+ * the append kernel and the gather kernel run back to back; results are identical.
+ */
+int barqkv_update(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,
+                  const barqkv_block_table* table,
+                  const int32_t* seq_start, const int32_t* cu_new,
+                  int32_t n, int32_t tokens_per_entry, int32_t total_new_tokens,
+                  const void* k_new, const void* v_new, const barqkv_rows_layout* new_rows,
+                  const int32_t* cu_out, int64_t total_tokens_hint,
+                  void* k_out, void* v_out, const barqkv_rows_layout* out_rows,
+                  int32_t mode, int32_t* status, int32_t* work, const int32_t* seq_lens_after,
+                  barqkv_stream_t stream);
 
 /*
  * barqkv_gather for callers that cannot allocate device memory.

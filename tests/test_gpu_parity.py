@@ -286,6 +286,51 @@ def test_ragged_chunked_prefill_and_decode_against_c_oracle(backend, cfg, mode):
     cache.check_device_status()
 
 
+@pytest.mark.parametrize("layout", ["HND", "NHD"])
+@pytest.mark.parametrize("cfg", [
+    dict(H=8, D=128, ps=16, dtype=torch.bfloat16, lens=(37, 50, 16, 0, 1, 255), news=((1,) * 6, (3, 0, 16, 5, 1, 2))),
+    dict(H=1, D=128, ps=16, dtype=torch.float16, lens=(15, 16, 17, 700), news=((1, 1, 1, 1), (16, 1, 15, 0))),
+    dict(H=2, D=64, ps=32, dtype=torch.float32, lens=(31, 64, 5), news=((1, 1, 1), (2, 32, 27))),
+    dict(H=3, D=5, ps=4, dtype=torch.float32, lens=(3, 9), news=((1, 1), (2, 4))),     # 20-byte rows: two launches
+])
+def test_update_in_one_launch_equals_append_then_gather(backend, cfg, layout):
+    """``update`` (append + gather, one kernel for decode-sized appends) against the two separate
+    calls on a twin cache: same pools, same gathered tensors, and the expected launch count."""
+    from barqtrain_b200 import BlockTableKVCache
+
+    H, D, ps, dtype = cfg["H"], cfg["D"], cfg["ps"], cfg["dtype"]
+    g = torch.Generator().manual_seed(61)
+    n = len(cfg["lens"])
+    order = torch.randperm(64, generator=g).tolist()
+
+    def make():
+        c = BlockTableKVCache(1, H, D, page_size=ps, num_pages=64, max_seqs=n, max_blocks_per_seq=48,
+                              dtype=dtype, device=DEV, free_order=order)
+        return c, [c.open(i) for i in range(n)]
+
+    fused, fs = make()
+    plain, pl = make()
+    k0 = S.randn(g, (sum(cfg["lens"]), H, D), dtype).to(DEV)
+    v0 = S.randn(g, (sum(cfg["lens"]), H, D), dtype).to(DEV)
+    fused.append_step(fs, cfg["lens"], [k0], [v0])
+    plain.append_step(pl, cfg["lens"], [k0], [v0])
+    one_launch = (D * k0.element_size()) % 16 == 0
+    for counts in cfg["news"]:
+        k = S.randn(g, (sum(counts), H, D), dtype).to(DEV)
+        v = S.randn(g, (sum(counts), H, D), dtype).to(DEV)
+        plain.append_step(pl, counts, [k], [v])
+        want_k, want_v = plain.gather(0, plain.begin_gather(pl), layout)
+        new = fused.begin_append(fs, counts)
+        fused.end_append(new)
+        full = fused.begin_gather(fs)
+        before = backend.launches
+        got_k, got_v = fused.update(0, new, full, k, v, layout)
+        assert backend.launches - before == (1 if one_launch else 2)
+        assert torch.equal(S.bits_dev(got_k), S.bits_dev(want_k)) and torch.equal(S.bits_dev(got_v), S.bits_dev(want_v))
+        assert torch.equal(S.bits_dev(fused.pools), S.bits_dev(plain.pools))
+    fused.check_device_status()
+
+
 def test_release_recycles_pages_and_keeps_live_sequences_intact(backend):
     """Continuous-batching churn in small: sequences finish, their pages go back to the free
     list and are handed to new sequences; live sequences always gather to what was appended."""
