@@ -16,7 +16,7 @@ from .kv_cache import (
     maybe_prepare_paged_kv_generate_kwargs,
     paged_kv_supported_for_model,
 )
-from .block_table import BlockTableKVCache, PageAllocator, PagePoolExhausted, PoolStats
+from .block_table import BlockTableKVCache, DecodeStepGraph, PageAllocator, PagePoolExhausted, PoolStats
 from ._ffi import load_cuda_backend
 
 __all__ = [
@@ -24,6 +24,7 @@ __all__ = [
     "BarqPagedKVCacheLayer",
     "BlockTableKVCache",
     "CudaMemorySnapshot",
+    "DecodeStepGraph",
     "PageAllocator",
     "PagePoolExhausted",
     "PoolStats",

@@ -126,6 +126,13 @@ struct GatherArgs {
     RowsB nr;
 };
 
+// Programmatic dependent launch: a kernel launched with the stream-serialization attribute may become
+// resident while the kernel before it in the stream is still running.  Every kernel here lets its
+// successor in early and itself waits, before touching global memory, until its predecessor has
+// completed and flushed; without the launch attribute both instructions do nothing.
+__device__ __forceinline__ void pdl_let_successor_in() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait_for_predecessor() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ void raise(int32_t* status, int bit) {
     if (status) atomicOr(status, bit);
 }
@@ -163,6 +170,8 @@ append_rows_kernel(const AppendArgs a) {
     const int tid = threadIdx.x;
     const int first_tok = blockIdx.x * a.tile;
     const int ntok = min(a.tile, a.total_tokens - first_tok);
+    pdl_let_successor_in();
+    pdl_wait_for_predecessor();
 
     bool refuse = false;
     if (LEGACY) {
@@ -348,6 +357,8 @@ gather_vector_kernel(const GatherArgs a) {
     __shared__ int s_rows[kGroup];
 
     int* s_cu = s_dyn;
+    pdl_let_successor_in();
+    pdl_wait_for_predecessor();
     scan_pages(a, s_cu, s_part);
     const int total = s_cu[a.n];
     int lo, hi, group_step;
@@ -487,6 +498,8 @@ gather_bulk_kernel(const GatherArgs a) {
         for (int s = 0; s < S; ++s) mbar_init(smem_addr(&s_bar[s]), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    pdl_let_successor_in();
+    pdl_wait_for_predecessor();
     scan_pages(a, s_cu, s_part);   // ends with a CTA barrier
 
     // This CTA's tiles come in groups of consecutive tiles of the flat list:
@@ -495,15 +508,23 @@ gather_bulk_kernel(const GatherArgs a) {
     //  - static: one contiguous share (interleave == 0) or every gridDim-th group.
     const int total = s_cu[a.n];
     const bool dynamic = a.work != nullptr;
-    const int gt = dynamic ? a.group_tiles : kGroup;
-    const int ngroups = (total + gt - 1) / gt;
+    const int gt_max = dynamic ? a.group_tiles : kGroup;
+    int gt = gt_max;                       // tiles in the current group
     int group_base, group_step = 0, end = total;
-    int pending = 0;                       // lane 0: group index fetched ahead of need
+    int pending = 0, pending_n = 0;        // lane 0: the group fetched ahead of need (first tile, tile count)
+    // Dynamic hand-out counts tiles; groups shrink as the work runs out (remaining / 2*CTAs,
+    // at most group_tiles, at least 1) so that the last groups are small and CTAs finish together.
+    auto fetch_ahead = [&](int seen) {
+        int k = (total - seen) / (2 * (int)gridDim.x);
+        k = max(1, min(k, gt_max));
+        pending_n = k;
+        pending = atomicAdd(a.work, k);
+    };
     if (dynamic) {
-        if (lane == 0) pending = atomicAdd(a.work, 1);
-        const int first = __shfl_sync(0xffffffffu, pending, 0);
-        group_base = first >= ngroups ? end : first * gt;
-        if (lane == 0 && group_base < end) pending = atomicAdd(a.work, 1);
+        if (lane == 0) fetch_ahead(0);
+        group_base = min(end, __shfl_sync(0xffffffffu, pending, 0));
+        gt = __shfl_sync(0xffffffffu, pending_n, 0);
+        if (lane == 0 && group_base < end) fetch_ahead(group_base);
     } else if (a.interleave) {
         group_base = (int)blockIdx.x * kGroup;
         group_step = (int)gridDim.x * kGroup;
@@ -577,9 +598,9 @@ gather_bulk_kernel(const GatherArgs a) {
                     ti = 0;
                     staged = false;
                     if (dynamic) {
-                        const int next = __shfl_sync(0xffffffffu, pending, 0);
-                        group_base = next >= ngroups ? end : next * gt;
-                        if (lane == 0 && group_base < end) pending = atomicAdd(a.work, 1);
+                        group_base = min(end, __shfl_sync(0xffffffffu, pending, 0));
+                        gt = __shfl_sync(0xffffffffu, pending_n, 0);
+                        if (lane == 0 && group_base < end) fetch_ahead(group_base);
                     } else {
                         group_base += group_step;
                     }
@@ -650,6 +671,7 @@ int g_knob_vector_ctas_per_sm = 0;
 int g_knob_interleave = -1;
 int g_knob_group_tiles = 0;
 int g_knob_static = 0;
+int g_knob_pdl = 0;
 
 struct DeviceInfo {
     int sms = 0;
@@ -775,6 +797,7 @@ int barqkv_set_tuning(int32_t knob, int32_t value) {
         case BARQKV_KNOB_INTERLEAVE: g_knob_interleave = value; return 0;
         case BARQKV_KNOB_GROUP_TILES: g_knob_group_tiles = value; return 0;
         case BARQKV_KNOB_STATIC_SHARES: g_knob_static = value; return 0;
+        case BARQKV_KNOB_PDL: g_knob_pdl = value; return 0;
         default: return fail(BARQKV_E_INVALID, "set_tuning: unknown knob");
     }
 }
@@ -998,7 +1021,22 @@ static int gather_common(const barqkv_pool_layout* pool, const void* k_pool, con
         const long long units_bound = tiles_bound * a.heads;
         const long long want = (units_bound + 2 * S - 1) / (2 * S);   // at least two ring rounds per CTA
         if (want < grid) grid = want < 1 ? 1 : want;
-        gather_bulk_kernel<<<(int)grid, 32, smem, st>>>(a);
+        if (g_knob_pdl) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3((unsigned)grid);
+            cfg.blockDim = dim3(32);
+            cfg.dynamicSmemBytes = smem;
+            cfg.stream = st;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[0].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            const cudaError_t le = cudaLaunchKernelEx(&cfg, gather_bulk_kernel, a);
+            if (le != cudaSuccess) return fail_cuda("gather launch", le);
+        } else {
+            gather_bulk_kernel<<<(int)grid, 32, smem, st>>>(a);
+        }
     } else {
         const size_t smem = (size_t)(n + 1) * 4;
         long long grid = (long long)d->sms * (g_knob_vector_ctas_per_sm ? g_knob_vector_ctas_per_sm : 8);

@@ -117,6 +117,7 @@ class ClockSampler:
 class DecodeWorkload:
     def __init__(self, world: int, rank: int, device: torch.device, total_steps: int, fused: bool = True):
         self.fused = fused          # one update() launch per layer instead of append() + gather()
+        self.graph = None
         from barqtrain_b200 import BlockTableKVCache
         from barqtrain_b200.sharding import kv_head_shard
 
@@ -205,15 +206,37 @@ class DecodeWorkload:
         self.step_no += 1
         return total
 
+    def enable_graph(self):
+        """Replay the step's launches from a CUDA graph (``DecodeStepGraph``): eager step, record, replay."""
+        from barqtrain_b200 import DecodeStepGraph
+
+        self.graph = DecodeStepGraph(self.cache, self.slots, capacity_tokens=self.out[0][0].size(1))
+        self.graph.k_in.copy_(self.new_k[0])
+        self.graph.v_in.copy_(self.new_v[0])
+        self.out = None                                    # the graph owns its output buffers
+        self.graph.step()
+        self.graph.record()
+        self.graph.step()
+        self.step_no += 2
+
     def resident_step(self, events=None):
+        if self.graph is not None:                          # inputs stay in the graph's resident buffers
+            self.step_no += 1
+            return self.graph.step()
         i = self.step_no % 4
         return self.step(self.new_k[i], self.new_v[i], events)
 
     def e2e_step(self):
         """Public-API step with host inputs: H2D of the step's new K/V, the hot path, D2H of the status word."""
-        self.stage_k.copy_(self.host_k, non_blocking=True)
-        self.stage_v.copy_(self.host_v, non_blocking=True)
-        total = self.step(self.stage_k, self.stage_v)
+        if self.graph is not None:
+            self.graph.k_in.copy_(self.host_k, non_blocking=True)
+            self.graph.v_in.copy_(self.host_v, non_blocking=True)
+            total = self.graph.step()
+            self.step_no += 1
+        else:
+            self.stage_k.copy_(self.host_k, non_blocking=True)
+            self.stage_v.copy_(self.host_v, non_blocking=True)
+            total = self.step(self.stage_k, self.stage_v)
         self.host_status.copy_(self.cache._status, non_blocking=True)
         torch.cuda.current_stream(self.device).synchronize()
         if int(self.host_status[0]) != 0:
@@ -241,8 +264,11 @@ def run_barqkv(args):
     backend = _ffi.require_cuda_backend()
     K, W = args.steps, max(args.warmup, 3)
     e2e_steps = max(3, min(K, 10))
-    total_steps = W + K + 3 + e2e_steps + 4
+    total_steps = W + K + 3 + e2e_steps + 8
     wl = DecodeWorkload(world, rank, device, total_steps, fused=not args.two_launches)
+    use_graph = not args.eager and not args.two_launches
+    if use_graph:
+        wl.enable_graph()
 
     def barrier():
         torch.cuda.synchronize(device)
@@ -276,6 +302,8 @@ def run_barqkv(args):
         stop.record()
         barrier()
     launches = backend.launches - launches0
+    if use_graph:
+        launches = K * wl.graph.launches_per_replay        # kernel nodes replayed; a replay makes no library call
     ms = max_over_ranks(start.elapsed_time(stop))
     job_bytes = (app_bytes + gat_bytes) * world
     value = job_bytes / (ms * 1e-3) / 1e9
@@ -286,16 +314,25 @@ def run_barqkv(args):
     # ---- roofline of the dominant kernel (gather), per launch ---------------------
     peak, peak_kind = measured_peak()
     per_tok = 4 * wl.H * wl.row_bytes
-    durs = [e0.elapsed_time(e1) * 1e-3 for e0, e1, _ in events]
-    # a sampled launch moves the gather's bytes plus (fused) the appended rows' bytes
-    gbytes = [(t + wl.B) * per_tok for _, _, t in events]
-    avg_dur = sum(durs) / len(durs)
-    achieved = (sum(gbytes) / len(gbytes)) / avg_dur / 1e9
+    if events:
+        durs = [e0.elapsed_time(e1) * 1e-3 for e0, e1, _ in events]
+        # a sampled launch moves the gather's bytes plus (fused) the appended rows' bytes
+        gbytes = [(t + wl.B) * per_tok for _, _, t in events]
+        avg_dur = sum(durs) / len(durs)
+        avg_bytes = sum(gbytes) / len(gbytes)
+        how = f"event pairs around {len(events)} sampled launches inside the timed region"
+    else:
+        # graph replay: the timed region is nothing but these launches back to back, so its CUDA-event
+        # time divided by the launch count is the launch duration (kernel plus the gap to the next one)
+        avg_dur = ms * 1e-3 / (K * wl.L)
+        avg_bytes = (app_bytes + gat_bytes) / (K * wl.L)
+        how = f"timed region / {K * wl.L} back-to-back launches of the replayed graph"
+    achieved = avg_bytes / avg_dur / 1e9
     roofline = {"bound": "hbm", "kernel": "gather_bulk_kernel" + (" (append fused)" if wl.fused else " + append_rows_kernel"),
-                "launches_sampled": len(events), "achieved": round(achieved, 1), "peak": peak,
+                "how": how, "achieved": round(achieved, 1), "peak": peak,
                 "peak_kind": peak_kind, "unit": "GB/s", "frac": round(achieved / peak, 4),
                 "frac_of_nominal_8TBs": round(achieved / NOMINAL_PEAK_GBS, 4),
-                "avg_launch_us": round(avg_dur * 1e6, 2), "bytes_per_launch": int(sum(gbytes) / len(gbytes)),
+                "avg_launch_us": round(avg_dur * 1e6, 2), "bytes_per_launch": int(avg_bytes),
                 "traffic": None}
     tpath = ROOT / "profiles" / "gather_bulk_traffic.json"
     if tpath.exists():
@@ -329,6 +366,8 @@ def run_barqkv(args):
                    "head_dim": wl.D, "page_size": wl.ps, "batch": wl.B, "prompt_lengths": "uniform[512,4096] seeded",
                    "sum_len_tokens": wl.sum_len(), "sharding": f"kv-head x{world}",
                    "step": "per layer: append 1 token/seq, gather all sequences to [H,sum_len,D]",
+                   "launch": ("one update() kernel per layer" if wl.fused else "append() + gather() per layer")
+                   + (", replayed from a CUDA graph" if use_graph else ", called from Python"),
                    "l2": "inputs larger than L2: each step reads ~%.1f GB of pool per GPU" % (gat_bytes / K / 2 / 1e9)},
         "pct_of_nominal_8TBs": round(100 * value / world / NOMINAL_PEAK_GBS, 2),
         "pct_of_measured_copy": round(100 * value / world / peak, 2),
@@ -498,53 +537,63 @@ def run_micro(args):
         e1.record()
         return e0, e1
 
-    reps = 1
-    if args.micro == "gather":
-        total = sum(lens)
-        k = torch.randn(total, H, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
-        cache.append_step(slots, lens, [k], [k])
-        gb = cache.begin_gather(slots)
-        shape = (H, total, D) if args.layout == "HND" else (total, H, D)
-        out = (torch.empty(shape, dtype=dtype, device=device), torch.empty(shape, dtype=dtype, device=device))
+    # Each case prepares its batch description on the stream it will launch on and returns
+    # (launch function, launches per call, algorithmic bytes per call).
+    def prepare():
+        if args.micro == "gather":
+            total = sum(lens)
+            if cache.lengths[slots[0]] == 0:
+                k = torch.randn(total, H, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
+                cache.append_step(slots, lens, [k], [k])
+            gb = cache.begin_gather(slots)
+            shape = (H, total, D) if args.layout == "HND" else (total, H, D)
+            out = (torch.empty(shape, dtype=dtype, device=device), torch.empty(shape, dtype=dtype, device=device))
 
-        def launch():
-            cache.gather(0, gb, args.layout, out=out, mode=args.mode)
-        nbytes = total * per_tok
-    elif args.micro == "append-prefill":
-        total = args.chunk * B
-        k = torch.randn(total, H, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
-        v = torch.randn(total, H, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
-        batch = cache.begin_append(slots, [args.chunk] * B)    # the same chunk lands on the same pages every launch
+            def launch():
+                for _ in range(args.reps):
+                    cache.gather(0, gb, args.layout, out=out, mode=args.mode)
+            return launch, args.reps, total * per_tok * args.reps
+        if args.micro == "append-prefill":
+            total = args.chunk * B
+            k = torch.randn(total, H, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
+            v = torch.randn(total, H, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
+            batch = cache.begin_append(slots, [args.chunk] * B)   # the same chunk lands on the same pages every launch
 
-        def launch():
-            cache.append(0, batch, k, v)
-        nbytes = total * per_tok
-    else:  # append-decode: `layers` back-to-back single-token appends form one timed group
+            def launch():
+                for _ in range(args.reps):
+                    cache.append(0, batch, k, v)
+            return launch, args.reps, total * per_tok * args.reps
+        # append-decode: `layers` back-to-back single-token appends form one timed group
         k = torch.randn(B, H, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
-        fill = k.repeat(1024, 1, 1)[: sum(lens)]
-        cache.append_step(slots, lens, [fill], [fill])
+        if cache.lengths[slots[0]] == 0:
+            fill = k.repeat(1024, 1, 1)[: sum(lens)]
+            cache.append_step(slots, lens, [fill], [fill])
         batch = cache.begin_append(slots, [1] * B)
-        reps = args.layers
 
         def launch():
             for _ in range(args.layers):
                 cache.append(0, batch, k, k)
-        nbytes = B * per_tok * args.layers
+        return launch, args.layers, B * per_tok * args.layers
 
-    for _ in range(args.warmup):
-        launch()
-    torch.cuda.synchronize(device)
     if args.graph:
-        # the launches recorded into a CUDA graph: what the kernels take without the host's call overhead
+        # the launches recorded into a CUDA graph: what the kernels take back to back, without host call overhead
         side = torch.cuda.Stream(device)
         with torch.cuda.stream(side):
-            launch()
+            launch, reps, nbytes = prepare()
+            for _ in range(max(args.warmup, 1)):
+                launch()
             torch.cuda.synchronize(device)
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=side):
                 launch()
-        evs = [timed(graph.replay) for _ in range(args.steps)]
+            graph.replay()
+            torch.cuda.synchronize(device)
+            evs = [timed(graph.replay) for _ in range(args.steps)]
     else:
+        launch, reps, nbytes = prepare()
+        for _ in range(args.warmup):
+            launch()
+        torch.cuda.synchronize(device)
         evs = [timed(launch) for _ in range(args.steps)]
     args.warmup = 0
     torch.cuda.synchronize(device)
@@ -588,6 +637,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="barqkv", choices=["barqkv", "reference"])
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="budget of the CPU baseline leg")
+    ap.add_argument("--eager", action="store_true",
+                    help="call update() per layer from Python every step instead of replaying a CUDA graph")
     ap.add_argument("--two-launches", action="store_true",
                     help="per layer call append() then gather() instead of the single update() launch")
     ap.add_argument("--micro", choices=["gather", "append-prefill", "append-decode"],
@@ -599,6 +650,7 @@ def main():
     ap.add_argument("--chunk", type=int, default=2048, help="tokens per sequence per append (append-prefill)")
     ap.add_argument("--layers", type=int, default=32, help="appends per timed group (append-decode)")
     ap.add_argument("--lengths", default="uniform", choices=["uniform", "loguniform"])
+    ap.add_argument("--reps", type=int, default=1, help="micro gather/append-prefill: launches per timed sample")
     ap.add_argument("--graph", action="store_true", help="micro cases: time a CUDA-graph replay of the launches")
     ap.add_argument("--tune", default="", help="gather knobs, e.g. stages=8,ctas=3,interleave=1 (micro cases)")
     args = ap.parse_args()

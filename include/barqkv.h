@@ -105,6 +105,7 @@ typedef struct barqkv_rows_layout {
 #define BARQKV_KNOB_INTERLEAVE 4         /* static shares only. 1: every gridDim-th group of 32 pages; 0: contiguous */
 #define BARQKV_KNOB_GROUP_TILES 5        /* pages handed out per atomic fetch by the bulk gather (1..32) */
 #define BARQKV_KNOB_STATIC_SHARES 6      /* 1: ignore `work` and split pages statically among CTAs */
+#define BARQKV_KNOB_PDL 7                /* 1: launch the bulk gather with programmatic stream serialization */
 
 int barqkv_version(void);
 const char* barqkv_last_error(void);

@@ -1,0 +1,54 @@
+"""The paged cache under Hugging Face ``generate()`` on a tiny random Llama: the tokens and the final
+logits must match the stock dynamic cache (the cache copies K/V bit for bit, so attention sees the
+same values; the operands differ only in stride)."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _tiny_llama():
+    from transformers import LlamaConfig, LlamaForCausalLM
+
+    torch.manual_seed(0)
+    cfg = LlamaConfig(vocab_size=211, hidden_size=128, intermediate_size=256, num_hidden_layers=3,
+                      num_attention_heads=4, num_key_value_heads=2, head_dim=32, max_position_embeddings=512,
+                      pad_token_id=0, bos_token_id=1, eos_token_id=None)
+    return LlamaForCausalLM(cfg).to("cuda").eval()
+
+
+def test_generate_with_paged_cache_matches_dynamic_cache(monkeypatch):
+    from barqtrain_b200 import BarqPagedKVCache, _ffi, create_paged_kv_cache
+    from barqtrain_b200.patch_models import patch_inference
+
+    backend = _ffi.require_cuda_backend()
+    model = _tiny_llama()
+    g = torch.Generator().manual_seed(3)
+    ids = torch.randint(2, 211, (2, 37), generator=g).to("cuda")
+    new_tokens = 24
+    with torch.no_grad():
+        want = model.generate(ids, max_new_tokens=new_tokens, do_sample=False)
+
+        launches = backend.launches
+        cache = create_paged_kv_cache(model, max_batch_size=2, max_cache_len=37 + new_tokens, page_size=16)
+        got = model.generate(ids, max_new_tokens=new_tokens, do_sample=False, past_key_values=cache, use_cache=True)
+    assert torch.equal(got, want)
+    # one native append per layer per forward: prompt pass + one pass per further token fed back
+    assert backend.launches - launches == 3 * new_tokens
+    assert cache.get_seq_length() == 37 + new_tokens - 1
+    assert cache.layers[0].seq_lens.cpu().tolist() == [37 + new_tokens - 1] * 2
+
+    # the reference's injection route: patch once, then plain generate() picks the paged cache up
+    monkeypatch.setenv("BARQTRAIN_PAGED_KV_MIN_CACHE_LEN", "0")
+    patch_inference(model)
+    assert model._barqtrain_paged_kv_supported and model._barqtrain_generate_paged_kv_patched
+    with torch.no_grad():
+        again = model.generate(ids, max_new_tokens=new_tokens, do_sample=False)
+    assert model._barqtrain_last_generate_used_paged_kv is True
+    assert torch.equal(again, want)
+    monkeypatch.setenv("BARQTRAIN_PAGED_KV_MIN_CACHE_LEN", "256")
+    with torch.no_grad():
+        short = model.generate(ids, max_new_tokens=4, do_sample=False)
+    assert model._barqtrain_last_generate_used_paged_kv is False and short.shape == (2, 41)
+    assert isinstance(cache, BarqPagedKVCache) and backend.read_status("cuda") == 0

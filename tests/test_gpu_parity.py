@@ -331,6 +331,56 @@ def test_update_in_one_launch_equals_append_then_gather(backend, cfg, layout):
     fused.check_device_status()
 
 
+@pytest.mark.parametrize("H", [8, 1])
+def test_decode_step_graph_replays_what_eager_steps_compute(backend, H):
+    """A decode step recorded into a CUDA graph: every replay must leave the same pools and gathered
+    tensors as eager append + gather on a twin cache, across page boundaries and growing lengths."""
+    from barqtrain_b200 import BlockTableKVCache, DecodeStepGraph
+
+    L, D, ps, dtype, B = 3, 128, 16, torch.bfloat16, 5
+    g = torch.Generator().manual_seed(17)
+    lens = [14, 15, 16, 33, 100]
+    order = torch.randperm(96, generator=g).tolist()
+
+    def make():
+        c = BlockTableKVCache(L, H, D, page_size=ps, num_pages=96, max_seqs=B, max_blocks_per_seq=16, dtype=dtype,
+                              device=DEV, free_order=order)
+        return c, [c.open(i) for i in range(B)]
+
+    fast, fs = make()
+    slow, ss = make()
+    k0 = [S.randn(g, (sum(lens), H, D), dtype).to(DEV) for _ in range(L)]
+    v0 = [S.randn(g, (sum(lens), H, D), dtype).to(DEV) for _ in range(L)]
+    fast.append_step(fs, lens, k0, v0)
+    slow.append_step(ss, lens, k0, v0)
+    steps = DecodeStepGraph(fast, fs, capacity_tokens=sum(lens) + B * 24)
+    for i in range(20):
+        if i == 2:
+            steps.record()
+        k = S.randn(g, (L, B, H, D), dtype).to(DEV)
+        v = S.randn(g, (L, B, H, D), dtype).to(DEV)
+        steps.k_in.copy_(k)
+        steps.v_in.copy_(v)
+        before = backend.launches
+        total = steps.step()
+        assert backend.launches - before == (L if i < 2 else 0)      # a replay makes no library call
+        assert i < 2 or steps.launches_per_replay == L
+        slow.append_step(ss, [1] * B, list(k.unbind(0)), list(v.unbind(0)))
+        gb = slow.begin_gather(ss)
+        assert total == gb.total == sum(lens) + B * (i + 1)
+        for layer in (L - 2, L - 1):                      # the two buffer pairs still hold the last two layers
+            want_k, want_v = slow.gather(layer, gb, "HND")
+            got_k, got_v = steps.outputs(layer)
+            assert torch.equal(S.bits_dev(got_k), S.bits_dev(want_k)), (i, layer)
+            assert torch.equal(S.bits_dev(got_v), S.bits_dev(want_v)), (i, layer)
+        assert torch.equal(S.bits_dev(fast.pools), S.bits_dev(slow.pools)), i
+    assert steps.graph is not None
+    with pytest.raises(ValueError, match="capacity"):
+        for _ in range(10):
+            steps.step()
+    backend.read_status(DEV)
+
+
 def test_release_recycles_pages_and_keeps_live_sequences_intact(backend):
     """Continuous-batching churn in small: sequences finish, their pages go back to the free
     list and are handed to new sequences; live sequences always gather to what was appended."""
