@@ -1,0 +1,215 @@
+"""Timed loops for the chunked-prefill, 70B-shaped gather and continuous-batching configurations.
+
+Each function builds the configuration's cache on ``device`` for this rank's KV-head shard, runs
+``warmup`` untimed and ``steps`` timed steps bracketed by CUDA events, and returns a dict with the
+algorithmic bytes moved on this rank, the elapsed milliseconds and a description.  Algorithmic bytes
+are 4*tokens*H*D*e per layer for both append and gather (K and V, read + write).
+"""
+
+from __future__ import annotations
+
+import math
+import time
+from typing import Dict
+
+import torch
+
+from ..block_table import BlockTableKVCache
+from ..sharding import kv_head_shard
+
+D = 128
+
+
+def _events():
+    return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+
+def chunked_prefill(world: int, rank: int, device, steps: int, warmup: int, page_size: int = 16,
+                    layers: int = 32, sync=lambda: None) -> Dict:
+    """32 layers, 8 KV heads, head_dim 128, fp16; 16 sequences of 8192 tokens appended in 2048-token
+    chunks into a pool shuffled by a seeded permutation.  A step appends one chunk of every sequence
+    in every layer; after four chunks the sequences are released and re-opened."""
+    _, H = kv_head_shard(8, world, rank)
+    B, chunk, chunks = 16, 2048, 4
+    dtype = torch.float16
+    pages = B * chunk * chunks // page_size
+    cache = BlockTableKVCache(layers, H, D, page_size=page_size, num_pages=pages, max_seqs=B,
+                              max_blocks_per_seq=chunk * chunks // page_size, dtype=dtype, device=device,
+                              seed=1237, zero_pages=False)
+    gen = torch.Generator(device=device).manual_seed(1237 + rank)
+    k = torch.randn(B * chunk, H, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
+    v = torch.randn(B * chunk, H, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
+    state = {"ids": list(range(B)), "slots": [cache.open(i) for i in range(B)], "done": 0, "next": B}
+
+    def step():
+        if state["done"] == chunks:
+            for sid in state["ids"]:
+                cache.release(sid)
+            state["ids"] = list(range(state["next"], state["next"] + B))
+            state["next"] += B
+            state["slots"] = [cache.open(i) for i in state["ids"]]
+            state["done"] = 0
+        batch = cache.begin_append(state["slots"], [chunk] * B)
+        for layer in range(layers):
+            cache.append(layer, batch, k, v)
+        cache.end_append(batch)
+        state["done"] += 1
+
+    for _ in range(max(warmup, 1)):
+        step()
+    sync()
+    e0, e1 = _events()
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    sync()
+    ms = e0.elapsed_time(e1)
+    cache.check_device_status()
+    per_step = 4 * B * chunk * H * D * 2 * layers
+    return {"bytes": per_step * steps, "ms": ms, "tokens": B * chunk * steps, "launches": layers * steps,
+            "config": {"workload": "chunked-prefill", "layers": layers, "kv_heads_per_gpu": H, "dtype": "fp16",
+                       "page_size": page_size, "sequences": B, "chunk_tokens": chunk,
+                       "step": "append one 2048-token chunk of 16 sequences in every layer",
+                       "l2": "inputs larger than L2: 268 MB per launch at 8 heads, pool 34 GB"}}
+
+
+def gather_70b(world: int, rank: int, device, steps: int, warmup: int, layers: int = 80,
+               sync=lambda: None) -> Dict:
+    """80 layers, 8 KV heads sharded by head, head_dim 128, bf16, page 16; 32 sequences with seeded
+    lengths log-uniform in [1k, 32k]; fragmented block tables.  A step gathers every sequence to
+    contiguous ``[H, sum_len, D]`` K and V in every layer."""
+    _, H = kv_head_shard(8, world, rank)
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(1238)
+    u = torch.rand(32, generator=g, dtype=torch.float64)
+    lens = [int(round(math.exp(math.log(1024) + float(x) * (math.log(32768) - math.log(1024))))) for x in u]
+    pages = sum(-(-n // 16) for n in lens)
+    cache = BlockTableKVCache(layers, H, D, page_size=16, num_pages=pages, max_seqs=32,
+                              max_blocks_per_seq=-(-max(lens) // 16), dtype=dtype, device=device,
+                              free_order=torch.randperm(pages, generator=g).tolist(), zero_pages=False)
+    slots = [cache.open(i) for i in range(32)]
+    gen = torch.Generator(device=device).manual_seed(1238 + rank)
+    total = sum(lens)
+    k = torch.randn(total, H, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
+    batch = cache.begin_append(slots, lens)
+    for layer in range(layers):                         # set-up: fill the pools through the append kernel
+        cache.append(layer, batch, k, k)
+    cache.end_append(batch)
+    del k
+    outs = [(torch.empty(H, total, D, dtype=dtype, device=device), torch.empty(H, total, D, dtype=dtype, device=device))
+            for _ in range(2)]
+    gb = cache.begin_gather(slots)
+
+    def step():
+        for layer in range(layers):
+            cache.gather(layer, gb, "HND", out=outs[layer & 1])
+
+    for _ in range(max(warmup, 1)):
+        step()
+    sync()
+    e0, e1 = _events()
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    sync()
+    ms = e0.elapsed_time(e1)
+    cache.check_device_status()
+    per_step = 4 * total * H * D * 2 * layers
+    return {"bytes": per_step * steps, "ms": ms, "tokens": total * steps, "launches": layers * steps,
+            "config": {"workload": "llama3-70b-gather", "layers": layers, "kv_heads_per_gpu": H, "dtype": "bf16",
+                       "page_size": 16, "sequences": 32, "sum_len_tokens": total,
+                       "lengths": "log-uniform [1024, 32768] seeded",
+                       "step": "gather all sequences to [H,sum_len,D] in every layer",
+                       "l2": "inputs larger than L2: %.2f GB per launch" % (4 * total * H * D * 2 / 1e9)}}
+
+
+def churn(world: int, rank: int, device, steps: int, warmup: int, layers: int = 32, sync=lambda: None) -> Dict:
+    """Continuous batching: 32 layers, 8 KV heads, head_dim 128, fp16, page 16; 256 live sequences with
+    initial lengths uniform in [128, 2048]; every step appends one token to every live sequence in every
+    layer, then each sequence finishes with seeded probability 0.01, returns its pages to the free list
+    and is replaced by a new sequence with a 512-token prefill."""
+    _, H = kv_head_shard(8, world, rank)
+    dtype = torch.float16
+    g = torch.Generator().manual_seed(1239)
+    live = 256
+    lens0 = torch.randint(128, 2049, (live,), generator=g).tolist()
+    total_steps = steps + max(warmup, 1)
+    cap = 2048 + total_steps + 512
+    pages = sum(-(-(n + total_steps) // 16) for n in lens0) + live * 8 + 4096
+    cache = BlockTableKVCache(layers, H, D, page_size=16, num_pages=pages, max_seqs=live,
+                              max_blocks_per_seq=-(-cap // 16), dtype=dtype, device=device,
+                              free_order=torch.randperm(pages, generator=g).tolist(), zero_pages=False)
+    gen = torch.Generator(device=device).manual_seed(1239 + rank)
+    rows = torch.randn(max(max(lens0), 512) * 8, H, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
+    ids = list(range(live))
+    slots = [cache.open(i) for i in ids]
+    next_id = live
+    # set-up: initial contents, in slices so that the packed source stays small
+    for lo in range(0, live, 8):
+        part, counts = slots[lo:lo + 8], lens0[lo:lo + 8]
+        batch = cache.begin_append(part, counts)
+        for layer in range(layers):
+            cache.append(layer, batch, rows[: sum(counts)], rows[: sum(counts)])
+        cache.end_append(batch)
+    one_all = rows[:live].expand(layers, -1, -1, -1)          # the step's new rows, [layers, live, H, D]
+    finished = (torch.rand(total_steps, live, generator=g) < 0.01).tolist()
+    counters = {"tokens": 0, "host_s": 0.0, "released": 0, "launches": 0}
+
+    def step(i):
+        nonlocal next_id
+        t0 = time.perf_counter()
+        batch = cache.begin_append(slots, [1] * live)
+        counters["host_s"] += time.perf_counter() - t0
+        cache.append_layers(batch, one_all, one_all)           # all layers' rows of the step in one launch
+        cache.end_append(batch)
+        counters["tokens"] += live
+        counters["launches"] += 1
+        gone = [j for j in range(live) if finished[i][j]]
+        if gone:
+            t0 = time.perf_counter()
+            fresh = []
+            for j in gone[:32]:                                  # the packed prefill source holds 32 prompts
+                cache.release(ids[j])
+                ids[j] = next_id
+                next_id += 1
+                slots[j] = cache.open(ids[j])
+                fresh.append(slots[j])
+            batch = cache.begin_append(fresh, [512] * len(fresh))
+            counters["host_s"] += time.perf_counter() - t0
+            prompt = rows[: 512 * len(fresh)].expand(layers, -1, -1, -1)
+            cache.append_layers(batch, prompt, prompt)
+            cache.end_append(batch)
+            counters["tokens"] += 512 * len(fresh)
+            counters["released"] += len(fresh)
+            counters["launches"] += 1
+
+    for i in range(max(warmup, 1)):
+        step(i)
+    sync()
+    for key in counters:
+        counters[key] = 0 if key != "host_s" else 0.0
+    e0, e1 = _events()
+    e0.record()
+    for i in range(steps):
+        step(max(warmup, 1) + i)
+    e1.record()
+    sync()
+    ms = e0.elapsed_time(e1)
+    cache.check_device_status()
+    st = cache.stats()
+    return {"bytes": 4 * counters["tokens"] * H * D * 2 * layers, "ms": ms, "tokens": counters["tokens"],
+            "launches": counters["launches"],
+            "config": {"workload": "continuous-batching-churn", "layers": layers, "kv_heads_per_gpu": H,
+                       "dtype": "fp16", "page_size": 16, "live_sequences": live,
+                       "step": "append 1 token to 256 sequences in every layer (one launch for all layers); finished "
+                               "sequences (p=0.01) release their pages and are replaced by a 512-token prefill",
+                       "l2": "decode appends are 1 MB per launch (L2-resident, launch-bound); prefills stream"},
+            "extra": {"sequences_released": counters["released"], "pages_total": st.pages_total,
+                      "pages_resident": st.pages_resident, "pages_peak": st.pages_peak,
+                      "bytes_peak": st.bytes_peak,
+                      "host_allocator_us_per_step": round(counters["host_s"] * 1e6 / max(steps, 1), 1)}}
+
+
+WORKLOADS = {"prefill": chunked_prefill, "gather70b": gather_70b, "churn": churn}

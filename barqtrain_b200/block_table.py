@@ -23,6 +23,8 @@ from __future__ import annotations
 
 import ctypes
 from dataclasses import dataclass
+
+import numpy as np
 from typing import Dict, Iterable, List, Optional, Sequence, Tuple
 
 import torch
@@ -166,7 +168,8 @@ class BlockTableKVCache:
         self._dirty_lo, self._dirty_hi = max_seqs, 0
         self._table = _ffi.BlockTable(self.table_dev.data_ptr(), None, max_seqs, max_blocks_per_seq, 0, 0)
 
-        self.lengths: List[int] = [0] * max_seqs       # tokens held, per slot
+        self.lengths = np.zeros(max_seqs, dtype=np.int64)      # tokens held, per slot
+        self._page_count = np.zeros(max_seqs, dtype=np.int64)  # pages owned, per slot (len(pages_of[slot]))
         self.pages_of: List[List[int]] = [[] for _ in range(max_seqs)]
         self._free_slots: List[int] = list(range(max_seqs - 1, -1, -1))
         self._slot_of: Dict[object, int] = {}
@@ -206,6 +209,7 @@ class BlockTableKVCache:
         self.allocator.give_back(self.pages_of[slot])
         used = len(self.pages_of[slot])
         self.pages_of[slot] = []
+        self._page_count[slot] = 0
         self._table_np[slot, :used] = -1
         self._mark_dirty(slot)
         self.lengths[slot] = 0
@@ -224,6 +228,7 @@ class BlockTableKVCache:
             )
         pages = self.allocator.take(need - have)
         self.pages_of[slot].extend(pages)
+        self._page_count[slot] = need
         self._table_np[slot, have:need] = pages
         self._mark_dirty(slot)
 
@@ -237,6 +242,7 @@ class BlockTableKVCache:
         if words > self._ring_words:
             self._ring_words = max(2 * words, 1 << 16)
             self._ring = [(torch.empty(self._ring_words, dtype=torch.int32).pin_memory(), None) for _ in range(8)]
+            self._ring_np = [buf.numpy() for buf, _ in self._ring]
             self._ring_pos = 0
         buf, event = self._ring[self._ring_pos]
         if event is not None:
@@ -244,8 +250,9 @@ class BlockTableKVCache:
         return buf
 
     def _stage_done(self) -> None:
-        buf, _ = self._ring[self._ring_pos]
-        event = torch.cuda.Event()
+        buf, event = self._ring[self._ring_pos]
+        if event is None:
+            event = torch.cuda.Event()
         event.record(torch.cuda.current_stream(self.device))
         self._ring[self._ring_pos] = (buf, event)
         self._ring_pos = (self._ring_pos + 1) % len(self._ring)
@@ -261,18 +268,22 @@ class BlockTableKVCache:
         self._stage_done()
         self._dirty_lo, self._dirty_hi = self.max_seqs, 0
 
-    def _describe(self, kind: str, slots: Sequence[int], first: List[int], counts: List[int]) -> _Descriptor:
-        n = len(slots)
-        cu = [0] * (n + 1)
-        for i, c in enumerate(counts):
-            cu[i + 1] = cu[i] + c
+    def _describe(self, kind: str, slots, first, counts) -> _Descriptor:
+        slots = np.asarray(slots, dtype=np.int64)
+        first = np.asarray(first, dtype=np.int64)
+        n = slots.size
+        cu = np.zeros(n + 1, dtype=np.int64)
+        np.cumsum(np.asarray(counts, dtype=np.int64), out=cu[1:])
         words = 3 * n + 1
         dev = self._desc_dev.get(kind)
         if dev is None or dev.numel() < words:
             dev = torch.empty(max(words, 3 * self.max_seqs + 1), dtype=torch.int32, device=self.device)
             self._desc_dev[kind] = dev
         buf = self._stage(words)
-        buf[:words] = torch.tensor(list(slots) + first + cu, dtype=torch.int32)
+        host = self._ring_np[self._ring_pos]
+        host[:n] = slots
+        host[n:2 * n] = first
+        host[2 * n:words] = cu
         # the device buffer is laid out for this n: [slots | first | cu]
         dev[:words].copy_(buf[:words], non_blocking=True)
         self._stage_done()
@@ -283,7 +294,10 @@ class BlockTableKVCache:
         table.slots = dev.data_ptr()
         stream = torch.cuda.current_stream(self.device).cuda_stream
         work = self.backend.work_words(self.device).data_ptr() if kind == "gather" else 0
-        return _Descriptor(n, dev, cu[n], first, cu, list(slots), ctypes.byref(table), stream, work)
+        desc = _Descriptor(n, dev, int(cu[n]), first.tolist(), cu.tolist(), slots.tolist(), ctypes.byref(table),
+                           stream, work)
+        desc.slots_np, desc.after_np = slots, first + (cu[1:] - cu[:-1])
+        return desc
 
     # -- append -------------------------------------------------------------------
     def begin_append(self, slots: Sequence[int], counts: Sequence[int]) -> _Descriptor:
@@ -291,10 +305,15 @@ class BlockTableKVCache:
 
         Use the returned batch for every layer's ``append`` of this step, then ``end_append``.
         """
-        counts = [int(c) for c in counts]
-        first = [self.lengths[s] for s in slots]
-        for s, c in zip(slots, counts):
-            self.reserve(s, self.lengths[s] + c)
+        slots = np.asarray(slots, dtype=np.int64)
+        counts = np.asarray(counts, dtype=np.int64)
+        if slots.shape != counts.shape:
+            raise ValueError("slots and counts must have the same length")
+        first = self.lengths[slots]
+        after = first + counts
+        need = -(-after // self.page_size)
+        for i in np.nonzero(need > self._page_count[slots])[0]:      # only sequences that cross into a new page
+            self.reserve(int(slots[i]), int(after[i]))
         self._flush_table()
         return self._describe("append", slots, first, counts)
 
@@ -327,6 +346,34 @@ class BlockTableKVCache:
         if rc:
             self.backend._check(rc)
 
+    def append_layers(self, batch: _Descriptor, k_all: torch.Tensor, v_all: torch.Tensor) -> None:
+        """All layers' appends of a step in one launch: ``k_all`` / ``v_all`` are
+        ``[num_layers, total_tokens, kv_heads, head_dim]`` (any layer and token strides, contiguous
+        last dimension)."""
+        total = batch.total
+        if total == 0:
+            return
+        shape = k_all.shape
+        if shape != v_all.shape or len(shape) != 4 or shape[0] != self.num_layers or shape[1] != total \
+                or shape[2] != self.num_kv_heads or shape[3] != self.head_dim:
+            raise ValueError(f"new rows must both be {(self.num_layers, total, self.num_kv_heads, self.head_dim)}")
+        if k_all.dtype != self.dtype or v_all.dtype != self.dtype or k_all.device != self.device \
+                or v_all.device != self.device:
+            raise ValueError("new rows must be in the cache dtype on the cache device")
+        strides = k_all.stride()
+        if strides[3] != 1 or v_all.stride() != strides:
+            k_all, v_all = k_all.contiguous(), v_all.contiguous()
+            strides = k_all.stride()
+        rows_ref = self._rows.get(strides[1:])
+        if rows_ref is None:
+            rows_ref = self._rows[strides[1:]] = self._rows_ref(0, strides[1], strides[2])
+        rc = self.backend.lib.barqkv_append_layers(
+            self._pool_ref, self._k_ptr[0], self._v_ptr[0], self.num_layers, self.pools.stride(0), batch.table_ref,
+            batch.p_first, batch.p_cu, batch.n, 0, total, k_all.data_ptr(), v_all.data_ptr(), rows_ref, strides[0],
+            self._status_ptr, batch.stream)
+        if rc:
+            self.backend._check(rc)
+
     def _rows_ref(self, seq_stride: int, tok_stride: int, head_stride: int):
         """A cached ctypes reference to a packed ``barqkv_rows_layout``."""
         layout = _ffi.RowsLayout(seq_stride, tok_stride, head_stride, 1, 0)
@@ -335,8 +382,7 @@ class BlockTableKVCache:
         return ctypes.byref(layout)
 
     def end_append(self, batch: _Descriptor) -> None:
-        for i, s in enumerate(batch.slots):
-            self.lengths[s] = batch.first[i] + (batch.cu[i + 1] - batch.cu[i])
+        self.lengths[batch.slots_np] = batch.after_np
 
     def append_step(self, slots: Sequence[int], counts: Sequence[int], k_layers, v_layers) -> None:
         """All layers of one step: ``k_layers[l]`` / ``v_layers[l]`` are that layer's packed rows."""
@@ -347,7 +393,8 @@ class BlockTableKVCache:
 
     # -- gather -------------------------------------------------------------------
     def begin_gather(self, slots: Sequence[int]) -> _Descriptor:
-        lens = [self.lengths[s] for s in slots]
+        slots = np.asarray(slots, dtype=np.int64)
+        lens = self.lengths[slots]
         self._flush_table()
         return self._describe("gather", slots, lens, lens)
 
@@ -551,8 +598,8 @@ class DecodeStepGraph:
         torch.cuda.synchronize(c.device)
         with torch.cuda.stream(self.stream):
             # descriptions with the right shape (n and buffer addresses); their contents are rewritten every step
-            new = c._describe("append", self.slots, [c.lengths[s] for s in self.slots], [1] * len(self.slots))
-            lens = [c.lengths[s] for s in self.slots]
+            lens = c.lengths[np.asarray(self.slots, dtype=np.int64)]
+            new = c._describe("append", self.slots, lens, [1] * len(self.slots))
             full = c._describe("gather", self.slots, lens, lens)
             torch.cuda.synchronize(c.device)
             graph = torch.cuda.CUDAGraph()

@@ -90,6 +90,8 @@ struct AppendArgs {
     int heads, page_size, row_bytes;
     long long pool_head, pool_page;   // bytes
     RowsB nr;
+    // several layers in one launch (gridDim.y = layers): byte strides between consecutive layers
+    long long pool_layer, new_layer;
     // reference-layout extras
     int32_t* seq_lens_rw;
     int32_t* ticket;
@@ -113,6 +115,7 @@ struct GatherArgs {
     int interleave;        // 1: CTAs take every gridDim-th group of tiles instead of one contiguous share
     int32_t* work;         // bulk kernel: [0] next group to hand out, [1] CTAs finished; null = static shares
     int group_tiles;       // bulk kernel, dynamic hand-out: (sequence, page) tiles per group
+    int static_permille;   // bulk kernel, dynamic hand-out: thousandths of the tiles split evenly up front
     int32_t* status;
     // Fused append ("update", bulk kernel only; k_new == null means plain gather): seq_lens then holds
     // the lengths BEFORE the append, entry i brings cu_new[i+1]-cu_new[i] (or tokens_per_entry) new rows,
@@ -170,6 +173,8 @@ append_rows_kernel(const AppendArgs a) {
     const int tid = threadIdx.x;
     const int first_tok = blockIdx.x * a.tile;
     const int ntok = min(a.tile, a.total_tokens - first_tok);
+    const long long layer_pool = (long long)blockIdx.y * a.pool_layer;
+    const long long layer_new = (long long)blockIdx.y * a.new_layer;
     pdl_let_successor_in();
     pdl_wait_for_predecessor();
 
@@ -230,8 +235,8 @@ append_rows_kernel(const AppendArgs a) {
                     const bool is_v = hk & 1;
                     const long long d = s_dst[t];
                     if (d >= 0) {
-                        const unsigned char* src = (is_v ? a.v_new : a.k_new) + s_src[t] + h * a.nr.head;
-                        unsigned char* dst = (is_v ? a.v_pool : a.k_pool) + d + h * a.pool_head;
+                        const unsigned char* src = (is_v ? a.v_new : a.k_new) + layer_new + s_src[t] + h * a.nr.head;
+                        unsigned char* dst = (is_v ? a.v_pool : a.k_pool) + layer_pool + d + h * a.pool_head;
                         val[u] = __ldcs(reinterpret_cast<const V*>(src) + vec);
                         out[u] = reinterpret_cast<V*>(dst) + vec;
                     }
@@ -512,19 +517,31 @@ gather_bulk_kernel(const GatherArgs a) {
     int gt = gt_max;                       // tiles in the current group
     int group_base, group_step = 0, end = total;
     int pending = 0, pending_n = 0;        // lane 0: the group fetched ahead of need (first tile, tile count)
-    // Dynamic hand-out counts tiles; groups shrink as the work runs out (remaining / 2*CTAs,
-    // at most group_tiles, at least 1) so that the last groups are small and CTAs finish together.
+    // Dynamic hand-out: every CTA first works through a fixed share of the front part of the list
+    // (a.static_permille of the tiles, no atomics, no fetch latency at the start), then takes groups
+    // of the rest from an atomic tile counter.  Those groups shrink as the work runs out
+    // (remaining / 2*CTAs, at most group_tiles, at least 1) so that all CTAs finish together.
+    const int share = dynamic ? (int)((long long)total * a.static_permille / 1000 / (int)gridDim.x) : 0;
+    const int dyn_first = share * (int)gridDim.x;           // first tile that is handed out dynamically
+    bool fixed_share = false;                               // still inside the fixed share
     auto fetch_ahead = [&](int seen) {
         int k = (total - seen) / (2 * (int)gridDim.x);
         k = max(1, min(k, gt_max));
         pending_n = k;
-        pending = atomicAdd(a.work, k);
+        pending = dyn_first + atomicAdd(a.work, k);
     };
     if (dynamic) {
-        if (lane == 0) fetch_ahead(0);
-        group_base = min(end, __shfl_sync(0xffffffffu, pending, 0));
-        gt = __shfl_sync(0xffffffffu, pending_n, 0);
-        if (lane == 0 && group_base < end) fetch_ahead(group_base);
+        if (lane == 0) fetch_ahead(dyn_first);
+        if (share > 0) {
+            fixed_share = true;
+            group_base = (int)blockIdx.x * share;
+            end = group_base + share;
+            gt = kGroup;
+        } else {
+            group_base = min(end, __shfl_sync(0xffffffffu, pending, 0));
+            gt = __shfl_sync(0xffffffffu, pending_n, 0);
+            if (lane == 0 && group_base < end) fetch_ahead(group_base);
+        }
     } else if (a.interleave) {
         group_base = (int)blockIdx.x * kGroup;
         group_step = (int)gridDim.x * kGroup;
@@ -597,7 +614,11 @@ gather_bulk_kernel(const GatherArgs a) {
                 if (++ti == gt || group_base + ti >= end) {
                     ti = 0;
                     staged = false;
-                    if (dynamic) {
+                    if (fixed_share && group_base + gt < end) {
+                        group_base += gt;                   // next group of the fixed share
+                    } else if (dynamic) {
+                        fixed_share = false;
+                        end = total;
                         group_base = min(end, __shfl_sync(0xffffffffu, pending, 0));
                         gt = __shfl_sync(0xffffffffu, pending_n, 0);
                         if (lane == 0 && group_base < end) fetch_ahead(group_base);
@@ -672,6 +693,7 @@ int g_knob_interleave = -1;
 int g_knob_group_tiles = 0;
 int g_knob_static = 0;
 int g_knob_pdl = 0;
+int g_knob_static_permille = -1;
 
 struct DeviceInfo {
     int sms = 0;
@@ -743,7 +765,7 @@ int vector_bytes(int row_bytes, std::initializer_list<long long> strides, std::i
 }
 
 template <bool LEGACY>
-int launch_append(const AppendArgs& a, int vec, int grid, int threads, cudaStream_t st) {
+int launch_append(const AppendArgs& a, int vec, dim3 grid, int threads, cudaStream_t st) {
     switch (vec) {
         case 16: append_rows_kernel<uint4, LEGACY><<<grid, threads, 0, st>>>(a); break;
         case 8: append_rows_kernel<uint2, LEGACY><<<grid, threads, 0, st>>>(a); break;
@@ -798,17 +820,20 @@ int barqkv_set_tuning(int32_t knob, int32_t value) {
         case BARQKV_KNOB_GROUP_TILES: g_knob_group_tiles = value; return 0;
         case BARQKV_KNOB_STATIC_SHARES: g_knob_static = value; return 0;
         case BARQKV_KNOB_PDL: g_knob_pdl = value; return 0;
+        case BARQKV_KNOB_STATIC_PERMILLE: g_knob_static_permille = value > 1000 ? 1000 : value; return 0;
         default: return fail(BARQKV_E_INVALID, "set_tuning: unknown knob");
     }
 }
 
-int barqkv_append(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,
-                  const barqkv_block_table* table,
-                  const int32_t* seq_start, const int32_t* cu_new,
-                  int32_t n, int32_t tokens_per_entry, int32_t total_tokens,
-                  const void* k_new, const void* v_new, const barqkv_rows_layout* new_rows,
-                  int32_t* status, barqkv_stream_t stream) {
+static int append_common(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,
+                         const barqkv_block_table* table,
+                         const int32_t* seq_start, const int32_t* cu_new,
+                         int32_t n, int32_t tokens_per_entry, int32_t total_tokens,
+                         const void* k_new, const void* v_new, const barqkv_rows_layout* new_rows,
+                         int32_t* status, barqkv_stream_t stream,
+                         int32_t layers, int64_t pool_layer_stride, int64_t new_layer_stride) {
     if (int rc = check_pool(pool)) return rc;
+    if (layers <= 0 || layers > 65535) return fail(BARQKV_E_INVALID, "append: layers must be in 1..65535");
     if (n < 0 || total_tokens < 0) return fail(BARQKV_E_INVALID, "append: negative batch size or token count");
     if (n == 0 || total_tokens == 0) return 0;
     if (int rc = check_table(table, n)) return rc;
@@ -845,12 +870,40 @@ int barqkv_append(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,
     a.nr.packed = new_rows->packed;
     a.status = status;
 
-    const int vec = vector_bytes(a.row_bytes, {a.pool_head, a.pool_page, a.nr.seq, a.nr.tok, a.nr.head},
+    a.pool_layer = pool_layer_stride * e;
+    a.new_layer = new_layer_stride * e;
+
+    const int vec = vector_bytes(a.row_bytes, {a.pool_head, a.pool_page, a.nr.seq, a.nr.tok, a.nr.head,
+                                               layers > 1 ? a.pool_layer : 0, layers > 1 ? a.new_layer : 0},
                                  {k_pool, v_pool, k_new, v_new});
     int threads;
-    append_shape(d, total_tokens, a.heads, a.row_bytes, vec, &a.tile, &threads);
-    const int grid = (total_tokens + a.tile - 1) / a.tile;
+    // tile chosen as if the layers' tokens were one batch, so that the whole grid covers the machine
+    long long work_tokens = (long long)total_tokens * layers;
+    if (work_tokens > 0x7fffffffLL) work_tokens = 0x7fffffffLL;
+    append_shape(d, (int)work_tokens, a.heads, a.row_bytes, vec, &a.tile, &threads);
+    const dim3 grid((unsigned)((total_tokens + a.tile - 1) / a.tile), (unsigned)layers);
     return launch_append<false>(a, vec, grid, threads, static_cast<cudaStream_t>(stream));
+}
+
+int barqkv_append(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,
+                  const barqkv_block_table* table,
+                  const int32_t* seq_start, const int32_t* cu_new,
+                  int32_t n, int32_t tokens_per_entry, int32_t total_tokens,
+                  const void* k_new, const void* v_new, const barqkv_rows_layout* new_rows,
+                  int32_t* status, barqkv_stream_t stream) {
+    return append_common(pool, k_pool, v_pool, table, seq_start, cu_new, n, tokens_per_entry, total_tokens, k_new, v_new,
+                         new_rows, status, stream, 1, 0, 0);
+}
+
+int barqkv_append_layers(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,
+                         int32_t layers, int64_t pool_layer_stride,
+                         const barqkv_block_table* table,
+                         const int32_t* seq_start, const int32_t* cu_new,
+                         int32_t n, int32_t tokens_per_entry, int32_t total_tokens,
+                         const void* k_new, const void* v_new, const barqkv_rows_layout* new_rows,
+                         int64_t new_layer_stride, int32_t* status, barqkv_stream_t stream) {
+    return append_common(pool, k_pool, v_pool, table, seq_start, cu_new, n, tokens_per_entry, total_tokens, k_new, v_new,
+                         new_rows, status, stream, layers, pool_layer_stride, new_layer_stride);
 }
 
 int barqkv_append_legacy(void* key_cache, void* value_cache, int32_t* seq_lens,
@@ -908,7 +961,7 @@ int barqkv_append_legacy(void* key_cache, void* value_cache, int32_t* seq_lens,
                                  {key_cache, value_cache, k_new, v_new});
     int threads;
     append_shape(d, a.total_tokens, heads, a.row_bytes, vec, &a.tile, &threads);
-    const int grid = (a.total_tokens + a.tile - 1) / a.tile;
+    const dim3 grid((unsigned)((a.total_tokens + a.tile - 1) / a.tile));
     return launch_append<true>(a, vec, grid, threads, static_cast<cudaStream_t>(stream));
 }
 
@@ -968,6 +1021,7 @@ static int gather_common(const barqkv_pool_layout* pool, const void* k_pool, con
     a.group_tiles = g_knob_group_tiles ? g_knob_group_tiles : (a.heads >= 8 ? 1 : 8 / a.heads);
     if (a.group_tiles > kGroup) a.group_tiles = kGroup;
     if (a.group_tiles < 1) a.group_tiles = 1;
+    a.static_permille = g_knob_static_permille >= 0 ? g_knob_static_permille : 0;
 
     int vec = vector_bytes(a.row_bytes, {a.pool_head, a.pool_page, a.orow.seq, a.orow.tok, a.orow.head},
                            {k_pool, v_pool, k_out, v_out});

@@ -170,7 +170,7 @@ class DecodeWorkload:
         torch.cuda.synchronize(device)
 
     def sum_len(self) -> int:
-        return sum(self.cache.lengths[s] for s in self.slots)
+        return int(sum(self.cache.lengths[s] for s in self.slots))
 
     def step_bytes(self, sum_len_after: int):
         """Algorithmic bytes of one step on THIS rank: (append, gather)."""
@@ -510,7 +510,7 @@ def run_micro(args):
     dtype = torch.bfloat16
     gen = torch.Generator(device=device).manual_seed(7)
     g = torch.Generator().manual_seed(CFG["seed"])
-    if args.micro == "gather":
+    if args.micro in ("gather", "update"):
         if args.lengths == "loguniform":          # the 70B-shaped gather configuration: 32 sequences in [1k, 32k]
             import math
             u = torch.rand(32, generator=g, dtype=torch.float64)
@@ -553,6 +553,22 @@ def run_micro(args):
                 for _ in range(args.reps):
                     cache.gather(0, gb, args.layout, out=out, mode=args.mode)
             return launch, args.reps, total * per_tok * args.reps
+        if args.micro == "update":
+            total = sum(lens)
+            k = torch.randn(total, H, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
+            if cache.lengths[slots[0]] == 0:
+                cache.append_step(slots, lens, [k], [k])
+            new = cache.begin_append(slots, [1] * B)     # every launch re-appends the same token: same work each time
+            cache.end_append(new)
+            full = cache.begin_gather(slots)
+            shape = (H, full.total, D) if args.layout == "HND" else (full.total, H, D)
+            out = (torch.empty(shape, dtype=dtype, device=device), torch.empty(shape, dtype=dtype, device=device))
+            k1 = k[:B].contiguous()
+
+            def launch():
+                for _ in range(args.reps):
+                    cache.update(0, new, full, k1, k1, args.layout, out=out, mode=args.mode)
+            return launch, args.reps, (full.total + B) * per_tok * args.reps
         if args.micro == "append-prefill":
             total = args.chunk * B
             k = torch.randn(total, H, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
@@ -609,6 +625,63 @@ def run_micro(args):
                       "frac_of_%s_peak" % kind: round(nbytes / med / 1e9 / peak, 4), "status": status}), flush=True)
 
 
+# ---------------------------------------------------------------------------
+# the other configurations (chunked prefill, 70B-shaped gather, continuous-batching churn)
+# ---------------------------------------------------------------------------
+def run_extra(args):
+    import torch.distributed as dist
+
+    from barqtrain_b200 import _ffi
+    from barqtrain_b200.benchmarks.workloads import WORKLOADS
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+    backend = _ffi.require_cuda_backend()
+
+    def barrier():
+        torch.cuda.synchronize(device)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    kwargs = {"page_size": args.page_size} if args.workload == "prefill" else {}
+    if args.layers_override:
+        kwargs["layers"] = args.layers_override
+    with ClockSampler(local) as clocks:
+        res = WORKLOADS[args.workload](world, rank, device, args.steps, max(args.warmup, 3), sync=barrier, **kwargs)
+    ms = res["ms"]
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    peak, kind = measured_peak()
+    value = res["bytes"] * world / (ms * 1e-3) / 1e9
+    line = {"metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": res["config"]["dtype"], "data": "synthetic",
+            "config": dict(res["config"], sharding=f"kv-head x{world}"),
+            "pct_of_nominal_8TBs": round(100 * value / world / NOMINAL_PEAK_GBS, 2),
+            "pct_of_%s_copy" % kind: round(100 * value / world / peak, 2),
+            "tokens_per_s": round(res["tokens"] / (ms * 1e-3), 1),
+            "us_per_launch": round(ms * 1e3 / max(res["launches"], 1), 2),
+            "gpu_launches": res["launches"], "clocks": clocks.summary}
+    if "extra" in res:
+        line["extra"] = res["extra"]
+    status = backend.read_status(device)
+    if status:
+        raise SystemExit(f"device guard fired: status {status}")
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -641,7 +714,7 @@ def main():
                     help="call update() per layer from Python every step instead of replaying a CUDA graph")
     ap.add_argument("--two-launches", action="store_true",
                     help="per layer call append() then gather() instead of the single update() launch")
-    ap.add_argument("--micro", choices=["gather", "append-prefill", "append-decode"],
+    ap.add_argument("--micro", choices=["gather", "update", "append-prefill", "append-decode"],
                     help="time one kernel alone on a one-layer case instead of the full step")
     ap.add_argument("--mode", default="auto", choices=["auto", "vector", "bulk"])
     ap.add_argument("--layout", default="HND", choices=["HND", "NHD"])
@@ -653,9 +726,14 @@ def main():
     ap.add_argument("--reps", type=int, default=1, help="micro gather/append-prefill: launches per timed sample")
     ap.add_argument("--graph", action="store_true", help="micro cases: time a CUDA-graph replay of the launches")
     ap.add_argument("--tune", default="", help="gather knobs, e.g. stages=8,ctas=3,interleave=1 (micro cases)")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "gather70b", "churn"],
+                    help="decode = the headline configuration; the others print the same line for their configuration")
+    ap.add_argument("--layers-override", type=int, default=0, help="fewer layers for a quick run of --workload")
     args = ap.parse_args()
     if args.micro:
         run_micro(args)
+    elif args.workload != "decode" and args.impl != "reference":
+        run_extra(args)
     elif args.impl == "reference":
         run_reference(args)
     else:

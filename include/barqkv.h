@@ -105,6 +105,7 @@ typedef struct barqkv_rows_layout {
 #define BARQKV_KNOB_INTERLEAVE 4         /* static shares only. 1: every gridDim-th group of 32 pages; 0: contiguous */
 #define BARQKV_KNOB_GROUP_TILES 5        /* pages handed out per atomic fetch by the bulk gather (1..32) */
 #define BARQKV_KNOB_STATIC_SHARES 6      /* 1: ignore `work` and split pages statically among CTAs */
+#define BARQKV_KNOB_STATIC_PERMILLE 8    /* thousandths of the pages split evenly among CTAs before the atomic hand-out (-1 = default) */
 #define BARQKV_KNOB_PDL 7                /* 1: launch the bulk gather with programmatic stream serialization */
 
 int barqkv_version(void);
@@ -137,6 +138,23 @@ int barqkv_append(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,
                   int32_t n, int32_t tokens_per_entry, int32_t total_tokens,
                   const void* k_new, const void* v_new, const barqkv_rows_layout* new_rows,
                   int32_t* status, barqkv_stream_t stream);
+
+/*
+ * barqkv_append for `layers` layers in ONE launch: layer l uses the pools at
+ * k_pool/v_pool + l*pool_layer_stride elements and the new rows at k_new/v_new +
+ * l*new_layer_stride elements; the block table, positions and counts are shared (every layer
+ * of a model appends the same tokens).  Replaces `layers` calls of the reference's
+ * paged_kv_append_ (one per BarqPagedKVCacheLayer, python/barqtrain/kv_cache.py:207-219) when a
+ * step's rows for all layers are at hand - a decode step is then one launch of 16 MiB instead of
+ * 32 launches of 512 KiB.
+ */
+int barqkv_append_layers(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,
+                         int32_t layers, int64_t pool_layer_stride,
+                         const barqkv_block_table* table,
+                         const int32_t* seq_start, const int32_t* cu_new,
+                         int32_t n, int32_t tokens_per_entry, int32_t total_tokens,
+                         const void* k_new, const void* v_new, const barqkv_rows_layout* new_rows,
+                         int64_t new_layer_stride, int32_t* status, barqkv_stream_t stream);
 
 /*
  * The reference's native entry point, same semantics:

@@ -331,6 +331,43 @@ def test_update_in_one_launch_equals_append_then_gather(backend, cfg, layout):
     fused.check_device_status()
 
 
+def test_all_layers_in_one_launch_equals_per_layer_appends(backend):
+    """``append_layers`` (gridDim.y = layers) against one ``append`` per layer on a twin cache."""
+    from barqtrain_b200 import BlockTableKVCache
+
+    L, H, D, ps, dtype = 5, 2, 128, 16, torch.float16
+    g = torch.Generator().manual_seed(23)
+    order = torch.randperm(80, generator=g).tolist()
+
+    def make():
+        c = BlockTableKVCache(L, H, D, page_size=ps, num_pages=80, max_seqs=4, max_blocks_per_seq=20, dtype=dtype,
+                              device=DEV, free_order=order)
+        return c, [c.open(i) for i in range(4)]
+
+    one, s1 = make()
+    many, s2 = make()
+    for counts in ((70, 3, 0, 129), (1, 1, 1, 1), (15, 0, 16, 2), (1, 1, 1, 1)):
+        total = sum(counts)
+        wide_k = S.randn(g, (L, total, H + 1, D), dtype).to(DEV)      # rows are a strided slice of a wider tensor
+        wide_v = S.randn(g, (L, total, H + 1, D), dtype).to(DEV)
+        k_all, v_all = wide_k[:, :, :H], wide_v[:, :, :H]
+        before = backend.launches
+        b1 = one.begin_append(s1, counts)
+        one.append_layers(b1, k_all, v_all)
+        one.end_append(b1)
+        assert backend.launches - before == 1
+        many.append_step(s2, counts, list(k_all.unbind(0)), list(v_all.unbind(0)))
+        assert torch.equal(S.bits_dev(one.pools), S.bits_dev(many.pools))
+    # the same rows for every layer (layer stride 0)
+    k1 = S.randn(g, (4, H, D), dtype).to(DEV)
+    b1 = one.begin_append(s1, [1] * 4)
+    one.append_layers(b1, k1.expand(L, 4, H, D), k1.expand(L, 4, H, D))
+    one.end_append(b1)
+    many.append_step(s2, [1] * 4, [k1] * L, [k1] * L)
+    assert torch.equal(S.bits_dev(one.pools), S.bits_dev(many.pools))
+    one.check_device_status()
+
+
 @pytest.mark.parametrize("H", [8, 1])
 def test_decode_step_graph_replays_what_eager_steps_compute(backend, H):
     """A decode step recorded into a CUDA graph: every replay must leave the same pools and gathered
