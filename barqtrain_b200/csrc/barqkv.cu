@@ -28,7 +28,9 @@
 //
 // Device-side guards never trap and never spin without a bound.
 
+#include <cuda.h>
 #include <cuda_runtime.h>
+#include <cudaTypedefs.h>
 #include <atomic>
 #include <initializer_list>
 #include <stdint.h>
@@ -116,6 +118,7 @@ struct GatherArgs {
     int32_t* work;         // bulk kernel: [0] next group to hand out, [1] CTAs finished; null = static shares
     int group_tiles;       // bulk kernel, dynamic hand-out: (sequence, page) tiles per group
     int static_permille;   // bulk kernel, dynamic hand-out: thousandths of the tiles split evenly up front
+    int tensor_store;      // bulk kernel: full pages go to a row-strided output with one tiled TMA store per K/V
     int32_t* status;
     // Fused append ("update", bulk kernel only; k_new == null means plain gather): seq_lens then holds
     // the lengths BEFORE the append, entry i brings cu_new[i+1]-cu_new[i] (or tokens_per_entry) new rows,
@@ -466,6 +469,15 @@ __device__ __forceinline__ void bulk_store(void* dst_gmem, uint32_t src_smem, ui
                  "r"(src_smem), "r"(bytes)
                  : "memory");
 }
+// Tiled TMA store of a [page_size][1 head][head_dim] box from dense shared memory into an output whose
+// rows are strided (token-major [tokens, heads, head_dim]); coordinates are (element 0, head, token).
+// The innermost coordinate is always 0, so the 16-byte rule on it holds by construction.
+__device__ __forceinline__ void tensor_store_3d(const CUtensorMap* map, uint32_t src_smem, int head, int token) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];" ::"l"(
+                     reinterpret_cast<uint64_t>(map)),
+                 "r"(0), "r"(head), "r"(token), "r"(src_smem)
+                 : "memory");
+}
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void bulk_wait_read() {
@@ -478,7 +490,8 @@ __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.a
 // issued once unit g + lag has been loaded (lag = stages - 2), so `lag` loads
 // are in flight while at most two stores are still reading shared memory.
 __global__ void __launch_bounds__(32)
-gather_bulk_kernel(const GatherArgs a) {
+gather_bulk_kernel(const GatherArgs a, const __grid_constant__ CUtensorMap out_map_k,
+                   const __grid_constant__ CUtensorMap out_map_v) {
     extern __shared__ __align__(128) unsigned char s_raw[];
     const int lane = threadIdx.x;
     const int S = a.stages;
@@ -496,7 +509,9 @@ gather_bulk_kernel(const GatherArgs a) {
     int* s_rows_old = s_rows + kGroup;                                      // [kGroup]
     int* s_slot_rows = s_rows_old + kGroup;                                 // [S]
     int* s_slot_rows_old = s_slot_rows + S;                                 // [S]
-    int* s_part = s_slot_rows_old + S;                                      // [1]
+    int* s_slot_tok = s_slot_rows_old + S;                                  // [S] output token index of the page's first row
+    int* s_slot_head = s_slot_tok + S;                                      // [S]
+    int* s_part = s_slot_head + S;                                          // [1]
     int* s_cu = s_part + 1;                                                 // [n + 1]
 
     if (lane == 0) {
@@ -590,6 +605,10 @@ gather_bulk_kernel(const GatherArgs a) {
                 s_slot_rows_old[islot] = rows_old;
                 s_slot_dst[islot] = s_dst[ti] + head * a.orow.head;
                 s_slot_pool[islot] = pool_off;
+                if (a.tensor_store) {
+                    s_slot_tok[islot] = (int)(s_dst[ti] / a.orow.tok);
+                    s_slot_head[islot] = head;
+                }
                 if (bytes) mbar_arrive_expect(bar, 2 * bytes); else mbar_arrive(bar);
             }
             __syncwarp();
@@ -654,6 +673,11 @@ gather_bulk_kernel(const GatherArgs a) {
                             bulk_store((lane ? a.v_out : a.k_out) + dst, sk + lane * page_bytes,
                                        (uint32_t)(rows * a.row_bytes));
                         }
+                    } else if (a.tensor_store && rows == a.page_size) {
+                        if (lane < 2) {
+                            tensor_store_3d(lane ? &out_map_v : &out_map_k, sk + lane * page_bytes, s_slot_head[cslot],
+                                            s_slot_tok[cslot]);
+                        }
                     } else {
                         for (int op = lane; op < 2 * rows; op += 32) {
                             const int r = op >> 1, kv = op & 1;
@@ -694,6 +718,7 @@ int g_knob_group_tiles = 0;
 int g_knob_static = 0;
 int g_knob_pdl = 0;
 int g_knob_static_permille = -1;
+int g_knob_tensor_store = -1;
 
 struct DeviceInfo {
     int sms = 0;
@@ -795,6 +820,41 @@ void append_shape(const DeviceInfo* d, int total_tokens, int heads, int row_byte
     *threads = th;
 }
 
+// cuTensorMapEncodeTiled through the runtime's driver entry point query (no link against libcuda).
+PFN_cuTensorMapEncodeTiled tensor_map_encoder() {
+    static PFN_cuTensorMapEncodeTiled fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled>(p);
+    }
+    return fn;
+}
+
+// Describes a packed token-major output [tokens][heads][head_dim] (strides in bytes) for page-sized stores.
+bool make_out_map(CUtensorMap* map, void* base, int elem_bytes, int head_dim, int heads, long long head_stride,
+                  long long tok_stride, long long tokens, int page_size) {
+    PFN_cuTensorMapEncodeTiled enc = tensor_map_encoder();
+    if (!enc) return false;
+    CUtensorMapDataType dt;
+    switch (elem_bytes) {
+        case 1: dt = CU_TENSOR_MAP_DATA_TYPE_UINT8; break;
+        case 2: dt = CU_TENSOR_MAP_DATA_TYPE_UINT16; break;
+        case 4: dt = CU_TENSOR_MAP_DATA_TYPE_UINT32; break;
+        default: dt = CU_TENSOR_MAP_DATA_TYPE_UINT64; break;
+    }
+    const cuuint64_t dims[3] = {(cuuint64_t)head_dim, (cuuint64_t)heads, (cuuint64_t)tokens};
+    const cuuint64_t strides[2] = {(cuuint64_t)head_stride, (cuuint64_t)tok_stride};
+    const cuuint32_t box[3] = {(cuuint32_t)head_dim, 1u, (cuuint32_t)page_size};
+    const cuuint32_t estr[3] = {1u, 1u, 1u};
+    return enc(map, dt, 3, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+               CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 }  // namespace
 
 extern "C" {
@@ -821,6 +881,7 @@ int barqkv_set_tuning(int32_t knob, int32_t value) {
         case BARQKV_KNOB_STATIC_SHARES: g_knob_static = value; return 0;
         case BARQKV_KNOB_PDL: g_knob_pdl = value; return 0;
         case BARQKV_KNOB_STATIC_PERMILLE: g_knob_static_permille = value > 1000 ? 1000 : value; return 0;
+        case BARQKV_KNOB_TENSOR_STORE: g_knob_tensor_store = value; return 0;
         default: return fail(BARQKV_E_INVALID, "set_tuning: unknown knob");
     }
 }
@@ -1058,7 +1119,7 @@ static int gather_common(const barqkv_pool_layout* pool, const void* k_pool, con
         if (S > 32) S = 32;
         a.stages = S;
         const size_t smem = (size_t)S * 2 * page_bytes + (size_t)S * 8 /*bar*/ + (size_t)S * 16 /*slot dst, pool*/ +
-                            3 * kGroup * 8 + 2 * kGroup * 4 + (size_t)S * 8 + 4 + (size_t)(n + 1) * 4;
+                            3 * kGroup * 8 + 2 * kGroup * 4 + (size_t)S * 16 + 4 + (size_t)(n + 1) * 4;
         if ((long long)smem > d->smem_optin)
             return fail(BARQKV_E_LIMIT, "gather: bulk pipeline does not fit in shared memory");
         if (!d->bulk_attr_set) {
@@ -1075,6 +1136,20 @@ static int gather_common(const barqkv_pool_layout* pool, const void* k_pool, con
         const long long units_bound = tiles_bound * a.heads;
         const long long want = (units_bound + 2 * S - 1) / (2 * S);   // at least two ring rounds per CTA
         if (want < grid) grid = want < 1 ? 1 : want;
+        // A token-major output (rows of a page are head-stride apart) takes one tiled TMA store per full
+        // page instead of page_size row copies, when the output is packed and its shape fits a tensor map.
+        CUtensorMap map_k, map_v;
+        memset(&map_k, 0, sizeof(map_k));
+        memset(&map_v, 0, sizeof(map_v));
+        if (a.orow.tok != a.row_bytes && a.orow.seq == 0 && a.orow.packed && g_knob_tensor_store != 0 &&
+            pool->head_dim <= 256 && a.page_size <= 256 && page_bytes % 128 == 0 && a.orow.tok > 0 && a.orow.head > 0 &&
+            a.orow.tok < (1LL << 40) && a.orow.head < (1LL << 40)) {
+            const long long tokens = 0x7fffffffLL;      // full pages never reach past their sequence; no clipping needed
+            a.tensor_store = make_out_map(&map_k, k_out, pool->elem_bytes, pool->head_dim, a.heads, a.orow.head,
+                                          a.orow.tok, tokens, a.page_size) &&
+                             make_out_map(&map_v, v_out, pool->elem_bytes, pool->head_dim, a.heads, a.orow.head,
+                                          a.orow.tok, tokens, a.page_size);
+        }
         if (g_knob_pdl) {
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = dim3((unsigned)grid);
@@ -1086,10 +1161,10 @@ static int gather_common(const barqkv_pool_layout* pool, const void* k_pool, con
             attr[0].val.programmaticStreamSerializationAllowed = 1;
             cfg.attrs = attr;
             cfg.numAttrs = 1;
-            const cudaError_t le = cudaLaunchKernelEx(&cfg, gather_bulk_kernel, a);
+            const cudaError_t le = cudaLaunchKernelEx(&cfg, gather_bulk_kernel, a, map_k, map_v);
             if (le != cudaSuccess) return fail_cuda("gather launch", le);
         } else {
-            gather_bulk_kernel<<<(int)grid, 32, smem, st>>>(a);
+            gather_bulk_kernel<<<(int)grid, 32, smem, st>>>(a, map_k, map_v);
         }
     } else {
         const size_t smem = (size_t)(n + 1) * 4;

@@ -106,6 +106,7 @@ typedef struct barqkv_rows_layout {
 #define BARQKV_KNOB_GROUP_TILES 5        /* pages handed out per atomic fetch by the bulk gather (1..32) */
 #define BARQKV_KNOB_STATIC_SHARES 6      /* 1: ignore `work` and split pages statically among CTAs */
 #define BARQKV_KNOB_STATIC_PERMILLE 8    /* thousandths of the pages split evenly among CTAs before the atomic hand-out (-1 = default) */
+#define BARQKV_KNOB_TENSOR_STORE 9       /* 0: token-major outputs use row copies only; default: tiled TMA store per full page */
 #define BARQKV_KNOB_PDL 7                /* 1: launch the bulk gather with programmatic stream serialization */
 
 int barqkv_version(void);
