@@ -25,7 +25,7 @@ def _events():
 
 
 def chunked_prefill(world: int, rank: int, device, steps: int, warmup: int, page_size: int = 16,
-                    layers: int = 32, sync=lambda: None) -> Dict:
+                    layers: int = 32, all_layers: bool = False, sync=lambda: None) -> Dict:
     """32 layers, 8 KV heads, head_dim 128, fp16; 16 sequences of 8192 tokens appended in 2048-token
     chunks into a pool shuffled by a seeded permutation.  A step appends one chunk of every sequence
     in every layer; after four chunks the sequences are released and re-opened."""
@@ -39,6 +39,7 @@ def chunked_prefill(world: int, rank: int, device, steps: int, warmup: int, page
     gen = torch.Generator(device=device).manual_seed(1237 + rank)
     k = torch.randn(B * chunk, H, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
     v = torch.randn(B * chunk, H, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
+    k_all, v_all = k.expand(layers, -1, -1, -1), v.expand(layers, -1, -1, -1)
     state = {"ids": list(range(B)), "slots": [cache.open(i) for i in range(B)], "done": 0, "next": B}
 
     def step():
@@ -50,8 +51,11 @@ def chunked_prefill(world: int, rank: int, device, steps: int, warmup: int, page
             state["slots"] = [cache.open(i) for i in state["ids"]]
             state["done"] = 0
         batch = cache.begin_append(state["slots"], [chunk] * B)
-        for layer in range(layers):
-            cache.append(layer, batch, k, v)
+        if all_layers:
+            cache.append_layers(batch, k_all, v_all)
+        else:
+            for layer in range(layers):
+                cache.append(layer, batch, k, v)
         cache.end_append(batch)
         state["done"] += 1
 
@@ -67,8 +71,9 @@ def chunked_prefill(world: int, rank: int, device, steps: int, warmup: int, page
     ms = e0.elapsed_time(e1)
     cache.check_device_status()
     per_step = 4 * B * chunk * H * D * 2 * layers
-    return {"bytes": per_step * steps, "ms": ms, "tokens": B * chunk * steps, "launches": layers * steps,
-            "config": {"workload": "chunked-prefill", "layers": layers, "kv_heads_per_gpu": H, "dtype": "fp16",
+    return {"bytes": per_step * steps, "ms": ms, "tokens": B * chunk * steps,
+            "launches": (1 if all_layers else layers) * steps,
+            "config": {"workload": "chunked-prefill", "launch": "all layers per launch" if all_layers else "one per layer", "layers": layers, "kv_heads_per_gpu": H, "dtype": "fp16",
                        "page_size": page_size, "sequences": B, "chunk_tokens": chunk,
                        "step": "append one 2048-token chunk of 16 sequences in every layer",
                        "l2": "inputs larger than L2: 268 MB per launch at 8 heads, pool 34 GB"}}

@@ -650,7 +650,7 @@ def run_extra(args):
             dist.barrier()
         torch.cuda.synchronize(device)
 
-    kwargs = {"page_size": args.page_size} if args.workload == "prefill" else {}
+    kwargs = {"page_size": args.page_size, "all_layers": args.all_layers} if args.workload == "prefill" else {}
     if args.layers_override:
         kwargs["layers"] = args.layers_override
     with ClockSampler(local) as clocks:
@@ -728,6 +728,8 @@ def main():
     ap.add_argument("--tune", default="", help="gather knobs, e.g. stages=8,ctas=3,interleave=1 (micro cases)")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "gather70b", "churn"],
                     help="decode = the headline configuration; the others print the same line for their configuration")
+    ap.add_argument("--all-layers", action="store_true",
+                    help="--workload prefill: append a chunk to all layers with one launch (rows for all layers at hand)")
     ap.add_argument("--layers-override", type=int, default=0, help="fewer layers for a quick run of --workload")
     args = ap.parse_args()
     if args.micro:

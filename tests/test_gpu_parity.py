@@ -565,3 +565,66 @@ def test_full_size_chunk_round_trip(backend, ps, dtype):
     owned[torch.tensor([p for s in slots for p in cache.pages_of[s]], device=DEV)] = True
     assert not cache.pools[0][:, :, ~owned].any()
     cache.check_device_status()
+
+
+@pytest.mark.parametrize("shape", ["decode-8b", "gather-70b"])
+def test_full_size_layer_against_c_oracle(backend, shape):
+    """One layer at the full width of the decode and the 70B-gather configurations (64 sequences
+    uniform [512, 4096] / 32 sequences log-uniform [1k, 32k]; 8 heads, head_dim 128, bf16, page 16,
+    shuffled pool): prefill, three fused decode updates, then every gathered byte and the whole pool
+    compared with the C oracle."""
+    from barqtrain_b200 import BlockTableKVCache
+    from oracle import c_oracle
+
+    H, D, ps, dtype = 8, 128, 16, torch.bfloat16
+    g = torch.Generator().manual_seed(1236 if shape == "decode-8b" else 1238)
+    lens = (S.ragged_lengths(g, 64, 512, 4096) if shape == "decode-8b"
+            else S.ragged_lengths(g, 32, 1024, 32768, log_uniform=True))
+    n, steps = len(lens), 3
+    pages = sum(-(-(x + steps) // ps) for x in lens)
+    order = torch.randperm(pages, generator=g).tolist()
+    cache = BlockTableKVCache(1, H, D, page_size=ps, num_pages=pages, max_seqs=n,
+                              max_blocks_per_seq=-(-(max(lens) + steps) // ps), dtype=dtype, device=DEV,
+                              free_order=order)
+    slots = [cache.open(i) for i in range(n)]
+    ref_k = torch.zeros(H, pages, ps, D, dtype=dtype)
+    ref_v = torch.zeros_like(ref_k)
+    gen = torch.Generator(device=DEV).manual_seed(5)
+    have = [0] * n
+
+    def rows(count):
+        k = torch.randn(count, H, D, generator=gen, device=DEV, dtype=torch.float32).to(dtype)
+        v = torch.randn(count, H, D, generator=gen, device=DEV, dtype=torch.float32).to(dtype)
+        return k, v
+
+    def mirror(batch, k, v):
+        start = torch.tensor(have, dtype=torch.int32)
+        cu = torch.tensor(batch.cu, dtype=torch.int32)
+        assert c_oracle.append_paged(ref_k, ref_v, cache.table_host.clone(), None, start, cu, k.cpu(), v.cpu()) == 0
+        for i in range(n):
+            have[i] += batch.cu[i + 1] - batch.cu[i]
+
+    k, v = rows(sum(lens))
+    batch = cache.begin_append(slots, lens)
+    cache.append(0, batch, k, v)
+    cache.end_append(batch)
+    mirror(batch, k, v)
+    for _ in range(steps):
+        k, v = rows(n)
+        new = cache.begin_append(slots, [1] * n)
+        cache.end_append(new)
+        full = cache.begin_gather(slots)
+        got_k, got_v = cache.update(0, new, full, k, v, "NHD")
+        mirror(new, k, v)
+    total = sum(have)
+    want_k = torch.zeros(total, H, D, dtype=dtype)
+    want_v = torch.zeros_like(want_k)
+    cu_out = torch.tensor(full.cu[:-1], dtype=torch.int32)
+    assert c_oracle.gather_paged(ref_k, ref_v, cache.table_host.clone(), None, torch.tensor(have, dtype=torch.int32),
+                                 cu_out, want_k, want_v) == 0
+    assert torch.equal(S.bits(got_k), S.bits(want_k)) and torch.equal(S.bits(got_v), S.bits(want_v))
+    kh, vh = cache.gather(0, full, "HND")
+    assert torch.equal(S.bits(kh.transpose(0, 1)), S.bits(want_k))
+    assert torch.equal(S.bits(vh.transpose(0, 1)), S.bits(want_v))
+    assert torch.equal(S.bits(cache.pools[0, 0]), S.bits(ref_k)) and torch.equal(S.bits(cache.pools[0, 1]), S.bits(ref_v))
+    cache.check_device_status()
