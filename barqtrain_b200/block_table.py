@@ -57,7 +57,7 @@ class PageAllocator:
         self.num_pages = num_pages
         self._free: List[int] = order
         self._head = 0
-        self._owned = bytearray(num_pages)
+        self._refs = [0] * num_pages            # sequences holding each page (forked sequences share full pages)
         self.pages_resident = 0
         self.pages_peak = 0
         self.alloc_calls = 0
@@ -76,22 +76,39 @@ class PageAllocator:
             del self._free[:self._head]
             self._head = 0
         for p in pages:
-            if self._owned[p]:
+            if self._refs[p]:
                 raise AssertionError(f"page {p} handed out twice")
-            self._owned[p] = 1
+            self._refs[p] = 1
         self.pages_resident += count
         self.pages_peak = max(self.pages_peak, self.pages_resident)
         self.alloc_calls += 1
         return pages
 
+    def share(self, pages: Iterable[int]) -> None:
+        """One more holder for pages that are already held (a forked sequence)."""
+        for p in pages:
+            if not self._refs[p]:
+                raise AssertionError(f"page {p} shared but not owned")
+            self._refs[p] += 1
+
+    def holders(self, page: int) -> int:
+        return self._refs[page]
+
     def give_back(self, pages: Iterable[int]) -> None:
+        """Drop one holder of each page; pages nobody holds any more join the back of the free list."""
         pages = list(pages)
         for p in pages:
-            if not self._owned[p]:
+            if not self._refs[p]:
                 raise AssertionError(f"page {p} released but not owned")
-            self._owned[p] = 0
-        self._free.extend(pages)
-        self.pages_resident -= len(pages)
+        freed = []
+        for p in pages:
+            self._refs[p] -= 1
+            if self._refs[p] < 0:
+                raise AssertionError(f"page {p} released twice")
+            if self._refs[p] == 0:
+                freed.append(p)
+        self._free.extend(freed)
+        self.pages_resident -= len(freed)
         self.release_calls += 1
 
 
@@ -173,6 +190,7 @@ class BlockTableKVCache:
         self.pages_of: List[List[int]] = [[] for _ in range(max_seqs)]
         self._free_slots: List[int] = list(range(max_seqs - 1, -1, -1))
         self._slot_of: Dict[object, int] = {}
+        self._fork_counter = 0
 
         # staging ring for descriptors and table uploads (pinned; reuse guarded by events)
         self._ring: List[Tuple[torch.Tensor, Optional[torch.cuda.Event]]] = []
@@ -235,6 +253,99 @@ class BlockTableKVCache:
     def _mark_dirty(self, slot: int) -> None:
         self._dirty_lo = min(self._dirty_lo, slot)
         self._dirty_hi = max(self._dirty_hi, slot + 1)
+
+    # -- forks, crops, beam reordering: table edits plus at most one page copy per sequence --------
+    def _copy_pages(self, pairs: List[Tuple[int, int]]) -> None:
+        if not pairs:
+            return
+        ids = torch.tensor([p[0] for p in pairs] + [p[1] for p in pairs], dtype=torch.int32, device=self.device)
+        n = len(pairs)
+        rc = self.backend.lib.barqkv_copy_pages(self._pool_ref, self._k_ptr[0], self._v_ptr[0], self.num_layers,
+                                                self.pools.stride(0), ids.data_ptr(), ids.data_ptr() + 4 * n, n,
+                                                self._status_ptr, torch.cuda.current_stream(self.device).cuda_stream)
+        if rc:
+            self.backend._check(rc)
+
+    def _set_pages(self, slot: int, pages: List[int]) -> None:
+        old = len(self.pages_of[slot])
+        self.pages_of[slot] = pages
+        self._page_count[slot] = len(pages)
+        self._table_np[slot, :len(pages)] = pages
+        if old > len(pages):
+            self._table_np[slot, len(pages):old] = -1
+        self._mark_dirty(slot)
+
+    def fork(self, seq_id, new_seq_id=None):
+        """A new sequence with the same contents as ``seq_id`` (the block-table form of the reference's
+        ``batch_repeat_interleave``, ``kv_cache.py:166-173``, which copies the whole cache row).
+
+        Full pages are shared between the two sequences; only a partial last page - the one both will
+        append into - is copied, in every layer.  Returns the new sequence's id.
+        """
+        src = self.slot(seq_id)
+        if new_seq_id is None:
+            new_seq_id = ("fork", self._fork_counter)
+            self._fork_counter += 1
+        dst = self.open(new_seq_id)
+        length = int(self.lengths[src])
+        full, partial = divmod(length, self.page_size)
+        pages = list(self.pages_of[src][:full])
+        self.allocator.share(pages)
+        if partial:
+            try:
+                fresh = self.allocator.take(1)[0]
+            except PagePoolExhausted:
+                self.allocator.give_back(pages)
+                self._slot_of.pop(new_seq_id)
+                self._free_slots.append(dst)
+                raise
+            self._copy_pages([(self.pages_of[src][full], fresh)])
+            pages.append(fresh)
+        self._set_pages(dst, pages)
+        self.lengths[dst] = length
+        return new_seq_id
+
+    def crop(self, seq_id, max_length: int) -> None:
+        """Shorten a sequence to ``max_length`` tokens (negative: that many fewer), as the reference's
+        ``crop`` does for a layer (``kv_cache.py:158-164``).  Pages no longer needed go back to the free
+        list; rows beyond the new length in the last kept page stay as they are."""
+        slot = self.slot(seq_id)
+        length = int(self.lengths[slot])
+        if max_length < 0:
+            max_length = length - abs(max_length)
+        new_length = min(length, max(max_length, 0))
+        keep = -(-new_length // self.page_size)
+        pages = self.pages_of[slot]
+        if keep < len(pages):
+            self.allocator.give_back(pages[keep:])
+            pages = pages[:keep]
+        if new_length % self.page_size and self.allocator.holders(pages[-1]) > 1:
+            # the sequence will append into a page it shares: give it a copy of its own first
+            fresh = self.allocator.take(1)[0]
+            self._copy_pages([(pages[-1], fresh)])
+            self.allocator.give_back([pages[-1]])
+            pages = pages[:-1] + [fresh]
+        self._set_pages(slot, list(pages))
+        self.lengths[slot] = new_length
+
+    def reorder(self, seq_ids: Sequence, beam_idx: Sequence[int]) -> List:
+        """Beam-search reordering: entry ``i`` of the new batch continues ``seq_ids[beam_idx[i]]``
+        (the reference's ``batch_select_indices`` / ``reorder_cache``, ``kv_cache.py:175-186``).
+        Returns the new batch's sequence ids; sequences no beam continues are released."""
+        chosen = [seq_ids[int(b)] for b in beam_idx]
+        kept = set(chosen)
+        for sid in seq_ids:                      # dropped beams first: their slots and pages serve the forks
+            if sid not in kept:
+                self.release(sid)
+        seen = set()
+        out = []
+        for sid in chosen:
+            if sid in seen:
+                out.append(self.fork(sid))
+            else:
+                seen.add(sid)
+                out.append(sid)
+        return out
 
     # -- host -> device staging ---------------------------------------------------
     def _stage(self, words: int) -> torch.Tensor:

@@ -275,6 +275,39 @@ append_rows_kernel(const AppendArgs a) {
 }
 
 // --------------------------------------------------------------------------
+// page copies (fork / beam search: a sequence's partial last page is duplicated)
+// --------------------------------------------------------------------------
+struct CopyArgs {
+    unsigned char* k_pool;
+    unsigned char* v_pool;
+    const int32_t* src;
+    const int32_t* dst;
+    int n, heads, num_pages, page_bytes;
+    long long pool_head, pool_page, pool_layer;
+    int32_t* status;
+};
+
+// gridDim = (pairs * heads, layers, 2 [K, V]); a CTA copies one page of one head.
+template <typename V>
+__global__ void __launch_bounds__(128)
+copy_pages_kernel(const CopyArgs a) {
+    pdl_let_successor_in();
+    pdl_wait_for_predecessor();
+    const int pair = blockIdx.x / a.heads;
+    const int head = blockIdx.x - pair * a.heads;
+    const int from = a.src[pair], to = a.dst[pair];
+    if (from < 0 || from >= a.num_pages || to < 0 || to >= a.num_pages) {
+        if (threadIdx.x == 0) raise(a.status, BARQKV_S_BAD_PAGE);
+        return;
+    }
+    unsigned char* base = (blockIdx.z ? a.v_pool : a.k_pool) + (long long)blockIdx.y * a.pool_layer + head * a.pool_head;
+    const V* in = reinterpret_cast<const V*>(base + (long long)from * a.pool_page);
+    V* out = reinterpret_cast<V*>(base + (long long)to * a.pool_page);
+    const int count = a.page_bytes / (int)sizeof(V);
+    for (int i = threadIdx.x; i < count; i += blockDim.x) out[i] = in[i];
+}
+
+// --------------------------------------------------------------------------
 // gather: shared work decomposition
 // --------------------------------------------------------------------------
 // Exclusive prefix sum of per-entry page counts into s_cu[0..n]; returns nothing,
@@ -965,6 +998,45 @@ int barqkv_append_layers(const barqkv_pool_layout* pool, void* k_pool, void* v_p
                          int64_t new_layer_stride, int32_t* status, barqkv_stream_t stream) {
     return append_common(pool, k_pool, v_pool, table, seq_start, cu_new, n, tokens_per_entry, total_tokens, k_new, v_new,
                          new_rows, status, stream, layers, pool_layer_stride, new_layer_stride);
+}
+
+int barqkv_copy_pages(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,
+                      int32_t layers, int64_t pool_layer_stride,
+                      const int32_t* src_pages, const int32_t* dst_pages, int32_t n,
+                      int32_t* status, barqkv_stream_t stream) {
+    if (int rc = check_pool(pool)) return rc;
+    if (n < 0 || layers <= 0 || layers > 65535) return fail(BARQKV_E_INVALID, "copy_pages: bad page or layer count");
+    if (n == 0) return 0;
+    if (!k_pool || !v_pool || !src_pages || !dst_pages) return fail(BARQKV_E_INVALID, "copy_pages: null pointer argument");
+    if ((long long)n * pool->num_heads > 0x7fffffffLL) return fail(BARQKV_E_LIMIT, "copy_pages: too many pages in one call");
+    const long long e = pool->elem_bytes;
+    CopyArgs a;
+    memset(&a, 0, sizeof(a));
+    a.k_pool = static_cast<unsigned char*>(k_pool);
+    a.v_pool = static_cast<unsigned char*>(v_pool);
+    a.src = src_pages;
+    a.dst = dst_pages;
+    a.n = n;
+    a.heads = pool->num_heads;
+    a.num_pages = pool->num_pages;
+    a.page_bytes = (int)(pool->page_size * pool->head_dim * e);
+    a.pool_head = pool->head_stride * e;
+    a.pool_page = pool->page_stride * e;
+    a.pool_layer = pool_layer_stride * e;
+    a.status = status;
+    const int vec = vector_bytes(a.page_bytes, {a.pool_head, a.pool_page, layers > 1 ? a.pool_layer : 0}, {k_pool, v_pool});
+    const dim3 grid((unsigned)(n * a.heads), (unsigned)layers, 2);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    switch (vec) {
+        case 16: copy_pages_kernel<uint4><<<grid, 128, 0, st>>>(a); break;
+        case 8: copy_pages_kernel<uint2><<<grid, 128, 0, st>>>(a); break;
+        case 4: copy_pages_kernel<uint32_t><<<grid, 128, 0, st>>>(a); break;
+        case 2: copy_pages_kernel<uint16_t><<<grid, 128, 0, st>>>(a); break;
+        default: copy_pages_kernel<uint8_t><<<grid, 128, 0, st>>>(a); break;
+    }
+    const cudaError_t ce = cudaGetLastError();
+    if (ce == cudaSuccess) g_launches.fetch_add(1, std::memory_order_relaxed);
+    return ce == cudaSuccess ? 0 : fail_cuda("copy_pages launch", ce);
 }
 
 int barqkv_append_legacy(void* key_cache, void* value_cache, int32_t* seq_lens,

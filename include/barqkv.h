@@ -158,6 +158,19 @@ int barqkv_append_layers(const barqkv_pool_layout* pool, void* k_pool, void* v_p
                          int64_t new_layer_stride, int32_t* status, barqkv_stream_t stream);
 
 /*
+ * Copy whole pages inside the pools: page src_pages[i] -> dst_pages[i] for every head, K and V, and
+ * `layers` layers (pool_layer_stride elements apart).
+ * Replaces: the physical row copies of batch_repeat_interleave / batch_select_indices
+ *           (python/barqtrain/kv_cache.py:166-186).  With a block table a forked sequence shares its
+ *           full pages with its parent and only the partial last page, which both will write, is
+ *           duplicated.
+ */
+int barqkv_copy_pages(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,
+                      int32_t layers, int64_t pool_layer_stride,
+                      const int32_t* src_pages, const int32_t* dst_pages, int32_t n,
+                      int32_t* status, barqkv_stream_t stream);
+
+/*
  * The reference's native entry point, same semantics:
  *   void paged_kv_append_(key_cache, value_cache, seq_lens, key_states, value_states)
  *   csrc/src/bindings.cpp:43-49,74-75 -> paged_kv_append_cuda

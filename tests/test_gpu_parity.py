@@ -478,6 +478,99 @@ def test_release_recycles_pages_and_keeps_live_sequences_intact(backend):
     cache.check_device_status()
 
 
+def test_fork_crop_and_beam_reorder_against_copied_reference_layers(backend):
+    """The reference copies whole cache rows for beam search (``batch_repeat_interleave``,
+    ``batch_select_indices``, kv_cache.py:166-186); here forks share full pages and copy one.  Contents
+    must equal deep copies of the reference layers after every operation and every later append."""
+    import copy
+
+    from barqtrain_b200 import BlockTableKVCache
+    from oracle.paged_kv_oracle import OracleLayer
+
+    L, H, D, ps, dtype = 2, 2, 64, 16, torch.float16
+    g = torch.Generator().manual_seed(88)
+    cache = BlockTableKVCache(L, H, D, page_size=ps, num_pages=40, max_seqs=8, max_blocks_per_seq=8, dtype=dtype,
+                              device=DEV, seed=4)
+    truth = {}                                   # seq id -> [OracleLayer per layer], reference contents
+
+    def append(ids, counts):
+        slots = [cache.slot(i) for i in ids]
+        batch = cache.begin_append(slots, counts)
+        for l in range(L):
+            k, v = S.randn(g, (sum(counts), H, D), dtype), S.randn(g, (sum(counts), H, D), dtype)
+            cache.append(l, batch, k.to(DEV), v.to(DEV))
+            at = 0
+            for i, c in zip(ids, counts):
+                if c:
+                    truth[i][l].append(k[at:at + c].transpose(0, 1).unsqueeze(0), v[at:at + c].transpose(0, 1).unsqueeze(0))
+                at += c
+        cache.end_append(batch)
+
+    def check(ids):
+        gb = cache.begin_gather([cache.slot(i) for i in ids])
+        for l in range(L):
+            kh, vh = cache.gather(l, gb, "HND")
+            for row, i in enumerate(ids):
+                wk, wv = truth[i][l].current_tensors()
+                a, b = gb.cu[row], gb.cu[row + 1]
+                assert b - a == truth[i][l].get_seq_length()
+                assert torch.equal(S.bits(kh[:, a:b]), S.bits(wk[0])), (l, i)
+                assert torch.equal(S.bits(vh[:, a:b]), S.bits(wv[0])), (l, i)
+        owned = {}
+        for i in ids:
+            for p in cache.pages_of[cache.slot(i)]:
+                owned[p] = owned.get(p, 0) + 1
+        assert all(cache.allocator.holders(p) == c for p, c in owned.items())
+        assert cache.stats().pages_resident == len(owned)
+
+    for i in "abc":
+        cache.open(i)
+        truth[i] = [OracleLayer(1, 128, ps) for _ in range(L)]
+    append(list("abc"), [21, 16, 40])
+    append(list("abc"), [1, 1, 1])
+    check(list("abc"))
+
+    def fork(src, dst):
+        cache.fork(src, dst)
+        truth[dst] = copy.deepcopy(truth[src])
+
+    fork("a", "a2")                              # 22 tokens: one full page shared, 6 rows copied
+    fork("b", "b2")                              # 17 tokens
+    cache.crop("c", 32)                          # exactly two pages: the fork copies nothing
+    for lay in truth["c"]:
+        lay.crop(32)
+    fork("c", "c2")
+    assert cache.pages_of[cache.slot("c")] == cache.pages_of[cache.slot("c2")]
+    ids = ["a", "a2", "b", "b2", "c", "c2"]
+    check(ids)
+    for _ in range(18):                          # diverge, crossing page boundaries
+        append(ids, [1] * len(ids))
+    check(ids)
+    cache.crop("a2", 10)                         # back into the page shared with "a": copy before writing
+    for lay in truth["a2"]:
+        lay.crop(10)
+    cache.crop("b2", -3)
+    for lay in truth["b2"]:
+        lay.crop(-3)
+    append(ids, [3, 9, 0, 2, 1, 1])
+    check(ids)
+    new_ids = cache.reorder(ids, [1, 1, 4, 1, 2, 2])     # beams continue a2 (three times), c, b (twice)
+    src = ["a2", "a2", "c", "a2", "b", "b"]
+    fresh = {}
+    for nid, sid in zip(new_ids, src):
+        fresh[nid] = truth[sid] if nid == sid else copy.deepcopy(truth[sid])
+    truth.clear()
+    truth.update(fresh)
+    assert sorted(map(str, new_ids)) == sorted(map(str, truth)) and cache.stats().sequences_live == 6
+    check(new_ids)
+    append(new_ids, [2] * 6)
+    check(new_ids)
+    for sid in new_ids:
+        cache.release(sid)
+    assert cache.stats().pages_resident == 0 and cache.allocator.pages_free == 40
+    cache.check_device_status()
+
+
 def test_corrupt_table_entry_is_skipped_and_flagged(backend):
     """A page id outside the pool never reaches memory: the rows are skipped, a status bit is set,
     the other sequences are unaffected and the context stays usable."""
