@@ -2,7 +2,7 @@
 // and the C ABI declared in include/barqkv.h.
 //
 // The path is integer-indexed byte movement, so there is no arithmetic on the
-// payload and no tensor-core use: the roofline is HBM bandwidth.  Three kernels:
+// payload and no tensor-core use: the roofline is HBM bandwidth.  Kernels:
 //
 //   append_rows_kernel   new K/V rows -> page slots through the block table.
 //                        A CTA takes a tile of consecutive new tokens, resolves
@@ -12,19 +12,27 @@
 //                        (16 B for every real configuration: a head_dim row is
 //                        256 B, i.e. 16 lanes, so one warp moves the K row and
 //                        the V row of a (token, head) pair per instruction).
+//                        gridDim.y carries layers when several are appended at
+//                        once; the LEGACY variant adds the reference layout's
+//                        semantics (capacity guard, seq_lens bump by ticket).
+//   gather_bulk_kernel   pages -> contiguous rows with the copy engine:
+//                        cp.async.bulk global -> shared (mbarrier complete_tx)
+//                        -> global (bulk_group), a ring of stages per one-warp
+//                        persistent CTA, the K page and V page of one head per
+//                        stage.  Token-major outputs take one tiled TMA store
+//                        per full page.  Optionally the step's new rows join
+//                        the stage and are also written to their page slots
+//                        (append fused into the gather: barqkv_update).  No
+//                        multicast, no peer memory.
 //   gather_vector_kernel pages -> contiguous rows with 16-byte ld/st through
 //                        registers; serves every alignment and layout.
-//   gather_bulk_kernel   pages -> contiguous rows with cp.async.bulk:
-//                        global -> shared (mbarrier complete_tx) -> global
-//                        (bulk_group), a ring of stages per one-warp CTA, whole
-//                        (page, head) tiles of K and V per stage.  No multicast,
-//                        no tensor map, no peer memory.
+//   copy_pages_kernel    whole-page duplicates for forked sequences.
 //
 // Both gathers share one work decomposition: every CTA scans the batch's page
-// counts into shared memory (the batch is small: <= kMaxEntries sequences),
-// takes an equal contiguous share of the flat (sequence, page) list, and
-// resolves block-table entries in groups of 32 into shared memory before the
-// copies that use them are issued.
+// counts into shared memory (the batch is small: <= kMaxEntries sequences) and
+// resolves block-table entries a group at a time into shared memory before the
+// copies that use them are issued.  The bulk gather hands (sequence, page) tiles
+// to its CTAs through an atomic counter; the vector gather splits them evenly.
 //
 // Device-side guards never trap and never spin without a bound.
 

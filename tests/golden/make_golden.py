@@ -26,7 +26,9 @@ import torch
 HERE = Path(__file__).resolve().parent
 sys.path.insert(0, str(HERE.parent.parent))
 
-REF = Path(os.environ.get("BARQTRAIN_REFERENCE", "/root/reference"))
+if "BARQTRAIN_REFERENCE" not in os.environ:
+    raise SystemExit("set BARQTRAIN_REFERENCE to a checkout of YASSERRMD/BarqTrain")
+REF = Path(os.environ["BARQTRAIN_REFERENCE"])
 os.environ["BARQTRAIN_AUTO_BUILD"] = "0"
 sys.dont_write_bytecode = True
 sys.path.insert(0, str(REF / "python"))
