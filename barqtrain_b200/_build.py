@@ -50,7 +50,7 @@ def is_stale() -> bool:
     if not LIBRARY.exists():
         return True
     built = LIBRARY.stat().st_mtime
-    deps = [SOURCE, HEADER_DIR / "barqkv.h"]
+    deps = [SOURCE, SOURCE.parent / "paged_attention.cuh", HEADER_DIR / "barqkv.h"]
     return any(d.exists() and d.stat().st_mtime > built for d in deps)
 
 

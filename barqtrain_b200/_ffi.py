@@ -58,7 +58,7 @@ class RowsLayout(ctypes.Structure):
 
 
 EXPORTS = ("barqkv_version", "barqkv_last_error", "barqkv_sm_count", "barqkv_launch_count", "barqkv_set_tuning", "barqkv_append",
-           "barqkv_append_layers", "barqkv_copy_pages", "barqkv_append_legacy", "barqkv_gather", "barqkv_update")
+           "barqkv_append_layers", "barqkv_copy_pages", "barqkv_append_legacy", "barqkv_gather", "barqkv_update", "barqkv_paged_decode_attention", "barqkv_paged_decode_workspace_bytes")
 KNOBS = {"stages": 1, "ctas": 2, "vctas": 3, "interleave": 4, "group": 5, "static": 6, "pdl": 7, "fixed": 8, "tensor_store": 9}
 
 
@@ -109,6 +109,12 @@ class CudaBackend:
                                              _i32, _i32, _i32, _ptr, _ptr, P(RowsLayout), _i64, _ptr, _ptr]
         lib.barqkv_copy_pages.restype = _i32
         lib.barqkv_copy_pages.argtypes = [P(PoolLayout), _ptr, _ptr, _i32, _i64, _ptr, _ptr, _i32, _ptr, _ptr]
+        lib.barqkv_paged_decode_workspace_bytes.restype = _i64
+        lib.barqkv_paged_decode_workspace_bytes.argtypes = [_i32, _i32, _i64]
+        lib.barqkv_paged_decode_attention.restype = _i32
+        lib.barqkv_paged_decode_attention.argtypes = [P(PoolLayout), _ptr, _ptr, P(BlockTable), _ptr, _i32,
+                                                      _ptr, _i64, _i64, _ptr, _i64, _i64, _i32, ctypes.c_float, _i32,
+                                                      _i64, _ptr, _i64, _ptr, _ptr]
         lib.barqkv_update.restype = _i32
         lib.barqkv_update.argtypes = [P(PoolLayout), _ptr, _ptr, P(BlockTable), _ptr, _ptr, _i32, _i32, _i32,
                                       _ptr, _ptr, P(RowsLayout), _ptr, _i64, _ptr, _ptr, P(RowsLayout),

@@ -191,6 +191,7 @@ class BlockTableKVCache:
         self._free_slots: List[int] = list(range(max_seqs - 1, -1, -1))
         self._slot_of: Dict[object, int] = {}
         self._fork_counter = 0
+        self._attn_ws, self._attn_ws_bytes = None, 0
 
         # staging ring for descriptors and table uploads (pinned; reuse guarded by events)
         self._ring: List[Tuple[torch.Tensor, Optional[torch.cuda.Event]]] = []
@@ -615,6 +616,42 @@ class BlockTableKVCache:
         if rc:
             self.backend._check(rc)
         return views
+
+    # -- attention straight from the pages (decode) ---------------------------------------
+    def decode_attention(self, layer: int, full: _Descriptor, q: torch.Tensor, scale: Optional[float] = None,
+                         out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``softmax(q k^T * scale) v`` for one query token per sequence, reading K/V from the pages.
+
+        ``full`` is a ``begin_gather`` description (lengths include the token appended this step);
+        ``q`` is ``[n, num_q_heads, head_dim]`` in the cache dtype, ``num_q_heads`` a multiple (<= 8x) of
+        the KV heads on this device.  Returns ``[n, num_q_heads, head_dim]``.  No gather is involved.
+        """
+        if q.dim() != 3 or q.shape[0] != full.n or q.shape[2] != self.head_dim or q.stride(2) != 1:
+            raise ValueError(f"q must be [{full.n}, num_q_heads, {self.head_dim}] with a contiguous last dimension")
+        if q.dtype != self.dtype or q.device != self.device or self.dtype not in (torch.bfloat16, torch.float16):
+            raise ValueError("q must be bf16 or fp16, in the cache dtype, on the cache device")
+        if out is None:
+            out = torch.empty_like(q, memory_format=torch.contiguous_format)
+        elif out.shape != q.shape or out.dtype != q.dtype or out.device != q.device or out.stride(2) != 1:
+            raise ValueError("out must match q")
+        if full.n == 0:
+            return out
+        max_len = max(full.first)
+        need = int(self.backend.lib.barqkv_paged_decode_workspace_bytes(full.n, self.num_kv_heads, max_len))
+        if need > self._attn_ws_bytes:
+            self._attn_ws = torch.empty(need, dtype=torch.uint8, device=self.device)
+            self._attn_ws_bytes = need
+        ws_ptr = self._attn_ws.data_ptr() if need else None
+        if scale is None:
+            scale = self.head_dim ** -0.5
+        rc = self.backend.lib.barqkv_paged_decode_attention(
+            self._pool_ref, self._k_ptr[layer], self._v_ptr[layer], full.table_ref, full.p_first, full.n,
+            q.data_ptr(), q.stride(0), q.stride(1), out.data_ptr(), out.stride(0), out.stride(1), q.shape[1],
+            float(scale), 1 if self.dtype == torch.bfloat16 else 0, max_len, ws_ptr, need, self._status_ptr,
+            full.stream)
+        if rc:
+            self.backend._check(rc)
+        return out
 
     def gather_sequence(self, layer: int, seq_id, layout: str = "HND") -> Tuple[torch.Tensor, torch.Tensor]:
         """One sequence as contiguous ``[H, len, D]`` (or ``[len, H, D]``)."""

@@ -37,6 +37,8 @@
 // Device-side guards never trap and never spin without a bound.
 
 #include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <cudaTypedefs.h>
 #include <atomic>
@@ -1360,3 +1362,5 @@ int barqkv_gather_noalloc(const barqkv_pool_layout* pool, const void* k_pool, co
 }
 
 }  // extern "C"
+
+#include "paged_attention.cuh"

@@ -1,0 +1,399 @@
+// Decode attention straight from the pages (included at the end of barqkv.cu; same translation unit).
+//
+// One query token per sequence attends over that sequence's K/V pages through the block table, so the
+// gather's copy is not needed for decode: K and V are read once, where gather + attention read them
+// twice and write them once.  Grouped-query attention: the `group` query heads that share a KV head
+// form the rows of one 16-row MMA tile.
+//
+//   paged_decode_kernel   one warp per (sequence, KV head, split of the sequence's pages).  Pages travel
+//                         through a ring of stages with tiled TMA loads (4-D tensor map over the pool,
+//                         128-byte swizzle, mbarrier completion; no multicast); Q.K^T and P.V run on
+//                         mma.sync m16n8k16 with ldmatrix from the swizzled tiles; softmax is kept
+//                         online in fp32 (base-2 exponent).  Memory-bound: the tensor-core work is
+//                         ~6 warp instructions per token, the limit is reading 512 B per token and head.
+//   paged_decode_merge    combines the splits' partial (max, sum, output) triples.
+//
+// Restrictions (checked on the host): 2-byte elements (bf16 / fp16), head_dim 128, page_size 16,
+// group <= 8.  Every wait is bounded; a guard failure skips the sequence and sets a status bit.
+
+namespace {
+
+constexpr int kAttnStages = 4;
+constexpr int kAttnPageBytes = 16 * 128 * 2;          // one head's page of K (or V): 4 KiB
+constexpr int kAttnStageBytes = 2 * kAttnPageBytes;   // K + V
+constexpr int kAttnSplitPages = 32;                   // pages per split by default (512 tokens)
+
+struct AttnArgs {
+    Table tb;
+    const int32_t* seq_lens;
+    const unsigned char* q;
+    unsigned char* out;
+    long long q_seq, q_head, o_seq, o_head;   // byte strides
+    float* ws_o;                              // [n][kv_heads][splits][8][128] partial outputs
+    float* ws_ml;                             // [n][kv_heads][splits][8][2]   (running max, running sum)
+    int n, kv_heads, group, split_pages, splits;
+    float scale_log2;                         // softmax scale * log2(e)
+    int32_t* status;
+};
+
+__device__ __forceinline__ void tensor_load_4d(uint32_t dst_smem, const CUtensorMap* map, int c0, int c1, int c2, int c3,
+                                               uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+        ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
+        : "memory");
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+
+template <bool BF16>
+__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                          uint32_t b1) {
+    if (BF16) {
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                     : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    } else {
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                     : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    }
+}
+
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    if (BF16) {
+        const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<const uint32_t*>(&v);
+    }
+    const __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// Byte offset of 16-byte chunk `chunk` (0..7) of row `r` (0..15) inside one 2 KiB half tile
+// ([16 rows][128 B]) written by TMA with the 128-byte swizzle.
+__device__ __forceinline__ uint32_t swz(int r, int chunk) {
+    return (uint32_t)(((r >> 3) << 10) + ((r & 7) << 7) + (((chunk ^ (r & 7)) & 7) << 4));
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(32)
+paged_decode_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v) {
+    extern __shared__ unsigned char s_attn_raw[];
+    __shared__ unsigned long long s_bar[kAttnStages];
+    // the 128-byte swizzle pattern repeats every 1024 bytes of shared-memory address: align the tiles to it
+    unsigned char* s_attn = s_attn_raw + ((1024u - (smem_addr(s_attn_raw) & 1023u)) & 1023u);
+    const int lane = threadIdx.x;
+    const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
+
+    pdl_let_successor_in();
+    pdl_wait_for_predecessor();
+    const int len = a.seq_lens[seq];
+    const int pages = (len + 15) >> 4;
+    const int p0 = split * a.split_pages;
+    if (len <= 0 || p0 >= pages) return;
+    const int p1 = min(pages, p0 + a.split_pages);
+    const int row = a.tb.slots ? a.tb.slots[seq] : seq;
+    if (row < 0 || row >= a.tb.rows || pages > a.tb.stride) {
+        if (lane == 0) raise(a.status, BARQKV_S_BAD_SLOT);
+        return;
+    }
+    if (lane == 0) {
+        for (int s = 0; s < kAttnStages; ++s) mbar_init(smem_addr(&s_bar[s]), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+
+    // Q as the A operand: rows = query heads of this KV head (lane/4), zero rows beyond the group.
+    const int g = lane >> 2, tq = lane & 3;
+    uint32_t qa[8][2];
+    {
+        const unsigned char* qrow = a.q + (long long)seq * a.q_seq + (long long)(kvh * a.group + g) * a.q_head;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+            qa[ks][0] = g < a.group ? *reinterpret_cast<const uint32_t*>(qrow + (ks * 16 + tq * 2) * 2) : 0u;
+            qa[ks][1] = g < a.group ? *reinterpret_cast<const uint32_t*>(qrow + (ks * 16 + 8 + tq * 2) * 2) : 0u;
+        }
+    }
+
+    float acc[16][4];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;      // for row g (the c0/c1 half of the fragments)
+
+    // block-table entries of this split, 32 at a time, one per lane
+    int table_base = p0;
+    int my_page = (p0 + lane < p1) ? a.tb.table[(long long)row * a.tb.stride + p0 + lane] : -1;
+    bool bad = false, dead = false;
+
+    auto issue = [&](int p) {                  // load page p of this split into stage (p - p0) % stages
+        if (p - table_base >= 32) {
+            table_base += 32;
+            my_page = (table_base + lane < p1) ? a.tb.table[(long long)row * a.tb.stride + table_base + lane] : -1;
+        }
+        const int phys = __shfl_sync(0xffffffffu, my_page, p - table_base);
+        const int st = (p - p0) % kAttnStages;
+        const uint32_t bar = smem_addr(&s_bar[st]);
+        const bool ok = phys >= 0 && phys < a.tb.num_pages;
+        if (!ok) bad = true;
+        if (lane == 0) {
+            if (ok) mbar_arrive_expect(bar, kAttnStageBytes); else mbar_arrive(bar);
+        }
+        __syncwarp();
+        if (ok && lane < 4) {
+            // lanes 0..3: K dims 0-63, K dims 64-127, V dims 0-63, V dims 64-127 (2 KiB each)
+            const uint32_t dst = smem_addr(s_attn + (size_t)st * kAttnStageBytes + lane * 2048);
+            tensor_load_4d(dst, lane < 2 ? &map_k : &map_v, (lane & 1) * 64, 0, phys, kvh, bar);
+        }
+    };
+
+    const int ahead = kAttnStages - 1;
+    for (int p = p0; p < min(p1, p0 + ahead); ++p) issue(p);
+
+    for (int p = p0; p < p1 && !dead; ++p) {
+        if (p + ahead < p1) issue(p + ahead);
+        const int st = (p - p0) % kAttnStages;
+        const uint32_t phase = (uint32_t)(((p - p0) / kAttnStages) & 1);
+        const uint32_t bar = smem_addr(&s_bar[st]);
+        const long long t0 = clock64();
+        while (!mbar_try_wait(bar, phase)) {
+            if (clock64() - t0 > kWaitCycles) { dead = true; break; }
+        }
+        dead = __any_sync(0xffffffffu, dead);
+        if (dead) break;
+        if (bad) continue;                     // keep draining the loads already issued, compute nothing
+
+        unsigned char* kt = s_attn + (size_t)st * kAttnStageBytes;
+        unsigned char* vt = kt + kAttnPageBytes;
+        const int valid = min(16, len - p * 16);          // rows of this page that hold tokens
+        if (valid < 16) {
+            // rows past the sequence's end hold whatever the page held before: keep them out of P.V
+            for (int idx = lane; idx < (16 - valid) * 16; idx += 32) {
+                const int r = valid + (idx >> 4), c = idx & 15;
+                *reinterpret_cast<uint4*>(vt + (c >> 3) * 2048 + ((r >> 3) << 10) + ((r & 7) << 7) + ((c & 7) << 4)) =
+                    make_uint4(0u, 0u, 0u, 0u);
+            }
+            __syncwarp();
+        }
+
+        // S = Q K^T for the page's 16 tokens: two n-tiles of 8 tokens
+        float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+        {
+            const int tile = lane >> 3, r8 = lane & 7;
+            const int trow = (tile >> 1) * 8 + r8;
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                const uint32_t addr = smem_addr(kt + (ks >> 2) * 2048) + swz(trow, (ks & 3) * 2 + (tile & 1));
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4(addr, b0, b1, b2, b3);
+                mma_16816<BF16>(s0, qa[ks][0], 0u, qa[ks][1], 0u, b0, b1);
+                mma_16816<BF16>(s1, qa[ks][0], 0u, qa[ks][1], 0u, b2, b3);
+            }
+        }
+        // online softmax for row g: this lane holds tokens tq*2, tq*2+1 (tile 0) and +8 (tile 1)
+        float x[4] = {s0[0] * a.scale_log2, s0[1] * a.scale_log2, s1[0] * a.scale_log2, s1[1] * a.scale_log2};
+        const int t_first = tq * 2;
+        if (t_first >= valid) x[0] = -INFINITY;
+        if (t_first + 1 >= valid) x[1] = -INFINITY;
+        if (t_first + 8 >= valid) x[2] = -INFINITY;
+        if (t_first + 9 >= valid) x[3] = -INFINITY;
+        float mx = fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run, mx);              // finite: token 0 of every page of a split is valid
+        const float alpha = exp2f(m_run - m_new);
+        const float e0 = exp2f(x[0] - m_new), e1 = exp2f(x[1] - m_new), e2 = exp2f(x[2] - m_new), e3 = exp2f(x[3] - m_new);
+        l_run = l_run * alpha + (e0 + e1 + e2 + e3);
+        m_run = m_new;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) { acc[i][0] *= alpha; acc[i][1] *= alpha; }
+        const uint32_t pa0 = pack2<BF16>(e0, e1), pa2 = pack2<BF16>(e2, e3);
+
+        // O += P V: sixteen n-tiles of 8 dims, two per ldmatrix
+        {
+            const int tile = lane >> 3, r8 = lane & 7;
+            const int trow = (tile & 1) * 8 + r8;
+#pragma unroll
+            for (int nb = 0; nb < 8; ++nb) {
+                const uint32_t addr = smem_addr(vt + (nb >> 2) * 2048) + swz(trow, (nb & 3) * 2 + (tile >> 1));
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4_trans(addr, b0, b1, b2, b3);
+                mma_16816<BF16>(acc[2 * nb], pa0, 0u, pa2, 0u, b0, b1);
+                mma_16816<BF16>(acc[2 * nb + 1], pa0, 0u, pa2, 0u, b2, b3);
+            }
+        }
+        __syncwarp();      // every lane is done with this stage before lane 0 re-arms it
+    }
+
+    if (dead || bad) {
+        if (lane == 0) raise(a.status, dead ? BARQKV_S_TIMEOUT : BARQKV_S_BAD_PAGE);
+        return;
+    }
+
+    float l_tot = l_run + __shfl_xor_sync(0xffffffffu, l_run, 1);
+    l_tot += __shfl_xor_sync(0xffffffffu, l_tot, 2);
+    if (g < a.group) {
+        if (a.splits == 1) {
+            unsigned char* orow = a.out + (long long)seq * a.o_seq + (long long)(kvh * a.group + g) * a.o_head;
+            const float inv = 1.f / l_tot;
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+                *reinterpret_cast<uint32_t*>(orow + (i * 8 + tq * 2) * 2) = pack2<BF16>(acc[i][0] * inv, acc[i][1] * inv);
+        } else {
+            const long long item = (((long long)seq * a.kv_heads + kvh) * a.splits + split) * 8 + g;
+            float* wo = a.ws_o + item * 128;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) *reinterpret_cast<float2*>(wo + i * 8 + tq * 2) = make_float2(acc[i][0], acc[i][1]);
+            if (tq == 0) *reinterpret_cast<float2*>(a.ws_ml + item * 2) = make_float2(m_run, l_tot);
+        }
+    }
+}
+
+// gridDim = (query heads, sequences), 128 threads: one output dim each.
+template <bool BF16>
+__global__ void __launch_bounds__(128)
+paged_decode_merge(const AttnArgs a) {
+    pdl_let_successor_in();
+    pdl_wait_for_predecessor();
+    const int qh = blockIdx.x, seq = blockIdx.y, d = threadIdx.x;
+    const int kvh = qh / a.group, g = qh - kvh * a.group;
+    const int len = a.seq_lens[seq];
+    if (len <= 0) return;
+    const int used = min(a.splits, (((len + 15) >> 4) + a.split_pages - 1) / a.split_pages);
+    const long long item0 = (((long long)seq * a.kv_heads + kvh) * a.splits) * 8 + g;
+    float m = -INFINITY;
+    for (int s = 0; s < used; ++s) m = fmaxf(m, a.ws_ml[(item0 + (long long)s * 8) * 2]);
+    float num = 0.f, den = 0.f;
+    for (int s = 0; s < used; ++s) {
+        const long long item = item0 + (long long)s * 8;
+        const float w = exp2f(a.ws_ml[item * 2] - m);
+        num += w * a.ws_o[item * 128 + d];
+        den += w * a.ws_ml[item * 2 + 1];
+    }
+    const float o = num / den;
+    unsigned char* orow = a.out + (long long)seq * a.o_seq + (long long)qh * a.o_head;
+    if (BF16) reinterpret_cast<__nv_bfloat16*>(orow)[d] = __float2bfloat16_rn(o);
+    else reinterpret_cast<__half*>(orow)[d] = __float2half_rn(o);
+}
+
+// 4-D map over one layer's K (or V) pool: (dim, row in page, page, head); box = 64 dims x 16 rows.
+bool make_pool_map(CUtensorMap* map, const void* base, const barqkv_pool_layout* pool) {
+    PFN_cuTensorMapEncodeTiled enc = tensor_map_encoder();
+    if (!enc) return false;
+    const long long e = pool->elem_bytes;
+    const cuuint64_t dims[4] = {(cuuint64_t)pool->head_dim, (cuuint64_t)pool->page_size, (cuuint64_t)pool->num_pages,
+                                (cuuint64_t)pool->num_heads};
+    const cuuint64_t strides[3] = {(cuuint64_t)(pool->head_dim * e), (cuuint64_t)(pool->page_stride * e),
+                                   (cuuint64_t)(pool->head_stride * e)};
+    const cuuint32_t box[4] = {64u, 16u, 1u, 1u};
+    const cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int attn_splits(long long max_len, int* split_pages) {
+    const long long pages = (max_len + 15) / 16;
+    int sp = kAttnSplitPages;
+    while ((pages + sp - 1) / sp > 64) sp *= 2;      // at most 64 splits
+    *split_pages = sp;
+    const long long splits = (pages + sp - 1) / sp;
+    return splits < 1 ? 1 : (int)splits;
+}
+
+}  // namespace
+
+extern "C" {
+
+int64_t barqkv_paged_decode_workspace_bytes(int32_t n, int32_t kv_heads, int64_t max_len) {
+    if (n <= 0 || kv_heads <= 0 || max_len <= 0) return 0;
+    int sp;
+    const int splits = attn_splits(max_len, &sp);
+    if (splits == 1) return 0;
+    return (int64_t)n * kv_heads * splits * 8 * (128 + 2) * (int64_t)sizeof(float);
+}
+
+int barqkv_paged_decode_attention(const barqkv_pool_layout* pool, const void* k_pool, const void* v_pool,
+                                  const barqkv_block_table* table, const int32_t* seq_lens, int32_t n,
+                                  const void* q, int64_t q_seq_stride, int64_t q_head_stride,
+                                  void* out, int64_t out_seq_stride, int64_t out_head_stride,
+                                  int32_t num_q_heads, float softmax_scale, int32_t is_bf16, int64_t max_len,
+                                  void* workspace, int64_t workspace_bytes, int32_t* status, barqkv_stream_t stream) {
+    if (int rc = check_pool(pool)) return rc;
+    if (n < 0) return fail(BARQKV_E_INVALID, "decode_attention: negative batch size");
+    if (n == 0) return 0;
+    if (int rc = check_table(table, n)) return rc;
+    if (!table->table) return fail(BARQKV_E_INVALID, "decode_attention: needs an explicit block table");
+    if (!k_pool || !v_pool || !seq_lens || !q || !out) return fail(BARQKV_E_INVALID, "decode_attention: null pointer argument");
+    if (pool->elem_bytes != 2 || pool->head_dim != 128 || pool->page_size != 16)
+        return fail(BARQKV_E_LIMIT, "decode_attention: supports 2-byte elements, head_dim 128, page_size 16");
+    if (num_q_heads <= 0 || num_q_heads % pool->num_heads || num_q_heads / pool->num_heads > 8)
+        return fail(BARQKV_E_LIMIT, "decode_attention: query heads must be 1..8 times the KV heads");
+    if (n > 65535 || pool->num_heads > 65535) return fail(BARQKV_E_LIMIT, "decode_attention: more than 65535 sequences or heads");
+    if (max_len <= 0) return fail(BARQKV_E_INVALID, "decode_attention: max_len (upper bound of the lengths) must be positive");
+    const long long e = 2;
+    if (!aligned(q, 4) || !aligned(out, 4) || !multiple(q_seq_stride * e, 4) || !multiple(q_head_stride * e, 4) ||
+        !multiple(out_seq_stride * e, 4) || !multiple(out_head_stride * e, 4))
+        return fail(BARQKV_E_INVALID, "decode_attention: q and out rows must be 4-byte aligned");
+    if (!aligned(k_pool, 16) || !aligned(v_pool, 16) || !multiple(pool->page_stride * e, 16) || !multiple(pool->head_stride * e, 16))
+        return fail(BARQKV_E_INVALID, "decode_attention: pools must be 16-byte aligned");
+    DeviceInfo* d = device_info();
+    if (!d) return fail(BARQKV_E_LAUNCH, "no CUDA device is current");
+
+    AttnArgs a;
+    memset(&a, 0, sizeof(a));
+    a.tb = make_table(table, pool->num_pages);
+    a.seq_lens = seq_lens;
+    a.q = static_cast<const unsigned char*>(q);
+    a.out = static_cast<unsigned char*>(out);
+    a.q_seq = q_seq_stride * e;
+    a.q_head = q_head_stride * e;
+    a.o_seq = out_seq_stride * e;
+    a.o_head = out_head_stride * e;
+    a.n = n;
+    a.kv_heads = pool->num_heads;
+    a.group = num_q_heads / pool->num_heads;
+    a.splits = attn_splits(max_len, &a.split_pages);
+    a.scale_log2 = softmax_scale * 1.4426950408889634f;
+    a.status = status;
+    if (a.splits > 1) {
+        const int64_t need = barqkv_paged_decode_workspace_bytes(n, a.kv_heads, max_len);
+        if (!workspace || workspace_bytes < need || !aligned(workspace, 16))
+            return fail(BARQKV_E_INVALID, "decode_attention: workspace missing or smaller than "
+                                          "barqkv_paged_decode_workspace_bytes(n, kv_heads, max_len)");
+        a.ws_o = static_cast<float*>(workspace);
+        a.ws_ml = a.ws_o + (size_t)n * a.kv_heads * a.splits * 8 * 128;
+    }
+    CUtensorMap map_k, map_v;
+    if (!make_pool_map(&map_k, k_pool, pool) || !make_pool_map(&map_v, v_pool, pool))
+        return fail(BARQKV_E_LAUNCH, "decode_attention: could not describe the pools to the copy engine");
+
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t smem = (size_t)kAttnStages * kAttnStageBytes + 1024;   // + slack to align the tiles to 1024 B
+    const dim3 grid((unsigned)a.splits, (unsigned)a.kv_heads, (unsigned)n);
+    if (is_bf16) paged_decode_kernel<true><<<grid, 32, smem, st>>>(a, map_k, map_v);
+    else paged_decode_kernel<false><<<grid, 32, smem, st>>>(a, map_k, map_v);
+    cudaError_t ce = cudaGetLastError();
+    if (ce != cudaSuccess) return fail_cuda("decode_attention launch", ce);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    if (a.splits > 1) {
+        const dim3 mgrid((unsigned)num_q_heads, (unsigned)n);
+        if (is_bf16) paged_decode_merge<true><<<mgrid, 128, 0, st>>>(a);
+        else paged_decode_merge<false><<<mgrid, 128, 0, st>>>(a);
+        ce = cudaGetLastError();
+        if (ce != cudaSuccess) return fail_cuda("decode_attention merge launch", ce);
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+    }
+    return 0;
+}
+
+}  // extern "C"

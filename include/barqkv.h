@@ -243,6 +243,27 @@ int barqkv_update(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,
                   barqkv_stream_t stream);
 
 /*
+ * Decode attention straight from the pages: one query token per sequence attends over the sequence's
+ * K/V through the block table, so the gather's copy is not needed for decode.
+ * No counterpart in the reference (its attention kernel, csrc/kernels/flash_attention.cu, reads
+ * contiguous K/V; the reference roadmap lists "attention over pages" as future work).  The numerical
+ * reference is softmax(q k^T * scale) v in fp32 over the gathered sequence.
+ * q / out: [n, num_q_heads, 128] in the pool's 2-byte type (is_bf16 selects bf16 or fp16), strides in
+ * elements; query head j uses KV head j / (num_q_heads / kv_heads).  seq_lens: lengths including the
+ * current token (append first).  max_len: an upper bound of the lengths known to the host; it fixes
+ * how many splits a sequence's pages are cut into.  workspace: device scratch of
+ * barqkv_paged_decode_workspace_bytes(n, kv_heads, max_len) bytes (0 when one split suffices).
+ * Limits: head_dim 128, page_size 16, 2-byte elements, at most 8 query heads per KV head.
+ */
+int64_t barqkv_paged_decode_workspace_bytes(int32_t n, int32_t kv_heads, int64_t max_len);
+int barqkv_paged_decode_attention(const barqkv_pool_layout* pool, const void* k_pool, const void* v_pool,
+                                  const barqkv_block_table* table, const int32_t* seq_lens, int32_t n,
+                                  const void* q, int64_t q_seq_stride, int64_t q_head_stride,
+                                  void* out, int64_t out_seq_stride, int64_t out_head_stride,
+                                  int32_t num_q_heads, float softmax_scale, int32_t is_bf16, int64_t max_len,
+                                  void* workspace, int64_t workspace_bytes, int32_t* status, barqkv_stream_t stream);
+
+/*
  * barqkv_gather for callers that cannot allocate device memory.
  * No counterpart in the reference (it never needs scratch memory).
  *

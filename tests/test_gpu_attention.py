@@ -1,0 +1,90 @@
+"""Decode attention over the pages against an fp32 reference over the gathered sequences.
+
+This is a floating-point kernel (bf16/fp16 inputs, fp32 accumulation, probabilities rounded to the input
+type before the P.V product), so the comparison has a tolerance: |got - want| <= 8e-3 + 2e-2 * |want|
+against softmax(q k^T / sqrt(d)) v computed by torch in fp32 on the same values.
+"""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+ATOL, RTOL = 8e-3, 2e-2
+
+
+def _reference(cache, layer, slots, q, scale):
+    gb = cache.begin_gather(slots)
+    kh, vh = cache.gather(layer, gb, "HND")                       # [Hkv, total, D]
+    n, hq, d = q.shape
+    group = hq // cache.num_kv_heads
+    want = torch.empty(n, hq, d, dtype=torch.float32, device=q.device)
+    for i in range(n):
+        a, b = gb.cu[i], gb.cu[i + 1]
+        k = kh[:, a:b].float().repeat_interleave(group, dim=0)     # [Hq, len, D]
+        v = vh[:, a:b].float().repeat_interleave(group, dim=0)
+        s = torch.einsum("hd,hld->hl", q[i].float(), k) * scale
+        want[i] = torch.einsum("hl,hld->hd", torch.softmax(s, dim=-1), v)
+    return gb, want
+
+
+@pytest.mark.parametrize("case", [
+    dict(dtype=torch.bfloat16, hkv=8, group=4, lens=(1, 15, 16, 17, 37, 500, 512, 513, 1500), seed=1),
+    dict(dtype=torch.float16, hkv=2, group=8, lens=(700, 33, 4096 + 5), seed=2),
+    dict(dtype=torch.bfloat16, hkv=4, group=1, lens=(64, 129, 2), seed=3),
+    dict(dtype=torch.float16, hkv=1, group=4, lens=(3000, 16, 1024), seed=4),
+])
+def test_decode_attention_matches_fp32_reference(case):
+    from barqtrain_b200 import BlockTableKVCache, _ffi
+
+    backend = _ffi.require_cuda_backend()
+    dtype, hkv, group, lens = case["dtype"], case["hkv"], case["group"], case["lens"]
+    D, ps, n = 128, 16, len(case["lens"])
+    g = torch.Generator(device=DEV).manual_seed(case["seed"])
+    pages = sum(-(-x // ps) for x in lens) + 3
+    cache = BlockTableKVCache(2, hkv, D, page_size=ps, num_pages=pages, max_seqs=n,
+                              max_blocks_per_seq=-(-max(lens) // ps), dtype=dtype, device=DEV, seed=case["seed"],
+                              zero_pages=False)
+    cache.pools.fill_(float("nan"))              # unused rows of partial pages must never leak into the result
+    slots = [cache.open(i) for i in range(n)]
+    total = sum(lens)
+    for layer in range(2):
+        k = torch.randn(total, hkv, D, generator=g, device=DEV, dtype=torch.float32).to(dtype)
+        v = torch.randn(total, hkv, D, generator=g, device=DEV, dtype=torch.float32).to(dtype)
+        batch = cache.begin_append(slots, lens) if layer == 0 else batch
+        cache.append(layer, batch, k, v)
+    cache.end_append(batch)
+    q = torch.randn(n, hkv * group, D, generator=g, device=DEV, dtype=torch.float32).to(dtype)
+    scale = D ** -0.5
+    for layer in range(2):
+        gb, want = _reference(cache, layer, slots, q, scale)
+        got = cache.decode_attention(layer, gb, q)
+        assert got.shape == q.shape and got.dtype == dtype
+        err = (got.float() - want).abs()
+        bound = ATOL + RTOL * want.abs()
+        assert bool((err <= bound).all()), f"max err {err.max().item():.4g}, worst excess {(err - bound).max().item():.4g}"
+        assert torch.isfinite(got.float()).all()
+    # a subset of the batch in another order, through a strided q view
+    order = list(range(n - 1, -1, -2))
+    wide = torch.randn(len(order), hkv * group + 1, D, generator=g, device=DEV, dtype=torch.float32).to(dtype)
+    q2 = wide[:, 1:]
+    gb, want = _reference(cache, 1, [slots[i] for i in order], q2, scale)
+    got = cache.decode_attention(1, gb, q2)
+    assert bool(((got.float() - want).abs() <= ATOL + RTOL * want.abs()).all())
+    assert backend.read_status(DEV) == 0
+
+
+def test_decode_attention_argument_limits():
+    from barqtrain_b200 import BlockTableKVCache, _ffi
+
+    cache = BlockTableKVCache(1, 2, 64, page_size=16, num_pages=4, max_seqs=1, max_blocks_per_seq=2,
+                              dtype=torch.bfloat16, device=DEV)
+    s = cache.open(0)
+    k = torch.zeros(3, 2, 64, dtype=torch.bfloat16, device=DEV)
+    cache.append_step([s], [3], [k], [k])
+    gb = cache.begin_gather([s])
+    with pytest.raises(_ffi.BarqKVError, match="head_dim 128"):
+        cache.decode_attention(0, gb, torch.zeros(1, 2, 64, dtype=torch.bfloat16, device=DEV))
+    with pytest.raises(ValueError):
+        cache.decode_attention(0, gb, torch.zeros(2, 2, 64, dtype=torch.bfloat16, device=DEV))
