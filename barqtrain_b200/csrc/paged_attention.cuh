@@ -301,10 +301,17 @@ bool make_pool_map(CUtensorMap* map, const void* base, const barqkv_pool_layout*
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-int attn_splits(long long max_len, int* split_pages) {
+// Pages per split: 32 (512 tokens) when the batch alone fills the machine, fewer when it does not
+// (few sequences or a single KV head per GPU), so that about eight one-warp CTAs per SM have work;
+// never more than 64 splits per sequence.
+int attn_splits(int n, int kv_heads, long long max_len, int* split_pages) {
     const long long pages = (max_len + 15) / 16;
+    int sms = 148;
+    if (DeviceInfo* d = device_info()) sms = d->sms;
+    long long per_cta = (long long)n * kv_heads * pages / (8LL * sms);
     int sp = kAttnSplitPages;
-    while ((pages + sp - 1) / sp > 64) sp *= 2;      // at most 64 splits
+    while (sp > 4 && sp > per_cta) sp >>= 1;
+    while ((pages + sp - 1) / sp > 64) sp *= 2;
     *split_pages = sp;
     const long long splits = (pages + sp - 1) / sp;
     return splits < 1 ? 1 : (int)splits;
@@ -317,7 +324,7 @@ extern "C" {
 int64_t barqkv_paged_decode_workspace_bytes(int32_t n, int32_t kv_heads, int64_t max_len) {
     if (n <= 0 || kv_heads <= 0 || max_len <= 0) return 0;
     int sp;
-    const int splits = attn_splits(max_len, &sp);
+    const int splits = attn_splits(n, kv_heads, max_len, &sp);
     if (splits == 1) return 0;
     return (int64_t)n * kv_heads * splits * 8 * (128 + 2) * (int64_t)sizeof(float);
 }
@@ -362,7 +369,7 @@ int barqkv_paged_decode_attention(const barqkv_pool_layout* pool, const void* k_
     a.n = n;
     a.kv_heads = pool->num_heads;
     a.group = num_q_heads / pool->num_heads;
-    a.splits = attn_splits(max_len, &a.split_pages);
+    a.splits = attn_splits(n, a.kv_heads, max_len, &a.split_pages);
     a.scale_log2 = softmax_scale * 1.4426950408889634f;
     a.status = status;
     if (a.splits > 1) {

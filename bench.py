@@ -510,7 +510,7 @@ def run_micro(args):
     dtype = torch.bfloat16
     gen = torch.Generator(device=device).manual_seed(7)
     g = torch.Generator().manual_seed(CFG["seed"])
-    if args.micro in ("gather", "update"):
+    if args.micro in ("gather", "update", "attention"):
         if args.lengths == "loguniform":          # the 70B-shaped gather configuration: 32 sequences in [1k, 32k]
             import math
             u = torch.rand(32, generator=g, dtype=torch.float64)
@@ -569,6 +569,21 @@ def run_micro(args):
                 for _ in range(args.reps):
                     cache.update(0, new, full, k1, k1, args.layout, out=out, mode=args.mode)
             return launch, args.reps, (full.total + B) * per_tok * args.reps
+        if args.micro == "attention":
+            total = sum(lens)
+            k = torch.randn(total, H, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
+            if cache.lengths[slots[0]] == 0:
+                cache.append_step(slots, lens, [k], [k])
+            full = cache.begin_gather(slots)
+            q = torch.randn(B, H * args.group, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
+            out = torch.empty_like(q)
+            cache.decode_attention(0, full, q, out=out)            # sizes the workspace outside any capture
+
+            def launch():
+                for _ in range(args.reps):
+                    cache.decode_attention(0, full, q, out=out)
+            # K and V are read once: 2 * tokens * H * D * e bytes (q and out are negligible)
+            return launch, args.reps, total * 2 * H * D * 2 * args.reps
         if args.micro == "append-prefill":
             total = args.chunk * B
             k = torch.randn(total, H, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
@@ -714,7 +729,7 @@ def main():
                     help="call update() per layer from Python every step instead of replaying a CUDA graph")
     ap.add_argument("--two-launches", action="store_true",
                     help="per layer call append() then gather() instead of the single update() launch")
-    ap.add_argument("--micro", choices=["gather", "update", "append-prefill", "append-decode"],
+    ap.add_argument("--micro", choices=["gather", "update", "attention", "append-prefill", "append-decode"],
                     help="time one kernel alone on a one-layer case instead of the full step")
     ap.add_argument("--mode", default="auto", choices=["auto", "vector", "bulk"])
     ap.add_argument("--layout", default="HND", choices=["HND", "NHD"])
@@ -723,6 +738,7 @@ def main():
     ap.add_argument("--chunk", type=int, default=2048, help="tokens per sequence per append (append-prefill)")
     ap.add_argument("--layers", type=int, default=32, help="appends per timed group (append-decode)")
     ap.add_argument("--lengths", default="uniform", choices=["uniform", "loguniform"])
+    ap.add_argument("--group", type=int, default=4, help="micro attention: query heads per KV head")
     ap.add_argument("--reps", type=int, default=1, help="micro gather/append-prefill: launches per timed sample")
     ap.add_argument("--graph", action="store_true", help="micro cases: time a CUDA-graph replay of the launches")
     ap.add_argument("--tune", default="", help="gather knobs, e.g. stages=8,ctas=3,interleave=1 (micro cases)")
