@@ -182,7 +182,8 @@ class BlockTableKVCache:
         self.table_host = torch.full((max_seqs, max_blocks_per_seq), -1, dtype=torch.int32).pin_memory()
         self.table_dev = torch.full((max_seqs, max_blocks_per_seq), -1, dtype=torch.int32, device=self.device)
         self._table_np = self.table_host.numpy()
-        self._dirty_lo, self._dirty_hi = max_seqs, 0
+        self._table_changes: List[Tuple[np.ndarray, np.ndarray]] = []
+        self._pairs_dev: Optional[torch.Tensor] = None
         self._table = _ffi.BlockTable(self.table_dev.data_ptr(), None, max_seqs, max_blocks_per_seq, 0, 0)
 
         self.lengths = np.zeros(max_seqs, dtype=np.int64)      # tokens held, per slot
@@ -230,7 +231,7 @@ class BlockTableKVCache:
         self.pages_of[slot] = []
         self._page_count[slot] = 0
         self._table_np[slot, :used] = -1
-        self._mark_dirty(slot)
+        self._note_table_change(slot, 0, [-1] * used)
         self.lengths[slot] = 0
         self._free_slots.append(slot)
 
@@ -249,11 +250,7 @@ class BlockTableKVCache:
         self.pages_of[slot].extend(pages)
         self._page_count[slot] = need
         self._table_np[slot, have:need] = pages
-        self._mark_dirty(slot)
-
-    def _mark_dirty(self, slot: int) -> None:
-        self._dirty_lo = min(self._dirty_lo, slot)
-        self._dirty_hi = max(self._dirty_hi, slot + 1)
+        self._note_table_change(slot, have, pages)
 
     # -- forks, crops, beam reordering: table edits plus at most one page copy per sequence --------
     def _copy_pages(self, pairs: List[Tuple[int, int]]) -> None:
@@ -271,10 +268,9 @@ class BlockTableKVCache:
         old = len(self.pages_of[slot])
         self.pages_of[slot] = pages
         self._page_count[slot] = len(pages)
-        self._table_np[slot, :len(pages)] = pages
-        if old > len(pages):
-            self._table_np[slot, len(pages):old] = -1
-        self._mark_dirty(slot)
+        row = list(pages) + [-1] * max(old - len(pages), 0)
+        self._table_np[slot, :len(row)] = row
+        self._note_table_change(slot, 0, row)
 
     def fork(self, seq_id, new_seq_id=None):
         """A new sequence with the same contents as ``seq_id`` (the block-table form of the reference's
@@ -349,36 +345,84 @@ class BlockTableKVCache:
         return out
 
     # -- host -> device staging ---------------------------------------------------
-    def _stage(self, words: int) -> torch.Tensor:
-        """A pinned int32 buffer nobody is reading any more."""
+    def _stage(self, words: int):
+        """A pinned int32 staging buffer nobody is reading any more: (numpy view, host address)."""
         if words > self._ring_words:
             self._ring_words = max(2 * words, 1 << 16)
             self._ring = [(torch.empty(self._ring_words, dtype=torch.int32).pin_memory(), None) for _ in range(8)]
             self._ring_np = [buf.numpy() for buf, _ in self._ring]
+            self._ring_ptr = [buf.data_ptr() for buf, _ in self._ring]
             self._ring_pos = 0
-        buf, event = self._ring[self._ring_pos]
+        _, event = self._ring[self._ring_pos]
         if event is not None:
             event.synchronize()
-        return buf
+        return self._ring_np[self._ring_pos], self._ring_ptr[self._ring_pos]
 
-    def _stage_done(self) -> None:
+    def _stage_done(self, stream) -> None:
         buf, event = self._ring[self._ring_pos]
         if event is None:
             event = torch.cuda.Event()
-        event.record(torch.cuda.current_stream(self.device))
+        event.record(stream)
         self._ring[self._ring_pos] = (buf, event)
         self._ring_pos = (self._ring_pos + 1) % len(self._ring)
 
+    def _reserve_many(self, slots: np.ndarray, have: np.ndarray, need: np.ndarray, lengths: np.ndarray) -> None:
+        """Pages for several sequences at once: one trip to the free list, vectorised table edits."""
+        over = np.nonzero(need > self.max_blocks)[0]
+        if over.size:
+            raise ValueError(
+                f"paged KV cache capacity exceeded: requested {int(lengths[over[0]])}, "
+                f"max_cache_len={self.max_blocks * self.page_size}"
+            )
+        extra = need - have
+        total = int(extra.sum())
+        pages = self.allocator.take(total)
+        starts = np.cumsum(extra) - extra
+        rows = np.repeat(slots, extra)
+        cols = np.repeat(have - starts, extra) + np.arange(total, dtype=np.int64)
+        page_arr = np.asarray(pages, dtype=np.int32)
+        self._table_np[rows, cols] = page_arr
+        self._table_changes.append(((rows * self.max_blocks + cols).astype(np.int32), page_arr))
+        self._page_count[slots] = need
+        at = 0
+        for slot, count in zip(slots.tolist(), extra.tolist()):
+            self.pages_of[slot].extend(pages[at:at + count])
+            at += count
+
+    def _note_table_change(self, slot: int, first_col: int, values) -> None:
+        """Remember entries of the host table that the device copy does not have yet."""
+        values = np.asarray(values, dtype=np.int32)
+        at = slot * self.max_blocks + first_col + np.arange(values.size, dtype=np.int32)
+        self._table_changes.append((at, values))
+
     def _flush_table(self) -> None:
-        lo, hi = self._dirty_lo, self._dirty_hi
-        if lo >= hi:
+        """Send the changed block-table entries (index, value pairs) and scatter them into the device table."""
+        if not self._table_changes:
             return
-        words = (hi - lo) * self.max_blocks
-        buf = self._stage(words)
-        buf[:words].view(hi - lo, self.max_blocks).copy_(self.table_host[lo:hi])
-        self.table_dev[lo:hi].copy_(buf[:words].view(hi - lo, self.max_blocks), non_blocking=True)
-        self._stage_done()
-        self._dirty_lo, self._dirty_hi = self.max_seqs, 0
+        at = np.concatenate([c[0] for c in self._table_changes])
+        values = np.concatenate([c[1] for c in self._table_changes])
+        several = len(self._table_changes) > 1
+        self._table_changes = []
+        if several:
+            # an entry written twice since the last flush (a released slot claimed again) keeps its last
+            # value: the scatter kernel applies the pairs in no particular order
+            _, last = np.unique(at[::-1], return_index=True)
+            keep = np.sort(at.size - 1 - last)
+            at, values = at[keep], values[keep]
+        m = at.size
+        if self._pairs_dev is None or self._pairs_dev.numel() < 2 * m:
+            self._pairs_dev = torch.empty(max(2 * m, 4096), dtype=torch.int32, device=self.device)
+        host, host_ptr = self._stage(2 * m)
+        host[0:2 * m:2] = at
+        host[1:2 * m:2] = values
+        stream = torch.cuda.current_stream(self.device)
+        lib = self.backend.lib
+        rc = lib.barqkv_upload(self._pairs_dev.data_ptr(), host_ptr, 8 * m, stream.cuda_stream)
+        rc = rc or lib.barqkv_table_scatter(self.table_dev.data_ptr(), self.max_seqs * self.max_blocks,
+                                            self._pairs_dev.data_ptr(), m, stream.cuda_stream)
+        if rc:
+            self.backend._check(rc)
+        self._stage_done(stream)
 
     def _describe(self, kind: str, slots, first, counts) -> _Descriptor:
         slots = np.asarray(slots, dtype=np.int64)
@@ -391,20 +435,22 @@ class BlockTableKVCache:
         if dev is None or dev.numel() < words:
             dev = torch.empty(max(words, 3 * self.max_seqs + 1), dtype=torch.int32, device=self.device)
             self._desc_dev[kind] = dev
-        buf = self._stage(words)
-        host = self._ring_np[self._ring_pos]
+        host, host_ptr = self._stage(words)
         host[:n] = slots
         host[n:2 * n] = first
         host[2 * n:words] = cu
         # the device buffer is laid out for this n: [slots | first | cu]
-        dev[:words].copy_(buf[:words], non_blocking=True)
-        self._stage_done()
+        cur = torch.cuda.current_stream(self.device)
+        rc = self.backend.lib.barqkv_upload(dev.data_ptr(), host_ptr, 4 * words, cur.cuda_stream)
+        if rc:
+            self.backend._check(rc)
+        self._stage_done(cur)
         table = self._tables.get(kind)
         if table is None:
             table = _ffi.BlockTable(self.table_dev.data_ptr(), None, self.max_seqs, self.max_blocks, 0, 0)
             self._tables[kind] = table
         table.slots = dev.data_ptr()
-        stream = torch.cuda.current_stream(self.device).cuda_stream
+        stream = cur.cuda_stream
         work = self.backend.work_words(self.device).data_ptr() if kind == "gather" else 0
         desc = _Descriptor(n, dev, int(cu[n]), first.tolist(), cu.tolist(), slots.tolist(), ctypes.byref(table),
                            stream, work)
@@ -424,8 +470,10 @@ class BlockTableKVCache:
         first = self.lengths[slots]
         after = first + counts
         need = -(-after // self.page_size)
-        for i in np.nonzero(need > self._page_count[slots])[0]:      # only sequences that cross into a new page
-            self.reserve(int(slots[i]), int(after[i]))
+        have = self._page_count[slots]
+        grow = np.nonzero(need > have)[0]                   # only sequences that cross into a new page
+        if grow.size:
+            self._reserve_many(slots[grow], have[grow], need[grow], after[grow])
         self._flush_table()
         return self._describe("append", slots, first, counts)
 

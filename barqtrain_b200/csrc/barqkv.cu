@@ -318,6 +318,21 @@ copy_pages_kernel(const CopyArgs a) {
 }
 
 // --------------------------------------------------------------------------
+// block-table maintenance: the host sends only the entries that changed
+// --------------------------------------------------------------------------
+// pairs[2*i] = flat index into the table, pairs[2*i+1] = new page id (or -1)
+__global__ void __launch_bounds__(128)
+table_scatter_kernel(int32_t* __restrict__ table, const int32_t* __restrict__ pairs, int n, long long table_words) {
+    pdl_let_successor_in();
+    pdl_wait_for_predecessor();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) {
+        const long long at = pairs[2 * i];
+        if (at >= 0 && at < table_words) table[at] = pairs[2 * i + 1];
+    }
+}
+
+// --------------------------------------------------------------------------
 // gather: shared work decomposition
 // --------------------------------------------------------------------------
 // Exclusive prefix sum of per-entry page counts into s_cu[0..n]; returns nothing,
@@ -1008,6 +1023,23 @@ int barqkv_append_layers(const barqkv_pool_layout* pool, void* k_pool, void* v_p
                          int64_t new_layer_stride, int32_t* status, barqkv_stream_t stream) {
     return append_common(pool, k_pool, v_pool, table, seq_start, cu_new, n, tokens_per_entry, total_tokens, k_new, v_new,
                          new_rows, status, stream, layers, pool_layer_stride, new_layer_stride);
+}
+
+int barqkv_upload(void* dst_device, const void* src_host, int64_t bytes, barqkv_stream_t stream) {
+    if (bytes < 0 || (bytes && (!dst_device || !src_host))) return fail(BARQKV_E_INVALID, "upload: bad arguments");
+    if (bytes == 0) return 0;
+    const cudaError_t e = cudaMemcpyAsync(dst_device, src_host, (size_t)bytes, cudaMemcpyHostToDevice,
+                                          static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? 0 : fail_cuda("upload", e);
+}
+
+int barqkv_table_scatter(int32_t* table, int64_t table_words, const int32_t* pairs, int32_t n, barqkv_stream_t stream) {
+    if (n < 0 || (n && (!table || !pairs))) return fail(BARQKV_E_INVALID, "table_scatter: bad arguments");
+    if (n == 0) return 0;
+    table_scatter_kernel<<<(n + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(table, pairs, n, table_words);
+    const cudaError_t ce = cudaGetLastError();
+    if (ce == cudaSuccess) g_launches.fetch_add(1, std::memory_order_relaxed);
+    return ce == cudaSuccess ? 0 : fail_cuda("table_scatter launch", ce);
 }
 
 int barqkv_copy_pages(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,

@@ -158,6 +158,16 @@ int barqkv_append_layers(const barqkv_pool_layout* pool, void* k_pool, void* v_p
                          int64_t new_layer_stride, int32_t* status, barqkv_stream_t stream);
 
 /*
+ * Host-side plumbing of the block table (no counterpart in the reference, which has no table):
+ * barqkv_upload is cudaMemcpyAsync host->device on `stream` (src should be pinned memory that stays
+ * untouched until the copy has run); barqkv_table_scatter writes n changed entries into the device
+ * table, pairs[2i] = flat index row*table_stride + column, pairs[2i+1] = page id (device int32[2n]).
+ * A step's description and its table changes travel in one upload, however large the table is.
+ */
+int barqkv_upload(void* dst_device, const void* src_host, int64_t bytes, barqkv_stream_t stream);
+int barqkv_table_scatter(int32_t* table, int64_t table_words, const int32_t* pairs, int32_t n, barqkv_stream_t stream);
+
+/*
  * Copy whole pages inside the pools: page src_pages[i] -> dst_pages[i] for every head, K and V, and
  * `layers` layers (pool_layer_stride elements apart).
  * Replaces: the physical row copies of batch_repeat_interleave / batch_select_indices

@@ -351,11 +351,11 @@ def test_all_layers_in_one_launch_equals_per_layer_appends(backend):
         wide_k = S.randn(g, (L, total, H + 1, D), dtype).to(DEV)      # rows are a strided slice of a wider tensor
         wide_v = S.randn(g, (L, total, H + 1, D), dtype).to(DEV)
         k_all, v_all = wide_k[:, :, :H], wide_v[:, :, :H]
-        before = backend.launches
         b1 = one.begin_append(s1, counts)
+        before = backend.launches
         one.append_layers(b1, k_all, v_all)
-        one.end_append(b1)
         assert backend.launches - before == 1
+        one.end_append(b1)
         many.append_step(s2, counts, list(k_all.unbind(0)), list(v_all.unbind(0)))
         assert torch.equal(S.bits_dev(one.pools), S.bits_dev(many.pools))
     # the same rows for every layer (layer stride 0)
@@ -400,7 +400,9 @@ def test_decode_step_graph_replays_what_eager_steps_compute(backend, H):
         steps.v_in.copy_(v)
         before = backend.launches
         total = steps.step()
-        assert backend.launches - before == (L if i < 2 else 0)      # a replay makes no library call
+        # eager steps launch one kernel per layer, a replay makes no launch through the library; either may
+        # be preceded by the small kernel that patches changed block-table entries
+        assert backend.launches - before in ((L, L + 1) if i < 2 else (0, 1))
         assert i < 2 or steps.launches_per_replay == L
         slow.append_step(ss, [1] * B, list(k.unbind(0)), list(v.unbind(0)))
         gb = slow.begin_gather(ss)
