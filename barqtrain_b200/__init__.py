@@ -17,9 +17,11 @@ from .kv_cache import (
     paged_kv_supported_for_model,
 )
 from .block_table import BlockTableKVCache, DecodeStepGraph, PageAllocator, PagePoolExhausted, PoolStats
+from .hf_block_cache import BarqBlockTableCache, use_paged_attention
 from ._ffi import load_cuda_backend
 
 __all__ = [
+    "BarqBlockTableCache",
     "BarqPagedKVCache",
     "BarqPagedKVCacheLayer",
     "BlockTableKVCache",
@@ -34,5 +36,6 @@ __all__ = [
     "load_cuda_backend",
     "maybe_prepare_paged_kv_generate_kwargs",
     "paged_kv_supported_for_model",
+    "use_paged_attention",
     "__version__",
 ]

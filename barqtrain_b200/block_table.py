@@ -534,9 +534,9 @@ class BlockTableKVCache:
         if rc:
             self.backend._check(rc)
 
-    def _rows_ref(self, seq_stride: int, tok_stride: int, head_stride: int):
-        """A cached ctypes reference to a packed ``barqkv_rows_layout``."""
-        layout = _ffi.RowsLayout(seq_stride, tok_stride, head_stride, 1, 0)
+    def _rows_ref(self, seq_stride: int, tok_stride: int, head_stride: int, packed: int = 1):
+        """A cached ctypes reference to a ``barqkv_rows_layout`` (packed unless told otherwise)."""
+        layout = _ffi.RowsLayout(seq_stride, tok_stride, head_stride, packed, 0)
         self._keep = getattr(self, "_keep", [])
         self._keep.append(layout)               # byref() does not own the structure
         return ctypes.byref(layout)
@@ -558,7 +558,7 @@ class BlockTableKVCache:
         self._flush_table()
         return self._describe("gather", slots, lens, lens)
 
-    def _output(self, layout: str, total: int, out):
+    def _output(self, layout: str, total: int, out, n: int = 0):
         """Output buffers, their row addressing and the views holding exactly ``total`` tokens.
 
         ``out`` may be larger than needed along the token dimension (``[H, cap, D]`` or
@@ -567,8 +567,10 @@ class BlockTableKVCache:
         stride of the call constant from step to step, which a recorded CUDA graph needs.
         """
         H, D = self.num_kv_heads, self.head_dim
+        if layout == "BHSD":
+            return self._output_padded(total, out, n)
         if layout not in ("HND", "NHD"):
-            raise ValueError("layout must be 'HND' or 'NHD'")
+            raise ValueError("layout must be 'HND', 'NHD' or 'BHSD'")
         if out is None:
             shape = (H, total, D) if layout == "HND" else (total, H, D)
             out = (torch.empty(shape, dtype=self.dtype, device=self.device),
@@ -599,6 +601,26 @@ class BlockTableKVCache:
             views = (k_out, v_out)
         return k_out, v_out, rows_ref, views
 
+    def _output_padded(self, total: int, out, n: int = 0):
+        """``[n, H, S, D]`` batch-major outputs (what Hugging Face attention takes): sequence ``i`` fills
+        ``[i, :, :len_i]``; rows beyond a sequence's length are left as they are."""
+        H, D = self.num_kv_heads, self.head_dim
+        if out is None:
+            raise ValueError("layout 'BHSD' needs out tensors [n, H, S, D] (S = longest sequence or more)")
+        k_out, v_out = out
+        shape = k_out.shape
+        ok = (len(shape) == 4 and shape[0] >= n and shape[1] == H and shape[3] == D and v_out.shape == shape
+              and k_out.is_contiguous() and v_out.is_contiguous() and k_out.dtype == self.dtype
+              and v_out.dtype == self.dtype and k_out.device == self.device and v_out.device == self.device)
+        if not ok:
+            raise ValueError("out tensors must be contiguous [n, H, S, D] in the cache dtype on the cache device")
+        S = shape[2]
+        key = ("BHSD", S)
+        rows_ref = self._rows.get(key)
+        if rows_ref is None:
+            rows_ref = self._rows[key] = self._rows_ref(H * S * D, D, S * D, packed=0)
+        return k_out, v_out, rows_ref, (k_out, v_out)
+
     def gather(self, layer: int, batch: _Descriptor, layout: str = "HND",
                out: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
                mode: Optional[str] = None) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -611,7 +633,7 @@ class BlockTableKVCache:
         larger fixed-capacity buffers (see ``_output``); views of the filled part are returned.
         """
         total = batch.total
-        k_out, v_out, rows_ref, views = self._output(layout, total, out)
+        k_out, v_out, rows_ref, views = self._output(layout, total, out, batch.n)
         if total == 0:
             return views
         rc = self._c_gather(self._pool_ref, self._k_ptr[layer], self._v_ptr[layer], batch.table_ref,
@@ -636,7 +658,7 @@ class BlockTableKVCache:
         if full.slots != new.slots:
             raise ValueError("update: the append and gather descriptions must list the same slots")
         total, H, D = full.total, self.num_kv_heads, self.head_dim
-        k_out, v_out, out_ref, views = self._output(layout, total, out)
+        k_out, v_out, out_ref, views = self._output(layout, total, out, full.n)
         if new.total:
             nshape = k_new.shape
             if nshape != v_new.shape or len(nshape) != 3 or nshape[0] != new.total or nshape[1] != H or nshape[2] != D:

@@ -52,3 +52,68 @@ def test_generate_with_paged_cache_matches_dynamic_cache(monkeypatch):
         short = model.generate(ids, max_new_tokens=4, do_sample=False)
     assert model._barqtrain_last_generate_used_paged_kv is False and short.shape == (2, 41)
     assert isinstance(cache, BarqPagedKVCache) and backend.read_status("cuda") == 0
+
+
+def _llama_128():
+    from transformers import LlamaConfig, LlamaForCausalLM
+
+    torch.manual_seed(1)
+    cfg = LlamaConfig(vocab_size=199, hidden_size=512, intermediate_size=512, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, head_dim=128, max_position_embeddings=512,
+                      pad_token_id=0, bos_token_id=1, eos_token_id=None)
+    return LlamaForCausalLM(cfg).to("cuda", torch.bfloat16).eval()
+
+
+@pytest.mark.parametrize("from_pages", [False, True])
+def test_block_table_cache_under_generate(from_pages):
+    """The block-table cache as a ``transformers`` cache: prefill + decode logits must match the stock
+    dynamic cache - exactly when attention runs on the gathered tensors (same values, same SDPA call),
+    within bf16 attention tolerance when decode attention reads the pages directly."""
+    from transformers import DynamicCache
+
+    from barqtrain_b200 import _ffi
+    from barqtrain_b200.hf_block_cache import BarqBlockTableCache, use_paged_attention
+
+    backend = _ffi.require_cuda_backend()
+    model = _llama_128()
+    g = torch.Generator().manual_seed(9)
+    ids = torch.randint(2, 199, (3, 45), generator=g).to("cuda")
+    steps = 20
+
+    def run(cache):
+        logits = []
+        with torch.no_grad():
+            out = model(ids, past_key_values=cache, use_cache=True)
+            logits.append(out.logits[:, -1].float())
+            tok = out.logits[:, -1].argmax(-1, keepdim=True)
+            fed = [tok]
+            for _ in range(steps):
+                out = model(fed[-1], past_key_values=cache, use_cache=True)
+                logits.append(out.logits[:, -1].float())
+                fed.append(forced[len(fed)] if forced is not None else out.logits[:, -1].argmax(-1, keepdim=True))
+        return logits, fed
+
+    forced = None
+    want, fed = run(DynamicCache(config=model.config))
+    forced = fed                                        # feed the same tokens so the runs stay comparable
+    if from_pages:
+        use_paged_attention(model)
+    launches = backend.launches
+    cache = BarqBlockTableCache(model.config, max_batch_size=3, max_cache_len=45 + steps + 1, page_size=16,
+                                attention_from_pages=from_pages)
+    got, _ = run(cache)
+    assert backend.launches > launches
+    assert cache.get_seq_length() == 45 + steps
+    assert cache.store.stats().pages_resident == 3 * -(-(45 + steps) // 16)
+    for i, (a, b) in enumerate(zip(got, want)):
+        if from_pages:
+            assert torch.allclose(a, b, atol=6e-2, rtol=5e-2), (i, (a - b).abs().max().item())
+        else:
+            assert torch.equal(a, b), (i, (a - b).abs().max().item())
+    # generate() end to end runs on it as well
+    with torch.no_grad():
+        out = model.generate(ids, max_new_tokens=8, do_sample=False,
+                             past_key_values=BarqBlockTableCache(model.config, 3, 45 + 8, 16, from_pages), use_cache=True)
+    assert out.shape == (3, 53)
+    model.config._attn_implementation = "sdpa"
+    assert backend.read_status("cuda") == 0
