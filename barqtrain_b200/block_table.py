@@ -348,6 +348,9 @@ class BlockTableKVCache:
     def _stage(self, words: int):
         """A pinned int32 staging buffer nobody is reading any more: (numpy view, host address)."""
         if words > self._ring_words:
+            for _, event in self._ring:            # copies out of the old buffers must have run before they go
+                if event is not None:
+                    event.synchronize()
             self._ring_words = max(2 * words, 1 << 16)
             self._ring = [(torch.empty(self._ring_words, dtype=torch.int32).pin_memory(), None) for _ in range(8)]
             self._ring_np = [buf.numpy() for buf, _ in self._ring]
