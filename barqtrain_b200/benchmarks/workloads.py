@@ -130,7 +130,8 @@ def gather_70b(world: int, rank: int, device, steps: int, warmup: int, layers: i
                        "l2": "inputs larger than L2: %.2f GB per launch" % (4 * total * H * D * 2 / 1e9)}}
 
 
-def churn(world: int, rank: int, device, steps: int, warmup: int, layers: int = 32, sync=lambda: None) -> Dict:
+def churn(world: int, rank: int, device, steps: int, warmup: int, layers: int = 32, verify: bool = False,
+          sync=lambda: None) -> Dict:
     """Continuous batching: 32 layers, 8 KV heads, head_dim 128, fp16, page 16; 256 live sequences with
     initial lengths uniform in [128, 2048]; every step appends one token to every live sequence in every
     layer, then each sequence finishes with seeded probability 0.01, returns its pages to the free list
@@ -152,8 +153,14 @@ def churn(world: int, rank: int, device, steps: int, warmup: int, layers: int = 
     slots = [cache.open(i) for i in ids]
     next_id = live
     # set-up: initial contents, in slices so that the packed source stays small
+    origin = [None] * live            # per live sequence: (first row, count) of its prefill in `rows`
+    decoded = [0] * live              # decode tokens appended since (each is rows[j])
     for lo in range(0, live, 8):
         part, counts = slots[lo:lo + 8], lens0[lo:lo + 8]
+        at = 0
+        for j, c in zip(range(lo, lo + 8), counts):
+            origin[j] = (at, c)
+            at += c
         batch = cache.begin_append(part, counts)
         for layer in range(layers):
             cache.append(layer, batch, rows[: sum(counts)], rows[: sum(counts)])
@@ -171,6 +178,8 @@ def churn(world: int, rank: int, device, steps: int, warmup: int, layers: int = 
         cache.end_append(batch)
         counters["tokens"] += live
         counters["launches"] += 1
+        for j in range(live):
+            decoded[j] += 1
         gone = [j for j in range(live) if finished[i][j]]
         if gone:
             t0 = time.perf_counter()
@@ -180,6 +189,7 @@ def churn(world: int, rank: int, device, steps: int, warmup: int, layers: int = 
                 ids[j] = next_id
                 next_id += 1
                 slots[j] = cache.open(ids[j])
+                origin[j], decoded[j] = (512 * len(fresh), 512), 0
                 fresh.append(slots[j])
             batch = cache.begin_append(fresh, [512] * len(fresh))
             counters["host_s"] += time.perf_counter() - t0
@@ -203,8 +213,22 @@ def churn(world: int, rank: int, device, steps: int, warmup: int, layers: int = 
     sync()
     ms = e0.elapsed_time(e1)
     cache.check_device_status()
+    verified = None
+    if verify:
+        # every live sequence must read back as its prefill rows followed by its decode rows, in both K and V
+        verified = True
+        gb = cache.begin_gather(slots)
+        for layer in sorted({0, layers - 1}):
+            kn, vn = cache.gather(layer, gb, "NHD")
+            for j in range(live):
+                first, count = origin[j]
+                want = torch.cat([rows[first:first + count], rows[j:j + 1].expand(decoded[j], -1, -1)])
+                a, b = gb.cu[j], gb.cu[j + 1]
+                if b - a != count + decoded[j] or not torch.equal(kn[a:b], want) or not torch.equal(vn[a:b], want):
+                    verified = False
     st = cache.stats()
     return {"bytes": 4 * counters["tokens"] * H * D * 2 * layers, "ms": ms, "tokens": counters["tokens"],
+            "verified": verified,
             "launches": counters["launches"],
             "config": {"workload": "continuous-batching-churn", "layers": layers, "kv_heads_per_gpu": H,
                        "dtype": "fp16", "page_size": 16, "live_sequences": live,

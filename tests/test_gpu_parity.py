@@ -723,3 +723,16 @@ def test_full_size_layer_against_c_oracle(backend, shape):
     assert torch.equal(S.bits(vh.transpose(0, 1)), S.bits(want_v))
     assert torch.equal(S.bits(cache.pools[0, 0]), S.bits(ref_k)) and torch.equal(S.bits(cache.pools[0, 1]), S.bits(ref_v))
     cache.check_device_status()
+
+
+def test_continuous_batching_churn_at_full_width_reads_back_exactly(backend):
+    """The churn configuration at full width (256 live sequences, 8 heads, head_dim 128, fp16, page 16;
+    two layers, 150 steps, about 380 sequences finished, released and replaced): after all the page
+    recycling every live sequence must gather to exactly the rows that were appended to it."""
+    from barqtrain_b200.benchmarks.workloads import churn
+
+    res = churn(1, 0, torch.device("cuda", 0), steps=150, warmup=2, layers=2, verify=True,
+                sync=lambda: torch.cuda.synchronize())
+    assert res["verified"] is True
+    assert res["extra"]["sequences_released"] > 200
+    assert res["extra"]["pages_peak"] >= res["extra"]["pages_resident"] > 0
