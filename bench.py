@@ -594,6 +594,21 @@ def run_micro(args):
                 for _ in range(args.reps):
                     cache.append(0, batch, k, v)
             return launch, args.reps, total * per_tok * args.reps
+        if args.micro == "append-layers":
+            # one decode token per sequence for `layers` layers in ONE launch (pools of all layers are one tensor)
+            many = BlockTableKVCache(args.layers, H, D, page_size=ps, num_pages=sum(-(-(n + 64) // ps) for n in lens),
+                                     max_seqs=B, max_blocks_per_seq=-(-(max(lens) + 64) // ps), dtype=dtype,
+                                     device=device, seed=5, zero_pages=False)
+            mslots = [many.open(i) for i in range(B)]
+            fill = many.begin_append(mslots, lens)          # lengths only: the decode rows land after them
+            many.end_append(fill)
+            k_all = torch.randn(args.layers, B, H, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
+            batch = many.begin_append(mslots, [1] * B)
+
+            def launch():
+                for _ in range(args.reps):
+                    many.append_layers(batch, k_all, k_all)
+            return launch, args.reps, B * per_tok * args.layers * args.reps
         # append-decode: `layers` back-to-back single-token appends form one timed group
         k = torch.randn(B, H, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
         if cache.lengths[slots[0]] == 0:
@@ -729,7 +744,7 @@ def main():
                     help="call update() per layer from Python every step instead of replaying a CUDA graph")
     ap.add_argument("--two-launches", action="store_true",
                     help="per layer call append() then gather() instead of the single update() launch")
-    ap.add_argument("--micro", choices=["gather", "update", "attention", "append-prefill", "append-decode"],
+    ap.add_argument("--micro", choices=["gather", "update", "attention", "append-prefill", "append-decode", "append-layers"],
                     help="time one kernel alone on a one-layer case instead of the full step")
     ap.add_argument("--mode", default="auto", choices=["auto", "vector", "bulk"])
     ap.add_argument("--layout", default="HND", choices=["HND", "NHD"])
