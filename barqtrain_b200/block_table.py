@@ -480,9 +480,13 @@ class BlockTableKVCache:
         self._flush_table()
         return self._describe("append", slots, first, counts)
 
-    def append(self, layer: int, batch: _Descriptor, k_new: torch.Tensor, v_new: torch.Tensor) -> None:
+    def append(self, layer: int, batch: _Descriptor, k_new: torch.Tensor, v_new: torch.Tensor,
+               rope: Optional[Tuple[torch.Tensor, torch.Tensor]] = None) -> None:
         """Scatter packed new rows ``[total_tokens, kv_heads, head_dim]`` (any strides with a
-        contiguous last dimension; ``[H, T, D].transpose(0, 1)`` works) into the layer's pages."""
+        contiguous last dimension; ``[H, T, D].transpose(0, 1)`` works) into the layer's pages.
+
+        ``rope=(cos, sin)``, each ``[total_tokens, head_dim]`` in the cache dtype: the K rows are stored as
+        ``k * cos + rotate_half(k) * sin`` (bit-identical to rotating first), saving that separate pass."""
         total = batch.total
         if total == 0:
             return
@@ -503,6 +507,24 @@ class BlockTableKVCache:
         rows_ref = self._rows.get(strides)
         if rows_ref is None:
             rows_ref = self._rows[strides] = self._rows_ref(0, strides[0], strides[1])
+        if rope is not None:
+            cos, sin = rope
+            want = (total, self.head_dim)
+            if cos.shape != want or sin.shape != want or cos.dtype != self.dtype or sin.dtype != self.dtype \
+                    or cos.device != self.device or sin.device != self.device:
+                raise ValueError(f"rope cos and sin must be {want} in the cache dtype on the cache device")
+            if cos.stride(1) != 1 or sin.stride() != cos.stride():
+                cos, sin = cos.contiguous(), sin.contiguous()
+            code = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}.get(self.dtype)
+            if code is None:
+                raise ValueError("rope needs a bf16, fp16 or fp32 cache")
+            rc = self.backend.lib.barqkv_append_rope(
+                self._pool_ref, self._k_ptr[layer], self._v_ptr[layer], batch.table_ref, batch.p_first, batch.p_cu,
+                batch.n, 0, total, k_new.data_ptr(), v_new.data_ptr(), rows_ref, cos.data_ptr(), sin.data_ptr(),
+                cos.stride(0), code, self._status_ptr, batch.stream)
+            if rc:
+                self.backend._check(rc)
+            return
         rc = self._c_append(self._pool_ref, self._k_ptr[layer], self._v_ptr[layer], batch.table_ref,
                             batch.p_first, batch.p_cu, batch.n, 0, total, k_new.data_ptr(), v_new.data_ptr(),
                             rows_ref, self._status_ptr, batch.stream)

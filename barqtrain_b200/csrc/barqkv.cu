@@ -173,6 +173,30 @@ __device__ __forceinline__ long long resolve_page(const Table& tb, int i, int j,
     return page;
 }
 
+// Where new token r of the call (flat index over the batch) goes and where its rows come from:
+// *dst = byte offset of its slot in head 0's pool (-1 = skip), *src = byte offset of its head-0 row.
+__device__ __forceinline__ void resolve_new_token(const AppendArgs& a, int r, long long* dst, long long* src) {
+    int i, t;
+    if (a.cu_new) {
+        int lo = 0, hi = a.n - 1;             // largest i with cu_new[i] <= r
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (a.cu_new[mid] <= r) lo = mid; else hi = mid - 1;
+        }
+        i = lo;
+        t = r - a.cu_new[i];
+    } else {
+        i = r / a.tokens_per_entry;
+        t = r - i * a.tokens_per_entry;
+    }
+    const int pos = a.seq_start[i] + t;
+    const int j = pos / a.page_size;
+    const int slot = pos - j * a.page_size;
+    const long long page = pos < 0 ? -1 : resolve_page(a.tb, i, j, a.status);
+    *dst = page < 0 ? -1 : page * a.pool_page + (long long)slot * a.row_bytes;
+    *src = (long long)i * a.nr.seq + (long long)(a.nr.packed ? r : t) * a.nr.tok;
+}
+
 // --------------------------------------------------------------------------
 // append
 // --------------------------------------------------------------------------
@@ -204,28 +228,7 @@ append_rows_kernel(const AppendArgs a) {
         refuse = s_flag != 0;
     }
 
-    if (tid < ntok && !refuse) {
-        const int r = first_tok + tid;
-        int i, t;
-        if (a.cu_new) {
-            int lo = 0, hi = a.n - 1;             // largest i with cu_new[i] <= r
-            while (lo < hi) {
-                const int mid = (lo + hi + 1) >> 1;
-                if (a.cu_new[mid] <= r) lo = mid; else hi = mid - 1;
-            }
-            i = lo;
-            t = r - a.cu_new[i];
-        } else {
-            i = r / a.tokens_per_entry;
-            t = r - i * a.tokens_per_entry;
-        }
-        const int pos = a.seq_start[i] + t;
-        const int j = pos / a.page_size;
-        const int slot = pos - j * a.page_size;
-        const long long page = pos < 0 ? -1 : resolve_page(a.tb, i, j, a.status);
-        s_dst[tid] = page < 0 ? -1 : page * a.pool_page + (long long)slot * a.row_bytes;
-        s_src[tid] = (long long)i * a.nr.seq + (long long)(a.nr.packed ? r : t) * a.nr.tok;
-    }
+    if (tid < ntok && !refuse) resolve_new_token(a, first_tok + tid, &s_dst[tid], &s_src[tid]);
     __syncthreads();
 
     if (!refuse) {
@@ -281,6 +284,99 @@ append_rows_kernel(const AppendArgs a) {
             }
             if (tid == 0) *a.ticket = 0;
         }
+    }
+}
+
+// --------------------------------------------------------------------------
+// append with rotary position embedding applied to the K rows on the way in
+// --------------------------------------------------------------------------
+// k_out[d]        = k[d]        * cos[d]        - k[d + D/2] * sin[d]
+// k_out[d + D/2]  = k[d + D/2]  * cos[d + D/2]  + k[d]       * sin[d + D/2]      (d < D/2)
+// i.e. k * cos + rotate_half(k) * sin with the halves convention of the reference's helper
+// (python/barqtrain/ops.py:376-428) and of Hugging Face models.  Each product and the sum are rounded
+// to the element type one by one, exactly as the unfused tensor expression rounds them, so the stored
+// rows are bit-identical to "rotate first, append after".  V rows are copied unchanged.
+template <typename T> struct RopeMath;
+template <> struct RopeMath<float> {
+    static __device__ __forceinline__ float rot(float a, float ca, float b, float sb, bool minus) {
+        const float p = __fmul_rn(a, ca), q = __fmul_rn(b, sb);
+        return minus ? __fsub_rn(p, q) : __fadd_rn(p, q);
+    }
+};
+template <> struct RopeMath<__nv_bfloat16> {
+    static __device__ __forceinline__ __nv_bfloat16 rot(__nv_bfloat16 a, __nv_bfloat16 ca, __nv_bfloat16 b,
+                                                       __nv_bfloat16 sb, bool minus) {
+        const float p = __bfloat162float(__float2bfloat16_rn(__fmul_rn(__bfloat162float(a), __bfloat162float(ca))));
+        const float q = __bfloat162float(__float2bfloat16_rn(__fmul_rn(__bfloat162float(b), __bfloat162float(sb))));
+        return __float2bfloat16_rn(minus ? __fsub_rn(p, q) : __fadd_rn(p, q));
+    }
+};
+template <> struct RopeMath<__half> {
+    static __device__ __forceinline__ __half rot(__half a, __half ca, __half b, __half sb, bool minus) {
+        const float p = __half2float(__float2half_rn(__fmul_rn(__half2float(a), __half2float(ca))));
+        const float q = __half2float(__float2half_rn(__fmul_rn(__half2float(b), __half2float(sb))));
+        return __float2half_rn(minus ? __fsub_rn(p, q) : __fadd_rn(p, q));
+    }
+};
+
+struct RopeArgs {
+    const unsigned char* cos;    // [total_tokens][head_dim] in the element type, row r for new token r
+    const unsigned char* sin;
+    long long tok;               // byte stride between token rows of cos / sin
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kAppendThreads)
+append_rope_kernel(const AppendArgs a, const RopeArgs rp) {
+    constexpr int E = 16 / (int)sizeof(T);            // elements per 16-byte vector
+    __shared__ long long s_dst[kAppendMaxTile];
+    __shared__ long long s_src[kAppendMaxTile];
+    const int tid = threadIdx.x;
+    const int first_tok = blockIdx.x * a.tile;
+    const int ntok = min(a.tile, a.total_tokens - first_tok);
+    pdl_let_successor_in();
+    pdl_wait_for_predecessor();
+    if (tid < ntok) resolve_new_token(a, first_tok + tid, &s_dst[tid], &s_src[tid]);
+    __syncthreads();
+
+    const int vpr = a.row_bytes / 16;                 // vectors per row
+    const int half = vpr / 2;                         // vectors per half row
+    // per token and head: `half` K items (two vectors each) and `vpr` V items (one vector each)
+    const int per_head = half + vpr;
+    const int per_tok = a.heads * per_head;
+    const int items = ntok * per_tok;
+    for (int idx = tid; idx < items; idx += blockDim.x) {
+        const int t = idx / per_tok;
+        const int rem = idx - t * per_tok;
+        const int h = rem / per_head;
+        const int w = rem - h * per_head;
+        const long long d = s_dst[t];
+        if (d < 0) continue;
+        if (w >= half) {                               // V: plain copy of vector w - half
+            const int vec = w - half;
+            const uint4 x = __ldcs(reinterpret_cast<const uint4*>(a.v_new + s_src[t] + h * a.nr.head) + vec);
+            reinterpret_cast<uint4*>(a.v_pool + d + h * a.pool_head)[vec] = x;
+            continue;
+        }
+        const uint4* krow = reinterpret_cast<const uint4*>(a.k_new + s_src[t] + h * a.nr.head);
+        const uint4* crow = reinterpret_cast<const uint4*>(rp.cos + (long long)(first_tok + t) * rp.tok);
+        const uint4* srow = reinterpret_cast<const uint4*>(rp.sin + (long long)(first_tok + t) * rp.tok);
+        union Pack { uint4 v; T e[E]; };
+        Pack lo, hi, clo, chi, slo, shi, olo, ohi;
+        lo.v = __ldcs(krow + w);
+        hi.v = __ldcs(krow + w + half);
+        clo.v = __ldg(crow + w);
+        chi.v = __ldg(crow + w + half);
+        slo.v = __ldg(srow + w);
+        shi.v = __ldg(srow + w + half);
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+            olo.e[e] = RopeMath<T>::rot(lo.e[e], clo.e[e], hi.e[e], slo.e[e], true);
+            ohi.e[e] = RopeMath<T>::rot(hi.e[e], chi.e[e], lo.e[e], shi.e[e], false);
+        }
+        uint4* out = reinterpret_cast<uint4*>(a.k_pool + d + h * a.pool_head);
+        out[w] = olo.v;
+        out[w + half] = ohi.v;
     }
 }
 
@@ -1023,6 +1119,75 @@ int barqkv_append_layers(const barqkv_pool_layout* pool, void* k_pool, void* v_p
                          int64_t new_layer_stride, int32_t* status, barqkv_stream_t stream) {
     return append_common(pool, k_pool, v_pool, table, seq_start, cu_new, n, tokens_per_entry, total_tokens, k_new, v_new,
                          new_rows, status, stream, layers, pool_layer_stride, new_layer_stride);
+}
+
+int barqkv_append_rope(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,
+                       const barqkv_block_table* table,
+                       const int32_t* seq_start, const int32_t* cu_new,
+                       int32_t n, int32_t tokens_per_entry, int32_t total_tokens,
+                       const void* k_new, const void* v_new, const barqkv_rows_layout* new_rows,
+                       const void* cos, const void* sin, int64_t rope_tok_stride, int32_t dtype,
+                       int32_t* status, barqkv_stream_t stream) {
+    if (int rc = check_pool(pool)) return rc;
+    if (n < 0 || total_tokens < 0) return fail(BARQKV_E_INVALID, "append_rope: negative batch size or token count");
+    if (n == 0 || total_tokens == 0) return 0;
+    if (int rc = check_table(table, n)) return rc;
+    if (!k_pool || !v_pool || !k_new || !v_new || !seq_start || !new_rows || !cos || !sin)
+        return fail(BARQKV_E_INVALID, "append_rope: null pointer argument");
+    if (!cu_new && (tokens_per_entry <= 0 || (long long)tokens_per_entry * n != total_tokens))
+        return fail(BARQKV_E_INVALID, "append_rope: without cu_new, total_tokens must equal n * tokens_per_entry");
+    if (new_rows->packed && !cu_new && tokens_per_entry != 1)
+        return fail(BARQKV_E_INVALID, "append_rope: packed rows with more than one token per entry need cu_new");
+    const int want_bytes = dtype == BARQKV_DTYPE_F32 ? 4 : 2;
+    if (dtype < BARQKV_DTYPE_BF16 || dtype > BARQKV_DTYPE_F32 || pool->elem_bytes != want_bytes)
+        return fail(BARQKV_E_INVALID, "append_rope: dtype must be bf16, fp16 or fp32 and match elem_bytes");
+    DeviceInfo* d = device_info();
+    if (!d) return fail(BARQKV_E_LAUNCH, "no CUDA device is current");
+
+    const long long e = pool->elem_bytes;
+    AppendArgs a;
+    memset(&a, 0, sizeof(a));
+    a.k_pool = static_cast<unsigned char*>(k_pool);
+    a.v_pool = static_cast<unsigned char*>(v_pool);
+    a.k_new = static_cast<const unsigned char*>(k_new);
+    a.v_new = static_cast<const unsigned char*>(v_new);
+    a.tb = make_table(table, pool->num_pages);
+    a.seq_start = seq_start;
+    a.cu_new = cu_new;
+    a.n = n;
+    a.tokens_per_entry = tokens_per_entry;
+    a.total_tokens = total_tokens;
+    a.heads = pool->num_heads;
+    a.page_size = pool->page_size;
+    a.row_bytes = (int)(pool->head_dim * e);
+    a.pool_head = pool->head_stride * e;
+    a.pool_page = pool->page_stride * e;
+    a.nr.seq = new_rows->seq_stride * e;
+    a.nr.tok = new_rows->tok_stride * e;
+    a.nr.head = new_rows->head_stride * e;
+    a.nr.packed = new_rows->packed;
+    a.status = status;
+    RopeArgs rp;
+    rp.cos = static_cast<const unsigned char*>(cos);
+    rp.sin = static_cast<const unsigned char*>(sin);
+    rp.tok = rope_tok_stride * e;
+    const int vec = vector_bytes(a.row_bytes, {a.pool_head, a.pool_page, a.nr.seq, a.nr.tok, a.nr.head, rp.tok},
+                                 {k_pool, v_pool, k_new, v_new, cos, sin});
+    if (vec != 16 || (a.row_bytes / 16) % 2)
+        return fail(BARQKV_E_INVALID, "append_rope: rows, strides and pointers must be 16-byte aligned and a half row "
+                                      "a whole number of 16-byte vectors");
+    int threads;
+    append_shape(d, total_tokens, a.heads, a.row_bytes, 16, &a.tile, &threads);
+    const int grid = (total_tokens + a.tile - 1) / a.tile;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    switch (dtype) {
+        case BARQKV_DTYPE_BF16: append_rope_kernel<__nv_bfloat16><<<grid, kAppendThreads, 0, st>>>(a, rp); break;
+        case BARQKV_DTYPE_F16: append_rope_kernel<__half><<<grid, kAppendThreads, 0, st>>>(a, rp); break;
+        default: append_rope_kernel<float><<<grid, kAppendThreads, 0, st>>>(a, rp); break;
+    }
+    const cudaError_t ce = cudaGetLastError();
+    if (ce == cudaSuccess) g_launches.fetch_add(1, std::memory_order_relaxed);
+    return ce == cudaSuccess ? 0 : fail_cuda("append_rope launch", ce);
 }
 
 int barqkv_upload(void* dst_device, const void* src_host, int64_t bytes, barqkv_stream_t stream) {

@@ -181,6 +181,27 @@ int barqkv_copy_pages(const barqkv_pool_layout* pool, void* k_pool, void* v_pool
                       int32_t* status, barqkv_stream_t stream);
 
 /*
+ * barqkv_append with rotary position embedding applied to the K rows on the way into the pages:
+ *   k_out = k * cos + rotate_half(k) * sin      (halves convention: rotate_half(x) = [-x2, x1])
+ * the formula of the reference's helper apply_rope_to_qk (python/barqtrain/ops.py:376-428) and of
+ * Hugging Face models, with cos / sin given per new token: [total_tokens, head_dim] in the pool's element
+ * type (dtype), rope_tok_stride elements apart, row r for packed new token r.  Products and sum are
+ * rounded to the element type one at a time, so the stored rows equal "rotate, then append" bit for bit;
+ * V rows are copied unchanged.  Saves the separate read and write of the new K rows.
+ * Needs 16-byte aligned rows, strides and pointers and head_dim a multiple of 16 (2-byte) / 8 (4-byte).
+ */
+#define BARQKV_DTYPE_BF16 0
+#define BARQKV_DTYPE_F16 1
+#define BARQKV_DTYPE_F32 2
+int barqkv_append_rope(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,
+                       const barqkv_block_table* table,
+                       const int32_t* seq_start, const int32_t* cu_new,
+                       int32_t n, int32_t tokens_per_entry, int32_t total_tokens,
+                       const void* k_new, const void* v_new, const barqkv_rows_layout* new_rows,
+                       const void* cos, const void* sin, int64_t rope_tok_stride, int32_t dtype,
+                       int32_t* status, barqkv_stream_t stream);
+
+/*
  * The reference's native entry point, same semantics:
  *   void paged_kv_append_(key_cache, value_cache, seq_lens, key_states, value_states)
  *   csrc/src/bindings.cpp:43-49,74-75 -> paged_kv_append_cuda

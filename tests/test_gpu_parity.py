@@ -736,3 +736,43 @@ def test_continuous_batching_churn_at_full_width_reads_back_exactly(backend):
     assert res["verified"] is True
     assert res["extra"]["sequences_released"] > 200
     assert res["extra"]["pages_peak"] >= res["extra"]["pages_resident"] > 0
+
+
+@pytest.mark.parametrize("dtype,D", [(torch.bfloat16, 128), (torch.float16, 64), (torch.float32, 32)])
+def test_rope_fused_into_append_equals_rotate_then_append(backend, dtype, D):
+    """``append(..., rope=(cos, sin))`` stores ``k*cos + rotate_half(k)*sin`` - the reference helper's
+    formula (ops.py:376-428) with per-token tables - bit for bit what rotating with tensor expressions
+    in the same dtype and appending afterwards stores; V is untouched."""
+    from barqtrain_b200 import BlockTableKVCache
+
+    H, ps = 3, 16
+    g = torch.Generator().manual_seed(41)
+    order = torch.randperm(40, generator=g).tolist()
+
+    def make():
+        c = BlockTableKVCache(1, H, D, page_size=ps, num_pages=40, max_seqs=3, max_blocks_per_seq=12, dtype=dtype,
+                              device=DEV, free_order=order)
+        return c, [c.open(i) for i in range(3)]
+
+    fused, fs = make()
+    plain, pl = make()
+    lens = [0, 0, 0]
+    for counts in ((37, 5, 100), (1, 1, 1), (0, 20, 3)):
+        total = sum(counts)
+        k = S.randn(g, (total, H, D), dtype).to(DEV)
+        v = S.randn(g, (total, H, D), dtype).to(DEV)
+        pos = torch.cat([torch.arange(lens[i], lens[i] + c) for i, c in enumerate(counts)]).float()
+        freqs = 1.0 / torch.pow(10000.0, torch.arange(D // 2).float() / (D // 2))
+        ang = pos[:, None] * freqs[None, :]
+        cos = torch.cat([ang.cos(), ang.cos()], dim=-1).to(dtype).to(DEV)         # [total, D], halves duplicated
+        sin = torch.cat([ang.sin(), ang.sin()], dim=-1).to(dtype).to(DEV)
+        rotated = k * cos[:, None, :] + torch.cat([-k[..., D // 2:], k[..., :D // 2]], dim=-1) * sin[:, None, :]
+        b1 = fused.begin_append(fs, counts)
+        fused.append(0, b1, k, v, rope=(cos, sin))
+        fused.end_append(b1)
+        b2 = plain.begin_append(pl, counts)
+        plain.append(0, b2, rotated, v)
+        plain.end_append(b2)
+        lens = [n + c for n, c in zip(lens, counts)]
+        assert torch.equal(S.bits_dev(fused.pools), S.bits_dev(plain.pools))
+    fused.check_device_status()
