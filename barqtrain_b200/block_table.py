@@ -804,12 +804,57 @@ class DecodeStepGraph:
         self.steps = 0
         self.launches_per_replay = 0
         self.graph: Optional[torch.cuda.CUDAGraph] = None
+        # One device buffer holds both descriptions of a step at fixed addresses:
+        # [slots(n) | start(n) | cu_new(n+1) | lengths_after(n) | cu_out(n+1)], rewritten by one upload per step.
+        n = B
+        self._slots_np = np.asarray(self.slots, dtype=np.int64)
+        self._desc = torch.zeros(5 * n + 2, dtype=torch.int32, device=c.device)
+        self._table = _ffi.BlockTable(c.table_dev.data_ptr(), self._desc.data_ptr(), c.max_seqs, c.max_blocks, 0, 0)
+        base = self._desc.data_ptr()
+        ones_cu = list(range(n + 1))
+        with torch.cuda.stream(self.stream):
+            work = c.backend.work_words(c.device).data_ptr()
+        ref = ctypes.byref(self._table)
+        self._new = _Descriptor(n, self._desc, n, [0] * n, ones_cu, self.slots, ref, self.stream.cuda_stream, 0)
+        self._full = _Descriptor(n, self._desc, 0, [0] * n, [0] * (n + 1), self.slots, ref, self.stream.cuda_stream, work)
+        self._full.p_first = base + 4 * (3 * n + 1)
+        self._full.p_cu = base + 4 * (4 * n + 1)
 
-    def _launch_layers(self, new: _Descriptor, full: _Descriptor) -> None:
+    def _launch_layers(self) -> None:
         c = self.cache
         for layer in range(c.num_layers):
-            c.update(layer, new, full, self._k_rows[layer], self._v_rows[layer], "HND", out=self.bufs[layer & 1],
-                     mode=self.mode, tokens_hint=self.capacity)
+            c.update(layer, self._new, self._full, self._k_rows[layer], self._v_rows[layer], "HND",
+                     out=self.bufs[layer & 1], mode=self.mode, tokens_hint=self.capacity)
+
+    def _describe_step(self) -> int:
+        """Host side of a step: pages for the new tokens, new lengths, one upload of both descriptions."""
+        c, sl, n = self.cache, self._slots_np, len(self.slots)
+        first = c.lengths[sl]
+        after = first + 1
+        total = int(after.sum())
+        if total > self.capacity:
+            raise ValueError(f"decode graph capacity {self.capacity} tokens exceeded by {total}")
+        need = -(-after // c.page_size)
+        have = c._page_count[sl]
+        grow = np.nonzero(need > have)[0]
+        if grow.size:
+            c._reserve_many(sl[grow], have[grow], need[grow], after[grow])
+        c._flush_table()
+        c.lengths[sl] = after
+        words = 5 * n + 2
+        host, host_ptr = c._stage(words)
+        host[:n] = sl
+        host[n:2 * n] = first
+        host[2 * n:3 * n + 1] = np.arange(n + 1)
+        host[3 * n + 1:4 * n + 1] = after
+        host[4 * n + 1] = 0
+        np.cumsum(after, out=host[4 * n + 2:words])
+        rc = c.backend.lib.barqkv_upload(self._desc.data_ptr(), host_ptr, 4 * words, self.stream.cuda_stream)
+        if rc:
+            c.backend._check(rc)
+        c._stage_done(self.stream)
+        self._full.total = total
+        return total
 
     def step(self) -> int:
         """Append one token per sequence in every layer and gather; returns the total tokens gathered."""
@@ -817,17 +862,13 @@ class DecodeStepGraph:
         caller = torch.cuda.current_stream(c.device)
         self.stream.wait_stream(caller)
         with torch.cuda.stream(self.stream):
-            new = c.begin_append(self.slots, [1] * len(self.slots))
-            c.end_append(new)
-            full = c.begin_gather(self.slots)
-            if full.total > self.capacity:
-                raise ValueError(f"decode graph capacity {self.capacity} tokens exceeded by {full.total}")
+            total = self._describe_step()
             if self.graph is not None:
-                # the recorded launches read the descriptions uploaded just above: same buffers, new contents
+                # the recorded launches read the descriptions uploaded just above: same buffer, new contents
                 self.graph.replay()
             else:
-                self._launch_layers(new, full)                # eager; the first one also sets kernel attributes
-            self.total = full.total
+                self._launch_layers()                         # eager; the first one also sets kernel attributes
+            self.total = total
         self.steps += 1
         caller.wait_stream(self.stream)
         return self.total
@@ -840,15 +881,10 @@ class DecodeStepGraph:
             raise RuntimeError("run one eager step() before record(): the first launch sets kernel attributes")
         torch.cuda.synchronize(c.device)
         with torch.cuda.stream(self.stream):
-            # descriptions with the right shape (n and buffer addresses); their contents are rewritten every step
-            lens = c.lengths[np.asarray(self.slots, dtype=np.int64)]
-            new = c._describe("append", self.slots, lens, [1] * len(self.slots))
-            full = c._describe("gather", self.slots, lens, lens)
-            torch.cuda.synchronize(c.device)
             graph = torch.cuda.CUDAGraph()
             counted = c.backend.launches
             with torch.cuda.graph(graph, stream=self.stream):
-                self._launch_layers(new, full)
+                self._launch_layers()
             self.launches_per_replay = c.backend.launches - counted     # kernel nodes in the graph
         self.graph = graph
 
