@@ -241,4 +241,62 @@ def churn(world: int, rank: int, device, steps: int, warmup: int, layers: int = 
                       "host_allocator_us_per_step": round(counters["host_s"] * 1e6 / max(steps, 1), 1)}}
 
 
-WORKLOADS = {"prefill": chunked_prefill, "gather70b": gather_70b, "churn": churn}
+def decode_attention(world: int, rank: int, device, steps: int, warmup: int, layers: int = 32,
+                     sync=lambda: None) -> Dict:
+    """The decode configuration (32 layers, 8 KV heads x 4 query heads, head_dim 128, bf16, page 16, 64
+    sequences uniform [512, 4096]) with attention reading the pages directly: a step is, per layer, the
+    append of one token per sequence and one attention call over the pages - no gather.  Bytes counted:
+    K and V read once (2*sum_len*H*D*e per layer) plus the append's 4*B*H*D*e."""
+    _, H = kv_head_shard(8, world, rank)
+    group, B, dtype = 4, 64, torch.bfloat16
+    g = torch.Generator().manual_seed(1236)
+    lens = torch.randint(512, 4097, (B,), generator=g).tolist()
+    total_steps = steps + max(warmup, 1)
+    pages = sum(-(-(n + total_steps) // 16) for n in lens)
+    cache = BlockTableKVCache(layers, H, D, page_size=16, num_pages=pages, max_seqs=B,
+                              max_blocks_per_seq=-(-(max(lens) + total_steps) // 16), dtype=dtype, device=device,
+                              free_order=torch.randperm(pages, generator=g).tolist(), zero_pages=False)
+    slots = [cache.open(i) for i in range(B)]
+    gen = torch.Generator(device=device).manual_seed(1236 + rank)
+    k = torch.randn(sum(lens), H, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
+    batch = cache.begin_append(slots, lens)
+    for layer in range(layers):
+        cache.append(layer, batch, k, k)
+    cache.end_append(batch)
+    del k
+    new_rows = torch.randn(layers, B, H, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
+    q = torch.randn(B, H * group, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
+    out = torch.empty_like(q)
+    moved = {"bytes": 0}
+
+    def step():
+        new = cache.begin_append(slots, [1] * B)
+        cache.end_append(new)
+        full = cache.begin_gather(slots)
+        for layer in range(layers):
+            cache.append(layer, new, new_rows[layer], new_rows[layer])
+            cache.decode_attention(layer, full, q, out=out)
+        moved["bytes"] += (2 * full.total + 4 * B) * H * D * 2 * layers
+
+    for _ in range(max(warmup, 1)):
+        step()
+    sync()
+    moved["bytes"] = 0
+    e0, e1 = _events()
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    sync()
+    ms = e0.elapsed_time(e1)
+    cache.check_device_status()
+    return {"bytes": moved["bytes"], "ms": ms, "tokens": B * steps, "launches": 3 * layers * steps,
+            "config": {"workload": "llama3-8b-decode-attention-from-pages", "layers": layers, "kv_heads_per_gpu": H,
+                       "query_heads_per_kv_head": group, "dtype": "bf16", "page_size": 16, "sequences": B,
+                       "step": "per layer: append 1 token/seq, then attention over the pages (no gather); bytes = K and V "
+                               "read once + appended rows",
+                       "l2": "inputs larger than L2: each step reads ~%.1f GB of pool per GPU"
+                             % (2 * sum(lens) * H * D * 2 * layers / 1e9)}}
+
+
+WORKLOADS = {"prefill": chunked_prefill, "gather70b": gather_70b, "churn": churn, "decode-attn": decode_attention}

@@ -757,7 +757,7 @@ def main():
     ap.add_argument("--reps", type=int, default=1, help="micro gather/append-prefill: launches per timed sample")
     ap.add_argument("--graph", action="store_true", help="micro cases: time a CUDA-graph replay of the launches")
     ap.add_argument("--tune", default="", help="gather knobs, e.g. stages=8,ctas=3,interleave=1 (micro cases)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "gather70b", "churn"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "gather70b", "churn", "decode-attn"],
                     help="decode = the headline configuration; the others print the same line for their configuration")
     ap.add_argument("--all-layers", action="store_true",
                     help="--workload prefill: append a chunk to all layers with one launch (rows for all layers at hand)")
