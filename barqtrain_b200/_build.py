@@ -61,9 +61,17 @@ def build_native(force: bool = False, verbose: bool = False) -> Path:
     if not SOURCE.exists():
         raise RuntimeError(f"CUDA source missing: {SOURCE}")
     LIBRARY.parent.mkdir(parents=True, exist_ok=True)
-    proc = subprocess.run(nvcc_command(verbose_ptxas=verbose), capture_output=True, text=True)
-    if proc.returncode != 0:
-        raise RuntimeError("nvcc failed:\n" + proc.stdout + proc.stderr)
+    # Build beside the target and rename: several processes (one per GPU) may get here at once, and a
+    # reader must never open a half-written library.
+    scratch = LIBRARY.with_name(f"{LIBRARY.name}.{os.getpid()}.tmp")
+    try:
+        proc = subprocess.run(nvcc_command(output=scratch, verbose_ptxas=verbose), capture_output=True, text=True)
+        if proc.returncode != 0:
+            raise RuntimeError("nvcc failed:\n" + proc.stdout + proc.stderr)
+        os.replace(scratch, LIBRARY)
+    finally:
+        if scratch.exists():
+            scratch.unlink()
     if verbose:
         print(proc.stdout + proc.stderr)
     return LIBRARY
