@@ -732,7 +732,8 @@ class BlockTableKVCache:
         if full.n == 0:
             return out
         max_len = max(full.first)
-        need = int(self.backend.lib.barqkv_paged_decode_workspace_bytes(full.n, self.num_kv_heads, max_len))
+        need = int(self.backend.lib.barqkv_paged_decode_workspace_bytes(full.n, self.num_kv_heads, max_len,
+                                                                        self.page_size))
         if need > self._attn_ws_bytes:
             self._attn_ws = torch.empty(need, dtype=torch.uint8, device=self.device)
             self._attn_ws_bytes = need

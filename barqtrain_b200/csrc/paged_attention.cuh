@@ -13,15 +13,19 @@
 //                         ~6 warp instructions per token, the limit is reading 512 B per token and head.
 //   paged_decode_merge    combines the splits' partial (max, sum, output) triples.
 //
-// Restrictions (checked on the host): 2-byte elements (bf16 / fp16), head_dim 128, page_size 16,
+// Restrictions (checked on the host): 2-byte elements (bf16 / fp16), head_dim 128, page_size 16, 32 or 64,
 // group <= 8.  Every wait is bounded; a guard failure skips the sequence and sets a status bit.
 
 namespace {
 
-constexpr int kAttnStages = 4;
-constexpr int kAttnPageBytes = 16 * 128 * 2;          // one head's page of K (or V): 4 KiB
-constexpr int kAttnStageBytes = 2 * kAttnPageBytes;   // K + V
-constexpr int kAttnSplitPages = 32;                   // pages per split by default (512 tokens)
+constexpr int kAttnSplitTokens = 512;                 // tokens per split by default
+// Per page size: bytes of one head's page of K (or V), of a stage (K + V), and ring depth.
+template <int PS> struct AttnTile {
+    static constexpr int kHalf = PS * 128;            // one half tile: PS rows x 64 dims x 2 bytes
+    static constexpr int kPage = 2 * kHalf;
+    static constexpr int kStage = 2 * kPage;
+    static constexpr int kStages = PS <= 16 ? 4 : 3;
+};
 
 struct AttnArgs {
     Table tb;
@@ -31,7 +35,7 @@ struct AttnArgs {
     long long q_seq, q_head, o_seq, o_head;   // byte strides
     float* ws_o;                              // [n][kv_heads][splits][8][128] partial outputs
     float* ws_ml;                             // [n][kv_heads][splits][8][2]   (running max, running sum)
-    int n, kv_heads, group, split_pages, splits;
+    int n, kv_heads, group, split_pages, splits, page_size;
     float scale_log2;                         // softmax scale * log2(e)
     int32_t* status;
 };
@@ -79,16 +83,21 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-// Byte offset of 16-byte chunk `chunk` (0..7) of row `r` (0..15) inside one 2 KiB half tile
-// ([16 rows][128 B]) written by TMA with the 128-byte swizzle.
+// Byte offset of 16-byte chunk `chunk` (0..7) of row `r` inside one half tile ([page_size rows][128 B])
+// written by TMA with the 128-byte swizzle (the pattern repeats every 8 rows = 1024 bytes).
 __device__ __forceinline__ uint32_t swz(int r, int chunk) {
     return (uint32_t)(((r >> 3) << 10) + ((r & 7) << 7) + (((chunk ^ (r & 7)) & 7) << 4));
 }
 
-template <bool BF16>
+template <bool BF16, int PS>
 __global__ void __launch_bounds__(32)
 paged_decode_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v) {
     extern __shared__ unsigned char s_attn_raw[];
+    using Tile = AttnTile<PS>;
+    constexpr int kAttnStages = Tile::kStages;
+    constexpr int kAttnStageBytes = Tile::kStage;
+    constexpr int kAttnPageBytes = Tile::kPage;
+    constexpr int kHalf = Tile::kHalf;
     __shared__ unsigned long long s_bar[kAttnStages];
     // the 128-byte swizzle pattern repeats every 1024 bytes of shared-memory address: align the tiles to it
     unsigned char* s_attn = s_attn_raw + ((1024u - (smem_addr(s_attn_raw) & 1023u)) & 1023u);
@@ -98,7 +107,7 @@ paged_decode_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap map_k,
     pdl_let_successor_in();
     pdl_wait_for_predecessor();
     const int len = a.seq_lens[seq];
-    const int pages = (len + 15) >> 4;
+    const int pages = (len + PS - 1) / PS;
     const int p0 = split * a.split_pages;
     if (len <= 0 || p0 >= pages) return;
     const int p1 = min(pages, p0 + a.split_pages);
@@ -150,8 +159,8 @@ paged_decode_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap map_k,
         }
         __syncwarp();
         if (ok && lane < 4) {
-            // lanes 0..3: K dims 0-63, K dims 64-127, V dims 0-63, V dims 64-127 (2 KiB each)
-            const uint32_t dst = smem_addr(s_attn + (size_t)st * kAttnStageBytes + lane * 2048);
+            // lanes 0..3: K dims 0-63, K dims 64-127, V dims 0-63, V dims 64-127 (one half tile each)
+            const uint32_t dst = smem_addr(s_attn + (size_t)st * kAttnStageBytes + lane * kHalf);
             tensor_load_4d(dst, lane < 2 ? &map_k : &map_v, (lane & 1) * 64, 0, phys, kvh, bar);
         }
     };
@@ -174,61 +183,66 @@ paged_decode_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap map_k,
 
         unsigned char* kt = s_attn + (size_t)st * kAttnStageBytes;
         unsigned char* vt = kt + kAttnPageBytes;
-        const int valid = min(16, len - p * 16);          // rows of this page that hold tokens
-        if (valid < 16) {
-            // rows past the sequence's end hold whatever the page held before: keep them out of P.V
-            for (int idx = lane; idx < (16 - valid) * 16; idx += 32) {
-                const int r = valid + (idx >> 4), c = idx & 15;
-                *reinterpret_cast<uint4*>(vt + (c >> 3) * 2048 + ((r >> 3) << 10) + ((r & 7) << 7) + ((c & 7) << 4)) =
-                    make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll 1
+        for (int sb = 0; sb < PS / 16; ++sb) {                    // 16 tokens at a time
+            const int valid = min(16, len - p * PS - sb * 16);    // rows of this block that hold tokens
+            if (valid <= 0) break;
+            const int r0 = sb * 16;
+            if (valid < 16) {
+                // rows past the sequence's end hold whatever the page held before: keep them out of P.V
+                for (int idx = lane; idx < (16 - valid) * 16; idx += 32) {
+                    const int r = r0 + valid + (idx >> 4), c = idx & 15;
+                    *reinterpret_cast<uint4*>(vt + (c >> 3) * kHalf + ((r >> 3) << 10) + ((r & 7) << 7) + ((c & 7) << 4)) =
+                        make_uint4(0u, 0u, 0u, 0u);
+                }
+                __syncwarp();
             }
-            __syncwarp();
-        }
 
-        // S = Q K^T for the page's 16 tokens: two n-tiles of 8 tokens
-        float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
-        {
-            const int tile = lane >> 3, r8 = lane & 7;
-            const int trow = (tile >> 1) * 8 + r8;
+            // S = Q K^T for the block's 16 tokens: two n-tiles of 8 tokens
+            float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+            {
+                const int tile = lane >> 3, r8 = lane & 7;
+                const int trow = r0 + (tile >> 1) * 8 + r8;
 #pragma unroll
-            for (int ks = 0; ks < 8; ++ks) {
-                const uint32_t addr = smem_addr(kt + (ks >> 2) * 2048) + swz(trow, (ks & 3) * 2 + (tile & 1));
-                uint32_t b0, b1, b2, b3;
-                ldmatrix_x4(addr, b0, b1, b2, b3);
-                mma_16816<BF16>(s0, qa[ks][0], 0u, qa[ks][1], 0u, b0, b1);
-                mma_16816<BF16>(s1, qa[ks][0], 0u, qa[ks][1], 0u, b2, b3);
+                for (int ks = 0; ks < 8; ++ks) {
+                    const uint32_t addr = smem_addr(kt + (ks >> 2) * kHalf) + swz(trow, (ks & 3) * 2 + (tile & 1));
+                    uint32_t b0, b1, b2, b3;
+                    ldmatrix_x4(addr, b0, b1, b2, b3);
+                    mma_16816<BF16>(s0, qa[ks][0], 0u, qa[ks][1], 0u, b0, b1);
+                    mma_16816<BF16>(s1, qa[ks][0], 0u, qa[ks][1], 0u, b2, b3);
+                }
             }
-        }
-        // online softmax for row g: this lane holds tokens tq*2, tq*2+1 (tile 0) and +8 (tile 1)
-        float x[4] = {s0[0] * a.scale_log2, s0[1] * a.scale_log2, s1[0] * a.scale_log2, s1[1] * a.scale_log2};
-        const int t_first = tq * 2;
-        if (t_first >= valid) x[0] = -INFINITY;
-        if (t_first + 1 >= valid) x[1] = -INFINITY;
-        if (t_first + 8 >= valid) x[2] = -INFINITY;
-        if (t_first + 9 >= valid) x[3] = -INFINITY;
-        float mx = fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3]));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-        const float m_new = fmaxf(m_run, mx);              // finite: token 0 of every page of a split is valid
-        const float alpha = exp2f(m_run - m_new);
-        const float e0 = exp2f(x[0] - m_new), e1 = exp2f(x[1] - m_new), e2 = exp2f(x[2] - m_new), e3 = exp2f(x[3] - m_new);
-        l_run = l_run * alpha + (e0 + e1 + e2 + e3);
-        m_run = m_new;
+            // online softmax for row g: this lane holds tokens tq*2, tq*2+1 (tile 0) and +8 (tile 1)
+            float x[4] = {s0[0] * a.scale_log2, s0[1] * a.scale_log2, s1[0] * a.scale_log2, s1[1] * a.scale_log2};
+            const int t_first = tq * 2;
+            if (t_first >= valid) x[0] = -INFINITY;
+            if (t_first + 1 >= valid) x[1] = -INFINITY;
+            if (t_first + 8 >= valid) x[2] = -INFINITY;
+            if (t_first + 9 >= valid) x[3] = -INFINITY;
+            float mx = fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3]));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float m_new = fmaxf(m_run, mx);              // finite: the first token of every block reached is valid
+            const float alpha = exp2f(m_run - m_new);
+            const float e0 = exp2f(x[0] - m_new), e1 = exp2f(x[1] - m_new), e2 = exp2f(x[2] - m_new), e3 = exp2f(x[3] - m_new);
+            l_run = l_run * alpha + (e0 + e1 + e2 + e3);
+            m_run = m_new;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) { acc[i][0] *= alpha; acc[i][1] *= alpha; }
-        const uint32_t pa0 = pack2<BF16>(e0, e1), pa2 = pack2<BF16>(e2, e3);
+            for (int i = 0; i < 16; ++i) { acc[i][0] *= alpha; acc[i][1] *= alpha; }
+            const uint32_t pa0 = pack2<BF16>(e0, e1), pa2 = pack2<BF16>(e2, e3);
 
-        // O += P V: sixteen n-tiles of 8 dims, two per ldmatrix
-        {
-            const int tile = lane >> 3, r8 = lane & 7;
-            const int trow = (tile & 1) * 8 + r8;
+            // O += P V: sixteen n-tiles of 8 dims, two per ldmatrix
+            {
+                const int tile = lane >> 3, r8 = lane & 7;
+                const int trow = r0 + (tile & 1) * 8 + r8;
 #pragma unroll
-            for (int nb = 0; nb < 8; ++nb) {
-                const uint32_t addr = smem_addr(vt + (nb >> 2) * 2048) + swz(trow, (nb & 3) * 2 + (tile >> 1));
-                uint32_t b0, b1, b2, b3;
-                ldmatrix_x4_trans(addr, b0, b1, b2, b3);
-                mma_16816<BF16>(acc[2 * nb], pa0, 0u, pa2, 0u, b0, b1);
-                mma_16816<BF16>(acc[2 * nb + 1], pa0, 0u, pa2, 0u, b2, b3);
+                for (int nb = 0; nb < 8; ++nb) {
+                    const uint32_t addr = smem_addr(vt + (nb >> 2) * kHalf) + swz(trow, (nb & 3) * 2 + (tile >> 1));
+                    uint32_t b0, b1, b2, b3;
+                    ldmatrix_x4_trans(addr, b0, b1, b2, b3);
+                    mma_16816<BF16>(acc[2 * nb], pa0, 0u, pa2, 0u, b0, b1);
+                    mma_16816<BF16>(acc[2 * nb + 1], pa0, 0u, pa2, 0u, b2, b3);
+                }
             }
         }
         __syncwarp();      // every lane is done with this stage before lane 0 re-arms it
@@ -268,7 +282,7 @@ paged_decode_merge(const AttnArgs a) {
     const int kvh = qh / a.group, g = qh - kvh * a.group;
     const int len = a.seq_lens[seq];
     if (len <= 0) return;
-    const int used = min(a.splits, (((len + 15) >> 4) + a.split_pages - 1) / a.split_pages);
+    const int used = min(a.splits, (((len + a.page_size - 1) / a.page_size) + a.split_pages - 1) / a.split_pages);
     const long long item0 = (((long long)seq * a.kv_heads + kvh) * a.splits) * 8 + g;
     float m = -INFINITY;
     for (int s = 0; s < used; ++s) m = fmaxf(m, a.ws_ml[(item0 + (long long)s * 8) * 2]);
@@ -294,7 +308,7 @@ bool make_pool_map(CUtensorMap* map, const void* base, const barqkv_pool_layout*
                                 (cuuint64_t)pool->num_heads};
     const cuuint64_t strides[3] = {(cuuint64_t)(pool->head_dim * e), (cuuint64_t)(pool->page_stride * e),
                                    (cuuint64_t)(pool->head_stride * e)};
-    const cuuint32_t box[4] = {64u, 16u, 1u, 1u};
+    const cuuint32_t box[4] = {64u, (cuuint32_t)pool->page_size, 1u, 1u};
     const cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
     return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, const_cast<void*>(base), dims, strides, box, estr,
                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
@@ -304,13 +318,13 @@ bool make_pool_map(CUtensorMap* map, const void* base, const barqkv_pool_layout*
 // Pages per split: 32 (512 tokens) when the batch alone fills the machine, fewer when it does not
 // (few sequences or a single KV head per GPU), so that about eight one-warp CTAs per SM have work;
 // never more than 64 splits per sequence.
-int attn_splits(int n, int kv_heads, long long max_len, int* split_pages) {
-    const long long pages = (max_len + 15) / 16;
+int attn_splits(int n, int kv_heads, long long max_len, int page_size, int* split_pages) {
+    const long long pages = (max_len + page_size - 1) / page_size;
     int sms = 148;
     if (DeviceInfo* d = device_info()) sms = d->sms;
     long long per_cta = (long long)n * kv_heads * pages / (8LL * sms);
-    int sp = kAttnSplitPages;
-    while (sp > 4 && sp > per_cta) sp >>= 1;
+    int sp = kAttnSplitTokens / page_size;
+    while (sp * page_size > 64 && sp > per_cta) sp >>= 1;
     while ((pages + sp - 1) / sp > 64) sp *= 2;
     *split_pages = sp;
     const long long splits = (pages + sp - 1) / sp;
@@ -321,10 +335,10 @@ int attn_splits(int n, int kv_heads, long long max_len, int* split_pages) {
 
 extern "C" {
 
-int64_t barqkv_paged_decode_workspace_bytes(int32_t n, int32_t kv_heads, int64_t max_len) {
-    if (n <= 0 || kv_heads <= 0 || max_len <= 0) return 0;
+int64_t barqkv_paged_decode_workspace_bytes(int32_t n, int32_t kv_heads, int64_t max_len, int32_t page_size) {
+    if (n <= 0 || kv_heads <= 0 || max_len <= 0 || page_size <= 0) return 0;
     int sp;
-    const int splits = attn_splits(n, kv_heads, max_len, &sp);
+    const int splits = attn_splits(n, kv_heads, max_len, page_size, &sp);
     if (splits == 1) return 0;
     return (int64_t)n * kv_heads * splits * 8 * (128 + 2) * (int64_t)sizeof(float);
 }
@@ -341,8 +355,9 @@ int barqkv_paged_decode_attention(const barqkv_pool_layout* pool, const void* k_
     if (int rc = check_table(table, n)) return rc;
     if (!table->table) return fail(BARQKV_E_INVALID, "decode_attention: needs an explicit block table");
     if (!k_pool || !v_pool || !seq_lens || !q || !out) return fail(BARQKV_E_INVALID, "decode_attention: null pointer argument");
-    if (pool->elem_bytes != 2 || pool->head_dim != 128 || pool->page_size != 16)
-        return fail(BARQKV_E_LIMIT, "decode_attention: supports 2-byte elements, head_dim 128, page_size 16");
+    if (pool->elem_bytes != 2 || pool->head_dim != 128 ||
+        (pool->page_size != 16 && pool->page_size != 32 && pool->page_size != 64))
+        return fail(BARQKV_E_LIMIT, "decode_attention: supports 2-byte elements, head_dim 128, page_size 16, 32 or 64");
     if (num_q_heads <= 0 || num_q_heads % pool->num_heads || num_q_heads / pool->num_heads > 8)
         return fail(BARQKV_E_LIMIT, "decode_attention: query heads must be 1..8 times the KV heads");
     if (n > 65535 || pool->num_heads > 65535) return fail(BARQKV_E_LIMIT, "decode_attention: more than 65535 sequences or heads");
@@ -369,14 +384,15 @@ int barqkv_paged_decode_attention(const barqkv_pool_layout* pool, const void* k_
     a.n = n;
     a.kv_heads = pool->num_heads;
     a.group = num_q_heads / pool->num_heads;
-    a.splits = attn_splits(n, a.kv_heads, max_len, &a.split_pages);
+    a.page_size = pool->page_size;
+    a.splits = attn_splits(n, a.kv_heads, max_len, a.page_size, &a.split_pages);
     a.scale_log2 = softmax_scale * 1.4426950408889634f;
     a.status = status;
     if (a.splits > 1) {
-        const int64_t need = barqkv_paged_decode_workspace_bytes(n, a.kv_heads, max_len);
+        const int64_t need = barqkv_paged_decode_workspace_bytes(n, a.kv_heads, max_len, a.page_size);
         if (!workspace || workspace_bytes < need || !aligned(workspace, 16))
             return fail(BARQKV_E_INVALID, "decode_attention: workspace missing or smaller than "
-                                          "barqkv_paged_decode_workspace_bytes(n, kv_heads, max_len)");
+                                          "barqkv_paged_decode_workspace_bytes(n, kv_heads, max_len, page_size)");
         a.ws_o = static_cast<float*>(workspace);
         a.ws_ml = a.ws_o + (size_t)n * a.kv_heads * a.splits * 8 * 128;
     }
@@ -385,10 +401,25 @@ int barqkv_paged_decode_attention(const barqkv_pool_layout* pool, const void* k_
         return fail(BARQKV_E_LAUNCH, "decode_attention: could not describe the pools to the copy engine");
 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const size_t smem = (size_t)kAttnStages * kAttnStageBytes + 1024;   // + slack to align the tiles to 1024 B
     const dim3 grid((unsigned)a.splits, (unsigned)a.kv_heads, (unsigned)n);
-    if (is_bf16) paged_decode_kernel<true><<<grid, 32, smem, st>>>(a, map_k, map_v);
-    else paged_decode_kernel<false><<<grid, 32, smem, st>>>(a, map_k, map_v);
+    auto launch = [&](auto kernel, size_t smem) -> cudaError_t {
+        if (smem > 48 * 1024) {
+            const cudaError_t se = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (se != cudaSuccess) return se;
+        }
+        kernel<<<grid, 32, smem, st>>>(a, map_k, map_v);
+        return cudaSuccess;
+    };
+    cudaError_t le;
+    // + 1024 bytes of slack to align the tiles to the swizzle period
+#define BARQKV_ATTN_LAUNCH(PS)                                                                                  \
+    le = is_bf16 ? launch(paged_decode_kernel<true, PS>, (size_t)AttnTile<PS>::kStages * AttnTile<PS>::kStage + 1024) \
+                 : launch(paged_decode_kernel<false, PS>, (size_t)AttnTile<PS>::kStages * AttnTile<PS>::kStage + 1024)
+    if (a.page_size == 16) { BARQKV_ATTN_LAUNCH(16); }
+    else if (a.page_size == 32) { BARQKV_ATTN_LAUNCH(32); }
+    else { BARQKV_ATTN_LAUNCH(64); }
+#undef BARQKV_ATTN_LAUNCH
+    if (le != cudaSuccess) return fail_cuda("decode_attention: cudaFuncSetAttribute", le);
     cudaError_t ce = cudaGetLastError();
     if (ce != cudaSuccess) return fail_cuda("decode_attention launch", ce);
     g_launches.fetch_add(1, std::memory_order_relaxed);

@@ -283,10 +283,10 @@ int barqkv_update(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,
  * elements; query head j uses KV head j / (num_q_heads / kv_heads).  seq_lens: lengths including the
  * current token (append first).  max_len: an upper bound of the lengths known to the host; it fixes
  * how many splits a sequence's pages are cut into.  workspace: device scratch of
- * barqkv_paged_decode_workspace_bytes(n, kv_heads, max_len) bytes (0 when one split suffices).
- * Limits: head_dim 128, page_size 16, 2-byte elements, at most 8 query heads per KV head.
+ * barqkv_paged_decode_workspace_bytes(n, kv_heads, max_len, page_size) bytes (0 when one split suffices).
+ * Limits: head_dim 128, page_size 16, 32 or 64, 2-byte elements, at most 8 query heads per KV head.
  */
-int64_t barqkv_paged_decode_workspace_bytes(int32_t n, int32_t kv_heads, int64_t max_len);
+int64_t barqkv_paged_decode_workspace_bytes(int32_t n, int32_t kv_heads, int64_t max_len, int32_t page_size);
 int barqkv_paged_decode_attention(const barqkv_pool_layout* pool, const void* k_pool, const void* v_pool,
                                   const barqkv_block_table* table, const int32_t* seq_lens, int32_t n,
                                   const void* q, int64_t q_seq_stride, int64_t q_head_stride,

@@ -34,13 +34,15 @@ def _reference(cache, layer, slots, q, scale):
     dict(dtype=torch.float16, hkv=2, group=8, lens=(700, 33, 4096 + 5), seed=2),
     dict(dtype=torch.bfloat16, hkv=4, group=1, lens=(64, 129, 2), seed=3),
     dict(dtype=torch.float16, hkv=1, group=4, lens=(3000, 16, 1024), seed=4),
+    dict(dtype=torch.bfloat16, hkv=2, group=4, lens=(1, 31, 32, 33, 47, 48, 49, 1000, 2100), seed=5, ps=32),
+    dict(dtype=torch.float16, hkv=2, group=2, lens=(63, 64, 65, 17, 700), seed=6, ps=64),
 ])
 def test_decode_attention_matches_fp32_reference(case):
     from barqtrain_b200 import BlockTableKVCache, _ffi
 
     backend = _ffi.require_cuda_backend()
     dtype, hkv, group, lens = case["dtype"], case["hkv"], case["group"], case["lens"]
-    D, ps, n = 128, 16, len(case["lens"])
+    D, ps, n = 128, case.get("ps", 16), len(case["lens"])
     g = torch.Generator(device=DEV).manual_seed(case["seed"])
     pages = sum(-(-x // ps) for x in lens) + 3
     cache = BlockTableKVCache(2, hkv, D, page_size=ps, num_pages=pages, max_seqs=n,
