@@ -3,7 +3,8 @@
 Each function builds the configuration's cache on ``device`` for this rank's KV-head shard, runs
 ``warmup`` untimed and ``steps`` timed steps bracketed by CUDA events, and returns a dict with the
 algorithmic bytes moved on this rank, the elapsed milliseconds and a description.  Algorithmic bytes
-are 4*tokens*H*D*e per layer for both append and gather (K and V, read + write).
+are 4*tokens*H*D*e per layer for both append and gather (K and V, read + write).  ``heads`` overrides
+the rank's share of the 8 KV heads (e.g. 1 to run an 8-GPU shard's work on a single GPU).
 """
 
 from __future__ import annotations
@@ -25,11 +26,11 @@ def _events():
 
 
 def chunked_prefill(world: int, rank: int, device, steps: int, warmup: int, page_size: int = 16,
-                    layers: int = 32, all_layers: bool = False, sync=lambda: None) -> Dict:
+                    layers: int = 32, all_layers: bool = False, heads: int = 0, sync=lambda: None) -> Dict:
     """32 layers, 8 KV heads, head_dim 128, fp16; 16 sequences of 8192 tokens appended in 2048-token
     chunks into a pool shuffled by a seeded permutation.  A step appends one chunk of every sequence
     in every layer; after four chunks the sequences are released and re-opened."""
-    _, H = kv_head_shard(8, world, rank)
+    H = heads or kv_head_shard(8, world, rank)[1]
     B, chunk, chunks = 16, 2048, 4
     dtype = torch.float16
     pages = B * chunk * chunks // page_size
@@ -79,12 +80,12 @@ def chunked_prefill(world: int, rank: int, device, steps: int, warmup: int, page
                        "l2": "inputs larger than L2: 268 MB per launch at 8 heads, pool 34 GB"}}
 
 
-def gather_70b(world: int, rank: int, device, steps: int, warmup: int, layers: int = 80,
+def gather_70b(world: int, rank: int, device, steps: int, warmup: int, layers: int = 80, heads: int = 0,
                sync=lambda: None) -> Dict:
     """80 layers, 8 KV heads sharded by head, head_dim 128, bf16, page 16; 32 sequences with seeded
     lengths log-uniform in [1k, 32k]; fragmented block tables.  A step gathers every sequence to
     contiguous ``[H, sum_len, D]`` K and V in every layer."""
-    _, H = kv_head_shard(8, world, rank)
+    H = heads or kv_head_shard(8, world, rank)[1]
     dtype = torch.bfloat16
     g = torch.Generator().manual_seed(1238)
     u = torch.rand(32, generator=g, dtype=torch.float64)
@@ -131,12 +132,12 @@ def gather_70b(world: int, rank: int, device, steps: int, warmup: int, layers: i
 
 
 def churn(world: int, rank: int, device, steps: int, warmup: int, layers: int = 32, verify: bool = False,
-          sync=lambda: None) -> Dict:
+          heads: int = 0, sync=lambda: None) -> Dict:
     """Continuous batching: 32 layers, 8 KV heads, head_dim 128, fp16, page 16; 256 live sequences with
     initial lengths uniform in [128, 2048]; every step appends one token to every live sequence in every
     layer, then each sequence finishes with seeded probability 0.01, returns its pages to the free list
     and is replaced by a new sequence with a 512-token prefill."""
-    _, H = kv_head_shard(8, world, rank)
+    H = heads or kv_head_shard(8, world, rank)[1]
     dtype = torch.float16
     g = torch.Generator().manual_seed(1239)
     live = 256
@@ -241,13 +242,13 @@ def churn(world: int, rank: int, device, steps: int, warmup: int, layers: int = 
                       "host_allocator_us_per_step": round(counters["host_s"] * 1e6 / max(steps, 1), 1)}}
 
 
-def decode_attention(world: int, rank: int, device, steps: int, warmup: int, layers: int = 32,
+def decode_attention(world: int, rank: int, device, steps: int, warmup: int, layers: int = 32, heads: int = 0,
                      sync=lambda: None) -> Dict:
     """The decode configuration (32 layers, 8 KV heads x 4 query heads, head_dim 128, bf16, page 16, 64
     sequences uniform [512, 4096]) with attention reading the pages directly: a step is, per layer, the
     append of one token per sequence and one attention call over the pages - no gather.  Bytes counted:
     K and V read once (2*sum_len*H*D*e per layer) plus the append's 4*B*H*D*e."""
-    _, H = kv_head_shard(8, world, rank)
+    H = heads or kv_head_shard(8, world, rank)[1]
     group, B, dtype = 4, 64, torch.bfloat16
     g = torch.Generator().manual_seed(1236)
     lens = torch.randint(512, 4097, (B,), generator=g).tolist()

@@ -57,7 +57,7 @@ class PageAllocator:
         self.num_pages = num_pages
         self._free: List[int] = order
         self._head = 0
-        self._refs = [0] * num_pages            # sequences holding each page (forked sequences share full pages)
+        self._refs = np.zeros(num_pages, dtype=np.int32)   # sequences holding each page (forks share full pages)
         self.pages_resident = 0
         self.pages_peak = 0
         self.alloc_calls = 0
@@ -75,10 +75,11 @@ class PageAllocator:
         if self._head > 4096 and self._head * 2 > len(self._free):
             del self._free[:self._head]
             self._head = 0
-        for p in pages:
-            if self._refs[p]:
-                raise AssertionError(f"page {p} handed out twice")
-            self._refs[p] = 1
+        if count:
+            idx = np.asarray(pages, dtype=np.int64)
+            if self._refs[idx].any():
+                raise AssertionError(f"page {pages[int(np.argmax(self._refs[idx] != 0))]} handed out twice")
+            self._refs[idx] = 1
         self.pages_resident += count
         self.pages_peak = max(self.pages_peak, self.pages_resident)
         self.alloc_calls += 1
@@ -86,27 +87,30 @@ class PageAllocator:
 
     def share(self, pages: Iterable[int]) -> None:
         """One more holder for pages that are already held (a forked sequence)."""
-        for p in pages:
-            if not self._refs[p]:
-                raise AssertionError(f"page {p} shared but not owned")
-            self._refs[p] += 1
+        idx = np.asarray(list(pages), dtype=np.int64)
+        if idx.size:
+            if (self._refs[idx] == 0).any():
+                raise AssertionError(f"page {int(idx[np.argmax(self._refs[idx] == 0)])} shared but not owned")
+            np.add.at(self._refs, idx, 1)
 
     def holders(self, page: int) -> int:
-        return self._refs[page]
+        return int(self._refs[page])
 
     def give_back(self, pages: Iterable[int]) -> None:
         """Drop one holder of each page; pages nobody holds any more join the back of the free list."""
-        pages = list(pages)
-        for p in pages:
-            if not self._refs[p]:
-                raise AssertionError(f"page {p} released but not owned")
-        freed = []
-        for p in pages:
-            self._refs[p] -= 1
-            if self._refs[p] < 0:
-                raise AssertionError(f"page {p} released twice")
-            if self._refs[p] == 0:
-                freed.append(p)
+        idx = np.asarray(list(pages), dtype=np.int64)
+        if idx.size == 0:
+            self.release_calls += 1
+            return
+        uniq, times = np.unique(idx, return_counts=True)
+        if (self._refs[uniq] < times).any():
+            bad = int(uniq[np.argmax(self._refs[uniq] < times)])
+            raise AssertionError(f"page {bad} released but not owned" if self._refs[bad] == 0
+                                 else f"page {bad} released twice")
+        self._refs[uniq] -= times.astype(np.int32)
+        # pages nobody holds any more, in the order they were given back
+        gone = self._refs[idx] == 0
+        freed = list(dict.fromkeys(idx[gone].tolist())) if times.max() > 1 else idx[gone].tolist()
         self._free.extend(freed)
         self.pages_resident -= len(freed)
         self.release_calls += 1
@@ -230,8 +234,9 @@ class BlockTableKVCache:
         used = len(self.pages_of[slot])
         self.pages_of[slot] = []
         self._page_count[slot] = 0
-        self._table_np[slot, :used] = -1
-        self._note_table_change(slot, 0, [-1] * used)
+        self._table_np[slot, :used] = -1      # host copy only: kernels never read entries beyond a sequence's
+        #                                         length, so the device copy may keep the stale ids until a new
+        #                                         owner of the row overwrites them
         self.lengths[slot] = 0
         self._free_slots.append(slot)
 

@@ -683,6 +683,8 @@ def run_extra(args):
     kwargs = {"page_size": args.page_size, "all_layers": args.all_layers} if args.workload == "prefill" else {}
     if args.layers_override:
         kwargs["layers"] = args.layers_override
+    if args.shard_heads:
+        kwargs["heads"] = args.shard_heads
     with ClockSampler(local) as clocks:
         res = WORKLOADS[args.workload](world, rank, device, args.steps, max(args.warmup, 3), sync=barrier, **kwargs)
     ms = res["ms"]
@@ -761,6 +763,8 @@ def main():
                     help="decode = the headline configuration; the others print the same line for their configuration")
     ap.add_argument("--all-layers", action="store_true",
                     help="--workload prefill: append a chunk to all layers with one launch (rows for all layers at hand)")
+    ap.add_argument("--shard-heads", type=int, default=0,
+                    help="--workload: KV heads on this GPU instead of 8/N (1 = an 8-GPU shard's work on one GPU)")
     ap.add_argument("--layers-override", type=int, default=0, help="fewer layers for a quick run of --workload")
     args = ap.parse_args()
     if args.micro:
