@@ -47,39 +47,45 @@ class PageAllocator:
     def __init__(self, num_pages: int, order: Optional[Sequence[int]] = None, seed: Optional[int] = None):
         if order is None:
             if seed is None:
-                order = range(num_pages)
+                order = np.arange(num_pages)
             else:
                 g = torch.Generator().manual_seed(seed)
-                order = torch.randperm(num_pages, generator=g).tolist()
-        order = [int(p) for p in order]
-        if sorted(order) != list(range(num_pages)):
+                order = torch.randperm(num_pages, generator=g).numpy()
+        ring = np.array(order, dtype=np.int32).reshape(-1)
+        if ring.size != num_pages or not np.array_equal(np.sort(ring), np.arange(num_pages, dtype=np.int32)):
             raise ValueError("free-list order must be a permutation of range(num_pages)")
         self.num_pages = num_pages
-        self._free: List[int] = order
-        self._head = 0
+        # a page is either free or held, so a ring of num_pages entries holds every possible free list
+        self._ring = ring
+        self._head = 0                       # ring index of the next page to hand out
+        self.pages_free = num_pages
         self._refs = np.zeros(num_pages, dtype=np.int32)   # sequences holding each page (forks share full pages)
+        self._mark = np.zeros(num_pages, dtype=np.int32)   # scratch for spotting a page listed twice
         self.pages_resident = 0
         self.pages_peak = 0
         self.alloc_calls = 0
         self.release_calls = 0
 
-    @property
-    def pages_free(self) -> int:
-        return len(self._free) - self._head
+    def free_pages(self) -> List[int]:
+        """The free list, front first."""
+        at = (self._head + np.arange(self.pages_free)) % max(self.num_pages, 1)
+        return self._ring[at].tolist()
 
-    def take(self, count: int) -> List[int]:
+    def take(self, count: int) -> np.ndarray:
+        """``count`` pages from the front of the free list, as an int32 array."""
         if count > self.pages_free:
             raise PagePoolExhausted(f"need {count} pages, {self.pages_free} free of {self.num_pages}")
-        pages = self._free[self._head:self._head + count]
-        self._head += count
-        if self._head > 4096 and self._head * 2 > len(self._free):
-            del self._free[:self._head]
-            self._head = 0
+        end = self._head + count
+        if end <= self.num_pages:
+            pages = self._ring[self._head:end].copy()
+        else:
+            pages = np.concatenate((self._ring[self._head:], self._ring[:end - self.num_pages]))
         if count:
-            idx = np.asarray(pages, dtype=np.int64)
-            if self._refs[idx].any():
-                raise AssertionError(f"page {pages[int(np.argmax(self._refs[idx] != 0))]} handed out twice")
-            self._refs[idx] = 1
+            if self._refs[pages].any():
+                raise AssertionError(f"page {int(pages[np.argmax(self._refs[pages] != 0)])} handed out twice")
+            self._refs[pages] = 1
+            self._head = end % self.num_pages
+        self.pages_free -= count
         self.pages_resident += count
         self.pages_peak = max(self.pages_peak, self.pages_resident)
         self.alloc_calls += 1
@@ -87,7 +93,7 @@ class PageAllocator:
 
     def share(self, pages: Iterable[int]) -> None:
         """One more holder for pages that are already held (a forked sequence)."""
-        idx = np.asarray(list(pages), dtype=np.int64)
+        idx = np.asarray(pages, dtype=np.int64).reshape(-1)
         if idx.size:
             if (self._refs[idx] == 0).any():
                 raise AssertionError(f"page {int(idx[np.argmax(self._refs[idx] == 0)])} shared but not owned")
@@ -98,22 +104,41 @@ class PageAllocator:
 
     def give_back(self, pages: Iterable[int]) -> None:
         """Drop one holder of each page; pages nobody holds any more join the back of the free list."""
-        idx = np.asarray(list(pages), dtype=np.int64)
-        if idx.size == 0:
-            self.release_calls += 1
-            return
-        uniq, times = np.unique(idx, return_counts=True)
-        if (self._refs[uniq] < times).any():
-            bad = int(uniq[np.argmax(self._refs[uniq] < times)])
-            raise AssertionError(f"page {bad} released but not owned" if self._refs[bad] == 0
-                                 else f"page {bad} released twice")
-        self._refs[uniq] -= times.astype(np.int32)
-        # pages nobody holds any more, in the order they were given back
-        gone = self._refs[idx] == 0
-        freed = list(dict.fromkeys(idx[gone].tolist())) if times.max() > 1 else idx[gone].tolist()
-        self._free.extend(freed)
-        self.pages_resident -= len(freed)
+        idx = np.asarray(pages, dtype=np.int64).reshape(-1)
         self.release_calls += 1
+        if idx.size == 0:
+            return
+        order = np.arange(idx.size, dtype=np.int32)
+        self._mark[idx] = order
+        if (self._mark[idx] == order).all():
+            # no page listed twice: one vectorised decrement
+            held = self._refs[idx]
+            if held.min() < 1:
+                raise AssertionError(f"page {int(idx[np.argmin(held)])} released but not owned")
+            held -= 1
+            self._refs[idx] = held
+            freed = idx[held == 0]
+        else:
+            uniq, times = np.unique(idx, return_counts=True)
+            if (self._refs[uniq] < times).any():
+                bad = int(uniq[np.argmax(self._refs[uniq] < times)])
+                raise AssertionError(f"page {bad} released but not owned" if self._refs[bad] == 0
+                                     else f"page {bad} released twice")
+            self._refs[uniq] -= times.astype(np.int32)
+            # pages nobody holds any more, in the order they were given back
+            freed = np.asarray(list(dict.fromkeys(idx[self._refs[idx] == 0].tolist())), dtype=np.int64)
+        n = freed.size
+        if n:
+            tail = (self._head + self.pages_free) % self.num_pages
+            end = tail + n
+            if end <= self.num_pages:
+                self._ring[tail:end] = freed
+            else:
+                cut = self.num_pages - tail
+                self._ring[tail:] = freed[:cut]
+                self._ring[:end - self.num_pages] = freed[cut:]
+            self.pages_free += n
+            self.pages_resident -= n
 
 
 @dataclass(frozen=True)
@@ -125,6 +150,20 @@ class PoolStats:
     bytes_resident: int
     bytes_peak: int
     sequences_live: int
+
+
+class _PagesOf:
+    """``cache.pages_of[slot]``: the slot's page ids in logical order (read from the host block table)."""
+
+    def __init__(self, cache):
+        self._cache = cache
+
+    def __getitem__(self, slot: int) -> List[int]:
+        c = self._cache
+        return c._table_np[slot, :int(c._page_count[slot])].tolist()
+
+    def __len__(self) -> int:
+        return self._cache.max_seqs
 
 
 class _Descriptor:
@@ -191,8 +230,8 @@ class BlockTableKVCache:
         self._table = _ffi.BlockTable(self.table_dev.data_ptr(), None, max_seqs, max_blocks_per_seq, 0, 0)
 
         self.lengths = np.zeros(max_seqs, dtype=np.int64)      # tokens held, per slot
-        self._page_count = np.zeros(max_seqs, dtype=np.int64)  # pages owned, per slot (len(pages_of[slot]))
-        self.pages_of: List[List[int]] = [[] for _ in range(max_seqs)]
+        self._page_count = np.zeros(max_seqs, dtype=np.int64)  # pages owned, per slot
+        self.pages_of = _PagesOf(self)                         # pages_of[slot] -> list of page ids, in order
         self._free_slots: List[int] = list(range(max_seqs - 1, -1, -1))
         self._slot_of: Dict[object, int] = {}
         self._fork_counter = 0
@@ -230,9 +269,8 @@ class BlockTableKVCache:
     def release(self, seq_id) -> None:
         """Return a sequence's pages to the free list and free its slot (data stays in the pages)."""
         slot = self._slot_of.pop(seq_id)
-        self.allocator.give_back(self.pages_of[slot])
-        used = len(self.pages_of[slot])
-        self.pages_of[slot] = []
+        used = int(self._page_count[slot])
+        self.allocator.give_back(self._table_np[slot, :used])
         self._page_count[slot] = 0
         self._table_np[slot, :used] = -1      # host copy only: kernels never read entries beyond a sequence's
         #                                         length, so the device copy may keep the stale ids until a new
@@ -243,7 +281,7 @@ class BlockTableKVCache:
     def reserve(self, slot: int, new_length: int) -> None:
         """Make sure the slot owns pages for ``new_length`` tokens."""
         need = -(-new_length // self.page_size)
-        have = len(self.pages_of[slot])
+        have = int(self._page_count[slot])
         if need <= have:
             return
         if need > self.max_blocks:
@@ -252,7 +290,6 @@ class BlockTableKVCache:
                 f"max_cache_len={self.max_blocks * self.page_size}"
             )
         pages = self.allocator.take(need - have)
-        self.pages_of[slot].extend(pages)
         self._page_count[slot] = need
         self._table_np[slot, have:need] = pages
         self._note_table_change(slot, have, pages)
@@ -270,8 +307,7 @@ class BlockTableKVCache:
             self.backend._check(rc)
 
     def _set_pages(self, slot: int, pages: List[int]) -> None:
-        old = len(self.pages_of[slot])
-        self.pages_of[slot] = pages
+        old = int(self._page_count[slot])
         self._page_count[slot] = len(pages)
         row = list(pages) + [-1] * max(old - len(pages), 0)
         self._table_np[slot, :len(row)] = row
@@ -295,7 +331,7 @@ class BlockTableKVCache:
         self.allocator.share(pages)
         if partial:
             try:
-                fresh = self.allocator.take(1)[0]
+                fresh = int(self.allocator.take(1)[0])
             except PagePoolExhausted:
                 self.allocator.give_back(pages)
                 self._slot_of.pop(new_seq_id)
@@ -323,7 +359,7 @@ class BlockTableKVCache:
             pages = pages[:keep]
         if new_length % self.page_size and self.allocator.holders(pages[-1]) > 1:
             # the sequence will append into a page it shares: give it a copy of its own first
-            fresh = self.allocator.take(1)[0]
+            fresh = int(self.allocator.take(1)[0])
             self._copy_pages([(pages[-1], fresh)])
             self.allocator.give_back([pages[-1]])
             pages = pages[:-1] + [fresh]
@@ -388,14 +424,9 @@ class BlockTableKVCache:
         starts = np.cumsum(extra) - extra
         rows = np.repeat(slots, extra)
         cols = np.repeat(have - starts, extra) + np.arange(total, dtype=np.int64)
-        page_arr = np.asarray(pages, dtype=np.int32)
-        self._table_np[rows, cols] = page_arr
-        self._table_changes.append(((rows * self.max_blocks + cols).astype(np.int32), page_arr))
+        self._table_np[rows, cols] = pages
+        self._table_changes.append(((rows * self.max_blocks + cols).astype(np.int32), pages))
         self._page_count[slots] = need
-        at = 0
-        for slot, count in zip(slots.tolist(), extra.tolist()):
-            self.pages_of[slot].extend(pages[at:at + count])
-            at += count
 
     def _note_table_change(self, slot: int, first_col: int, values) -> None:
         """Remember entries of the host table that the device copy does not have yet."""

@@ -114,18 +114,25 @@ def test_argument_errors_come_back_as_codes_with_messages():
 # ---------------------------------------------------------------------------
 def test_allocator_order_accounting_and_reuse():
     a = PageAllocator(8, order=[5, 2, 7, 0, 1, 3, 4, 6])
-    assert a.take(3) == [5, 2, 7] and a.pages_resident == 3 and a.pages_free == 5
-    assert a.take(2) == [0, 1] and a.pages_peak == 5
+    assert a.take(3).tolist() == [5, 2, 7] and a.pages_resident == 3 and a.pages_free == 5
+    assert a.take(2).tolist() == [0, 1] and a.pages_peak == 5
     a.give_back([2, 5])
     assert a.pages_resident == 3 and a.pages_peak == 5
-    assert a.take(4) == [3, 4, 6, 2]                       # released pages queue up behind the initial order
+    assert a.take(4).tolist() == [3, 4, 6, 2]                       # released pages queue up behind the initial order
     with pytest.raises(PagePoolExhausted):
         a.take(2)
     assert a.pages_resident == 7                           # a refused request changes nothing
     with pytest.raises(AssertionError):
         a.give_back([5, 5])                                # never owned twice
+    assert a.pages_resident == 7 and a.free_pages() == [5]
+    a.give_back([6, 3, 0])                                 # the ring wraps: freed pages keep their order
+    assert a.free_pages() == [5, 6, 3, 0] and a.take(3).tolist() == [5, 6, 3]
+    a.share([1, 4]); a.give_back([1, 4, 1])                # a shared page goes back once both holders let go
+    assert a.free_pages() == [0, 1] and a.holders(4) == 1
+    with pytest.raises(AssertionError):
+        a.give_back([7, 0])                                # 0 is free
     seeded = PageAllocator(64, seed=1235)
-    assert sorted(seeded._free) == list(range(64)) and seeded._free != list(range(64))
+    assert sorted(seeded.free_pages()) == list(range(64)) and seeded.free_pages() != list(range(64))
     with pytest.raises(ValueError):
         PageAllocator(4, order=[0, 1, 1, 2])
 
