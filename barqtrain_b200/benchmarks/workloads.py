@@ -13,6 +13,7 @@ import math
 import time
 from typing import Dict
 
+import numpy as np
 import torch
 
 from ..block_table import BlockTableKVCache
@@ -155,7 +156,7 @@ def churn(world: int, rank: int, device, steps: int, warmup: int, layers: int = 
     next_id = live
     # set-up: initial contents, in slices so that the packed source stays small
     origin = [None] * live            # per live sequence: (first row, count) of its prefill in `rows`
-    decoded = [0] * live              # decode tokens appended since (each is rows[j])
+    decoded = np.zeros(live, dtype=np.int64)   # decode tokens appended since (each is rows[j])
     for lo in range(0, live, 8):
         part, counts = slots[lo:lo + 8], lens0[lo:lo + 8]
         at = 0
@@ -167,21 +168,21 @@ def churn(world: int, rank: int, device, steps: int, warmup: int, layers: int = 
             cache.append(layer, batch, rows[: sum(counts)], rows[: sum(counts)])
         cache.end_append(batch)
     one_all = rows[:live].expand(layers, -1, -1, -1)          # the step's new rows, [layers, live, H, D]
-    finished = (torch.rand(total_steps, live, generator=g) < 0.01).tolist()
+    finished = (torch.rand(total_steps, live, generator=g) < 0.01).numpy()
+    ones = np.ones(live, dtype=np.int64)
     counters = {"tokens": 0, "host_s": 0.0, "released": 0, "launches": 0}
 
     def step(i):
         nonlocal next_id
         t0 = time.perf_counter()
-        batch = cache.begin_append(slots, [1] * live)
+        batch = cache.begin_append(slots, ones)
         counters["host_s"] += time.perf_counter() - t0
         cache.append_layers(batch, one_all, one_all)           # all layers' rows of the step in one launch
         cache.end_append(batch)
         counters["tokens"] += live
         counters["launches"] += 1
-        for j in range(live):
-            decoded[j] += 1
-        gone = [j for j in range(live) if finished[i][j]]
+        decoded[:] += 1
+        gone = np.nonzero(finished[i])[0].tolist()
         if gone:
             t0 = time.perf_counter()
             fresh = []
@@ -223,9 +224,9 @@ def churn(world: int, rank: int, device, steps: int, warmup: int, layers: int = 
             kn, vn = cache.gather(layer, gb, "NHD")
             for j in range(live):
                 first, count = origin[j]
-                want = torch.cat([rows[first:first + count], rows[j:j + 1].expand(decoded[j], -1, -1)])
+                want = torch.cat([rows[first:first + count], rows[j:j + 1].expand(int(decoded[j]), -1, -1)])
                 a, b = gb.cu[j], gb.cu[j + 1]
-                if b - a != count + decoded[j] or not torch.equal(kn[a:b], want) or not torch.equal(vn[a:b], want):
+                if b - a != count + int(decoded[j]) or not torch.equal(kn[a:b], want) or not torch.equal(vn[a:b], want):
                     verified = False
     st = cache.stats()
     return {"bytes": 4 * counters["tokens"] * H * D * 2 * layers, "ms": ms, "tokens": counters["tokens"],

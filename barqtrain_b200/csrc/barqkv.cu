@@ -128,6 +128,7 @@ struct GatherArgs {
     int32_t* work;         // bulk kernel: [0] next group to hand out, [1] CTAs finished; null = static shares
     int group_tiles;       // bulk kernel, dynamic hand-out: (sequence, page) tiles per group
     int static_permille;   // bulk kernel, dynamic hand-out: thousandths of the tiles split evenly up front
+    int first_group;       // bulk kernel, dynamic hand-out: tiles of every CTA's first group (fetched before the scan)
     int tensor_store;      // bulk kernel: full pages go to a row-strided output with one tiled TMA store per K/V
     int32_t* status;
     // Fused append ("update", bulk kernel only; k_new == null means plain gather): seq_lens then holds
@@ -674,6 +675,11 @@ gather_bulk_kernel(const GatherArgs a, const __grid_constant__ CUtensorMap out_m
     }
     pdl_let_successor_in();
     pdl_wait_for_predecessor();
+    // The first group's size comes from the host's bound of the tile count, so its fetch can travel
+    // to L2 and back while the lengths are being scanned.
+    const bool early = a.work != nullptr && a.static_permille == 0;
+    int early_first = 0;
+    if (early && lane == 0) early_first = atomicAdd(a.work, a.first_group);
     scan_pages(a, s_cu, s_part);   // ends with a CTA barrier
 
     // This CTA's tiles come in groups of consecutive tiles of the flat list:
@@ -700,7 +706,10 @@ gather_bulk_kernel(const GatherArgs a, const __grid_constant__ CUtensorMap out_m
         pending = dyn_first + atomicAdd(a.work, k);
     };
     if (dynamic) {
-        if (lane == 0) fetch_ahead(dyn_first);
+        if (lane == 0) {
+            if (early) { pending = early_first; pending_n = a.first_group; }
+            else fetch_ahead(dyn_first);
+        }
         if (share > 0) {
             fixed_share = true;
             group_base = (int)blockIdx.x * share;
@@ -873,6 +882,8 @@ int g_knob_static = 0;
 int g_knob_pdl = 0;
 int g_knob_static_permille = -1;
 int g_knob_tensor_store = -1;
+int g_knob_attn_promotion = -1;
+int g_knob_attn_split_tokens = 0;
 
 struct DeviceInfo {
     int sms = 0;
@@ -1036,6 +1047,8 @@ int barqkv_set_tuning(int32_t knob, int32_t value) {
         case BARQKV_KNOB_PDL: g_knob_pdl = value; return 0;
         case BARQKV_KNOB_STATIC_PERMILLE: g_knob_static_permille = value > 1000 ? 1000 : value; return 0;
         case BARQKV_KNOB_TENSOR_STORE: g_knob_tensor_store = value; return 0;
+        case BARQKV_KNOB_ATTN_L2_PROMOTION: g_knob_attn_promotion = value; return 0;
+        case BARQKV_KNOB_ATTN_SPLIT_TOKENS: g_knob_attn_split_tokens = value; return 0;
         default: return fail(BARQKV_E_INVALID, "set_tuning: unknown knob");
     }
 }
@@ -1393,6 +1406,9 @@ static int gather_common(const barqkv_pool_layout* pool, const void* k_pool, con
     if (use_bulk) {
         int S = (int)(64 * 1024 / (2 * page_bytes));
         if (S > 8) S = 8;
+        // A launch with few units (a single KV head per GPU) is dominated by filling and draining the
+        // rings: half the depth, twice the CTAs.
+        if (tiles_bound * a.heads < 96LL * d->sms && S > 4) S = 4;
         if (g_knob_stages) S = g_knob_stages;
         if (S < 3) S = 3;
         if (S > 32) S = 32;
@@ -1415,6 +1431,10 @@ static int gather_common(const barqkv_pool_layout* pool, const void* k_pool, con
         const long long units_bound = tiles_bound * a.heads;
         const long long want = (units_bound + 2 * S - 1) / (2 * S);   // at least two ring rounds per CTA
         if (want < grid) grid = want < 1 ? 1 : want;
+        {
+            long long k = tiles_bound / (2 * grid);
+            a.first_group = (int)(k < 1 ? 1 : (k > a.group_tiles ? a.group_tiles : k));
+        }
         // A token-major output (rows of a page are head-stride apart) takes one tiled TMA store per full
         // page instead of page_size row copies, when the output is packed and its shape fits a tensor map.
         CUtensorMap map_k, map_v;

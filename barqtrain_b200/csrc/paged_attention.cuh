@@ -310,8 +310,11 @@ bool make_pool_map(CUtensorMap* map, const void* base, const barqkv_pool_layout*
                                    (cuuint64_t)(pool->head_stride * e)};
     const cuuint32_t box[4] = {64u, (cuuint32_t)pool->page_size, 1u, 1u};
     const cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+    const CUtensorMapL2promotion promo = g_knob_attn_promotion == 1   ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B
+                                         : g_knob_attn_promotion == 2 ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B
+                                                                      : CU_TENSOR_MAP_L2_PROMOTION_NONE;
     return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, const_cast<void*>(base), dims, strides, box, estr,
-               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, promo,
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -323,7 +326,8 @@ int attn_splits(int n, int kv_heads, long long max_len, int page_size, int* spli
     int sms = 148;
     if (DeviceInfo* d = device_info()) sms = d->sms;
     long long per_cta = (long long)n * kv_heads * pages / (8LL * sms);
-    int sp = kAttnSplitTokens / page_size;
+    int sp = (g_knob_attn_split_tokens > 0 ? g_knob_attn_split_tokens : kAttnSplitTokens) / page_size;
+    if (sp < 1) sp = 1;
     while (sp * page_size > 64 && sp > per_cta) sp >>= 1;
     while ((pages + sp - 1) / sp > 64) sp *= 2;
     *split_pages = sp;

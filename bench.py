@@ -115,7 +115,8 @@ class ClockSampler:
 # the GPU arm
 # ---------------------------------------------------------------------------
 class DecodeWorkload:
-    def __init__(self, world: int, rank: int, device: torch.device, total_steps: int, fused: bool = True):
+    def __init__(self, world: int, rank: int, device: torch.device, total_steps: int, fused: bool = True,
+                 heads: int = 0):
         self.fused = fused          # one update() launch per layer instead of append() + gather()
         self.graph = None
         from barqtrain_b200 import BlockTableKVCache
@@ -125,6 +126,8 @@ class DecodeWorkload:
         if CFG["kv_heads"] % world:
             raise SystemExit(f"--gpus must divide the {CFG['kv_heads']} KV heads")
         self.first_head, self.H = kv_head_shard(CFG["kv_heads"], world, rank)   # this rank's KV heads
+        if heads:                    # experiments: another shard size on this GPU (1 = an 8-GPU rank's work)
+            self.H = heads
         self.dtype = torch.bfloat16
         self.device = device
         g, self.prompts = seeded_lengths()
@@ -265,7 +268,9 @@ def run_barqkv(args):
     K, W = args.steps, max(args.warmup, 3)
     e2e_steps = max(3, min(K, 10))
     total_steps = W + K + 3 + e2e_steps + 8
-    wl = DecodeWorkload(world, rank, device, total_steps, fused=not args.two_launches)
+    if args.tune:
+        backend.set_tuning(**{k: int(v) for k, v in (kv.split("=") for kv in args.tune.split(","))})
+    wl = DecodeWorkload(world, rank, device, total_steps, fused=not args.two_launches, heads=args.shard_heads)
     use_graph = not args.eager and not args.two_launches
     if use_graph:
         wl.enable_graph()

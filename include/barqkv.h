@@ -107,6 +107,8 @@ typedef struct barqkv_rows_layout {
 #define BARQKV_KNOB_STATIC_SHARES 6      /* 1: ignore `work` and split pages statically among CTAs */
 #define BARQKV_KNOB_STATIC_PERMILLE 8    /* thousandths of the pages split evenly among CTAs before the atomic hand-out (-1 = default) */
 #define BARQKV_KNOB_TENSOR_STORE 9       /* 0: token-major outputs use row copies only; default: tiled TMA store per full page */
+#define BARQKV_KNOB_ATTN_L2_PROMOTION 10 /* decode attention: L2 promotion of the page loads. 0 none, 1 128 B, 2 256 B (-1 = default) */
+#define BARQKV_KNOB_ATTN_SPLIT_TOKENS 11 /* decode attention: tokens per split before adapting to the batch (0 = default 512) */
 #define BARQKV_KNOB_PDL 7                /* 1: launch the bulk gather with programmatic stream serialization */
 
 int barqkv_version(void);
