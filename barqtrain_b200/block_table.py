@@ -235,7 +235,7 @@ class BlockTableKVCache:
         self._free_slots: List[int] = list(range(max_seqs - 1, -1, -1))
         self._slot_of: Dict[object, int] = {}
         self._fork_counter = 0
-        self._attn_ws, self._attn_ws_bytes = None, 0
+        self._attn_ws, self._attn_ws_bytes, self._attn_tickets = None, 0, 0
 
         # staging ring for descriptors and table uploads (pinned; reuse guarded by events)
         self._ring: List[Tuple[torch.Tensor, Optional[torch.cuda.Event]]] = []
@@ -770,9 +770,17 @@ class BlockTableKVCache:
         max_len = max(full.first)
         need = int(self.backend.lib.barqkv_paged_decode_workspace_bytes(full.n, self.num_kv_heads, max_len,
                                                                         self.page_size))
-        if need > self._attn_ws_bytes:
-            self._attn_ws = torch.empty(need, dtype=torch.uint8, device=self.device)
-            self._attn_ws_bytes = need
+        if need:
+            # the front of the workspace holds one ticket per (sequence, KV head) that must be zero on entry;
+            # calls leave their own tickets zero, but a smaller batch's partial results may lie where a
+            # larger batch's tickets go
+            tickets = 4 * full.n * self.num_kv_heads
+            if need > self._attn_ws_bytes:
+                self._attn_ws = torch.zeros(need, dtype=torch.uint8, device=self.device)
+                self._attn_ws_bytes = need
+            elif tickets > self._attn_tickets:
+                self._attn_ws[:tickets].zero_()
+            self._attn_tickets = tickets
         ws_ptr = self._attn_ws.data_ptr() if need else None
         if scale is None:
             scale = self.head_dim ** -0.5

@@ -11,7 +11,10 @@
 //                         mma.sync m16n8k16 with ldmatrix from the swizzled tiles; softmax is kept
 //                         online in fp32 (base-2 exponent).  Memory-bound: the tensor-core work is
 //                         ~6 warp instructions per token, the limit is reading 512 B per token and head.
-//   paged_decode_merge    combines the splits' partial (max, sum, output) triples.
+//                         With several splits per sequence each warp leaves a partial (max, sum, output)
+//                         triple in the workspace and takes a ticket; the warp that takes a sequence's
+//                         last ticket combines the triples (they are still in L2) and writes the output,
+//                         so no second launch is needed.
 //
 // Restrictions (checked on the host): 2-byte elements (bf16 / fp16), head_dim 128, page_size 16, 32 or 64,
 // group <= 8.  Every wait is bounded; a guard failure skips the sequence and sets a status bit.
@@ -35,6 +38,7 @@ struct AttnArgs {
     long long q_seq, q_head, o_seq, o_head;   // byte strides
     float* ws_o;                              // [n][kv_heads][splits][8][128] partial outputs
     float* ws_ml;                             // [n][kv_heads][splits][8][2]   (running max, running sum)
+    int32_t* tickets;                         // [n][kv_heads] splits that have left their partials; zero between calls
     int n, kv_heads, group, split_pages, splits, page_size;
     float scale_log2;                         // softmax scale * log2(e)
     int32_t* status;
@@ -106,12 +110,13 @@ paged_decode_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap map_k,
 
     pdl_let_successor_in();
     pdl_wait_for_predecessor();
+    // the length and the table row are independent loads: both are in flight before either is used
     const int len = a.seq_lens[seq];
+    const int row = a.tb.slots ? a.tb.slots[seq] : seq;
     const int pages = (len + PS - 1) / PS;
     const int p0 = split * a.split_pages;
     if (len <= 0 || p0 >= pages) return;
     const int p1 = min(pages, p0 + a.split_pages);
-    const int row = a.tb.slots ? a.tb.slots[seq] : seq;
     if (row < 0 || row >= a.tb.rows || pages > a.tb.stride) {
         if (lane == 0) raise(a.status, BARQKV_S_BAD_SLOT);
         return;
@@ -248,55 +253,79 @@ paged_decode_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap map_k,
         __syncwarp();      // every lane is done with this stage before lane 0 re-arms it
     }
 
-    if (dead || bad) {
-        if (lane == 0) raise(a.status, dead ? BARQKV_S_TIMEOUT : BARQKV_S_BAD_PAGE);
-        return;
-    }
+    const bool failed = dead || bad;
+    if (failed && lane == 0) raise(a.status, dead ? BARQKV_S_TIMEOUT : BARQKV_S_BAD_PAGE);
 
     float l_tot = l_run + __shfl_xor_sync(0xffffffffu, l_run, 1);
     l_tot += __shfl_xor_sync(0xffffffffu, l_tot, 2);
-    if (g < a.group) {
-        if (a.splits == 1) {
+    if (a.splits == 1) {
+        if (!failed && g < a.group) {
             unsigned char* orow = a.out + (long long)seq * a.o_seq + (long long)(kvh * a.group + g) * a.o_head;
             const float inv = 1.f / l_tot;
 #pragma unroll
             for (int i = 0; i < 16; ++i)
                 *reinterpret_cast<uint32_t*>(orow + (i * 8 + tq * 2) * 2) = pack2<BF16>(acc[i][0] * inv, acc[i][1] * inv);
-        } else {
-            const long long item = (((long long)seq * a.kv_heads + kvh) * a.splits + split) * 8 + g;
-            float* wo = a.ws_o + item * 128;
+        }
+        return;
+    }
+
+    const long long item0 = (((long long)seq * a.kv_heads + kvh) * a.splits) * 8;
+    if (!failed && g < a.group) {
+        const long long item = item0 + (long long)split * 8 + g;
+        float* wo = a.ws_o + item * 128;
 #pragma unroll
-            for (int i = 0; i < 16; ++i) *reinterpret_cast<float2*>(wo + i * 8 + tq * 2) = make_float2(acc[i][0], acc[i][1]);
-            if (tq == 0) *reinterpret_cast<float2*>(a.ws_ml + item * 2) = make_float2(m_run, l_tot);
+        for (int i = 0; i < 16; ++i) __stcg(reinterpret_cast<float2*>(wo + i * 8 + tq * 2), make_float2(acc[i][0], acc[i][1]));
+        if (tq == 0) __stcg(reinterpret_cast<float2*>(a.ws_ml + item * 2), make_float2(m_run, l_tot));
+    }
+    // Every split of the sequence that has pages takes one ticket once its partial is visible; the
+    // last one to arrive combines them.  A split that failed a guard still takes its ticket, so the
+    // counter returns to zero whatever happens (the status word says that the output is not valid).
+    const int used = min(a.splits, (pages + a.split_pages - 1) / a.split_pages);
+    int32_t* ticket = a.tickets + (long long)seq * a.kv_heads + kvh;
+    __syncwarp();                 // the lanes' stores are ordered before lane 0's fence (cumulativity)
+    int last = 0;
+    if (lane == 0) {
+        __threadfence();
+        last = atomicAdd(ticket, 1) == used - 1;
+        if (last) {
+            __threadfence();
+            *ticket = 0;
         }
     }
-}
+    last = __shfl_sync(0xffffffffu, last, 0);
+    if (!last) return;
 
-// gridDim = (query heads, sequences), 128 threads: one output dim each.
-template <bool BF16>
-__global__ void __launch_bounds__(128)
-paged_decode_merge(const AttnArgs a) {
-    pdl_let_successor_in();
-    pdl_wait_for_predecessor();
-    const int qh = blockIdx.x, seq = blockIdx.y, d = threadIdx.x;
-    const int kvh = qh / a.group, g = qh - kvh * a.group;
-    const int len = a.seq_lens[seq];
-    if (len <= 0) return;
-    const int used = min(a.splits, (((len + a.page_size - 1) / a.page_size) + a.split_pages - 1) / a.split_pages);
-    const long long item0 = (((long long)seq * a.kv_heads + kvh) * a.splits) * 8 + g;
-    float m = -INFINITY;
-    for (int s = 0; s < used; ++s) m = fmaxf(m, a.ws_ml[(item0 + (long long)s * 8) * 2]);
-    float num = 0.f, den = 0.f;
-    for (int s = 0; s < used; ++s) {
-        const long long item = item0 + (long long)s * 8;
-        const float w = exp2f(a.ws_ml[item * 2] - m);
-        num += w * a.ws_o[item * 128 + d];
-        den += w * a.ws_ml[item * 2 + 1];
+    // Eight lanes per query head, sixteen output dims per lane; the partials were written by other
+    // SMs, so they are read from L2.  All loads of a pass are independent of one another.
+    const int sub = lane & 7;
+    for (int r = lane >> 3; r < a.group; r += 4) {
+        const float* ml = a.ws_ml + (item0 + r) * 2;
+        const float* po = a.ws_o + (item0 + r) * 128 + sub * 16;
+        float m = -INFINITY;
+#pragma unroll 8
+        for (int s = 0; s < used; ++s) m = fmaxf(m, __ldcg(ml + (long long)s * 16));
+        float num[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) num[i] = 0.f;
+        float den = 0.f;
+#pragma unroll 2
+        for (int s = 0; s < used; ++s) {
+            const float2 x = __ldcg(reinterpret_cast<const float2*>(ml + (long long)s * 16));
+            const float4* o4 = reinterpret_cast<const float4*>(po + (long long)s * 1024);
+            const float4 o0 = __ldcg(o4), o1 = __ldcg(o4 + 1), o2 = __ldcg(o4 + 2), o3 = __ldcg(o4 + 3);
+            const float w = exp2f(x.x - m);
+            num[0] += w * o0.x; num[1] += w * o0.y; num[2] += w * o0.z; num[3] += w * o0.w;
+            num[4] += w * o1.x; num[5] += w * o1.y; num[6] += w * o1.z; num[7] += w * o1.w;
+            num[8] += w * o2.x; num[9] += w * o2.y; num[10] += w * o2.z; num[11] += w * o2.w;
+            num[12] += w * o3.x; num[13] += w * o3.y; num[14] += w * o3.z; num[15] += w * o3.w;
+            den += w * x.y;
+        }
+        const float inv = 1.f / den;
+        unsigned char* orow = a.out + (long long)seq * a.o_seq + (long long)(kvh * a.group + r) * a.o_head + sub * 32;
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            *reinterpret_cast<uint32_t*>(orow + i * 4) = pack2<BF16>(num[2 * i] * inv, num[2 * i + 1] * inv);
     }
-    const float o = num / den;
-    unsigned char* orow = a.out + (long long)seq * a.o_seq + (long long)qh * a.o_head;
-    if (BF16) reinterpret_cast<__nv_bfloat16*>(orow)[d] = __float2bfloat16_rn(o);
-    else reinterpret_cast<__half*>(orow)[d] = __float2half_rn(o);
 }
 
 // 4-D map over one layer's K (or V) pool: (dim, row in page, page, head); box = 64 dims x 16 rows.
@@ -335,6 +364,9 @@ int attn_splits(int n, int kv_heads, long long max_len, int page_size, int* spli
     return splits < 1 ? 1 : (int)splits;
 }
 
+// The tickets sit at the front of the workspace, padded so that the partial outputs stay 16-byte aligned.
+int64_t attn_ticket_bytes(int n, int kv_heads) { return (((int64_t)n * kv_heads * 4) + 15) / 16 * 16; }
+
 }  // namespace
 
 extern "C" {
@@ -344,7 +376,7 @@ int64_t barqkv_paged_decode_workspace_bytes(int32_t n, int32_t kv_heads, int64_t
     int sp;
     const int splits = attn_splits(n, kv_heads, max_len, page_size, &sp);
     if (splits == 1) return 0;
-    return (int64_t)n * kv_heads * splits * 8 * (128 + 2) * (int64_t)sizeof(float);
+    return attn_ticket_bytes(n, kv_heads) + (int64_t)n * kv_heads * splits * 8 * (128 + 2) * (int64_t)sizeof(float);
 }
 
 int barqkv_paged_decode_attention(const barqkv_pool_layout* pool, const void* k_pool, const void* v_pool,
@@ -397,7 +429,8 @@ int barqkv_paged_decode_attention(const barqkv_pool_layout* pool, const void* k_
         if (!workspace || workspace_bytes < need || !aligned(workspace, 16))
             return fail(BARQKV_E_INVALID, "decode_attention: workspace missing or smaller than "
                                           "barqkv_paged_decode_workspace_bytes(n, kv_heads, max_len, page_size)");
-        a.ws_o = static_cast<float*>(workspace);
+        a.tickets = static_cast<int32_t*>(workspace);
+        a.ws_o = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + attn_ticket_bytes(n, a.kv_heads));
         a.ws_ml = a.ws_o + (size_t)n * a.kv_heads * a.splits * 8 * 128;
     }
     CUtensorMap map_k, map_v;
@@ -427,14 +460,6 @@ int barqkv_paged_decode_attention(const barqkv_pool_layout* pool, const void* k_
     cudaError_t ce = cudaGetLastError();
     if (ce != cudaSuccess) return fail_cuda("decode_attention launch", ce);
     g_launches.fetch_add(1, std::memory_order_relaxed);
-    if (a.splits > 1) {
-        const dim3 mgrid((unsigned)num_q_heads, (unsigned)n);
-        if (is_bf16) paged_decode_merge<true><<<mgrid, 128, 0, st>>>(a);
-        else paged_decode_merge<false><<<mgrid, 128, 0, st>>>(a);
-        ce = cudaGetLastError();
-        if (ce != cudaSuccess) return fail_cuda("decode_attention merge launch", ce);
-        g_launches.fetch_add(1, std::memory_order_relaxed);
-    }
     return 0;
 }
 

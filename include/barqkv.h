@@ -284,8 +284,13 @@ int barqkv_update(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,
  * q / out: [n, num_q_heads, 128] in the pool's 2-byte type (is_bf16 selects bf16 or fp16), strides in
  * elements; query head j uses KV head j / (num_q_heads / kv_heads).  seq_lens: lengths including the
  * current token (append first).  max_len: an upper bound of the lengths known to the host; it fixes
- * how many splits a sequence's pages are cut into.  workspace: device scratch of
+ * how many splits a sequence's pages are cut into.  workspace: 16-byte aligned device scratch of
  * barqkv_paged_decode_workspace_bytes(n, kv_heads, max_len, page_size) bytes (0 when one split suffices).
+ * Its first 4 * n * kv_heads bytes are per-sequence tickets (the split that finishes last combines the
+ * partial results inside the same launch): they must be zero on entry and every call leaves them zero,
+ * so a workspace that is zero-filled once serves any number of calls with the same n and kv_heads; zero
+ * the front again before a call with a larger n * kv_heads.  Calls that may overlap on the device need
+ * separate workspaces.
  * Limits: head_dim 128, page_size 16, 32 or 64, 2-byte elements, at most 8 query heads per KV head.
  */
 int64_t barqkv_paged_decode_workspace_bytes(int32_t n, int32_t kv_heads, int64_t max_len, int32_t page_size);

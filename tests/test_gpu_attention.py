@@ -90,3 +90,35 @@ def test_decode_attention_argument_limits():
         cache.decode_attention(0, gb, torch.zeros(1, 2, 64, dtype=torch.bfloat16, device=DEV))
     with pytest.raises(ValueError):
         cache.decode_attention(0, gb, torch.zeros(2, 2, 64, dtype=torch.bfloat16, device=DEV))
+
+
+def test_decode_attention_workspace_survives_changing_batches():
+    """Sequences long enough for several splits, attended in batches of changing size through the one
+    workspace the cache keeps: the per-sequence tickets at its front must be zero again after every
+    call, and a larger batch after a smaller one must not trip over the smaller one's partial results."""
+    from barqtrain_b200 import BlockTableKVCache, _ffi
+
+    backend = _ffi.require_cuda_backend()
+    dtype, hkv, group, D, ps = torch.bfloat16, 2, 4, 128, 16
+    lens = [1500, 2100, 700, 1024, 3000, 513, 40, 1800, 2500, 900, 1300, 2047]
+    n = len(lens)
+    g = torch.Generator(device=DEV).manual_seed(11)
+    cache = BlockTableKVCache(1, hkv, D, page_size=ps, num_pages=sum(-(-x // ps) for x in lens), max_seqs=n,
+                              max_blocks_per_seq=-(-max(lens) // ps), dtype=dtype, device=DEV, seed=11)
+    slots = [cache.open(i) for i in range(n)]
+    total = sum(lens)
+    k = torch.randn(total, hkv, D, generator=g, device=DEV, dtype=torch.float32).to(dtype)
+    v = torch.randn(total, hkv, D, generator=g, device=DEV, dtype=torch.float32).to(dtype)
+    batch = cache.begin_append(slots, lens)
+    cache.append(0, batch, k, v)
+    cache.end_append(batch)
+    scale = D ** -0.5
+    for take in (n, 2, n, n, 5, 1, 9, n):
+        part = slots[:take]
+        q = torch.randn(take, hkv * group, D, generator=g, device=DEV, dtype=torch.float32).to(dtype)
+        gb, want = _reference(cache, 0, part, q, scale)
+        got = cache.decode_attention(0, gb, q)
+        assert bool(((got.float() - want).abs() <= ATOL + RTOL * want.abs()).all()), f"batch of {take}"
+        words = cache._attn_ws[: 4 * take * hkv].view(torch.int32)
+        assert int(words.abs().sum()) == 0, "tickets left non-zero"
+    assert backend.read_status(DEV) == 0
