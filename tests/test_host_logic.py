@@ -137,6 +137,51 @@ def test_allocator_order_accounting_and_reuse():
         PageAllocator(4, order=[0, 1, 1, 2])
 
 
+def test_allocator_random_operations_match_a_plain_model():
+    """Seeded random take / share / give_back sequences against a dict-and-list model: same pages in the
+    same order, same holder counts, same resident and free figures, and the ring never loses a page."""
+    import random
+
+    for seed in range(6):
+        rng = random.Random(seed)
+        num = rng.choice([1, 7, 64, 257])
+        order = list(range(num))
+        rng.shuffle(order)
+        a = PageAllocator(num, order=order)
+        free, refs, held = list(order), {}, []          # model: free list, holders per page, one entry per holding
+        for _ in range(400):
+            op = rng.random()
+            if op < 0.45:
+                count = rng.randint(0, max(1, num // 3))
+                if count > len(free):
+                    with pytest.raises(PagePoolExhausted):
+                        a.take(count)
+                    continue
+                want, free = free[:count], free[count:]
+                assert a.take(count).tolist() == want
+                for p in want:
+                    refs[p] = 1
+                    held.append(p)
+            elif op < 0.6 and held:
+                some = rng.sample(sorted(set(held)), k=min(len(set(held)), rng.randint(1, 4)))
+                a.share(some)
+                for p in some:
+                    refs[p] += 1
+                    held.append(p)
+            elif held:
+                k = rng.randint(1, min(len(held), 9))
+                rng.shuffle(held)
+                back, held = held[:k], held[k:]
+                a.give_back(back)
+                for p in back:
+                    refs[p] -= 1
+                free += [p for p in dict.fromkeys(back) if refs[p] == 0]     # in the order first mentioned
+            assert a.free_pages() == free
+            assert a.pages_free == len(free) and a.pages_resident == num - len(free)
+            assert all(a.holders(p) == refs.get(p, 0) for p in range(num))
+        assert sorted(a.free_pages() + sorted(set(held))) == list(range(num))
+
+
 # ---------------------------------------------------------------------------
 # reference API: factory, kwargs injection (reference tests/test_kv_cache.py:50-107), no CPU path
 # ---------------------------------------------------------------------------
