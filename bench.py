@@ -502,6 +502,58 @@ def cpu_baseline_native(prompts, budget_s: float = 5.0):
 # ---------------------------------------------------------------------------
 # single-kernel cases (the commands the ncu summaries under profiles/ were made with)
 # ---------------------------------------------------------------------------
+def run_micro_legacy(args):
+    """The reference's native entry point on the reference's own cache layout, one layer:
+    ``paged_kv_append_(key_cache[B,H,blocks,ps,D], value_cache, seq_lens, key_states[B,H,T,D], value_states)``.
+    ``--impl barqkv`` times libbarqkv's implementation of it, ``--impl reference`` the reference's own CUDA
+    kernel (built from a reference checkout into ``oracle/_ref`` by ``oracle/ref_cuda.py``)."""
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(device)
+    if args.impl == "reference":
+        from oracle import ref_cuda
+
+        module = ref_cuda.load()
+        if module is None:
+            print(json.dumps({"micro": "append-legacy", "impl": "reference",
+                              "unavailable": "oracle/_ref holds no build of the reference kernel"}))
+            return
+        call = module.paged_kv_append_
+    else:
+        from barqtrain_b200 import _ffi
+
+        call = _ffi.require_cuda_backend().paged_kv_append_
+    H, D, ps, dtype = args.heads, CFG["head_dim"], args.page_size, torch.float16
+    gen = torch.Generator(device=device).manual_seed(7)
+    cases = {"prefill": (16, args.chunk, 4 * args.chunk), "decode": (CFG["batch"], 1, 4096)}
+    out = {"micro": "append-legacy", "impl": args.impl, "heads": H, "page_size": ps, "dtype": "fp16", "cases": {}}
+    for name, (B, T, capacity) in cases.items():
+        blocks = capacity // ps
+        keys = torch.zeros(B, H, blocks, ps, D, dtype=dtype, device=device)
+        values = torch.zeros_like(keys)
+        seq_lens = torch.zeros(B, dtype=torch.int32, device=device)
+        k = torch.randn(B, H, T, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
+        v = torch.randn(B, H, T, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
+        per_round = min(capacity // T, 64)            # calls before the lengths are reset
+        samples = []
+        for it in range(args.warmup + args.steps):
+            seq_lens.zero_()
+            torch.cuda.synchronize(device)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(per_round):
+                call(keys, values, seq_lens, k, v)
+            e1.record()
+            torch.cuda.synchronize(device)
+            if it >= args.warmup:
+                samples.append(e0.elapsed_time(e1) * 1e3 / per_round)
+        us = statistics.median(samples)
+        nbytes = 4 * B * T * H * D * 2
+        out["cases"][name] = {"batch": B, "tokens_per_sequence": T, "calls_per_sample": per_round,
+                              "us_per_call": round(us, 2), "bytes_per_call": nbytes,
+                              "gbs": round(nbytes / us / 1e3, 1)}
+    print(json.dumps(out))
+
+
 def run_micro(args):
     """One kernel alone on a small case of the workload's shape: per-launch CUDA-event times."""
     from barqtrain_b200 import BlockTableKVCache, _ffi
@@ -751,7 +803,7 @@ def main():
                     help="call update() per layer from Python every step instead of replaying a CUDA graph")
     ap.add_argument("--two-launches", action="store_true",
                     help="per layer call append() then gather() instead of the single update() launch")
-    ap.add_argument("--micro", choices=["gather", "update", "attention", "append-prefill", "append-decode", "append-layers"],
+    ap.add_argument("--micro", choices=["gather", "update", "attention", "append-prefill", "append-decode", "append-layers", "append-legacy"],
                     help="time one kernel alone on a one-layer case instead of the full step")
     ap.add_argument("--mode", default="auto", choices=["auto", "vector", "bulk"])
     ap.add_argument("--layout", default="HND", choices=["HND", "NHD"])
@@ -772,7 +824,9 @@ def main():
                     help="--workload: KV heads on this GPU instead of 8/N (1 = an 8-GPU shard's work on one GPU)")
     ap.add_argument("--layers-override", type=int, default=0, help="fewer layers for a quick run of --workload")
     args = ap.parse_args()
-    if args.micro:
+    if args.micro == "append-legacy":
+        run_micro_legacy(args)
+    elif args.micro:
         run_micro(args)
     elif args.workload != "decode" and args.impl != "reference":
         run_extra(args)
