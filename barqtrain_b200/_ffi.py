@@ -58,7 +58,7 @@ class RowsLayout(ctypes.Structure):
 
 
 EXPORTS = ("barqkv_version", "barqkv_last_error", "barqkv_sm_count", "barqkv_launch_count", "barqkv_set_tuning", "barqkv_append",
-           "barqkv_append_layers", "barqkv_append_rope", "barqkv_upload", "barqkv_table_scatter", "barqkv_copy_pages", "barqkv_append_legacy", "barqkv_gather", "barqkv_update", "barqkv_paged_decode_attention", "barqkv_paged_decode_workspace_bytes")
+           "barqkv_append_layers", "barqkv_append_rope", "barqkv_upload", "barqkv_max_length", "barqkv_table_scatter", "barqkv_copy_pages", "barqkv_append_legacy", "barqkv_gather", "barqkv_update", "barqkv_paged_decode_attention", "barqkv_paged_decode_workspace_bytes")
 KNOBS = {"stages": 1, "ctas": 2, "vctas": 3, "interleave": 4, "group": 5, "static": 6, "pdl": 7, "fixed": 8, "tensor_store": 9,
          "attn_promotion": 10, "attn_split": 11}
 
@@ -132,6 +132,9 @@ class CudaBackend:
         self._status: Dict[int, "object"] = {}
         self._tickets: Dict[Tuple[int, int], "object"] = {}
         self._work: Dict[Tuple[int, int], "object"] = {}
+        self._legacy_sig, self._legacy_plan, self._legacy_rows = None, None, None
+        lib.barqkv_max_length.restype = _i32
+        lib.barqkv_max_length.argtypes = [_ptr, _i32, ctypes.POINTER(_i32), _ptr]
 
     @property
     def launches(self) -> int:
@@ -231,6 +234,52 @@ class CudaBackend:
         """
         import torch
 
+        # Same tensors, shapes, strides and types as the previous call: its validation still holds.
+        stream = torch.cuda.current_stream(key_cache.device).cuda_stream if key_cache.is_cuda else None
+        sig = (stream, key_cache.data_ptr(), value_cache.data_ptr(), seq_lens.data_ptr(), key_cache.shape, value_cache.shape,
+               key_cache.stride(), value_cache.stride(), key_states.shape, value_states.shape, key_states.stride(),
+               value_states.stride(), key_cache.dtype, value_cache.dtype, key_states.dtype, value_states.dtype,
+               seq_lens.dtype, seq_lens.shape, seq_lens.stride(), key_states.device, value_states.device)
+        plan = self._legacy_plan if sig == self._legacy_sig else None
+        if plan is None:
+            plan = self._validate_legacy(key_cache, value_cache, seq_lens, key_states, value_states)
+            if plan is None:
+                return
+            if plan[-1]:                       # cacheable: nothing had to be converted or copied
+                self._legacy_sig, self._legacy_plan = sig, plan
+        batch, max_batch, heads, tokens, head_dim, max_blocks, page_size, elem, rows_ref, device, ticket, status, _ = plan
+
+        lens, k_new, v_new = seq_lens, key_states, value_states
+        if not plan[-1]:
+            if lens.dtype != torch.int32 or not lens.is_contiguous():
+                lens = seq_lens.to(torch.int32).contiguous()
+            if k_new.stride(3) != 1 and k_new.size(3) > 1:
+                k_new = k_new.contiguous()
+            if v_new.stride() != k_new.stride():
+                k_new, v_new = k_new.contiguous(), v_new.contiguous()
+            rows_ref = ctypes.byref(RowsLayout(k_new.stride(0), k_new.stride(2), k_new.stride(1), 0, 0))
+        if max_start is None:
+            out = ctypes.c_int32(0)
+            self._check(self.lib.barqkv_max_length(lens.data_ptr(), batch, ctypes.byref(out), stream))
+            max_start = out.value
+        capacity = max_blocks * page_size
+        if max_start + tokens > capacity:
+            raise RuntimeError(
+                f"paged KV cache capacity exceeded: requested {max_start + tokens} tokens, max_cache_len={capacity}")
+        if tokens == 0:
+            return
+        self._check(self.lib.barqkv_append_legacy(
+            key_cache.data_ptr(), value_cache.data_ptr(), lens.data_ptr(), k_new.data_ptr(), v_new.data_ptr(),
+            rows_ref, batch, max_batch, heads, tokens, head_dim, max_blocks, page_size, elem,
+            ticket.data_ptr(), status.data_ptr(), stream))
+        if lens is not seq_lens:
+            seq_lens[:batch].add_(tokens)
+
+    def _validate_legacy(self, key_cache, value_cache, seq_lens, key_states, value_states):
+        """The reference launcher's argument checks, in its order and with its messages
+        (``paged_kv_cache.cu:64-90``).  Returns the call's constants, or ``None`` for an empty batch."""
+        import torch
+
         def need(cond, msg):
             if not cond:
                 raise RuntimeError(msg)
@@ -256,43 +305,26 @@ class CudaBackend:
         need(heads == key_cache.size(1), "key_cache kv_heads dimension does not match key_states")
         need(head_dim == key_cache.size(4), "key_cache head_dim dimension does not match key_states")
         need(batch <= seq_lens.size(0), "seq_lens batch dimension is too small")
-
-        lens = seq_lens
-        if lens.dtype != torch.int32 or not lens.is_contiguous():
-            lens = seq_lens.to(torch.int32).contiguous()
         if batch == 0:
-            return
-        if max_start is None:
-            max_start = int(lens[:batch].max().item())
-        capacity = max_blocks * page_size
-        need(max_start + tokens <= capacity,
-             f"paged KV cache capacity exceeded: requested {max_start + tokens} tokens, max_cache_len={capacity}")
-        if tokens == 0:
-            return
-
-        def rows_of(t):
-            if t.stride(3) != 1 and t.size(3) > 1:
-                t = t.contiguous()
-            return t
-
-        k_new, v_new = rows_of(key_states), rows_of(value_states)
-        if v_new.stride() != k_new.stride():
-            k_new, v_new = k_new.contiguous(), v_new.contiguous()
-        rows = RowsLayout(k_new.stride(0), k_new.stride(2), k_new.stride(1), 0, 0)
+            return None
 
         device = key_cache.device
+        direct = (seq_lens.dtype == torch.int32 and seq_lens.is_contiguous()
+                  and (key_states.stride(3) == 1 or key_states.size(3) <= 1)
+                  and value_states.stride() == key_states.stride())
+        rows_ref = None
+        if direct:
+            rows = RowsLayout(key_states.stride(0), key_states.stride(2), key_states.stride(1), 0, 0)
+            self._legacy_rows = rows                      # keeps the struct behind the reference alive
+            rows_ref = ctypes.byref(rows)
         stream = self._stream(device)
         ticket = self._tickets.get((device.index, stream))
         if ticket is None:
             ticket = torch.zeros(1, dtype=torch.int32, device=device)
             self._tickets[(device.index, stream)] = ticket
         status = self.status_word(device)
-        self._check(self.lib.barqkv_append_legacy(
-            key_cache.data_ptr(), value_cache.data_ptr(), lens.data_ptr(), k_new.data_ptr(), v_new.data_ptr(),
-            ctypes.byref(rows), batch, max_batch, heads, tokens, head_dim, max_blocks, page_size,
-            key_cache.element_size(), ticket.data_ptr(), status.data_ptr(), stream))
-        if lens is not seq_lens:
-            seq_lens[:batch].add_(tokens)
+        return (batch, max_batch, heads, tokens, head_dim, max_blocks, page_size, key_cache.element_size(), rows_ref,
+                device, ticket, status, direct)
 
 
 def _wrap(lib: ctypes.CDLL) -> CudaBackend:

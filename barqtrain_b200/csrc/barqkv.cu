@@ -1211,6 +1211,22 @@ int barqkv_upload(void* dst_device, const void* src_host, int64_t bytes, barqkv_
     return e == cudaSuccess ? 0 : fail_cuda("upload", e);
 }
 
+int barqkv_max_length(const int32_t* seq_lens, int32_t n, int32_t* max_out, barqkv_stream_t stream) {
+    if (n < 0 || !max_out || (n && !seq_lens)) return fail(BARQKV_E_INVALID, "max_length: bad arguments");
+    if (n > 8192) return fail(BARQKV_E_LIMIT, "max_length: more than 8192 entries");
+    *max_out = 0;
+    if (n == 0) return 0;
+    static thread_local int32_t host[8192];
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t e = cudaMemcpyAsync(host, seq_lens, (size_t)n * 4, cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return fail_cuda("max_length", e);
+    int32_t m = host[0];
+    for (int i = 1; i < n; ++i) m = host[i] > m ? host[i] : m;
+    *max_out = m;
+    return 0;
+}
+
 int barqkv_table_scatter(int32_t* table, int64_t table_words, const int32_t* pairs, int32_t n, barqkv_stream_t stream) {
     if (n < 0 || (n && (!table || !pairs))) return fail(BARQKV_E_INVALID, "table_scatter: bad arguments");
     if (n == 0) return 0;

@@ -551,6 +551,23 @@ def run_micro_legacy(args):
         out["cases"][name] = {"batch": B, "tokens_per_sequence": T, "calls_per_sample": per_round,
                               "us_per_call": round(us, 2), "bytes_per_call": nbytes,
                               "gbs": round(nbytes / us / 1e3, 1)}
+        if args.impl != "reference":
+            # the drop-in cache layer mirrors the lengths on the host, so its calls carry the largest
+            # length with them and never read the device
+            samples = []
+            for it in range(args.warmup + args.steps):
+                seq_lens.zero_()
+                torch.cuda.synchronize(device)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for i in range(per_round):
+                    call(keys, values, seq_lens, k, v, max_start=i * T)
+                e1.record()
+                torch.cuda.synchronize(device)
+                if it >= args.warmup:
+                    samples.append(e0.elapsed_time(e1) * 1e3 / per_round)
+            us = statistics.median(samples)
+            out["cases"][name]["host_mirrored_lengths"] = {"us_per_call": round(us, 2), "gbs": round(nbytes / us / 1e3, 1)}
     print(json.dumps(out))
 
 

@@ -160,6 +160,15 @@ int barqkv_append_layers(const barqkv_pool_layout* pool, void* k_pool, void* v_p
                          int64_t new_layer_stride, int32_t* status, barqkv_stream_t stream);
 
 /*
+ * Largest of seq_lens[0..n) (device int32), read back on `stream`: copies the n values to the host,
+ * waits for `stream` and returns the maximum in *max_out.  Replaces the launcher's capacity read
+ * `seq_lens_int.narrow(0, 0, batch_size).max().item<int32_t>()` (csrc/kernels/paged_kv_cache.cu:93),
+ * which costs a slice, a reduction kernel and a blocking read; callers that mirror the lengths on the
+ * host do not need it at all.  n <= 8192.
+ */
+int barqkv_max_length(const int32_t* seq_lens, int32_t n, int32_t* max_out, barqkv_stream_t stream);
+
+/*
  * Host-side plumbing of the block table (no counterpart in the reference, which has no table):
  * barqkv_upload is cudaMemcpyAsync host->device on `stream` (src should be pinned memory that stays
  * untouched until the copy has run); barqkv_table_scatter writes n changed entries into the device
