@@ -1213,16 +1213,19 @@ int barqkv_upload(void* dst_device, const void* src_host, int64_t bytes, barqkv_
 
 int barqkv_max_length(const int32_t* seq_lens, int32_t n, int32_t* max_out, barqkv_stream_t stream) {
     if (n < 0 || !max_out || (n && !seq_lens)) return fail(BARQKV_E_INVALID, "max_length: bad arguments");
-    if (n > 8192) return fail(BARQKV_E_LIMIT, "max_length: more than 8192 entries");
     *max_out = 0;
     if (n == 0) return 0;
-    static thread_local int32_t host[8192];
+    constexpr int kChunk = 8192;
+    static thread_local int32_t host[kChunk];
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    cudaError_t e = cudaMemcpyAsync(host, seq_lens, (size_t)n * 4, cudaMemcpyDeviceToHost, st);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
-    if (e != cudaSuccess) return fail_cuda("max_length", e);
-    int32_t m = host[0];
-    for (int i = 1; i < n; ++i) m = host[i] > m ? host[i] : m;
+    int32_t m = INT32_MIN;
+    for (int at = 0; at < n; at += kChunk) {
+        const int count = n - at < kChunk ? n - at : kChunk;
+        cudaError_t e = cudaMemcpyAsync(host, seq_lens + at, (size_t)count * 4, cudaMemcpyDeviceToHost, st);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+        if (e != cudaSuccess) return fail_cuda("max_length", e);
+        for (int i = 0; i < count; ++i) m = host[i] > m ? host[i] : m;
+    }
     *max_out = m;
     return 0;
 }

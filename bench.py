@@ -626,6 +626,20 @@ def run_micro(args):
             def launch():
                 for _ in range(args.reps):
                     cache.gather(0, gb, args.layout, out=out, mode=args.mode)
+            if args.impl == "torch":
+                # Comparison point, not a product path: the same pages collected by torch's index_select
+                # (whole pages, so the rows past a sequence's end in its last page travel too; the bytes
+                # counted are those pages').
+                ids = torch.tensor([p for s_ in slots for p in cache.pages_of[s_]], dtype=torch.int64, device=device)
+                k_pool, v_pool = cache.pools[0, 0], cache.pools[0, 1]                  # [H, P, ps, D]
+                outs = (torch.empty(H, ids.numel(), ps, D, dtype=dtype, device=device),
+                        torch.empty(H, ids.numel(), ps, D, dtype=dtype, device=device))
+
+                def launch_torch():
+                    for _ in range(args.reps):
+                        torch.index_select(k_pool, 1, ids, out=outs[0])
+                        torch.index_select(v_pool, 1, ids, out=outs[1])
+                return launch_torch, 2 * args.reps, ids.numel() * ps * per_tok * args.reps
             return launch, args.reps, total * per_tok * args.reps
         if args.micro == "update":
             total = sum(lens)
@@ -721,7 +735,7 @@ def run_micro(args):
     med = times[len(times) // 2]
     peak, kind = measured_peak()
     status = backend.read_status(device)
-    print(json.dumps({"micro": args.micro, "tune": args.tune, "graph": bool(args.graph), "launches_per_sample": reps,
+    print(json.dumps({"micro": args.micro, "impl": args.impl, "tune": args.tune, "graph": bool(args.graph), "launches_per_sample": reps,
                       "us_per_launch": round(med * 1e6 / reps, 2), "mode": args.mode, "layout": args.layout, "heads": H, "page_size": ps,
                       "sequences": B, "tokens": sum(lens) if args.micro == "gather" else None,
                       "bytes_per_launch": nbytes, "us_median": round(med * 1e6, 2), "us_min": round(times[0] * 1e6, 2),
@@ -814,7 +828,9 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="barqkv", choices=["barqkv", "reference"])
+    ap.add_argument("--impl", default="barqkv", choices=["barqkv", "reference", "torch"],
+                    help="reference: the reference's CPU path (default run) or CUDA kernel (--micro append-legacy); "
+                         "torch: --micro gather with torch.index_select over the pages, for comparison")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="budget of the CPU baseline leg")
     ap.add_argument("--eager", action="store_true",
                     help="call update() per layer from Python every step instead of replaying a CUDA graph")

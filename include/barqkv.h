@@ -164,7 +164,7 @@ int barqkv_append_layers(const barqkv_pool_layout* pool, void* k_pool, void* v_p
  * waits for `stream` and returns the maximum in *max_out.  Replaces the launcher's capacity read
  * `seq_lens_int.narrow(0, 0, batch_size).max().item<int32_t>()` (csrc/kernels/paged_kv_cache.cu:93),
  * which costs a slice, a reduction kernel and a blocking read; callers that mirror the lengths on the
- * host do not need it at all.  n <= 8192.
+ * host do not need it at all.
  */
 int barqkv_max_length(const int32_t* seq_lens, int32_t n, int32_t* max_out, barqkv_stream_t stream);
 
