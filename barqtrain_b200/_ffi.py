@@ -118,11 +118,11 @@ class CudaBackend:
         lib.barqkv_copy_pages.restype = _i32
         lib.barqkv_copy_pages.argtypes = [P(PoolLayout), _ptr, _ptr, _i32, _i64, _ptr, _ptr, _i32, _ptr, _ptr]
         lib.barqkv_paged_decode_workspace_bytes.restype = _i64
-        lib.barqkv_paged_decode_workspace_bytes.argtypes = [_i32, _i32, _i64, _i32]
+        lib.barqkv_paged_decode_workspace_bytes.argtypes = [_i32, _i32, _i64, _i64, _i32]
         lib.barqkv_paged_decode_attention.restype = _i32
         lib.barqkv_paged_decode_attention.argtypes = [P(PoolLayout), _ptr, _ptr, P(BlockTable), _ptr, _i32,
                                                       _ptr, _i64, _i64, _ptr, _i64, _i64, _i32, ctypes.c_float, _i32,
-                                                      _i64, _ptr, _i64, _ptr, _ptr]
+                                                      _i64, _i64, _ptr, _i64, _ptr, _ptr]
         lib.barqkv_update.restype = _i32
         lib.barqkv_update.argtypes = [P(PoolLayout), _ptr, _ptr, P(BlockTable), _ptr, _ptr, _i32, _i32, _i32,
                                       _ptr, _ptr, P(RowsLayout), _ptr, _i64, _ptr, _ptr, P(RowsLayout),

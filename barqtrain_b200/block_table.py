@@ -768,7 +768,8 @@ class BlockTableKVCache:
         if full.n == 0:
             return out
         max_len = max(full.first)
-        need = int(self.backend.lib.barqkv_paged_decode_workspace_bytes(full.n, self.num_kv_heads, max_len,
+        total_len = full.total          # the sum of the lengths: sizes the splits for small batches
+        need = int(self.backend.lib.barqkv_paged_decode_workspace_bytes(full.n, self.num_kv_heads, max_len, total_len,
                                                                         self.page_size))
         if need:
             # the front of the workspace holds one ticket per (sequence, KV head) that must be zero on entry;
@@ -787,7 +788,7 @@ class BlockTableKVCache:
         rc = self.backend.lib.barqkv_paged_decode_attention(
             self._pool_ref, self._k_ptr[layer], self._v_ptr[layer], full.table_ref, full.p_first, full.n,
             q.data_ptr(), q.stride(0), q.stride(1), out.data_ptr(), out.stride(0), out.stride(1), q.shape[1],
-            float(scale), 1 if self.dtype == torch.bfloat16 else 0, max_len, ws_ptr, need, self._status_ptr,
+            float(scale), 1 if self.dtype == torch.bfloat16 else 0, max_len, total_len, ws_ptr, need, self._status_ptr,
             full.stream)
         if rc:
             self.backend._check(rc)

@@ -347,17 +347,34 @@ bool make_pool_map(CUtensorMap* map, const void* base, const barqkv_pool_layout*
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// Pages per split: 32 (512 tokens) when the batch alone fills the machine, fewer when it does not
-// (few sequences or a single KV head per GPU), so that about eight one-warp CTAs per SM have work;
-// never more than 64 splits per sequence.
-int attn_splits(int n, int kv_heads, long long max_len, int page_size, int* split_pages) {
+// Pages per split.  Default 32 (512 tokens): enough CTAs for the tail when the batch fills the machine
+// several times over.  When it does not (few sequences, a single KV head per GPU) the split is sized so
+// that the CTAs with work fill the resident slots once or twice: from the caller's total of the lengths
+// when it is given, else from the longest length alone by halving.  Never more than 64 splits per sequence.
+int attn_splits(int n, int kv_heads, long long max_len, long long total_len, int page_size, int* split_pages) {
     const long long pages = (max_len + page_size - 1) / page_size;
     int sms = 148;
     if (DeviceInfo* d = device_info()) sms = d->sms;
-    long long per_cta = (long long)n * kv_heads * pages / (8LL * sms);
-    int sp = (g_knob_attn_split_tokens > 0 ? g_knob_attn_split_tokens : kAttnSplitTokens) / page_size;
-    if (sp < 1) sp = 1;
-    while (sp * page_size > 64 && sp > per_cta) sp >>= 1;
+    const int cap = (g_knob_attn_split_tokens > 0 ? g_knob_attn_split_tokens : kAttnSplitTokens) / page_size;
+    int sp = cap < 1 ? 1 : cap;
+    if (total_len > 0 && g_knob_attn_split_tokens <= 0) {
+        const int floor_pages = 64 / page_size > 1 ? 64 / page_size : 1;
+        const long long slots = (long long)sms * (page_size <= 16 ? 6 : page_size <= 32 ? 4 : 2);   // resident one-warp CTAs
+        const long long units = ((total_len + page_size - 1) / page_size + n) * kv_heads;           // (page, head) units, rounded up
+        const long long partial = (long long)n * kv_heads / 2;                                      // last splits are half full on average
+        for (int waves = 1; waves <= 2; ++waves) {
+            const long long room = waves * slots - partial;
+            if (room <= 0) continue;
+            const long long fit = (units + room - 1) / room;
+            if (fit <= sp) {
+                sp = (int)(fit < floor_pages ? floor_pages : fit);
+                break;
+            }
+        }
+    } else {
+        const long long per_cta = (long long)n * kv_heads * pages / (8LL * sms);
+        while (sp * page_size > 64 && sp > per_cta) sp >>= 1;
+    }
     while ((pages + sp - 1) / sp > 64) sp *= 2;
     *split_pages = sp;
     const long long splits = (pages + sp - 1) / sp;
@@ -371,10 +388,11 @@ int64_t attn_ticket_bytes(int n, int kv_heads) { return (((int64_t)n * kv_heads 
 
 extern "C" {
 
-int64_t barqkv_paged_decode_workspace_bytes(int32_t n, int32_t kv_heads, int64_t max_len, int32_t page_size) {
+int64_t barqkv_paged_decode_workspace_bytes(int32_t n, int32_t kv_heads, int64_t max_len, int64_t total_len,
+                                            int32_t page_size) {
     if (n <= 0 || kv_heads <= 0 || max_len <= 0 || page_size <= 0) return 0;
     int sp;
-    const int splits = attn_splits(n, kv_heads, max_len, page_size, &sp);
+    const int splits = attn_splits(n, kv_heads, max_len, total_len, page_size, &sp);
     if (splits == 1) return 0;
     return attn_ticket_bytes(n, kv_heads) + (int64_t)n * kv_heads * splits * 8 * (128 + 2) * (int64_t)sizeof(float);
 }
@@ -384,6 +402,7 @@ int barqkv_paged_decode_attention(const barqkv_pool_layout* pool, const void* k_
                                   const void* q, int64_t q_seq_stride, int64_t q_head_stride,
                                   void* out, int64_t out_seq_stride, int64_t out_head_stride,
                                   int32_t num_q_heads, float softmax_scale, int32_t is_bf16, int64_t max_len,
+                                  int64_t total_len,
                                   void* workspace, int64_t workspace_bytes, int32_t* status, barqkv_stream_t stream) {
     if (int rc = check_pool(pool)) return rc;
     if (n < 0) return fail(BARQKV_E_INVALID, "decode_attention: negative batch size");
@@ -421,14 +440,14 @@ int barqkv_paged_decode_attention(const barqkv_pool_layout* pool, const void* k_
     a.kv_heads = pool->num_heads;
     a.group = num_q_heads / pool->num_heads;
     a.page_size = pool->page_size;
-    a.splits = attn_splits(n, a.kv_heads, max_len, a.page_size, &a.split_pages);
+    a.splits = attn_splits(n, a.kv_heads, max_len, total_len, a.page_size, &a.split_pages);
     a.scale_log2 = softmax_scale * 1.4426950408889634f;
     a.status = status;
     if (a.splits > 1) {
-        const int64_t need = barqkv_paged_decode_workspace_bytes(n, a.kv_heads, max_len, a.page_size);
+        const int64_t need = barqkv_paged_decode_workspace_bytes(n, a.kv_heads, max_len, total_len, a.page_size);
         if (!workspace || workspace_bytes < need || !aligned(workspace, 16))
             return fail(BARQKV_E_INVALID, "decode_attention: workspace missing or smaller than "
-                                          "barqkv_paged_decode_workspace_bytes(n, kv_heads, max_len, page_size)");
+                                          "barqkv_paged_decode_workspace_bytes(n, kv_heads, max_len, total_len, page_size)");
         a.tickets = static_cast<int32_t*>(workspace);
         a.ws_o = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + attn_ticket_bytes(n, a.kv_heads));
         a.ws_ml = a.ws_o + (size_t)n * a.kv_heads * a.splits * 8 * 128;

@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define BARQKV_VERSION 100 /* major*100 + minor */
+#define BARQKV_VERSION 101 /* major*100 + minor */
 
 /* host-side return codes */
 #define BARQKV_OK 0
@@ -292,9 +292,11 @@ int barqkv_update(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,
  * reference is softmax(q k^T * scale) v in fp32 over the gathered sequence.
  * q / out: [n, num_q_heads, 128] in the pool's 2-byte type (is_bf16 selects bf16 or fp16), strides in
  * elements; query head j uses KV head j / (num_q_heads / kv_heads).  seq_lens: lengths including the
- * current token (append first).  max_len: an upper bound of the lengths known to the host; it fixes
- * how many splits a sequence's pages are cut into.  workspace: 16-byte aligned device scratch of
- * barqkv_paged_decode_workspace_bytes(n, kv_heads, max_len, page_size) bytes (0 when one split suffices).
+ * current token (append first).  max_len: an upper bound of the lengths known to the host; total_len:
+ * the host's sum of the lengths, or 0 when it is not known.  The two fix how many splits a sequence's
+ * pages are cut into (with the sum the splits are sized to fill the GPU's resident CTAs once or twice
+ * when the batch is small); pass the same values to both functions.  workspace: 16-byte aligned device
+ * scratch of barqkv_paged_decode_workspace_bytes(...) bytes (0 when one split suffices).
  * Its first 4 * n * kv_heads bytes are per-sequence tickets (the split that finishes last combines the
  * partial results inside the same launch): they must be zero on entry and every call leaves them zero,
  * so a workspace that is zero-filled once serves any number of calls with the same n and kv_heads; zero
@@ -302,12 +304,14 @@ int barqkv_update(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,
  * separate workspaces.
  * Limits: head_dim 128, page_size 16, 32 or 64, 2-byte elements, at most 8 query heads per KV head.
  */
-int64_t barqkv_paged_decode_workspace_bytes(int32_t n, int32_t kv_heads, int64_t max_len, int32_t page_size);
+int64_t barqkv_paged_decode_workspace_bytes(int32_t n, int32_t kv_heads, int64_t max_len, int64_t total_len,
+                                            int32_t page_size);
 int barqkv_paged_decode_attention(const barqkv_pool_layout* pool, const void* k_pool, const void* v_pool,
                                   const barqkv_block_table* table, const int32_t* seq_lens, int32_t n,
                                   const void* q, int64_t q_seq_stride, int64_t q_head_stride,
                                   void* out, int64_t out_seq_stride, int64_t out_head_stride,
                                   int32_t num_q_heads, float softmax_scale, int32_t is_bf16, int64_t max_len,
+                                  int64_t total_len,
                                   void* workspace, int64_t workspace_bytes, int32_t* status, barqkv_stream_t stream);
 
 /*
