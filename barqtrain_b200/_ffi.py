@@ -200,8 +200,9 @@ class CudaBackend:
         return int(self.lib.barqkv_sm_count())
 
     def set_tuning(self, **knobs: int) -> None:
-        """Experiment knobs of the gather kernels (0 = default): ``stages``, ``ctas``, ``vctas``,
-        ``interleave``, ``group``, ``static``."""
+        """Experiment knobs (process-wide; the ``BARQKV_KNOB_*`` values of the header). Gather: ``stages``,
+        ``ctas``, ``vctas``, ``interleave``, ``group``, ``static``, ``fixed``, ``pdl``, ``tensor_store``;
+        decode attention: ``attn_promotion``, ``attn_split``."""
         for name, value in knobs.items():
             self._check(self.lib.barqkv_set_tuning(KNOBS[name], int(value)))
 

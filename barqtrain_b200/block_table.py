@@ -152,6 +152,9 @@ class PoolStats:
     sequences_live: int
 
 
+_GATHER_MAX_ENTRIES = 8192      # sequences one gather launch can scan (the library's limit)
+
+
 class _PagesOf:
     """``cache.pages_of[slot]``: the slot's page ids in logical order (read from the host block table)."""
 
@@ -697,6 +700,21 @@ class BlockTableKVCache:
         k_out, v_out, rows_ref, views = self._output(layout, total, out, batch.n)
         if total == 0:
             return views
+        if batch.n > _GATHER_MAX_ENTRIES:
+            # a launch scans at most 8192 sequences: larger batches go in slices of the same description
+            # (the offsets in ``cu`` are absolute, so every slice writes to its own part of the output)
+            for lo in range(0, batch.n, _GATHER_MAX_ENTRIES):
+                count = min(_GATHER_MAX_ENTRIES, batch.n - lo)
+                table = _ffi.BlockTable(self.table_dev.data_ptr(), batch.p_slots + 4 * lo, self.max_seqs,
+                                        self.max_blocks, 0, 0)
+                rc = self._c_gather(self._pool_ref, self._k_ptr[layer], self._v_ptr[layer], ctypes.byref(table),
+                                    batch.p_first + 4 * lo, batch.p_cu + 4 * lo, count,
+                                    batch.cu[lo + count] - batch.cu[lo], k_out.data_ptr(), v_out.data_ptr(),
+                                    rows_ref, _ffi.MODES[mode or self.gather_mode], self._status_ptr, batch.work,
+                                    batch.stream)
+                if rc:
+                    self.backend._check(rc)
+            return views
         rc = self._c_gather(self._pool_ref, self._k_ptr[layer], self._v_ptr[layer], batch.table_ref,
                             batch.p_first, batch.p_cu, batch.n, total, k_out.data_ptr(), v_out.data_ptr(),
                             rows_ref, _ffi.MODES[mode or self.gather_mode], self._status_ptr, batch.work,
@@ -718,6 +736,9 @@ class BlockTableKVCache:
         """
         if full.slots != new.slots:
             raise ValueError("update: the append and gather descriptions must list the same slots")
+        if full.n > _GATHER_MAX_ENTRIES:             # beyond one launch's scan: append, then gather in slices
+            self.append(layer, new, k_new, v_new)
+            return self.gather(layer, full, layout, out=out, mode=mode)
         total, H, D = full.total, self.num_kv_heads, self.head_dim
         k_out, v_out, out_ref, views = self._output(layout, total, out, full.n)
         if new.total:

@@ -776,3 +776,42 @@ def test_rope_fused_into_append_equals_rotate_then_append(backend, dtype, D):
         lens = [n + c for n, c in zip(lens, counts)]
         assert torch.equal(S.bits_dev(fused.pools), S.bits_dev(plain.pools))
     fused.check_device_status()
+
+
+def test_more_sequences_than_one_launch_scans(backend):
+    from barqtrain_b200 import BlockTableKVCache
+
+    """9000 short sequences in one batch: a gather launch scans at most 8192, so the cache slices the
+    batch; the result must still be every sequence's rows back to back, in both layouts and through
+    update()."""
+    H, D, ps, n = 1, 16, 4, 9000
+    g = torch.Generator().manual_seed(77)
+    lens = torch.randint(1, 10, (n,), generator=g).tolist()
+    pages = sum(-(-(x + 1) // ps) for x in lens)
+    cache = BlockTableKVCache(1, H, D, page_size=ps, num_pages=pages, max_seqs=n, max_blocks_per_seq=3,
+                              dtype=torch.float16, device=DEV, seed=77)
+    slots = [cache.open(i) for i in range(n)]
+    total = sum(lens)
+    k = torch.randn(total, H, D, generator=g, dtype=torch.float32).to(torch.float16).to(DEV)
+    v = torch.randn(total, H, D, generator=g, dtype=torch.float32).to(torch.float16).to(DEV)
+    batch = cache.begin_append(slots, lens)
+    cache.append(0, batch, k, v)
+    cache.end_append(batch)
+    gb = cache.begin_gather(slots)
+    kn, vn = cache.gather(0, gb, "NHD")
+    assert torch.equal(kn, k) and torch.equal(vn, v)
+    kh, vh = cache.gather(0, gb, "HND")
+    assert torch.equal(kh, k.transpose(0, 1)) and torch.equal(vh, v.transpose(0, 1))
+    # one more token each through update(): old rows then the new row, per sequence
+    k1 = torch.randn(n, H, D, generator=g, dtype=torch.float32).to(torch.float16).to(DEV)
+    new = cache.begin_append(slots, [1] * n)
+    cache.end_append(new)
+    full = cache.begin_gather(slots)
+    ku, vu = cache.update(0, new, full, k1, k1, "NHD")
+    cu_old = torch.tensor(gb.cu[:-1])
+    at_new = torch.tensor(full.cu[1:]) - 1
+    assert torch.equal(ku[at_new.to(DEV)], k1)
+    keep = torch.ones(full.total, dtype=torch.bool)
+    keep[at_new] = False
+    assert torch.equal(ku[keep.to(DEV)], k) and torch.equal(vu[keep.to(DEV)], v)
+    assert cu_old.numel() == n and backend.read_status(DEV) == 0
