@@ -107,6 +107,13 @@ def test_argument_errors_come_back_as_codes_with_messages():
                                    ctypes.byref(rows), 0, None, None, None)
     assert rc == -3 and b"8192" in backend.lib.barqkv_last_error()
     assert backend.lib.barqkv_set_tuning(99, 1) == -1
+    # decode-attention workspace: none while one split per sequence suffices, else counters + partial results
+    ws = backend.lib.barqkv_paged_decode_workspace_bytes
+    assert ws(64, 8, 64, 0, 16) == 0 and ws(0, 8, 4096, 0, 16) == 0
+    big = ws(64, 8, 4096, 0, 16)
+    assert big > 0 and big % 16 == 0 and big == ws(64, 8, 4096, 0, 16)
+    # the sum of the lengths is an optional hint; with it the answer is still a whole number of 16-byte units
+    assert ws(4, 1, 4096, 4 * 4096, 16) > 0 and ws(4, 1, 4096, 4 * 4096, 16) % 16 == 0
     out = ctypes.c_int32(7)
     assert backend.lib.barqkv_max_length(None, 0, ctypes.byref(out), None) == 0 and out.value == 0   # empty: no device work
     assert backend.lib.barqkv_max_length(None, 4, ctypes.byref(out), None) == -1
