@@ -58,7 +58,7 @@ class RowsLayout(ctypes.Structure):
 
 
 EXPORTS = ("barqkv_version", "barqkv_last_error", "barqkv_sm_count", "barqkv_launch_count", "barqkv_set_tuning", "barqkv_append",
-           "barqkv_append_layers", "barqkv_append_rope", "barqkv_upload", "barqkv_max_length", "barqkv_table_scatter", "barqkv_copy_pages", "barqkv_append_legacy", "barqkv_gather", "barqkv_update", "barqkv_paged_decode_attention", "barqkv_paged_decode_workspace_bytes")
+           "barqkv_append_layers", "barqkv_append_rope", "barqkv_upload", "barqkv_max_length", "barqkv_table_scatter", "barqkv_copy_pages", "barqkv_append_legacy", "barqkv_gather", "barqkv_gather_layers", "barqkv_update", "barqkv_paged_decode_attention", "barqkv_paged_decode_workspace_bytes")
 KNOBS = {"stages": 1, "ctas": 2, "vctas": 3, "interleave": 4, "group": 5, "static": 6, "pdl": 7, "fixed": 8, "tensor_store": 9,
          "attn_promotion": 10, "attn_split": 11}
 
@@ -105,6 +105,9 @@ class CudaBackend:
         lib.barqkv_gather.restype = _i32
         lib.barqkv_gather.argtypes = [P(PoolLayout), _ptr, _ptr, P(BlockTable), _ptr, _ptr, _i32, _i64,
                                       _ptr, _ptr, P(RowsLayout), _i32, _ptr, _ptr, _ptr]
+        lib.barqkv_gather_layers.restype = _i32
+        lib.barqkv_gather_layers.argtypes = [P(PoolLayout), _ptr, _ptr, _i32, _i64, P(BlockTable), _ptr, _ptr, _i32, _i64,
+                                             _ptr, _ptr, P(RowsLayout), _i64, _ptr, _ptr, _ptr]
         lib.barqkv_append_layers.restype = _i32
         lib.barqkv_append_layers.argtypes = [P(PoolLayout), _ptr, _ptr, _i32, _i64, P(BlockTable), _ptr, _ptr,
                                              _i32, _i32, _i32, _ptr, _ptr, P(RowsLayout), _i64, _ptr, _ptr]

@@ -82,10 +82,11 @@ def chunked_prefill(world: int, rank: int, device, steps: int, warmup: int, page
 
 
 def gather_70b(world: int, rank: int, device, steps: int, warmup: int, layers: int = 80, heads: int = 0,
-               sync=lambda: None) -> Dict:
+               all_layers: bool = False, sync=lambda: None) -> Dict:
     """80 layers, 8 KV heads sharded by head, head_dim 128, bf16, page 16; 32 sequences with seeded
     lengths log-uniform in [1k, 32k]; fragmented block tables.  A step gathers every sequence to
-    contiguous ``[H, sum_len, D]`` K and V in every layer."""
+    contiguous ``[H, sum_len, D]`` K and V in every layer: one launch per layer into two alternating
+    outputs, or (``all_layers``) one launch for all layers into ``[layers, H, sum_len, D]``."""
     H = heads or kv_head_shard(8, world, rank)[1]
     dtype = torch.bfloat16
     g = torch.Generator().manual_seed(1238)
@@ -104,13 +105,20 @@ def gather_70b(world: int, rank: int, device, steps: int, warmup: int, layers: i
         cache.append(layer, batch, k, k)
     cache.end_append(batch)
     del k
-    outs = [(torch.empty(H, total, D, dtype=dtype, device=device), torch.empty(H, total, D, dtype=dtype, device=device))
-            for _ in range(2)]
     gb = cache.begin_gather(slots)
+    if all_layers:
+        out_all = (torch.empty(layers, H, total, D, dtype=dtype, device=device),
+                   torch.empty(layers, H, total, D, dtype=dtype, device=device))
 
-    def step():
-        for layer in range(layers):
-            cache.gather(layer, gb, "HND", out=outs[layer & 1])
+        def step():
+            cache.gather_layers(gb, "HND", out=out_all)
+    else:
+        outs = [(torch.empty(H, total, D, dtype=dtype, device=device), torch.empty(H, total, D, dtype=dtype, device=device))
+                for _ in range(2)]
+
+        def step():
+            for layer in range(layers):
+                cache.gather(layer, gb, "HND", out=outs[layer & 1])
 
     for _ in range(max(warmup, 1)):
         step()
@@ -124,8 +132,9 @@ def gather_70b(world: int, rank: int, device, steps: int, warmup: int, layers: i
     ms = e0.elapsed_time(e1)
     cache.check_device_status()
     per_step = 4 * total * H * D * 2 * layers
-    return {"bytes": per_step * steps, "ms": ms, "tokens": total * steps, "launches": layers * steps,
-            "config": {"workload": "llama3-70b-gather", "layers": layers, "kv_heads_per_gpu": H, "dtype": "bf16",
+    return {"bytes": per_step * steps, "ms": ms, "tokens": total * steps, "launches": (1 if all_layers else layers) * steps,
+            "config": {"workload": "llama3-70b-gather", "launch": "all layers per launch" if all_layers else "one per layer",
+                       "layers": layers, "kv_heads_per_gpu": H, "dtype": "bf16",
                        "page_size": 16, "sequences": 32, "sum_len_tokens": total,
                        "lengths": "log-uniform [1024, 32768] seeded",
                        "step": "gather all sequences to [H,sum_len,D] in every layer",

@@ -723,6 +723,49 @@ class BlockTableKVCache:
             self.backend._check(rc)
         return views
 
+    def gather_layers(self, batch: _Descriptor, layout: str = "HND",
+                      out: Optional[Tuple[torch.Tensor, torch.Tensor]] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Every layer's ``gather`` of the batch in one launch: ``[num_layers, kv_heads, total_tokens,
+        head_dim]`` (``"HND"``) or ``[num_layers, total_tokens, kv_heads, head_dim]`` (``"NHD"``) for K and V.
+
+        For callers that want all layers at once (exporting a cache, re-laying it out for another attention
+        backend); the launch's fixed cost is paid once instead of once per layer.  A decode step cannot use
+        it: a layer's new rows depend on the layer before.
+        """
+        if layout not in ("HND", "NHD"):
+            raise ValueError("layout must be 'HND' or 'NHD'")
+        total, L, H, D = batch.total, self.num_layers, self.num_kv_heads, self.head_dim
+        shape = (L, H, total, D) if layout == "HND" else (L, total, H, D)
+        if out is None:
+            out = (torch.empty(shape, dtype=self.dtype, device=self.device),
+                   torch.empty(shape, dtype=self.dtype, device=self.device))
+        k_out, v_out = out
+        if tuple(k_out.shape) != shape or v_out.shape != k_out.shape or not k_out.is_contiguous() \
+                or not v_out.is_contiguous() or k_out.dtype != self.dtype or v_out.dtype != self.dtype \
+                or k_out.device != self.device or v_out.device != self.device:
+            raise ValueError(f"out tensors must be contiguous {shape} in the cache dtype on the cache device")
+        if total == 0:
+            return k_out, v_out
+        if batch.n > _GATHER_MAX_ENTRIES:
+            for layer in range(L):
+                self.gather(layer, batch, layout, out=(k_out[layer], v_out[layer]))
+            return k_out, v_out
+        key = ("layers", layout, total)
+        rows_ref = self._rows.get(key)
+        if rows_ref is None:
+            if len(self._rows) > 4096:
+                self._rows.clear()
+                self._keep = []
+            rows_ref = self._rows[key] = (self._rows_ref(0, D, total * D) if layout == "HND"
+                                          else self._rows_ref(0, H * D, D))
+        rc = self.backend.lib.barqkv_gather_layers(
+            self._pool_ref, self._k_ptr[0], self._v_ptr[0], L, self.pools.stride(0), batch.table_ref, batch.p_first,
+            batch.p_cu, batch.n, total, k_out.data_ptr(), v_out.data_ptr(), rows_ref, k_out.stride(0),
+            self._status_ptr, batch.work, batch.stream)
+        if rc:
+            self.backend._check(rc)
+        return k_out, v_out
+
     # -- append + gather in one call ------------------------------------------------
     def update(self, layer: int, new: _Descriptor, full: _Descriptor, k_new: torch.Tensor, v_new: torch.Tensor,
                layout: str = "HND", out: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,

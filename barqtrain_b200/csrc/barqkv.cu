@@ -129,6 +129,8 @@ struct GatherArgs {
     int group_tiles;       // bulk kernel, dynamic hand-out: (sequence, page) tiles per group
     int static_permille;   // bulk kernel, dynamic hand-out: thousandths of the tiles split evenly up front
     int first_group;       // bulk kernel, dynamic hand-out: tiles of every CTA's first group (fetched before the scan)
+    int layers;            // bulk kernel: the batch is gathered from this many pools, one launch (1 = the usual case)
+    long long pool_layer, out_layer;   // byte strides between layers' pools and outputs
     int tensor_store;      // bulk kernel: full pages go to a row-strided output with one tiled TMA store per K/V
     int32_t* status;
     // Fused append ("update", bulk kernel only; k_new == null means plain gather): seq_lens then holds
@@ -686,7 +688,8 @@ gather_bulk_kernel(const GatherArgs a, const __grid_constant__ CUtensorMap out_m
     //  - dynamic (a.work != null): groups of a.group_tiles handed out by an atomic
     //    counter, so SMs that reach memory faster simply take more groups;
     //  - static: one contiguous share (interleave == 0) or every gridDim-th group.
-    const int total = s_cu[a.n];
+    const int tiles = s_cu[a.n];               // (sequence, page) tiles of one layer
+    const int total = tiles * a.layers;        // the flat list repeats them layer after layer
     const bool dynamic = a.work != nullptr;
     const int gt_max = dynamic ? a.group_tiles : kGroup;
     int gt = gt_max;                       // tiles in the current group
@@ -744,9 +747,11 @@ gather_bulk_kernel(const GatherArgs a, const __grid_constant__ CUtensorMap out_m
             if (!staged) {
                 __syncwarp();
                 if (lane < gt && group_base + lane < end) {
-                    const TileInfo t = resolve_tile(a, s_cu, group_base + lane);
-                    s_src[lane] = t.src;
-                    s_dst[lane] = t.dst;
+                    const int flat = group_base + lane;
+                    const int layer = a.layers > 1 ? flat / tiles : 0;
+                    const TileInfo t = resolve_tile(a, s_cu, flat - layer * tiles);
+                    s_src[lane] = t.src + layer * a.pool_layer;
+                    s_dst[lane] = t.dst + layer * a.out_layer;
                     s_new[lane] = t.new_src;
                     s_rows[lane] = t.rows;
                     s_rows_old[lane] = t.rows_old;
@@ -1346,6 +1351,11 @@ struct FusedRows {
     int tokens_per_entry;
 };
 constexpr int kNotFusable = 1;   // gather_common: the fused form cannot run on these arguments
+// Several layers' pools gathered by one launch (barqkv_gather_layers); null = one layer.
+struct LayerSpan {
+    int layers;
+    long long pool_stride, out_stride;   // elements
+};
 
 static int gather_common(const barqkv_pool_layout* pool, const void* k_pool, const void* v_pool,
                          const barqkv_block_table* table,
@@ -1353,7 +1363,7 @@ static int gather_common(const barqkv_pool_layout* pool, const void* k_pool, con
                          int64_t total_tokens_hint,
                          void* k_out, void* v_out, const barqkv_rows_layout* out_rows,
                          int32_t mode, int32_t* status, int32_t* work, barqkv_stream_t stream,
-                         const FusedRows* fused) {
+                         const FusedRows* fused, const LayerSpan* span = nullptr) {
     if (int rc = check_pool(pool)) return rc;
     if (n < 0) return fail(BARQKV_E_INVALID, "gather: negative batch size");
     if (n == 0) return 0;
@@ -1394,8 +1404,15 @@ static int gather_common(const barqkv_pool_layout* pool, const void* k_pool, con
     if (a.group_tiles > kGroup) a.group_tiles = kGroup;
     if (a.group_tiles < 1) a.group_tiles = 1;
     a.static_permille = g_knob_static_permille >= 0 ? g_knob_static_permille : 0;
+    a.layers = 1;
+    if (span) {
+        a.layers = span->layers;
+        a.pool_layer = span->pool_stride * e;
+        a.out_layer = span->out_stride * e;
+    }
 
-    int vec = vector_bytes(a.row_bytes, {a.pool_head, a.pool_page, a.orow.seq, a.orow.tok, a.orow.head},
+    int vec = vector_bytes(a.row_bytes, {a.pool_head, a.pool_page, a.orow.seq, a.orow.tok, a.orow.head,
+                                         a.pool_layer, a.out_layer},
                            {k_pool, v_pool, k_out, v_out});
     if (fused) {
         a.k_new = static_cast<const unsigned char*>(fused->k_new);
@@ -1421,6 +1438,12 @@ static int gather_common(const barqkv_pool_layout* pool, const void* k_pool, con
     // Upper bound of (sequence, page) tiles, to keep tiny gathers from launching a full machine.
     long long tiles_bound = 0x7fffffffLL;
     if (total_tokens_hint > 0) tiles_bound = (total_tokens_hint + a.page_size - 1) / a.page_size + n;
+    if (a.layers > 1) {
+        if (!use_bulk) return fail(BARQKV_E_INVALID, "gather_layers: needs the bulk path (16-byte aligned rows and strides)");
+        if (total_tokens_hint <= 0) return fail(BARQKV_E_INVALID, "gather_layers: needs the total number of tokens");
+        tiles_bound *= a.layers;
+        if (tiles_bound > 0x7fffffffLL) return fail(BARQKV_E_LIMIT, "gather_layers: too many (layer, sequence, page) tiles");
+    }
 
     if (use_bulk) {
         int S = (int)(64 * 1024 / (2 * page_bytes));
@@ -1459,7 +1482,7 @@ static int gather_common(const barqkv_pool_layout* pool, const void* k_pool, con
         CUtensorMap map_k, map_v;
         memset(&map_k, 0, sizeof(map_k));
         memset(&map_v, 0, sizeof(map_v));
-        if (a.orow.tok != a.row_bytes && a.orow.seq == 0 && a.orow.packed && g_knob_tensor_store != 0 &&
+        if (a.layers == 1 && a.orow.tok != a.row_bytes && a.orow.seq == 0 && a.orow.packed && g_knob_tensor_store != 0 &&
             pool->head_dim <= 256 && a.page_size <= 256 && page_bytes % 128 == 0 && a.orow.tok > 0 && a.orow.head > 0 &&
             a.orow.tok < (1LL << 40) && a.orow.head < (1LL << 40)) {
             const long long tokens = 0x7fffffffLL;      // full pages never reach past their sequence; no clipping needed
@@ -1510,6 +1533,19 @@ int barqkv_gather(const barqkv_pool_layout* pool, const void* k_pool, const void
                   int32_t mode, int32_t* status, int32_t* work, barqkv_stream_t stream) {
     return gather_common(pool, k_pool, v_pool, table, seq_lens, cu_out, n, total_tokens_hint, k_out, v_out, out_rows,
                          mode, status, work, stream, nullptr);
+}
+
+int barqkv_gather_layers(const barqkv_pool_layout* pool, const void* k_pool, const void* v_pool,
+                         int32_t layers, int64_t pool_layer_stride, const barqkv_block_table* table,
+                         const int32_t* seq_lens, const int32_t* cu_out, int32_t n, int64_t total_tokens,
+                         void* k_out, void* v_out, const barqkv_rows_layout* out_rows, int64_t out_layer_stride,
+                         int32_t* status, int32_t* work, barqkv_stream_t stream) {
+    if (layers <= 0 || layers > 65535) return fail(BARQKV_E_INVALID, "gather_layers: bad layer count");
+    if (pool_layer_stride < 0 || out_layer_stride < 0) return fail(BARQKV_E_INVALID, "gather_layers: negative layer stride");
+    if (!work) return fail(BARQKV_E_INVALID, "gather_layers: needs the two-word work buffer");
+    const LayerSpan span{layers, pool_layer_stride, out_layer_stride};
+    return gather_common(pool, k_pool, v_pool, table, seq_lens, cu_out, n, total_tokens, k_out, v_out, out_rows,
+                         BARQKV_MODE_BULK, status, work, stream, nullptr, layers > 1 ? &span : nullptr);
 }
 
 int barqkv_update(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,

@@ -769,6 +769,8 @@ def run_extra(args):
         torch.cuda.synchronize(device)
 
     kwargs = {"page_size": args.page_size, "all_layers": args.all_layers} if args.workload == "prefill" else {}
+    if args.workload == "gather70b":
+        kwargs["all_layers"] = args.all_layers
     if args.layers_override:
         kwargs["layers"] = args.layers_override
     if args.shard_heads:
@@ -852,7 +854,7 @@ def main():
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "gather70b", "churn", "decode-attn"],
                     help="decode = the headline configuration; the others print the same line for their configuration")
     ap.add_argument("--all-layers", action="store_true",
-                    help="--workload prefill: append a chunk to all layers with one launch (rows for all layers at hand)")
+                    help="--workload prefill / gather70b: all layers with one launch (all layers' rows / outputs at hand)")
     ap.add_argument("--shard-heads", type=int, default=0,
                     help="--workload: KV heads on this GPU instead of 8/N (1 = an 8-GPU shard's work on one GPU)")
     ap.add_argument("--layers-override", type=int, default=0, help="fewer layers for a quick run of --workload")

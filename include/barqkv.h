@@ -285,6 +285,20 @@ int barqkv_update(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,
                   barqkv_stream_t stream);
 
 /*
+ * barqkv_gather for several layers in one launch: layer l reads the pools at k_pool / v_pool +
+ * l * pool_layer_stride and writes its outputs at k_out / v_out + l * out_layer_stride (strides in
+ * elements); everything else as in barqkv_gather, bulk path only (16-byte aligned rows and strides),
+ * `work` and total_tokens (the sum of the lengths, or an upper bound) required.  The fixed cost of a launch
+ * is paid once instead of once per layer, which matters when a GPU holds one KV head.
+ * No counterpart in the reference (its gather is a view per layer, kv_cache.py:129-133).
+ */
+int barqkv_gather_layers(const barqkv_pool_layout* pool, const void* k_pool, const void* v_pool,
+                         int32_t layers, int64_t pool_layer_stride, const barqkv_block_table* table,
+                         const int32_t* seq_lens, const int32_t* cu_out, int32_t n, int64_t total_tokens,
+                         void* k_out, void* v_out, const barqkv_rows_layout* out_rows, int64_t out_layer_stride,
+                         int32_t* status, int32_t* work, barqkv_stream_t stream);
+
+/*
  * Decode attention straight from the pages: one query token per sequence attends over the sequence's
  * K/V through the block table, so the gather's copy is not needed for decode.
  * No counterpart in the reference (its attention kernel, csrc/kernels/flash_attention.cu, reads

@@ -815,3 +815,34 @@ def test_more_sequences_than_one_launch_scans(backend):
     keep[at_new] = False
     assert torch.equal(ku[keep.to(DEV)], k) and torch.equal(vu[keep.to(DEV)], v)
     assert cu_old.numel() == n and backend.read_status(DEV) == 0
+
+
+@pytest.mark.parametrize("layout", ["HND", "NHD"])
+def test_all_layers_in_one_gather_launch(backend, layout):
+    """gather_layers() against gather() per layer: ragged lengths, shuffled pool, partial last pages."""
+    from barqtrain_b200 import BlockTableKVCache
+
+    L, H, D, ps = 5, 2, 64, 16
+    lens = [37, 1, 16, 250, 33, 64, 129]
+    g = torch.Generator().manual_seed(91)
+    pages = sum(-(-x // ps) for x in lens) + 2
+    cache = BlockTableKVCache(L, H, D, page_size=ps, num_pages=pages, max_seqs=len(lens), max_blocks_per_seq=16,
+                              dtype=torch.bfloat16, device=DEV, seed=91)
+    slots = [cache.open(i) for i in range(len(lens))]
+    total = sum(lens)
+    batch = cache.begin_append(slots, lens)
+    for layer in range(L):
+        k = torch.randn(total, H, D, generator=g, dtype=torch.float32).to(torch.bfloat16).to(DEV)
+        v = torch.randn(total, H, D, generator=g, dtype=torch.float32).to(torch.bfloat16).to(DEV)
+        cache.append(layer, batch, k, v)
+    cache.end_append(batch)
+    order = [3, 0, 6, 2, 5]                                     # a subset, in another order
+    gb = cache.begin_gather([slots[i] for i in order])
+    before = backend.launches
+    k_all, v_all = cache.gather_layers(gb, layout)
+    assert backend.launches - before == 1
+    assert k_all.shape[0] == L
+    for layer in range(L):
+        k1, v1 = cache.gather(layer, gb, layout)
+        assert torch.equal(S.bits(k_all[layer]), S.bits(k1)) and torch.equal(S.bits(v_all[layer]), S.bits(v1))
+    assert backend.read_status(DEV) == 0
