@@ -1474,7 +1474,9 @@ static int gather_common(const barqkv_pool_layout* pool, const void* k_pool, con
         const long long want = (units_bound + 2 * S - 1) / (2 * S);   // at least two ring rounds per CTA
         if (want < grid) grid = want < 1 ? 1 : want;
         {
-            long long k = tiles_bound / (2 * grid);
+            // half the size the guided hand-out would start with: tiles_bound is an upper bound, and a
+            // first group sized from a loose one must not starve the other CTAs
+            long long k = tiles_bound / (4 * grid);
             a.first_group = (int)(k < 1 ? 1 : (k > a.group_tiles ? a.group_tiles : k));
         }
         // A token-major output (rows of a page are head-stride apart) takes one tiled TMA store per full
