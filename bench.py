@@ -43,6 +43,22 @@ CFG = dict(name="llama3-8b-decode", layers=32, kv_heads=8, head_dim=128, dtype="
            prompt_lo=512, prompt_hi=4096, seed=1236)
 
 
+def init_nccl(dist, device) -> None:
+    """Create the process group and its communicator with file descriptor 1 pointed at stderr: NCCL
+    prints its version banner to stdout when the communicator comes up, and stdout carries the JSON line."""
+    sys.stdout.flush()
+    saved = os.dup(1)
+    os.dup2(2, 1)
+    try:
+        dist.init_process_group("nccl", device_id=device)
+        dist.barrier()
+        torch.cuda.synchronize(device)
+    finally:
+        sys.stdout.flush()
+        os.dup2(saved, 1)
+        os.close(saved)
+
+
 def measured_peak():
     path = ROOT / "MEASURED_PEAKS.json"
     if path.exists():
@@ -260,7 +276,7 @@ def run_barqkv(args):
     torch.cuda.set_device(device)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=device)
+        init_nccl(dist, device)
 
     from barqtrain_b200 import _ffi
 
@@ -759,7 +775,7 @@ def run_extra(args):
     torch.cuda.set_device(device)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=device)
+        init_nccl(dist, device)
     backend = _ffi.require_cuda_backend()
 
     def barrier():
