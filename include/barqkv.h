@@ -3,7 +3,8 @@
  *
  * C ABI of libbarqkv.so.  Every entry point takes raw device pointers, plain
  * integers and a CUDA stream; nothing here allocates device memory, takes a
- * lock, or synchronises with the device.  All functions return 0 on success
+ * lock, or synchronises with the device (barqkv_max_length, whose job is a
+ * blocking read of the lengths, is the one exception).  All functions return 0 on success
  * or a negative BARQKV_E_* code; barqkv_last_error() then holds a message for
  * the calling thread.  Work is enqueued on the given stream and runs
  * asynchronously; device-side guards (bad block-table entry, capacity) never
