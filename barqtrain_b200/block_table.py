@@ -174,21 +174,41 @@ class _Descriptor:
     ``[slots(n) | first(n) | cu(n + 1)]`` where ``first`` is the start position
     (append) or the length (gather) and ``cu`` the packed row offsets."""
 
-    def __init__(self, n: int, dev: torch.Tensor, total: int, host_first: List[int], host_cu: List[int],
-                 slots: List[int], table_ref=None, stream: int = 0, work: int = 0):
+    def __init__(self, n: int, dev: torch.Tensor, total: int, host_first, host_cu, slots, table_ref=None,
+                 stream: int = 0, work: int = 0):
         self.table_ref = table_ref      # ctypes reference to a barqkv_block_table whose `slots` points into `dev`
         self.stream = stream            # the CUDA stream the description was uploaded on
         self.work = work                # gather only: the stream's hand-out counters
         self.n = n
         self.dev = dev
         self.total = total
-        self.first = host_first
-        self.cu = host_cu
-        self.slots = slots
+        # host copies, as lists or numpy arrays; the list views below are made when somebody asks
+        self._first, self._cu, self._slots = host_first, host_cu, slots
         base = dev.data_ptr()
         self.p_slots = base
         self.p_first = base + 4 * n
         self.p_cu = base + 8 * n
+
+    @staticmethod
+    def _as_list(values) -> List[int]:
+        return values if isinstance(values, list) else values.tolist()
+
+    @property
+    def first(self) -> List[int]:
+        """Start positions (append) or lengths (gather), one per entry."""
+        self._first = self._as_list(self._first)
+        return self._first
+
+    @property
+    def cu(self) -> List[int]:
+        """Packed row offsets: entry ``i`` owns rows ``cu[i]:cu[i + 1]``."""
+        self._cu = self._as_list(self._cu)
+        return self._cu
+
+    @property
+    def slots(self) -> List[int]:
+        self._slots = self._as_list(self._slots)
+        return self._slots
 
 
 class BlockTableKVCache:
@@ -467,7 +487,7 @@ class BlockTableKVCache:
         self._stage_done(stream)
 
     def _describe(self, kind: str, slots, first, counts) -> _Descriptor:
-        slots = np.asarray(slots, dtype=np.int64)
+        slots = np.array(slots, dtype=np.int64)            # a copy: the description keeps it
         first = np.asarray(first, dtype=np.int64)
         n = slots.size
         cu = np.zeros(n + 1, dtype=np.int64)
@@ -494,9 +514,9 @@ class BlockTableKVCache:
         table.slots = dev.data_ptr()
         stream = cur.cuda_stream
         work = self.backend.work_words(self.device).data_ptr() if kind == "gather" else 0
-        desc = _Descriptor(n, dev, int(cu[n]), first.tolist(), cu.tolist(), slots.tolist(), ctypes.byref(table),
-                           stream, work)
+        desc = _Descriptor(n, dev, int(cu[n]), first, cu, slots, ctypes.byref(table), stream, work)
         desc.slots_np, desc.after_np = slots, first + (cu[1:] - cu[:-1])
+        desc.max_first = int(first.max()) if n else 0
         return desc
 
     # -- append -------------------------------------------------------------------
@@ -777,7 +797,7 @@ class BlockTableKVCache:
         ``begin_gather`` of the same slots made after it.  For decode-sized appends this is one
         kernel launch instead of two.
         """
-        if full.slots != new.slots:
+        if full.n != new.n or not np.array_equal(full.slots_np, new.slots_np):
             raise ValueError("update: the append and gather descriptions must list the same slots")
         if full.n > _GATHER_MAX_ENTRIES:             # beyond one launch's scan: append, then gather in slices
             self.append(layer, new, k_new, v_new)
@@ -831,7 +851,7 @@ class BlockTableKVCache:
             raise ValueError("out must match q")
         if full.n == 0:
             return out
-        max_len = max(full.first)
+        max_len = full.max_first
         total_len = full.total          # the sum of the lengths: sizes the splits for small batches
         need = int(self.backend.lib.barqkv_paged_decode_workspace_bytes(full.n, self.num_kv_heads, max_len, total_len,
                                                                         self.page_size))
@@ -927,6 +947,7 @@ class DecodeStepGraph:
         ref = ctypes.byref(self._table)
         self._new = _Descriptor(n, self._desc, n, [0] * n, ones_cu, self.slots, ref, self.stream.cuda_stream, 0)
         self._full = _Descriptor(n, self._desc, 0, [0] * n, [0] * (n + 1), self.slots, ref, self.stream.cuda_stream, work)
+        self._new.slots_np = self._full.slots_np = self._slots_np
         self._full.p_first = base + 4 * (3 * n + 1)
         self._full.p_cu = base + 4 * (4 * n + 1)
 
