@@ -57,8 +57,11 @@ class RowsLayout(ctypes.Structure):
     _fields_ = [("seq_stride", _i64), ("tok_stride", _i64), ("head_stride", _i64), ("packed", _i32), ("reserved", _i32)]
 
 
-EXPORTS = ("barqkv_version", "barqkv_last_error", "barqkv_sm_count", "barqkv_launch_count", "barqkv_set_tuning", "barqkv_append",
-           "barqkv_append_layers", "barqkv_append_rope", "barqkv_upload", "barqkv_max_length", "barqkv_table_scatter", "barqkv_copy_pages", "barqkv_append_legacy", "barqkv_gather", "barqkv_gather_layers", "barqkv_update", "barqkv_paged_decode_attention", "barqkv_paged_decode_workspace_bytes")
+EXPORTS = ("barqkv_version", "barqkv_last_error", "barqkv_sm_count", "barqkv_launch_count",
+           "barqkv_set_tuning", "barqkv_append", "barqkv_append_layers", "barqkv_append_rope", "barqkv_upload",
+           "barqkv_max_length", "barqkv_table_scatter", "barqkv_copy_pages", "barqkv_append_legacy",
+           "barqkv_gather", "barqkv_gather_layers", "barqkv_update", "barqkv_paged_decode_attention",
+           "barqkv_paged_decode_workspace_bytes")
 KNOBS = {"stages": 1, "ctas": 2, "vctas": 3, "interleave": 4, "group": 5, "static": 6, "pdl": 7, "fixed": 8, "tensor_store": 9,
          "attn_promotion": 10, "attn_split": 11}
 

@@ -75,7 +75,9 @@ def chunked_prefill(world: int, rank: int, device, steps: int, warmup: int, page
     per_step = 4 * B * chunk * H * D * 2 * layers
     return {"bytes": per_step * steps, "ms": ms, "tokens": B * chunk * steps,
             "launches": (1 if all_layers else layers) * steps,
-            "config": {"workload": "chunked-prefill", "launch": "all layers per launch" if all_layers else "one per layer", "layers": layers, "kv_heads_per_gpu": H, "dtype": "fp16",
+            "config": {"workload": "chunked-prefill",
+                       "launch": "all layers per launch" if all_layers else "one per layer",
+                       "layers": layers, "kv_heads_per_gpu": H, "dtype": "fp16",
                        "page_size": page_size, "sequences": B, "chunk_tokens": chunk,
                        "step": "append one 2048-token chunk of 16 sequences in every layer",
                        "l2": "inputs larger than L2: 268 MB per launch at 8 heads, pool 34 GB"}}
