@@ -324,7 +324,9 @@ def run_barqkv(args):
         barrier()
     launches = backend.launches - launches0
     if use_graph:
-        launches = K * wl.graph.launches_per_replay        # kernel nodes replayed; a replay makes no library call
+        # kernel nodes replayed (a replay makes no library call) plus what the library launched itself in
+        # the region: the small table-scatter kernel of the steps in which a sequence enters a new page
+        launches += K * wl.graph.launches_per_replay
     ms = max_over_ranks(start.elapsed_time(stop))
     job_bytes = (app_bytes + gat_bytes) * world
     value = job_bytes / (ms * 1e-3) / 1e9
