@@ -12,6 +12,7 @@ PACKAGE_DIR = Path(__file__).resolve().parent
 SOURCE = PACKAGE_DIR / "csrc" / "barqkv.cu"
 HEADER_DIR = PACKAGE_DIR.parent / "include"
 LIBRARY = PACKAGE_DIR / "lib" / "libbarqkv.so"
+TUNING_LIBRARY = PACKAGE_DIR / "lib" / "libbarqkv_tuning.so"     # -DBARQKV_TUNING: adds barqkv_set_tuning, for sweeps
 
 
 def detect_cuda_home() -> Optional[str]:
@@ -29,7 +30,7 @@ def detect_cuda_home() -> Optional[str]:
     return None
 
 
-def nvcc_command(output: Path = LIBRARY, verbose_ptxas: bool = False) -> List[str]:
+def nvcc_command(output: Path = LIBRARY, verbose_ptxas: bool = False, tuning: bool = False) -> List[str]:
     home = detect_cuda_home()
     if home is None:
         raise RuntimeError("no CUDA toolkit found (set CUDA_HOME)")
@@ -43,6 +44,8 @@ def nvcc_command(output: Path = LIBRARY, verbose_ptxas: bool = False) -> List[st
     ]
     if verbose_ptxas:
         cmd[1:1] = ["-Xptxas", "-v"]
+    if tuning:
+        cmd[1:1] = ["-DBARQKV_TUNING"]
     return cmd
 
 
@@ -50,12 +53,19 @@ def is_stale() -> bool:
     if not LIBRARY.exists():
         return True
     built = LIBRARY.stat().st_mtime
-    deps = [SOURCE, SOURCE.parent / "paged_attention.cuh", HEADER_DIR / "barqkv.h"]
+    deps = [SOURCE, SOURCE.parent / "paged_attention.cuh", HEADER_DIR / "barqkv.h", HEADER_DIR / "barqkv_experimental.h"]
     return any(d.exists() and d.stat().st_mtime > built for d in deps)
 
 
-def build_native(force: bool = False, verbose: bool = False) -> Path:
-    """Compile the library if it is missing or older than its sources; returns its path."""
+def build_native(force: bool = False, verbose: bool = False, tuning: bool = False) -> Path:
+    """Compile the library if it is missing or older than its sources; returns its path.
+    ``tuning=True`` builds the experiment variant (always) beside it."""
+    if tuning:
+        TUNING_LIBRARY.parent.mkdir(parents=True, exist_ok=True)
+        proc = subprocess.run(nvcc_command(output=TUNING_LIBRARY, tuning=True), capture_output=True, text=True)
+        if proc.returncode != 0:
+            raise RuntimeError("nvcc failed:\n" + proc.stdout + proc.stderr)
+        return TUNING_LIBRARY
     if not force and not is_stale():
         return LIBRARY
     if not SOURCE.exists():

@@ -33,6 +33,7 @@ _CUDA_BUILD_FAILED = False
 S_BAD_PAGE, S_CAPACITY, S_TIMEOUT, S_BAD_SLOT = 1, 2, 4, 8
 MODE_AUTO, MODE_VECTOR, MODE_BULK = 0, 1, 2
 MODES = {"auto": MODE_AUTO, "vector": MODE_VECTOR, "bulk": MODE_BULK}
+FLAG_DESC_STABLE = 0x100
 
 _i32, _i64, _ptr = ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p
 
@@ -58,12 +59,15 @@ class RowsLayout(ctypes.Structure):
 
 
 EXPORTS = ("barqkv_version", "barqkv_last_error", "barqkv_sm_count", "barqkv_launch_count",
-           "barqkv_set_tuning", "barqkv_append", "barqkv_append_layers", "barqkv_append_rope", "barqkv_upload",
+           "barqkv_append", "barqkv_append_layers", "barqkv_append_rope", "barqkv_upload",
            "barqkv_max_length", "barqkv_table_scatter", "barqkv_copy_pages", "barqkv_append_legacy",
            "barqkv_gather", "barqkv_gather_layers", "barqkv_update", "barqkv_paged_decode_attention",
-           "barqkv_paged_decode_workspace_bytes")
+           "barqkv_paged_decode_workspace_bytes", "barqkv_update_layers", "barqkv_gather_wait_selftest",
+           "barqkv_gather_noalloc")
+# experiment knobs: only a library built with -DBARQKV_TUNING exports barqkv_set_tuning (include/barqkv_experimental.h)
 KNOBS = {"stages": 1, "ctas": 2, "vctas": 3, "interleave": 4, "group": 5, "static": 6, "pdl": 7, "fixed": 8, "tensor_store": 9,
-         "attn_promotion": 10, "attn_split": 11}
+         "attn_promotion": 10, "attn_split": 11, "append_bulk": 12}
+STATIC_WORK_SLOTS = 32
 
 
 def _env_enabled(name: str, default: str = "1") -> bool:
@@ -76,10 +80,12 @@ def _detect_cuda_home() -> Optional[str]:
 
 
 def _open_library() -> ctypes.CDLL:
-    """Open the prebuilt library; raises ``OSError`` when it is not there."""
-    if not _build.LIBRARY.exists():
-        raise OSError(f"{_build.LIBRARY} has not been built")
-    return ctypes.CDLL(str(_build.LIBRARY))
+    """Open the prebuilt library; raises ``OSError`` when it is not there.  ``BARQKV_TUNING_LIB=1``
+    opens the experiment build (with ``barqkv_set_tuning``) instead, for parameter sweeps."""
+    path = _build.TUNING_LIBRARY if _env_enabled("BARQKV_TUNING_LIB", "0") else _build.LIBRARY
+    if not path.exists():
+        raise OSError(f"{path} has not been built")
+    return ctypes.CDLL(str(path))
 
 
 class BarqKVError(RuntimeError):
@@ -96,12 +102,14 @@ class CudaBackend:
         lib.barqkv_version.restype = _i32
         lib.barqkv_last_error.restype = ctypes.c_char_p
         lib.barqkv_sm_count.restype = _i32
-        lib.barqkv_set_tuning.restype = _i32
-        lib.barqkv_set_tuning.argtypes = [_i32, _i32]
+        self.tunable = hasattr(lib, "barqkv_set_tuning")
+        if self.tunable:
+            lib.barqkv_set_tuning.restype = _i32
+            lib.barqkv_set_tuning.argtypes = [_i32, _i32]
         P = ctypes.POINTER
         lib.barqkv_append.restype = _i32
         lib.barqkv_append.argtypes = [P(PoolLayout), _ptr, _ptr, P(BlockTable), _ptr, _ptr, _i32, _i32, _i32,
-                                      _ptr, _ptr, P(RowsLayout), _ptr, _ptr]
+                                      _ptr, _ptr, P(RowsLayout), _ptr, _ptr, _i32, _ptr]
         lib.barqkv_append_legacy.restype = _i32
         lib.barqkv_append_legacy.argtypes = [_ptr, _ptr, _ptr, _ptr, _ptr, P(RowsLayout),
                                              _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _ptr, _ptr, _ptr]
@@ -113,7 +121,7 @@ class CudaBackend:
                                              _ptr, _ptr, P(RowsLayout), _i64, _ptr, _ptr, _ptr]
         lib.barqkv_append_layers.restype = _i32
         lib.barqkv_append_layers.argtypes = [P(PoolLayout), _ptr, _ptr, _i32, _i64, P(BlockTable), _ptr, _ptr,
-                                             _i32, _i32, _i32, _ptr, _ptr, P(RowsLayout), _i64, _ptr, _ptr]
+                                             _i32, _i32, _i32, _ptr, _ptr, P(RowsLayout), _i64, _ptr, _ptr, _i32, _ptr]
         lib.barqkv_append_rope.restype = _i32
         lib.barqkv_append_rope.argtypes = [P(PoolLayout), _ptr, _ptr, P(BlockTable), _ptr, _ptr, _i32, _i32, _i32,
                                            _ptr, _ptr, P(RowsLayout), _ptr, _ptr, _i64, _i32, _ptr, _ptr]
@@ -133,11 +141,22 @@ class CudaBackend:
         lib.barqkv_update.argtypes = [P(PoolLayout), _ptr, _ptr, P(BlockTable), _ptr, _ptr, _i32, _i32, _i32,
                                       _ptr, _ptr, P(RowsLayout), _ptr, _i64, _ptr, _ptr, P(RowsLayout),
                                       _i32, _ptr, _ptr, _ptr, _ptr]
+        lib.barqkv_update_layers.restype = _i32
+        lib.barqkv_update_layers.argtypes = [P(PoolLayout), _ptr, _ptr, _i32, _i64, P(BlockTable), _ptr, _ptr, _i32, _i32,
+                                             _i32, _ptr, _ptr, P(RowsLayout), _i64, _ptr, _i64, P(_ptr), P(_ptr), _i32,
+                                             P(RowsLayout), _i32, _ptr, _ptr, _ptr, _ptr]
+        lib.barqkv_gather_wait_selftest.restype = _i32
+        lib.barqkv_gather_wait_selftest.argtypes = [P(PoolLayout), _ptr, _ptr, P(BlockTable), _ptr, _ptr, _i32, _ptr, _ptr,
+                                                    P(RowsLayout), _i64, _ptr, _ptr]
+        lib.barqkv_gather_noalloc.restype = _i32
+        lib.barqkv_gather_noalloc.argtypes = [P(PoolLayout), _ptr, _ptr, P(BlockTable), _ptr, _ptr, _i32, _i64,
+                                              _ptr, _ptr, P(RowsLayout), _i32, _ptr, _i32, _ptr]
         self.version = int(lib.barqkv_version())
         lib.barqkv_launch_count.restype = _i64
         self._status: Dict[int, "object"] = {}
         self._tickets: Dict[Tuple[int, int], "object"] = {}
         self._work: Dict[Tuple[int, int], "object"] = {}
+        self._work_turn: Dict[Tuple[int, int], int] = {}
         self._legacy_sig, self._legacy_plan, self._legacy_rows = None, None, None
         lib.barqkv_max_length.restype = _i32
         lib.barqkv_max_length.argtypes = [_ptr, _i32, ctypes.POINTER(_i32), _ptr]
@@ -190,7 +209,7 @@ class CudaBackend:
             raise BarqKVError("device-side guard: " + ", ".join(names))
 
     def work_words(self, device):
-        """Device int32[2] scratch of the bulk gather's page hand-out, one per (device, current stream)."""
+        """Device int32[4] scratch of the bulk kernels' page hand-out, one per (device, current stream)."""
         import torch
 
         device = torch.device(device)
@@ -198,27 +217,57 @@ class CudaBackend:
         key = (index, self._stream(torch.device("cuda", index)))
         words = self._work.get(key)
         if words is None:
-            words = torch.zeros(2, dtype=torch.int32, device=torch.device("cuda", index))
+            # two counter pairs: single launches use the first, barqkv_update_layers alternates between both
+            words = torch.zeros(4, dtype=torch.int32, device=torch.device("cuda", index))
             self._work[key] = words
         return words
+
+    def take_work(self, index: int, stream: int) -> int:
+        """Address of the counter pair the next bulk launch on ``stream`` should use.  The stream's four
+        words hold two pairs handed out in turn, so that two launches adjacent in the stream never share
+        one (a launch flagged ``FLAG_DESC_STABLE`` takes its first pages while its predecessor still runs)."""
+        import torch
+
+        key = (index, stream)
+        words = self._work.get(key)
+        if words is None:
+            words = torch.zeros(4, dtype=torch.int32, device=torch.device("cuda", index))
+            self._work[key] = words
+        turn = self._work_turn.get(key, 0)
+        self._work_turn[key] = turn ^ 1
+        return words.data_ptr() + 8 * turn
 
     def sm_count(self) -> int:
         return int(self.lib.barqkv_sm_count())
 
     def set_tuning(self, **knobs: int) -> None:
-        """Experiment knobs (process-wide; the ``BARQKV_KNOB_*`` values of the header). Gather: ``stages``,
-        ``ctas``, ``vctas``, ``interleave``, ``group``, ``static``, ``fixed``, ``pdl``, ``tensor_store``;
-        decode attention: ``attn_promotion``, ``attn_split``."""
+        """Experiment knobs (process-wide; the ``BARQKV_KNOB_*`` values of ``barqkv_experimental.h``); only a
+        library built with ``-DBARQKV_TUNING`` has them (``BARQKV_TUNING_LIB=1`` selects that build).  Gather:
+        ``stages``, ``ctas``, ``vctas``, ``interleave``, ``group``, ``static``, ``fixed``, ``pdl``, ``tensor_store``;
+        append: ``append_bulk``; decode attention: ``attn_promotion``, ``attn_split``."""
+        if not self.tunable:
+            raise BarqKVError("this libbarqkv.so has no tuning knobs: build the experiment library "
+                              "(barqtrain_b200._build.build_native(tuning=True)) and set BARQKV_TUNING_LIB=1")
         for name, value in knobs.items():
             self._check(self.lib.barqkv_set_tuning(KNOBS[name], int(value)))
 
     # -- raw calls (pointers as ints) -----------------------------------------
     def append_raw(self, pool: PoolLayout, k_pool: int, v_pool: int, table: BlockTable, seq_start: int,
                    cu_new: Optional[int], n: int, tokens_per_entry: int, total_tokens: int,
-                   k_new: int, v_new: int, rows: RowsLayout, status: Optional[int], stream: int) -> None:
+                   k_new: int, v_new: int, rows: RowsLayout, status: Optional[int], stream: int,
+                   work: Optional[int] = None) -> None:
         self._check(self.lib.barqkv_append(ctypes.byref(pool), k_pool, v_pool, ctypes.byref(table), seq_start, cu_new,
                                            n, tokens_per_entry, total_tokens, k_new, v_new, ctypes.byref(rows),
-                                           status, stream))
+                                           status, work, 0, stream))
+
+    def gather_noalloc_raw(self, pool: PoolLayout, k_pool: int, v_pool: int, table: BlockTable, seq_lens: int,
+                           cu_out: Optional[int], n: int, total_tokens_hint: int, k_out: int, v_out: int,
+                           rows: RowsLayout, mode: int, status: Optional[int], work_slot: int, stream: int) -> None:
+        """``barqkv_gather_noalloc``: the gather whose hand-out counters live in the library's built-in array
+        (``work_slot`` in ``range(STATIC_WORK_SLOTS)``), for callers that cannot allocate device memory."""
+        self._check(self.lib.barqkv_gather_noalloc(ctypes.byref(pool), k_pool, v_pool, ctypes.byref(table), seq_lens,
+                                                   cu_out, n, total_tokens_hint, k_out, v_out, ctypes.byref(rows), mode,
+                                                   status, work_slot, stream))
 
     def gather_raw(self, pool: PoolLayout, k_pool: int, v_pool: int, table: BlockTable, seq_lens: int,
                    cu_out: Optional[int], n: int, total_tokens_hint: int, k_out: int, v_out: int,

@@ -39,9 +39,13 @@ def chunked_prefill(world: int, rank: int, device, steps: int, warmup: int, page
                               max_blocks_per_seq=chunk * chunks // page_size, dtype=dtype, device=device,
                               seed=1237, zero_pages=False)
     gen = torch.Generator(device=device).manual_seed(1237 + rank)
-    k = torch.randn(B * chunk, H, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
-    v = torch.randn(B * chunk, H, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
-    k_all, v_all = k.expand(layers, -1, -1, -1), v.expand(layers, -1, -1, -1)
+    # every layer appends rows of its own ([layers, tokens, H, D] for K and for V), so no layer's reads can be
+    # served by what another layer left in L2
+    k_all = torch.empty(layers, B * chunk, H, D, dtype=dtype, device=device)
+    v_all = torch.empty_like(k_all)
+    for layer in range(layers):
+        k_all[layer] = torch.randn(B * chunk, H, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
+        v_all[layer] = torch.randn(B * chunk, H, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
     state = {"ids": list(range(B)), "slots": [cache.open(i) for i in range(B)], "done": 0, "next": B}
 
     def step():
@@ -57,7 +61,7 @@ def chunked_prefill(world: int, rank: int, device, steps: int, warmup: int, page
             cache.append_layers(batch, k_all, v_all)
         else:
             for layer in range(layers):
-                cache.append(layer, batch, k, v)
+                cache.append(layer, batch, k_all[layer], v_all[layer])
         cache.end_append(batch)
         state["done"] += 1
 
@@ -80,7 +84,8 @@ def chunked_prefill(world: int, rank: int, device, steps: int, warmup: int, page
                        "layers": layers, "kv_heads_per_gpu": H, "dtype": "fp16",
                        "page_size": page_size, "sequences": B, "chunk_tokens": chunk,
                        "step": "append one 2048-token chunk of 16 sequences in every layer",
-                       "l2": "inputs larger than L2: 268 MB per launch at 8 heads, pool 34 GB"}}
+                       "l2": "inputs larger than L2: every layer reads its own 134 MB of K and of V rows at 8 heads "
+                             "(%.1f GB of sources), pool %.0f GB" % (2 * k_all.numel() * 2 / 1e9, cache.pools.numel() * 2 / 1e9)}}
 
 
 def gather_70b(world: int, rank: int, device, steps: int, warmup: int, layers: int = 80, heads: int = 0,
@@ -178,7 +183,10 @@ def churn(world: int, rank: int, device, steps: int, warmup: int, layers: int = 
         for layer in range(layers):
             cache.append(layer, batch, rows[: sum(counts)], rows[: sum(counts)])
         cache.end_append(batch)
-    one_all = rows[:live].expand(layers, -1, -1, -1)          # the step's new rows, [layers, live, H, D]
+    # the step's new rows, [layers, live, H, D], and the replacement prompts' rows, [layers, 32 * 512, H, D]: every
+    # layer has rows of its own (layer l holds the shared rows, so that the read-back check stays simple)
+    one_all = rows[:live].unsqueeze(0).repeat(layers, 1, 1, 1)
+    prompt_all = rows[: 512 * 32].unsqueeze(0).repeat(layers, 1, 1, 1)
     finished = (torch.rand(total_steps, live, generator=g) < 0.01).numpy()
     ones = np.ones(live, dtype=np.int64)
     counters = {"tokens": 0, "host_s": 0.0, "released": 0, "launches": 0}
@@ -197,7 +205,8 @@ def churn(world: int, rank: int, device, steps: int, warmup: int, layers: int = 
         if gone:
             t0 = time.perf_counter()
             fresh = []
-            for j in gone[:32]:                                  # the packed prefill source holds 32 prompts
+            for j in gone[:32]:        # the packed prefill source holds 32 prompts; more than 32 of 256 finishing in
+                #                        one step at p = 0.01 has probability < 1e-30, the rest would wait a step
                 cache.release(ids[j])
                 ids[j] = next_id
                 next_id += 1
@@ -206,7 +215,7 @@ def churn(world: int, rank: int, device, steps: int, warmup: int, layers: int = 
                 fresh.append(slots[j])
             batch = cache.begin_append(fresh, [512] * len(fresh))
             counters["host_s"] += time.perf_counter() - t0
-            prompt = rows[: 512 * len(fresh)].expand(layers, -1, -1, -1)
+            prompt = prompt_all[:, : 512 * len(fresh)]
             cache.append_layers(batch, prompt, prompt)
             cache.end_append(batch)
             counters["tokens"] += 512 * len(fresh)

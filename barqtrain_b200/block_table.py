@@ -176,9 +176,11 @@ class _Descriptor:
 
     def __init__(self, n: int, dev: torch.Tensor, total: int, host_first, host_cu, slots, table_ref=None,
                  stream: int = 0, work: int = 0):
+        self.kind, self.generation = None, 0     # set by the cache: which shared device buffer holds it, and its turn
+        self.used_at = -1               # the cache's upload count when a kernel last used this description
         self.table_ref = table_ref      # ctypes reference to a barqkv_block_table whose `slots` points into `dev`
         self.stream = stream            # the CUDA stream the description was uploaded on
-        self.work = work                # gather only: the stream's hand-out counters
+        self.work = work                # the stream's hand-out counters (bulk gather, bulk append)
         self.n = n
         self.dev = dev
         self.total = total
@@ -265,6 +267,8 @@ class BlockTableKVCache:
         self._ring_pos = 0
         self._ring_words = 0
         self._desc_dev: Dict[str, torch.Tensor] = {}
+        self._desc_turn: Dict[str, int] = {}
+        self._uploads = 0               # descriptions uploaded + table scatters enqueued so far
         self._tables: Dict[str, _ffi.BlockTable] = {}
         self._status = self.backend.status_word(self.device)
         # per-call constants of the native calls, resolved once
@@ -377,12 +381,15 @@ class BlockTableKVCache:
         new_length = min(length, max(max_length, 0))
         keep = -(-new_length // self.page_size)
         pages = self.pages_of[slot]
+        fresh = None
+        if new_length % self.page_size and self.allocator.holders(pages[keep - 1]) > 1:
+            # The sequence will append into a page it shares: it gets a copy of its own.  That page is taken
+            # before anything is given back, so an exhausted pool raises with the cache unchanged.
+            fresh = int(self.allocator.take(1)[0])
         if keep < len(pages):
             self.allocator.give_back(pages[keep:])
             pages = pages[:keep]
-        if new_length % self.page_size and self.allocator.holders(pages[-1]) > 1:
-            # the sequence will append into a page it shares: give it a copy of its own first
-            fresh = int(self.allocator.take(1)[0])
+        if fresh is not None:
             self._copy_pages([(pages[-1], fresh)])
             self.allocator.give_back([pages[-1]])
             pages = pages[:-1] + [fresh]
@@ -485,6 +492,7 @@ class BlockTableKVCache:
         if rc:
             self.backend._check(rc)
         self._stage_done(stream)
+        self._uploads += 1
 
     def _describe(self, kind: str, slots, first, counts) -> _Descriptor:
         slots = np.array(slots, dtype=np.int64)            # a copy: the description keeps it
@@ -507,16 +515,35 @@ class BlockTableKVCache:
         if rc:
             self.backend._check(rc)
         self._stage_done(cur)
+        self._uploads += 1
         table = self._tables.get(kind)
         if table is None:
             table = _ffi.BlockTable(self.table_dev.data_ptr(), None, self.max_seqs, self.max_blocks, 0, 0)
             self._tables[kind] = table
         table.slots = dev.data_ptr()
         stream = cur.cuda_stream
-        work = self.backend.work_words(self.device).data_ptr() if kind == "gather" else 0
+        work = self.backend.work_words(self.device).data_ptr()      # the stream's hand-out counters
         desc = _Descriptor(n, dev, int(cu[n]), first, cu, slots, ctypes.byref(table), stream, work)
         desc.slots_np, desc.after_np = slots, first + (cu[1:] - cu[:-1])
         desc.max_first = int(first.max()) if n else 0
+        # The device buffer of a kind is rewritten by the next begin_* of that kind: an older description
+        # would silently address the newer one's contents, so every use checks that it is still current.
+        self._desc_turn[kind] = self._desc_turn.get(kind, 0) + 1
+        desc.kind, desc.generation = kind, self._desc_turn[kind]
+        return desc
+
+    def _launch_terms(self, desc: _Descriptor) -> Tuple[int, int]:
+        """(work pointer, flag) for the next kernel that uses ``desc``.  The flag says that nothing the kernel
+        reads besides K/V has been uploaded or scattered since an earlier kernel used the same description -
+        true from the second layer of a step on - which lets the kernel's prologue overlap its predecessor."""
+        flag = _ffi.FLAG_DESC_STABLE if desc.used_at == self._uploads else 0
+        desc.used_at = self._uploads
+        return self.backend.take_work(self.device.index, desc.stream), flag
+
+    def _current(self, desc: _Descriptor) -> _Descriptor:
+        if desc.kind is not None and desc.generation != self._desc_turn.get(desc.kind):
+            raise RuntimeError(f"this {desc.kind} description is stale: a later begin_{desc.kind} of this cache "
+                               f"has rewritten the device buffer it points to")
         return desc
 
     # -- append -------------------------------------------------------------------
@@ -546,7 +573,7 @@ class BlockTableKVCache:
 
         ``rope=(cos, sin)``, each ``[total_tokens, head_dim]`` in the cache dtype: the K rows are stored as
         ``k * cos + rotate_half(k) * sin`` (bit-identical to rotating first), saving that separate pass."""
-        total = batch.total
+        total = self._current(batch).total
         if total == 0:
             return
         shape = k_new.shape
@@ -584,9 +611,10 @@ class BlockTableKVCache:
             if rc:
                 self.backend._check(rc)
             return
+        work, flag = self._launch_terms(batch)
         rc = self._c_append(self._pool_ref, self._k_ptr[layer], self._v_ptr[layer], batch.table_ref,
                             batch.p_first, batch.p_cu, batch.n, 0, total, k_new.data_ptr(), v_new.data_ptr(),
-                            rows_ref, self._status_ptr, batch.stream)
+                            rows_ref, self._status_ptr, work, flag, batch.stream)
         if rc:
             self.backend._check(rc)
 
@@ -594,7 +622,7 @@ class BlockTableKVCache:
         """All layers' appends of a step in one launch: ``k_all`` / ``v_all`` are
         ``[num_layers, total_tokens, kv_heads, head_dim]`` (any layer and token strides, contiguous
         last dimension)."""
-        total = batch.total
+        total = self._current(batch).total
         if total == 0:
             return
         shape = k_all.shape
@@ -614,7 +642,7 @@ class BlockTableKVCache:
         rc = self.backend.lib.barqkv_append_layers(
             self._pool_ref, self._k_ptr[0], self._v_ptr[0], self.num_layers, self.pools.stride(0), batch.table_ref,
             batch.p_first, batch.p_cu, batch.n, 0, total, k_all.data_ptr(), v_all.data_ptr(), rows_ref, strides[0],
-            self._status_ptr, batch.stream)
+            self._status_ptr, self.backend.take_work(self.device.index, batch.stream), 0, batch.stream)
         if rc:
             self.backend._check(rc)
 
@@ -716,28 +744,33 @@ class BlockTableKVCache:
         flash-attention operand).  ``batch.cu`` holds the offsets.  ``out`` may be a pair of
         larger fixed-capacity buffers (see ``_output``); views of the filled part are returned.
         """
-        total = batch.total
+        total = self._current(batch).total
         k_out, v_out, rows_ref, views = self._output(layout, total, out, batch.n)
         if total == 0:
             return views
         if batch.n > _GATHER_MAX_ENTRIES:
-            # a launch scans at most 8192 sequences: larger batches go in slices of the same description
-            # (the offsets in ``cu`` are absolute, so every slice writes to its own part of the output)
+            # a launch scans at most 8192 sequences: larger batches go in slices of the same description.
+            # Packed outputs: the offsets in ``cu`` are absolute, so every slice writes to its own part.
+            # Padded [n, H, S, D] outputs are addressed by the entry's index within the launch, so a
+            # slice's output pointers start at its first batch row.
+            row_bytes = k_out.stride(0) * self.elem if layout == "BHSD" else 0
             for lo in range(0, batch.n, _GATHER_MAX_ENTRIES):
                 count = min(_GATHER_MAX_ENTRIES, batch.n - lo)
                 table = _ffi.BlockTable(self.table_dev.data_ptr(), batch.p_slots + 4 * lo, self.max_seqs,
                                         self.max_blocks, 0, 0)
                 rc = self._c_gather(self._pool_ref, self._k_ptr[layer], self._v_ptr[layer], ctypes.byref(table),
                                     batch.p_first + 4 * lo, batch.p_cu + 4 * lo, count,
-                                    batch.cu[lo + count] - batch.cu[lo], k_out.data_ptr(), v_out.data_ptr(),
-                                    rows_ref, _ffi.MODES[mode or self.gather_mode], self._status_ptr, batch.work,
-                                    batch.stream)
+                                    batch.cu[lo + count] - batch.cu[lo], k_out.data_ptr() + lo * row_bytes,
+                                    v_out.data_ptr() + lo * row_bytes,
+                                    rows_ref, _ffi.MODES[mode or self.gather_mode], self._status_ptr,
+                                    self.backend.take_work(self.device.index, batch.stream), batch.stream)
                 if rc:
                     self.backend._check(rc)
             return views
+        work, flag = self._launch_terms(batch)
         rc = self._c_gather(self._pool_ref, self._k_ptr[layer], self._v_ptr[layer], batch.table_ref,
                             batch.p_first, batch.p_cu, batch.n, total, k_out.data_ptr(), v_out.data_ptr(),
-                            rows_ref, _ffi.MODES[mode or self.gather_mode], self._status_ptr, batch.work,
+                            rows_ref, _ffi.MODES[mode or self.gather_mode] | flag, self._status_ptr, work,
                             batch.stream)
         if rc:
             self.backend._check(rc)
@@ -754,7 +787,7 @@ class BlockTableKVCache:
         """
         if layout not in ("HND", "NHD"):
             raise ValueError("layout must be 'HND' or 'NHD'")
-        total, L, H, D = batch.total, self.num_layers, self.num_kv_heads, self.head_dim
+        total, L, H, D = self._current(batch).total, self.num_layers, self.num_kv_heads, self.head_dim
         shape = (L, H, total, D) if layout == "HND" else (L, total, H, D)
         if out is None:
             out = (torch.empty(shape, dtype=self.dtype, device=self.device),
@@ -781,7 +814,7 @@ class BlockTableKVCache:
         rc = self.backend.lib.barqkv_gather_layers(
             self._pool_ref, self._k_ptr[0], self._v_ptr[0], L, self.pools.stride(0), batch.table_ref, batch.p_first,
             batch.p_cu, batch.n, total, k_out.data_ptr(), v_out.data_ptr(), rows_ref, k_out.stride(0),
-            self._status_ptr, batch.work, batch.stream)
+            self._status_ptr, self.backend.take_work(self.device.index, batch.stream), batch.stream)
         if rc:
             self.backend._check(rc)
         return k_out, v_out
@@ -797,6 +830,7 @@ class BlockTableKVCache:
         ``begin_gather`` of the same slots made after it.  For decode-sized appends this is one
         kernel launch instead of two.
         """
+        self._current(new), self._current(full)
         if full.n != new.n or not np.array_equal(full.slots_np, new.slots_np):
             raise ValueError("update: the append and gather descriptions must list the same slots")
         if full.n > _GATHER_MAX_ENTRIES:             # beyond one launch's scan: append, then gather in slices
@@ -823,14 +857,67 @@ class BlockTableKVCache:
             new_ref, k_ptr, v_ptr = self._rows_ref(0, H * D, D), None, None
         if total == 0:
             return views
+        work, flag = self._launch_terms(full)
+        if new.used_at != self._uploads:          # both descriptions must be unchanged since their last use
+            flag = 0
+        new.used_at = self._uploads
         rc = self._c_update(self._pool_ref, self._k_ptr[layer], self._v_ptr[layer], new.table_ref,
                             new.p_first, new.p_cu, new.n, 0, new.total, k_ptr, v_ptr, new_ref,
                             full.p_cu, tokens_hint or total, k_out.data_ptr(), v_out.data_ptr(), out_ref,
-                            _ffi.MODES[mode or self.gather_mode], self._status_ptr, full.work, full.p_first,
+                            _ffi.MODES[mode or self.gather_mode] | flag, self._status_ptr, work, full.p_first,
                             full.stream)
         if rc:
             self.backend._check(rc)
         return views
+
+    def update_layers(self, new: _Descriptor, full: _Descriptor, k_all: torch.Tensor, v_all: torch.Tensor,
+                      outs: Sequence[Tuple[torch.Tensor, torch.Tensor]], layout: str = "HND",
+                      mode: Optional[str] = None, tokens_hint: Optional[int] = None) -> None:
+        """``update`` of every layer with one native call (``barqkv_update_layers``): ``k_all`` / ``v_all`` are
+        ``[num_layers, new_tokens, kv_heads, head_dim]``; layer ``l`` writes its gathered rows to
+        ``outs[l % len(outs)]`` (pairs of fixed-capacity buffers as ``update`` takes them).  For callers that
+        hold every layer's new rows before the first launch - a recorded decode step."""
+        self._current(new), self._current(full)
+        if full.n != new.n or not np.array_equal(full.slots_np, new.slots_np):
+            raise ValueError("update_layers: the append and gather descriptions must list the same slots")
+        L, H, D = self.num_layers, self.num_kv_heads, self.head_dim
+        shape = k_all.shape
+        if shape != v_all.shape or len(shape) != 4 or shape[0] != L or shape[1] != new.total or shape[2] != H \
+                or shape[3] != D:
+            raise ValueError(f"new rows must both be {(L, new.total, H, D)}")
+        if k_all.dtype != self.dtype or v_all.dtype != self.dtype or k_all.device != self.device \
+                or v_all.device != self.device:
+            raise ValueError("new rows must be in the cache dtype on the cache device")
+        strides = k_all.stride()
+        if strides[3] != 1 or v_all.stride() != strides:
+            k_all, v_all = k_all.contiguous(), v_all.contiguous()
+            strides = k_all.stride()
+        if full.n > _GATHER_MAX_ENTRIES or full.total == 0 or new.total == 0:
+            for layer in range(L):
+                self.update(layer, new, full, k_all[layer], v_all[layer], layout, out=outs[layer % len(outs)], mode=mode,
+                            tokens_hint=tokens_hint)
+            return
+        new_ref = self._rows.get(strides[1:])
+        if new_ref is None:
+            new_ref = self._rows[strides[1:]] = self._rows_ref(0, strides[1], strides[2])
+        out_ref = None
+        k_ptrs, v_ptrs = (ctypes.c_void_p * len(outs))(), (ctypes.c_void_p * len(outs))()
+        for i, out in enumerate(outs):
+            k_out, v_out, ref, _ = self._output(layout, full.total, out, full.n)
+            if out_ref is not None and ref is not out_ref:
+                raise ValueError("update_layers: all output pairs must have the same shape")
+            out_ref = ref
+            k_ptrs[i], v_ptrs[i] = k_out.data_ptr(), v_out.data_ptr()
+        rc = self.backend.lib.barqkv_update_layers(
+            self._pool_ref, self._k_ptr[0], self._v_ptr[0], L, self.pools.stride(0), new.table_ref, new.p_first, new.p_cu,
+            new.n, 0, new.total, k_all.data_ptr(), v_all.data_ptr(), new_ref, strides[0], full.p_cu,
+            tokens_hint or full.total, k_ptrs, v_ptrs, len(outs), out_ref, _ffi.MODES[mode or self.gather_mode],
+            self._status_ptr, full.work, full.p_first, full.stream)
+        # the layers alternated between the stream's two counter pairs starting with the first: the next
+        # launch on this stream takes the pair the last layer did not use
+        self.backend._work_turn[(self.device.index, full.stream)] = (L & 1)
+        if rc:
+            self.backend._check(rc)
 
     # -- attention straight from the pages (decode) ---------------------------------------
     def decode_attention(self, layer: int, full: _Descriptor, q: torch.Tensor, scale: Optional[float] = None,
@@ -841,6 +928,7 @@ class BlockTableKVCache:
         ``q`` is ``[n, num_q_heads, head_dim]`` in the cache dtype, ``num_q_heads`` a multiple (<= 8x) of
         the KV heads on this device.  Returns ``[n, num_q_heads, head_dim]``.  No gather is involved.
         """
+        self._current(full)
         if q.dim() != 3 or q.shape[0] != full.n or q.shape[2] != self.head_dim or q.stride(2) != 1:
             raise ValueError(f"q must be [{full.n}, num_q_heads, {self.head_dim}] with a contiguous last dimension")
         if q.dtype != self.dtype or q.device != self.device or self.dtype not in (torch.bfloat16, torch.float16):
@@ -860,11 +948,14 @@ class BlockTableKVCache:
             # calls leave their own tickets zero, but a smaller batch's partial results may lie where a
             # larger batch's tickets go
             tickets = 4 * full.n * self.num_kv_heads
-            if need > self._attn_ws_bytes:
-                self._attn_ws = torch.zeros(need, dtype=torch.uint8, device=self.device)
-                self._attn_ws_bytes = need
-            elif tickets > self._attn_tickets:
-                self._attn_ws[:tickets].zero_()
+            # allocated and zero-filled on the stream the kernel will run on (the description's), so the
+            # fill is ordered before the launch and a freed workspace is not reused under a running kernel
+            with torch.cuda.stream(torch.cuda.ExternalStream(full.stream, device=self.device)):
+                if need > self._attn_ws_bytes:
+                    self._attn_ws = torch.zeros(need, dtype=torch.uint8, device=self.device)
+                    self._attn_ws_bytes = need
+                elif tickets > self._attn_tickets:
+                    self._attn_ws[:tickets].zero_()
             self._attn_tickets = tickets
         ws_ptr = self._attn_ws.data_ptr() if need else None
         if scale is None:
@@ -918,8 +1009,13 @@ class DecodeStepGraph:
     """
 
     def __init__(self, cache: BlockTableKVCache, slots: Sequence[int], capacity_tokens: int,
-                 mode: Optional[str] = None):
-        self.cache, self.slots, self.mode = cache, list(slots), mode
+                 mode: Optional[str] = None, what: str = "update"):
+        """``what``: ``"update"`` (append + gather per layer, the default), ``"append"`` (the append alone, one
+        launch per layer) or ``"append_layers"`` (the append alone, one launch for all layers); the append-only
+        forms need no output buffers and ignore ``capacity_tokens``."""
+        if what not in ("update", "append", "append_layers"):
+            raise ValueError("what must be 'update', 'append' or 'append_layers'")
+        self.cache, self.slots, self.mode, self.what = cache, list(slots), mode, what
         c = cache
         B = len(self.slots)
         self.capacity = int(capacity_tokens)
@@ -929,7 +1025,7 @@ class DecodeStepGraph:
         self._k_rows, self._v_rows = self.k_in.unbind(0), self.v_in.unbind(0)
         self.bufs = [(torch.empty(c.num_kv_heads, self.capacity, c.head_dim, dtype=c.dtype, device=c.device),
                       torch.empty(c.num_kv_heads, self.capacity, c.head_dim, dtype=c.dtype, device=c.device))
-                     for _ in range(2)]
+                     for _ in range(2)] if what == "update" else []
         self.total = 0
         self.steps = 0
         self.launches_per_replay = 0
@@ -953,9 +1049,17 @@ class DecodeStepGraph:
 
     def _launch_layers(self) -> None:
         c = self.cache
-        for layer in range(c.num_layers):
-            c.update(layer, self._new, self._full, self._k_rows[layer], self._v_rows[layer], "HND",
-                     out=self.bufs[layer & 1], mode=self.mode, tokens_hint=self.capacity)
+        if self.what == "append":
+            for layer in range(c.num_layers):
+                c.append(layer, self._new, self._k_rows[layer], self._v_rows[layer])
+            return
+        if self.what == "append_layers":
+            c.append_layers(self._new, self.k_in, self.v_in)
+            return
+        # one native call issues every layer's launch; from the second layer on each is a programmatic
+        # dependent of the one before (its prologue overlaps that layer's tail)
+        self.cache.update_layers(self._new, self._full, self.k_in, self.v_in, self.bufs, "HND", mode=self.mode,
+                                 tokens_hint=self.capacity)
 
     def _describe_step(self) -> int:
         """Host side of a step: pages for the new tokens, new lengths, one upload of both descriptions."""
@@ -963,7 +1067,7 @@ class DecodeStepGraph:
         first = c.lengths[sl]
         after = first + 1
         total = int(after.sum())
-        if total > self.capacity:
+        if total > self.capacity and self.what == "update":
             raise ValueError(f"decode graph capacity {self.capacity} tokens exceeded by {total}")
         need = -(-after // c.page_size)
         have = c._page_count[sl]
@@ -984,6 +1088,7 @@ class DecodeStepGraph:
         if rc:
             c.backend._check(rc)
         c._stage_done(self.stream)
+        c._uploads += 1
         self._full.total = total
         return total
 
@@ -1011,6 +1116,7 @@ class DecodeStepGraph:
         if self.steps == 0:
             raise RuntimeError("run one eager step() before record(): the first launch sets kernel attributes")
         torch.cuda.synchronize(c.device)
+        self._new.used_at = self._full.used_at = -1      # the first recorded launch waits for whatever precedes a replay
         with torch.cuda.stream(self.stream):
             graph = torch.cuda.CUDAGraph()
             counted = c.backend.launches

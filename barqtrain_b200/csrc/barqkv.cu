@@ -42,12 +42,17 @@
 #include <cuda_runtime.h>
 #include <cudaTypedefs.h>
 #include <atomic>
+#include <mutex>
 #include <initializer_list>
 #include <stdint.h>
 #include <stdio.h>
 #include <string.h>
+#include <utility>
 
 #include "barqkv.h"
+#ifdef BARQKV_TUNING
+#include "barqkv_experimental.h"
+#endif
 
 namespace {
 
@@ -59,6 +64,7 @@ constexpr int kGroup = 32;             // (sequence, page) tiles resolved at a t
 constexpr int kUnroll = 4;
 constexpr int kBulkMaxStage = 32 * 1024;   // K page + V page of one head
 constexpr long long kWaitCycles = 2000000000LL;  // ~1 s: bound of any mbarrier wait
+constexpr long long kDrainCycles = 2000000LL;    // ~1 ms: after a give-up, per copy still on its way
 
 thread_local char g_err[256] = "";
 std::atomic<long long> g_launches{0};   // kernels enqueued by this library, process-wide
@@ -108,6 +114,8 @@ struct AppendArgs {
     int32_t* seq_lens_rw;
     int32_t* ticket;
     int capacity;
+    int early;              // the batch description and the block table are older than the kernel before this one in
+                            // the stream: they may be read while that kernel is still running
     int32_t* status;
 };
 
@@ -132,6 +140,10 @@ struct GatherArgs {
     int layers;            // bulk kernel: the batch is gathered from this many pools, one launch (1 = the usual case)
     long long pool_layer, out_layer;   // byte strides between layers' pools and outputs
     int tensor_store;      // bulk kernel: full pages go to a row-strided output with one tiled TMA store per K/V
+    int early;             // bulk kernel: the batch description and the block table are older than the kernel before
+                           // this one in the stream, so they may be read before that kernel has finished
+    long long wait_cycles; // bulk kernel: bound of every mbarrier wait, in clock cycles
+    int extra_tx;          // bulk kernel, self-test only: bytes every stage expects beyond those its copies bring
     int32_t* status;
     // Fused append ("update", bulk kernel only; k_new == null means plain gather): seq_lens then holds
     // the lengths BEFORE the append, entry i brings cu_new[i+1]-cu_new[i] (or tokens_per_entry) new rows,
@@ -146,9 +158,10 @@ struct GatherArgs {
 };
 
 // Programmatic dependent launch: a kernel launched with the stream-serialization attribute may become
-// resident while the kernel before it in the stream is still running.  Every kernel here lets its
-// successor in early and itself waits, before touching global memory, until its predecessor has
-// completed and flushed; without the launch attribute both instructions do nothing.
+// resident while the kernel before it in the stream is still running.  pdl_wait_for_predecessor() blocks
+// until that kernel has completed and its writes are visible; pdl_let_successor_in() allows the kernel
+// after this one to become resident.  Every kernel here calls them in that order, so at most two kernels
+// of a stream overlap.  Without the launch attribute both instructions do nothing.
 __device__ __forceinline__ void pdl_let_successor_in() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait_for_predecessor() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
@@ -215,8 +228,10 @@ append_rows_kernel(const AppendArgs a) {
     const int ntok = min(a.tile, a.total_tokens - first_tok);
     const long long layer_pool = (long long)blockIdx.y * a.pool_layer;
     const long long layer_new = (long long)blockIdx.y * a.new_layer;
-    pdl_let_successor_in();
-    pdl_wait_for_predecessor();
+    if (LEGACY || !a.early) {
+        pdl_wait_for_predecessor();
+        pdl_let_successor_in();
+    }
 
     bool refuse = false;
     if (LEGACY) {
@@ -233,6 +248,10 @@ append_rows_kernel(const AppendArgs a) {
 
     if (tid < ntok && !refuse) resolve_new_token(a, first_tok + tid, &s_dst[tid], &s_src[tid]);
     __syncthreads();
+    if (!LEGACY && a.early) {
+        pdl_wait_for_predecessor();     // the look-ups above ran beside the previous kernel's tail; the rows wait for it
+        pdl_let_successor_in();
+    }
 
     if (!refuse) {
         const int vpr = a.row_bytes / (int)sizeof(V);      // vectors per row
@@ -337,8 +356,8 @@ append_rope_kernel(const AppendArgs a, const RopeArgs rp) {
     const int tid = threadIdx.x;
     const int first_tok = blockIdx.x * a.tile;
     const int ntok = min(a.tile, a.total_tokens - first_tok);
-    pdl_let_successor_in();
     pdl_wait_for_predecessor();
+    pdl_let_successor_in();
     if (tid < ntok) resolve_new_token(a, first_tok + tid, &s_dst[tid], &s_src[tid]);
     __syncthreads();
 
@@ -400,8 +419,8 @@ struct CopyArgs {
 template <typename V>
 __global__ void __launch_bounds__(128)
 copy_pages_kernel(const CopyArgs a) {
-    pdl_let_successor_in();
     pdl_wait_for_predecessor();
+    pdl_let_successor_in();
     const int pair = blockIdx.x / a.heads;
     const int head = blockIdx.x - pair * a.heads;
     const int from = a.src[pair], to = a.dst[pair];
@@ -422,8 +441,8 @@ copy_pages_kernel(const CopyArgs a) {
 // pairs[2*i] = flat index into the table, pairs[2*i+1] = new page id (or -1)
 __global__ void __launch_bounds__(128)
 table_scatter_kernel(int32_t* __restrict__ table, const int32_t* __restrict__ pairs, int n, long long table_words) {
-    pdl_let_successor_in();
     pdl_wait_for_predecessor();
+    pdl_let_successor_in();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) {
         const long long at = pairs[2 * i];
@@ -522,8 +541,8 @@ gather_vector_kernel(const GatherArgs a) {
     __shared__ int s_rows[kGroup];
 
     int* s_cu = s_dyn;
-    pdl_let_successor_in();
     pdl_wait_for_predecessor();
+    pdl_let_successor_in();
     scan_pages(a, s_cu, s_part);
     const int total = s_cu[a.n];
     int lo, hi, group_step;
@@ -675,8 +694,13 @@ gather_bulk_kernel(const GatherArgs a, const __grid_constant__ CUtensorMap out_m
         for (int s = 0; s < S; ++s) mbar_init(smem_addr(&s_bar[s]), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    pdl_let_successor_in();
-    pdl_wait_for_predecessor();
+    // Everything up to the first copy reads only the batch description and the block table.  When the
+    // caller vouches that those are older than the kernel before this one (a.early), that part runs
+    // while that kernel is still draining; otherwise it starts after it.
+    if (!a.early) {
+        pdl_wait_for_predecessor();
+        pdl_let_successor_in();
+    }
     // The first group's size comes from the host's bound of the tile count, so its fetch can travel
     // to L2 and back while the lengths are being scanned.
     const bool early = a.work != nullptr && a.static_permille == 0;
@@ -742,23 +766,31 @@ gather_bulk_kernel(const GatherArgs a, const __grid_constant__ CUtensorMap out_m
     long long issued = 0, consumed = 0;
     bool dead = false;
 
+    // Resolve the current group's tiles (block-table look-ups included) into shared memory.
+    auto stage_group = [&]() {
+        __syncwarp();
+        if (lane < gt && group_base + lane < end) {
+            const int flat = group_base + lane;
+            const int layer = a.layers > 1 ? flat / tiles : 0;
+            const TileInfo t = resolve_tile(a, s_cu, flat - layer * tiles);
+            s_src[lane] = t.src + layer * a.pool_layer;
+            s_dst[lane] = t.dst + layer * a.out_layer;
+            s_new[lane] = t.new_src;
+            s_rows[lane] = t.rows;
+            s_rows_old[lane] = t.rows_old;
+        }
+        __syncwarp();
+        staged = true;
+    };
+    if (a.early) {
+        if (more) stage_group();
+        pdl_wait_for_predecessor();     // from here on the pools, the new rows and the outputs are touched
+        pdl_let_successor_in();
+    }
+
     while ((more || consumed < issued) && !dead) {
         if (more) {
-            if (!staged) {
-                __syncwarp();
-                if (lane < gt && group_base + lane < end) {
-                    const int flat = group_base + lane;
-                    const int layer = a.layers > 1 ? flat / tiles : 0;
-                    const TileInfo t = resolve_tile(a, s_cu, flat - layer * tiles);
-                    s_src[lane] = t.src + layer * a.pool_layer;
-                    s_dst[lane] = t.dst + layer * a.out_layer;
-                    s_new[lane] = t.new_src;
-                    s_rows[lane] = t.rows;
-                    s_rows_old[lane] = t.rows_old;
-                }
-                __syncwarp();
-                staged = true;
-            }
+            if (!staged) stage_group();
             if (issued >= S) {
                 bulk_wait_read<1>();       // the stores that read this stage one ring round ago are done with it
                 __syncwarp();
@@ -777,7 +809,7 @@ gather_bulk_kernel(const GatherArgs a, const __grid_constant__ CUtensorMap out_m
                     s_slot_tok[islot] = (int)(s_dst[ti] / a.orow.tok);
                     s_slot_head[islot] = head;
                 }
-                if (bytes) mbar_arrive_expect(bar, 2 * bytes); else mbar_arrive(bar);
+                if (bytes) mbar_arrive_expect(bar, 2 * bytes + (uint32_t)a.extra_tx); else mbar_arrive(bar);
             }
             __syncwarp();
             unsigned char* stage = s_data + (size_t)islot * 2 * page_bytes;
@@ -820,7 +852,7 @@ gather_bulk_kernel(const GatherArgs a, const __grid_constant__ CUtensorMap out_m
             const uint32_t bar = smem_addr(&s_bar[cslot]);
             const long long t0 = clock64();
             while (!mbar_try_wait(bar, cphase)) {
-                if (clock64() - t0 > kWaitCycles) { dead = true; break; }
+                if (clock64() - t0 > a.wait_cycles) { dead = true; break; }
             }
             dead = __any_sync(0xffffffffu, dead);
             if (!dead) {
@@ -861,7 +893,20 @@ gather_bulk_kernel(const GatherArgs a, const __grid_constant__ CUtensorMap out_m
         }
     }
     bulk_wait_read<0>();
-    if (dead && lane == 0) raise(a.status, BARQKV_S_TIMEOUT);
+    if (dead) {
+        // Gave up on a wait: nothing more is issued.  Copies already on their way into this CTA's shared
+        // memory get a last, short chance to land before the CTA leaves (a landed copy flips its barrier;
+        // one that never will is not waited for twice).
+        const long long grace = a.wait_cycles < kDrainCycles ? a.wait_cycles : kDrainCycles;
+        while (consumed < issued) {
+            const uint32_t bar = smem_addr(&s_bar[cslot]);
+            const long long t0 = clock64();
+            while (!mbar_try_wait(bar, cphase) && clock64() - t0 <= grace) {}
+            ++consumed;
+            if (++cslot == S) { cslot = 0; cphase ^= 1; }
+        }
+        if (lane == 0) raise(a.status, BARQKV_S_TIMEOUT);
+    }
     if (dynamic && lane == 0) {
         // The last CTA to finish re-arms the counters for the next launch.
         __threadfence();
@@ -875,40 +920,284 @@ gather_bulk_kernel(const GatherArgs a, const __grid_constant__ CUtensorMap out_m
 }
 
 // --------------------------------------------------------------------------
+// append with bulk asynchronous copies (page-sized appends: prefill chunks)
+// --------------------------------------------------------------------------
+// The mirror image of the bulk gather.  A "tile" is the part of one page that one batch entry's new
+// tokens fill (a whole page except at the ends of the entry's token range); a "unit" is a tile of one
+// head, K and V together in one ring stage.  The new rows of a unit come in with ONE copy per K / V:
+//   - rows of a head adjacent in memory ([heads, tokens, head_dim] sources): a plain bulk copy;
+//   - token-major sources ([tokens, heads, head_dim], rows of a head one token-stride apart): a tiled
+//     TMA load of a [page_size][1 head][head_dim] box starting at the tile's first token.  The box is
+//     always page_size rows; rows past the tile (the next tokens, or zero fill past the last token)
+//     land in the stage and are simply not stored.  The innermost coordinate is always 0.
+// and leave with one bulk store into the page's slots.  Units are handed to the persistent one-warp
+// CTAs through the same atomic counter scheme as in the gather.  No multicast, no peer memory.
+struct AppendBulkArgs {
+    int stages;
+    int32_t* work;          // [0] next tile to hand out, [1] CTAs finished
+    int group_tiles, first_group;
+    int tensor_load;        // 1: tiled TMA loads (token-major source); 0: plain bulk copies (rows adjacent)
+    int layers;
+    long long wait_cycles;
+};
+
+// Tiles entry i contributes: pages its new tokens touch.
+__device__ __forceinline__ int entry_new_tiles(const AppendArgs& a, int i) {
+    const int cnt = a.cu_new ? a.cu_new[i + 1] - a.cu_new[i] : a.tokens_per_entry;
+    const int start = a.seq_start[i];
+    if (cnt <= 0 || start < 0) return 0;
+    return (start + cnt - 1) / a.page_size - start / a.page_size + 1;
+}
+
+__global__ void __launch_bounds__(32)
+append_bulk_kernel(const AppendArgs a, const AppendBulkArgs x, const __grid_constant__ CUtensorMap map_k,
+                   const __grid_constant__ CUtensorMap map_v) {
+    extern __shared__ __align__(128) unsigned char s_raw[];
+    const int lane = threadIdx.x;
+    const int S = x.stages;
+    const int lag = S - 2;
+    const int page_bytes = a.page_size * a.row_bytes;
+
+    unsigned char* s_data = s_raw;                                          // [S][2][page_bytes]
+    unsigned long long* s_bar = reinterpret_cast<unsigned long long*>(s_data + (size_t)S * 2 * page_bytes);
+    long long* s_slot_dst = reinterpret_cast<long long*>(s_bar + S);        // [S] pool offset incl. head and first row
+    long long* s_dst = s_slot_dst + S;                                      // [kGroup] pool offset of the tile's first row, head 0
+    long long* s_src = s_dst + kGroup;                                      // [kGroup] byte offset of the tile's first new row, head 0
+    int* s_tok = reinterpret_cast<int*>(s_src + kGroup);                    // [kGroup] flat index of the tile's first new token
+    int* s_rows = s_tok + kGroup;                                           // [kGroup]
+    int* s_lay = s_rows + kGroup;                                           // [kGroup]
+    int* s_slot_rows = s_lay + kGroup;                                      // [S]
+    int* s_cu = s_slot_rows + S;                                            // [n + 1]
+
+    if (lane == 0) {
+        for (int s = 0; s < S; ++s) mbar_init(smem_addr(&s_bar[s]), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (!a.early) {
+        pdl_wait_for_predecessor();
+        pdl_let_successor_in();
+    }
+    int early_first = 0;
+    if (lane == 0) early_first = atomicAdd(x.work, x.first_group);
+
+    // exclusive prefix sum of the entries' tile counts (one warp; the batch is small)
+    {
+        const int n = a.n;
+        const int chunk = (n + 31) / 32;
+        const int lo = min(n, lane * chunk), hi = min(n, lo + chunk);
+        int sum = 0;
+        for (int i = lo; i < hi; ++i) sum += entry_new_tiles(a, i);
+        int incl = sum;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int up = __shfl_up_sync(0xffffffffu, incl, d);
+            if (lane >= d) incl += up;
+        }
+        int run = incl - sum;
+        for (int i = lo; i < hi; ++i) {
+            s_cu[i] = run;
+            run += entry_new_tiles(a, i);
+        }
+        const int all = __shfl_sync(0xffffffffu, incl, 31);
+        if (lane == 0) s_cu[n] = all;
+        __syncwarp();
+    }
+    const int tiles = s_cu[a.n];
+    const int total = tiles * x.layers;
+    const int gt_max = x.group_tiles;
+    int gt, group_base;
+    int pending = 0, pending_n = 0;
+    auto fetch_ahead = [&](int seen) {
+        int k = (total - seen) / (2 * (int)gridDim.x);
+        k = max(1, min(k, gt_max));
+        pending_n = k;
+        pending = atomicAdd(x.work, k);
+    };
+    group_base = min(total, __shfl_sync(0xffffffffu, early_first, 0));
+    gt = x.first_group;
+    if (lane == 0 && group_base < total) fetch_ahead(group_base);
+
+    bool more = group_base < total;
+    bool staged = false;
+    int ti = 0, head = 0;
+    int islot = 0, cslot = 0;
+    uint32_t cphase = 0;
+    long long issued = 0, consumed = 0;
+    bool dead = false;
+
+    auto stage_group = [&]() {
+                __syncwarp();
+                if (lane < gt && group_base + lane < total) {
+                    const int flat = group_base + lane;
+                    const int layer = x.layers > 1 ? flat / tiles : 0;
+                    const int q = flat - layer * tiles;
+                    int lo = 0, hi = a.n - 1;             // largest i with s_cu[i] <= q
+                    while (lo < hi) {
+                        const int mid = (lo + hi + 1) >> 1;
+                        if (s_cu[mid] <= q) lo = mid; else hi = mid - 1;
+                    }
+                    const int i = lo;
+                    const int start = a.seq_start[i];
+                    const int cnt = a.cu_new ? a.cu_new[i + 1] - a.cu_new[i] : a.tokens_per_entry;
+                    const int j = start / a.page_size + (q - s_cu[i]);
+                    const int first = max(start, j * a.page_size);                 // first position this tile fills
+                    const int last = min(start + cnt, (j + 1) * a.page_size);      // one past the last
+                    const int t = first - start;                                   // index among the entry's new tokens
+                    const long long base = a.cu_new ? (long long)a.cu_new[i] : (long long)i * a.tokens_per_entry;
+                    const long long page = resolve_page(a.tb, i, j, a.status);
+                    s_rows[lane] = page < 0 ? 0 : last - first;
+                    s_dst[lane] = page * a.pool_page + (long long)(first - j * a.page_size) * a.row_bytes +
+                                  layer * a.pool_layer;
+                    s_src[lane] = (long long)i * a.nr.seq + (a.nr.packed ? base + t : (long long)t) * a.nr.tok +
+                                  layer * a.new_layer;
+                    s_tok[lane] = (int)(base + t);
+                    s_lay[lane] = layer;
+                }
+                __syncwarp();
+                staged = true;
+    };
+    if (a.early) {
+        if (more) stage_group();
+        pdl_wait_for_predecessor();     // from here on the new rows are read and the pools written
+        pdl_let_successor_in();
+    }
+
+    while ((more || consumed < issued) && !dead) {
+        if (more) {
+            if (!staged) stage_group();
+            if (issued >= S) {
+                bulk_wait_read<1>();       // the store that read this stage one ring round ago is done with it
+                __syncwarp();
+            }
+            const int rows = s_rows[ti];
+            const uint32_t bar = smem_addr(&s_bar[islot]);
+            const uint32_t tx = x.tensor_load ? (uint32_t)page_bytes : (uint32_t)(rows * a.row_bytes);
+            if (lane == 0) {
+                s_slot_rows[islot] = rows;
+                s_slot_dst[islot] = s_dst[ti] + head * a.pool_head;
+                if (rows) mbar_arrive_expect(bar, 2 * tx); else mbar_arrive(bar);
+            }
+            __syncwarp();
+            if (lane < 2 && rows) {
+                const uint32_t dst = smem_addr(s_data + (size_t)islot * 2 * page_bytes + lane * page_bytes);
+                if (x.tensor_load) {
+                    asm volatile(
+                        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+                        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(lane ? &map_v : &map_k)), "r"(0), "r"(head), "r"(s_tok[ti]),
+                        "r"(s_lay[ti]), "r"(bar)
+                        : "memory");
+                } else {
+                    bulk_load(dst, (lane ? a.v_new : a.k_new) + s_src[ti] + head * a.nr.head, tx, bar);
+                }
+            }
+            ++issued;
+            if (++islot == S) islot = 0;
+            if (++head == a.heads) {
+                head = 0;
+                if (++ti == gt || group_base + ti >= total) {
+                    ti = 0;
+                    staged = false;
+                    group_base = min(total, __shfl_sync(0xffffffffu, pending, 0));
+                    gt = __shfl_sync(0xffffffffu, pending_n, 0);
+                    if (lane == 0 && group_base < total) fetch_ahead(group_base);
+                    more = group_base < total;
+                }
+            }
+        }
+        if (issued - consumed > lag || (!more && consumed < issued)) {
+            const uint32_t bar = smem_addr(&s_bar[cslot]);
+            const long long t0 = clock64();
+            while (!mbar_try_wait(bar, cphase)) {
+                if (clock64() - t0 > x.wait_cycles) { dead = true; break; }
+            }
+            dead = __any_sync(0xffffffffu, dead);
+            if (!dead) {
+                const int rows = s_slot_rows[cslot];
+                if (rows) {
+                    fence_async_smem();
+                    if (lane < 2) {
+                        bulk_store((lane ? a.v_pool : a.k_pool) + s_slot_dst[cslot],
+                                   smem_addr(s_data + (size_t)cslot * 2 * page_bytes + lane * page_bytes),
+                                   (uint32_t)(rows * a.row_bytes));
+                    }
+                }
+                bulk_commit();
+                ++consumed;
+                if (++cslot == S) { cslot = 0; cphase ^= 1; }
+            }
+        }
+    }
+    bulk_wait_read<0>();
+    if (dead) {
+        const long long grace = x.wait_cycles < kDrainCycles ? x.wait_cycles : kDrainCycles;
+        while (consumed < issued) {
+            const uint32_t bar = smem_addr(&s_bar[cslot]);
+            const long long t0 = clock64();
+            while (!mbar_try_wait(bar, cphase) && clock64() - t0 <= grace) {}
+            ++consumed;
+            if (++cslot == S) { cslot = 0; cphase ^= 1; }
+        }
+        if (lane == 0) raise(a.status, BARQKV_S_TIMEOUT);
+    }
+    if (lane == 0) {
+        __threadfence();
+        const int finished = atomicAdd(x.work + 1, 1);
+        if (finished == (int)gridDim.x - 1) {
+            __threadfence();
+            x.work[0] = 0;
+            x.work[1] = 0;
+        }
+    }
+}
+
+// --------------------------------------------------------------------------
 // host side
 // --------------------------------------------------------------------------
-// Tuning knobs (barqkv_set_tuning); 0 = automatic.
-int g_knob_stages = 0;
-int g_knob_bulk_ctas_per_sm = 0;
-int g_knob_vector_ctas_per_sm = 0;
-int g_knob_interleave = -1;
-int g_knob_group_tiles = 0;
-int g_knob_static = 0;
-int g_knob_pdl = 0;
-int g_knob_static_permille = -1;
-int g_knob_tensor_store = -1;
-int g_knob_attn_promotion = -1;
-int g_knob_attn_split_tokens = 0;
+// Experiment knobs.  A normal build has none: the values below are compile-time defaults and the library
+// keeps no mutable process-wide settings.  A build with -DBARQKV_TUNING turns them into variables that
+// barqkv_set_tuning (include/barqkv_experimental.h) changes; that build is for sweeps, not for serving.
+struct Knobs {
+    int stages = 0;              // ring stages of the bulk gather; 0 = automatic
+    int bulk_ctas_per_sm = 0;    // 0 = as many as shared memory holds
+    int vector_ctas_per_sm = 0;
+    int interleave = -1;
+    int group_tiles = 0;
+    int static_shares = 0;
+    int pdl = -1;                // -1: programmatic dependent launch where the entry point allows it; 0: never
+    int static_permille = -1;
+    int tensor_store = -1;
+    int attn_promotion = -1;
+    int attn_split_tokens = 0;
+    int append_bulk = -1;        // -1: page-sized appends go through the copy engine; 0: always the row kernel
+};
+#ifdef BARQKV_TUNING
+Knobs g_knobs;
+#else
+constexpr Knobs g_knobs{};
+#endif
 
 struct DeviceInfo {
     int sms = 0;
     int smem_optin = 0;
-    bool bulk_attr_set = false;
+    std::atomic<bool> bulk_attr_set{false};     // cudaFuncSetAttribute done for the bulk gather / bulk append
+    std::atomic<bool> append_attr_set{false};
 };
 DeviceInfo g_dev[64];
+std::once_flag g_dev_once[64];
 
+// Properties of the current device, queried once per device however many threads ask first.
 DeviceInfo* device_info() {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
     DeviceInfo* d = &g_dev[dev];
-    if (d->sms == 0) {
+    std::call_once(g_dev_once[dev], [d, dev]() {
         int sms = 0, optin = 0;
-        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return nullptr;
-        if (cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) return nullptr;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return;
+        if (cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) return;
         d->smem_optin = optin;
         d->sms = sms;
-    }
-    return d;
+    });
+    return d->sms > 0 ? d : nullptr;
 }
 
 inline bool aligned(const void* p, int a) { return (reinterpret_cast<uintptr_t>(p) % (uintptr_t)a) == 0; }
@@ -959,16 +1248,36 @@ int vector_bytes(int row_bytes, std::initializer_list<long long> strides, std::i
     return 1;
 }
 
+// Launch `kernel`; with `dependent` as a programmatic dependent of the kernel before it in the stream, so that
+// the part of it that precedes its griddepcontrol.wait may run while that kernel is still finishing.
+template <typename... KernelArgs, typename... Args>
+cudaError_t launch(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool dependent,
+                   Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = dependent ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
 template <bool LEGACY>
 int launch_append(const AppendArgs& a, int vec, dim3 grid, int threads, cudaStream_t st) {
+    const bool dep = !LEGACY && a.early != 0;
+    cudaError_t e;
     switch (vec) {
-        case 16: append_rows_kernel<uint4, LEGACY><<<grid, threads, 0, st>>>(a); break;
-        case 8: append_rows_kernel<uint2, LEGACY><<<grid, threads, 0, st>>>(a); break;
-        case 4: append_rows_kernel<uint32_t, LEGACY><<<grid, threads, 0, st>>>(a); break;
-        case 2: append_rows_kernel<uint16_t, LEGACY><<<grid, threads, 0, st>>>(a); break;
-        default: append_rows_kernel<uint8_t, LEGACY><<<grid, threads, 0, st>>>(a); break;
+        case 16: e = launch(append_rows_kernel<uint4, LEGACY>, grid, dim3(threads), 0, st, dep, a); break;
+        case 8: e = launch(append_rows_kernel<uint2, LEGACY>, grid, dim3(threads), 0, st, dep, a); break;
+        case 4: e = launch(append_rows_kernel<uint32_t, LEGACY>, grid, dim3(threads), 0, st, dep, a); break;
+        case 2: e = launch(append_rows_kernel<uint16_t, LEGACY>, grid, dim3(threads), 0, st, dep, a); break;
+        default: e = launch(append_rows_kernel<uint8_t, LEGACY>, grid, dim3(threads), 0, st, dep, a); break;
     }
-    const cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) e = cudaGetLastError();
     if (e == cudaSuccess) g_launches.fetch_add(1, std::memory_order_relaxed);
     return e == cudaSuccess ? 0 : fail_cuda("append launch", e);
 }
@@ -1025,6 +1334,26 @@ bool make_out_map(CUtensorMap* map, void* base, int elem_bytes, int head_dim, in
                CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Describes token-major new rows [layers][tokens][heads][head_dim] (strides in bytes) for page-sized loads.
+bool make_rows_map(CUtensorMap* map, const void* base, int elem_bytes, int head_dim, int heads, long long head_stride,
+                   long long tok_stride, long long tokens, int layers, long long layer_stride, int page_size) {
+    PFN_cuTensorMapEncodeTiled enc = tensor_map_encoder();
+    if (!enc) return false;
+    CUtensorMapDataType dt;
+    switch (elem_bytes) {
+        case 1: dt = CU_TENSOR_MAP_DATA_TYPE_UINT8; break;
+        case 2: dt = CU_TENSOR_MAP_DATA_TYPE_UINT16; break;
+        case 4: dt = CU_TENSOR_MAP_DATA_TYPE_UINT32; break;
+        default: dt = CU_TENSOR_MAP_DATA_TYPE_UINT64; break;
+    }
+    const cuuint64_t dims[4] = {(cuuint64_t)head_dim, (cuuint64_t)heads, (cuuint64_t)tokens, (cuuint64_t)layers};
+    const cuuint64_t strides[3] = {(cuuint64_t)head_stride, (cuuint64_t)tok_stride, (cuuint64_t)layer_stride};
+    const cuuint32_t box[4] = {(cuuint32_t)head_dim, 1u, (cuuint32_t)page_size, 1u};
+    const cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+    return enc(map, dt, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 }  // namespace
 
 extern "C" {
@@ -1041,31 +1370,35 @@ int barqkv_sm_count(void) {
     return d->sms;
 }
 
+#ifdef BARQKV_TUNING
 int barqkv_set_tuning(int32_t knob, int32_t value) {
     switch (knob) {
-        case BARQKV_KNOB_BULK_STAGES: g_knob_stages = value; return 0;
-        case BARQKV_KNOB_BULK_CTAS_PER_SM: g_knob_bulk_ctas_per_sm = value; return 0;
-        case BARQKV_KNOB_VECTOR_CTAS_PER_SM: g_knob_vector_ctas_per_sm = value; return 0;
-        case BARQKV_KNOB_INTERLEAVE: g_knob_interleave = value; return 0;
-        case BARQKV_KNOB_GROUP_TILES: g_knob_group_tiles = value; return 0;
-        case BARQKV_KNOB_STATIC_SHARES: g_knob_static = value; return 0;
-        case BARQKV_KNOB_PDL: g_knob_pdl = value; return 0;
-        case BARQKV_KNOB_STATIC_PERMILLE: g_knob_static_permille = value > 1000 ? 1000 : value; return 0;
-        case BARQKV_KNOB_TENSOR_STORE: g_knob_tensor_store = value; return 0;
-        case BARQKV_KNOB_ATTN_L2_PROMOTION: g_knob_attn_promotion = value; return 0;
-        case BARQKV_KNOB_ATTN_SPLIT_TOKENS: g_knob_attn_split_tokens = value; return 0;
+        case BARQKV_KNOB_BULK_STAGES: g_knobs.stages = value; return 0;
+        case BARQKV_KNOB_BULK_CTAS_PER_SM: g_knobs.bulk_ctas_per_sm = value; return 0;
+        case BARQKV_KNOB_VECTOR_CTAS_PER_SM: g_knobs.vector_ctas_per_sm = value; return 0;
+        case BARQKV_KNOB_INTERLEAVE: g_knobs.interleave = value; return 0;
+        case BARQKV_KNOB_GROUP_TILES: g_knobs.group_tiles = value; return 0;
+        case BARQKV_KNOB_STATIC_SHARES: g_knobs.static_shares = value; return 0;
+        case BARQKV_KNOB_PDL: g_knobs.pdl = value; return 0;
+        case BARQKV_KNOB_STATIC_PERMILLE: g_knobs.static_permille = value > 1000 ? 1000 : value; return 0;
+        case BARQKV_KNOB_TENSOR_STORE: g_knobs.tensor_store = value; return 0;
+        case BARQKV_KNOB_ATTN_L2_PROMOTION: g_knobs.attn_promotion = value; return 0;
+        case BARQKV_KNOB_ATTN_SPLIT_TOKENS: g_knobs.attn_split_tokens = value; return 0;
+        case BARQKV_KNOB_APPEND_BULK: g_knobs.append_bulk = value; return 0;
         default: return fail(BARQKV_E_INVALID, "set_tuning: unknown knob");
     }
 }
+#endif
 
 static int append_common(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,
                          const barqkv_block_table* table,
                          const int32_t* seq_start, const int32_t* cu_new,
                          int32_t n, int32_t tokens_per_entry, int32_t total_tokens,
                          const void* k_new, const void* v_new, const barqkv_rows_layout* new_rows,
-                         int32_t* status, barqkv_stream_t stream,
+                         int32_t* status, int32_t* work, int32_t flags, barqkv_stream_t stream,
                          int32_t layers, int64_t pool_layer_stride, int64_t new_layer_stride) {
     if (int rc = check_pool(pool)) return rc;
+    if (flags & ~BARQKV_FLAG_DESC_STABLE) return fail(BARQKV_E_INVALID, "append: unknown flag");
     if (layers <= 0 || layers > 65535) return fail(BARQKV_E_INVALID, "append: layers must be in 1..65535");
     if (n < 0 || total_tokens < 0) return fail(BARQKV_E_INVALID, "append: negative batch size or token count");
     if (n == 0 || total_tokens == 0) return 0;
@@ -1105,10 +1438,81 @@ static int append_common(const barqkv_pool_layout* pool, void* k_pool, void* v_p
 
     a.pool_layer = pool_layer_stride * e;
     a.new_layer = new_layer_stride * e;
+    a.early = (flags & BARQKV_FLAG_DESC_STABLE) && g_knobs.pdl != 0 ? 1 : 0;
 
     const int vec = vector_bytes(a.row_bytes, {a.pool_head, a.pool_page, a.nr.seq, a.nr.tok, a.nr.head,
                                                layers > 1 ? a.pool_layer : 0, layers > 1 ? a.new_layer : 0},
                                  {k_pool, v_pool, k_new, v_new});
+    // Page-sized appends (on average at least a page per entry: prefill chunks) move whole pages with the
+    // copy engine when the caller lends the two hand-out counters and the rows' layout allows one copy per
+    // page: rows of a head adjacent in memory, or a packed token-major source a tensor map can describe.
+    const long long page_bytes = (long long)a.page_size * a.row_bytes;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (work && g_knobs.append_bulk != 0 && vec == 16 && n <= kMaxEntries && 2 * page_bytes <= kBulkMaxStage &&
+        total_tokens >= (long long)n * a.page_size) {
+        const bool adjacent = a.nr.tok == a.row_bytes;
+        const bool mappable = a.nr.packed && a.nr.seq == 0 && a.nr.tok > 0 && a.nr.head > 0 && a.nr.tok < (1LL << 40) &&
+                              a.nr.head < (1LL << 40) && pool->head_dim <= 256 && a.page_size <= 256 &&
+                              page_bytes % 128 == 0 && (layers == 1 || (a.new_layer > 0 && a.new_layer < (1LL << 40)));
+        CUtensorMap map_k, map_v;
+        memset(&map_k, 0, sizeof(map_k));
+        memset(&map_v, 0, sizeof(map_v));
+        bool tensor_load = false;
+        if (!adjacent && mappable) {
+            const long long lstride = layers > 1 ? a.new_layer : a.nr.tok;
+            tensor_load = make_rows_map(&map_k, k_new, pool->elem_bytes, pool->head_dim, a.heads, a.nr.head, a.nr.tok,
+                                        total_tokens, layers, lstride, a.page_size) &&
+                          make_rows_map(&map_v, v_new, pool->elem_bytes, pool->head_dim, a.heads, a.nr.head, a.nr.tok,
+                                        total_tokens, layers, lstride, a.page_size);
+        }
+        if (adjacent || tensor_load) {
+            AppendBulkArgs x;
+            memset(&x, 0, sizeof(x));
+            x.work = work;
+            x.tensor_load = tensor_load ? 1 : 0;
+            x.layers = layers;
+            x.wait_cycles = kWaitCycles;
+            long long tiles_bound = ((long long)total_tokens + a.page_size - 1) / a.page_size + n;
+            tiles_bound *= layers;
+            if (tiles_bound <= 0x7fffffffLL) {
+                int S = (int)(64 * 1024 / (2 * page_bytes));
+                if (S > 8) S = 8;
+                if (tiles_bound * a.heads < 96LL * d->sms && S > 4) S = 4;
+                if (g_knobs.stages) S = g_knobs.stages;
+                if (S < 3) S = 3;
+                if (S > 32) S = 32;
+                x.stages = S;
+                const size_t smem = (size_t)S * 2 * page_bytes + (size_t)S * 8 /*bar*/ + (size_t)S * 8 /*slot dst*/ +
+                                    2 * kGroup * 8 + 3 * kGroup * 4 + (size_t)S * 4 + (size_t)(n + 1) * 4 + 16;
+                if ((long long)smem <= d->smem_optin) {
+                    if (!d->append_attr_set.load(std::memory_order_acquire)) {
+                        const cudaError_t ce = cudaFuncSetAttribute(append_bulk_kernel,
+                                                                    cudaFuncAttributeMaxDynamicSharedMemorySize, d->smem_optin);
+                        if (ce != cudaSuccess) return fail_cuda("append: cudaFuncSetAttribute", ce);
+                        d->append_attr_set.store(true, std::memory_order_release);
+                    }
+                    int per_sm = (int)((220 * 1024) / (smem + 1024));
+                    if (per_sm < 1) per_sm = 1;
+                    if (per_sm > 8) per_sm = 8;
+                    if (g_knobs.bulk_ctas_per_sm) per_sm = g_knobs.bulk_ctas_per_sm;
+                    long long grid = (long long)d->sms * per_sm;
+                    const long long want = (tiles_bound * a.heads + 1) / 2;      // at least two units per CTA
+                    if (want < grid) grid = want < 1 ? 1 : want;
+                    x.group_tiles = g_knobs.group_tiles ? g_knobs.group_tiles : (a.heads >= 8 ? 1 : 8 / a.heads);
+                    if (x.group_tiles > kGroup) x.group_tiles = kGroup;
+                    if (x.group_tiles < 1) x.group_tiles = 1;
+                    const long long k = tiles_bound / (4 * grid);
+                    x.first_group = (int)(k < 1 ? 1 : (k > x.group_tiles ? x.group_tiles : k));
+                    cudaError_t ce = launch(append_bulk_kernel, dim3((unsigned)grid), dim3(32), smem, st, a.early != 0, a, x,
+                                            map_k, map_v);
+                    if (ce == cudaSuccess) ce = cudaGetLastError();
+                    if (ce == cudaSuccess) g_launches.fetch_add(1, std::memory_order_relaxed);
+                    return ce == cudaSuccess ? 0 : fail_cuda("append launch", ce);
+                }
+            }
+        }
+    }
+
     int threads;
     // tile chosen as if the layers' tokens were one batch, so that the whole grid covers the machine
     long long work_tokens = (long long)total_tokens * layers;
@@ -1123,9 +1527,9 @@ int barqkv_append(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,
                   const int32_t* seq_start, const int32_t* cu_new,
                   int32_t n, int32_t tokens_per_entry, int32_t total_tokens,
                   const void* k_new, const void* v_new, const barqkv_rows_layout* new_rows,
-                  int32_t* status, barqkv_stream_t stream) {
+                  int32_t* status, int32_t* work, int32_t flags, barqkv_stream_t stream) {
     return append_common(pool, k_pool, v_pool, table, seq_start, cu_new, n, tokens_per_entry, total_tokens, k_new, v_new,
-                         new_rows, status, stream, 1, 0, 0);
+                         new_rows, status, work, flags, stream, 1, 0, 0);
 }
 
 int barqkv_append_layers(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,
@@ -1134,9 +1538,9 @@ int barqkv_append_layers(const barqkv_pool_layout* pool, void* k_pool, void* v_p
                          const int32_t* seq_start, const int32_t* cu_new,
                          int32_t n, int32_t tokens_per_entry, int32_t total_tokens,
                          const void* k_new, const void* v_new, const barqkv_rows_layout* new_rows,
-                         int64_t new_layer_stride, int32_t* status, barqkv_stream_t stream) {
+                         int64_t new_layer_stride, int32_t* status, int32_t* work, int32_t flags, barqkv_stream_t stream) {
     return append_common(pool, k_pool, v_pool, table, seq_start, cu_new, n, tokens_per_entry, total_tokens, k_new, v_new,
-                         new_rows, status, stream, layers, pool_layer_stride, new_layer_stride);
+                         new_rows, status, work, flags, stream, layers, pool_layer_stride, new_layer_stride);
 }
 
 int barqkv_append_rope(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,
@@ -1357,13 +1761,24 @@ struct LayerSpan {
     long long pool_stride, out_stride;   // elements
 };
 
+// How a gather is launched, beyond what its arguments describe.
+struct LaunchOpts {
+    bool after_own_kernel = false;   // the kernel before this one in the stream is this library's gather over the
+                                     // same, unchanged batch description and block table: launch as its programmatic
+                                     // dependent and let the prologue overlap its tail
+    long long wait_cycles = kWaitCycles;
+    int extra_tx = 0;                // self-test: make every stage wait for bytes that never come
+    int max_ctas = 0;                // self-test: cap of the grid (0 = none)
+    bool validate_only = false;      // check the arguments, enqueue nothing
+};
+
 static int gather_common(const barqkv_pool_layout* pool, const void* k_pool, const void* v_pool,
                          const barqkv_block_table* table,
                          const int32_t* seq_lens, const int32_t* cu_out, int32_t n,
                          int64_t total_tokens_hint,
                          void* k_out, void* v_out, const barqkv_rows_layout* out_rows,
                          int32_t mode, int32_t* status, int32_t* work, barqkv_stream_t stream,
-                         const FusedRows* fused, const LayerSpan* span = nullptr) {
+                         const FusedRows* fused, const LayerSpan* span = nullptr, const LaunchOpts& opts = LaunchOpts()) {
     if (int rc = check_pool(pool)) return rc;
     if (n < 0) return fail(BARQKV_E_INVALID, "gather: negative batch size");
     if (n == 0) return 0;
@@ -1372,6 +1787,8 @@ static int gather_common(const barqkv_pool_layout* pool, const void* k_pool, con
     if (!k_pool || !v_pool || !k_out || !v_out || !seq_lens || !out_rows)
         return fail(BARQKV_E_INVALID, "gather: null pointer argument");
     if (out_rows->packed && !cu_out) return fail(BARQKV_E_INVALID, "gather: packed output needs cu_out");
+    const bool stable = (mode & BARQKV_FLAG_DESC_STABLE) != 0;
+    mode &= ~BARQKV_FLAG_DESC_STABLE;
     if (mode < BARQKV_MODE_AUTO || mode > BARQKV_MODE_BULK) return fail(BARQKV_E_INVALID, "gather: unknown mode");
     DeviceInfo* d = device_info();
     if (!d) return fail(BARQKV_E_LAUNCH, "no CUDA device is current");
@@ -1398,12 +1815,14 @@ static int gather_common(const barqkv_pool_layout* pool, const void* k_pool, con
     a.orow.head = out_rows->head_stride * e;
     a.orow.packed = out_rows->packed;
     a.status = status;
-    a.interleave = g_knob_interleave < 0 ? 0 : g_knob_interleave;
-    a.work = g_knob_static ? nullptr : work;
-    a.group_tiles = g_knob_group_tiles ? g_knob_group_tiles : (a.heads >= 8 ? 1 : 8 / a.heads);
+    a.interleave = g_knobs.interleave < 0 ? 0 : g_knobs.interleave;
+    a.work = g_knobs.static_shares ? nullptr : work;
+    a.group_tiles = g_knobs.group_tiles ? g_knobs.group_tiles : (a.heads >= 8 ? 1 : 8 / a.heads);
     if (a.group_tiles > kGroup) a.group_tiles = kGroup;
     if (a.group_tiles < 1) a.group_tiles = 1;
-    a.static_permille = g_knob_static_permille >= 0 ? g_knob_static_permille : 0;
+    a.static_permille = g_knobs.static_permille >= 0 ? g_knobs.static_permille : 0;
+    a.wait_cycles = opts.wait_cycles;
+    a.extra_tx = opts.extra_tx;
     a.layers = 1;
     if (span) {
         a.layers = span->layers;
@@ -1451,7 +1870,7 @@ static int gather_common(const barqkv_pool_layout* pool, const void* k_pool, con
         // A launch with few units (a single KV head per GPU) is dominated by filling and draining the
         // rings: half the depth, twice the CTAs.
         if (tiles_bound * a.heads < 96LL * d->sms && S > 4) S = 4;
-        if (g_knob_stages) S = g_knob_stages;
+        if (g_knobs.stages) S = g_knobs.stages;
         if (S < 3) S = 3;
         if (S > 32) S = 32;
         a.stages = S;
@@ -1459,16 +1878,16 @@ static int gather_common(const barqkv_pool_layout* pool, const void* k_pool, con
                             3 * kGroup * 8 + 2 * kGroup * 4 + (size_t)S * 16 + 4 + (size_t)(n + 1) * 4;
         if ((long long)smem > d->smem_optin)
             return fail(BARQKV_E_LIMIT, "gather: bulk pipeline does not fit in shared memory");
-        if (!d->bulk_attr_set) {
+        if (!d->bulk_attr_set.load(std::memory_order_acquire)) {
             const cudaError_t ce = cudaFuncSetAttribute(gather_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                         d->smem_optin);
             if (ce != cudaSuccess) return fail_cuda("gather: cudaFuncSetAttribute", ce);
-            d->bulk_attr_set = true;
+            d->bulk_attr_set.store(true, std::memory_order_release);
         }
         int per_sm = (int)((220 * 1024) / (smem + 1024));
         if (per_sm < 1) per_sm = 1;
         if (per_sm > 8) per_sm = 8;
-        if (g_knob_bulk_ctas_per_sm) per_sm = g_knob_bulk_ctas_per_sm;
+        if (g_knobs.bulk_ctas_per_sm) per_sm = g_knobs.bulk_ctas_per_sm;
         long long grid = (long long)d->sms * per_sm;
         const long long units_bound = tiles_bound * a.heads;
         const long long want = (units_bound + 2 * S - 1) / (2 * S);   // at least two ring rounds per CTA
@@ -1484,7 +1903,7 @@ static int gather_common(const barqkv_pool_layout* pool, const void* k_pool, con
         CUtensorMap map_k, map_v;
         memset(&map_k, 0, sizeof(map_k));
         memset(&map_v, 0, sizeof(map_v));
-        if (a.layers == 1 && a.orow.tok != a.row_bytes && a.orow.seq == 0 && a.orow.packed && g_knob_tensor_store != 0 &&
+        if (a.layers == 1 && a.orow.tok != a.row_bytes && a.orow.seq == 0 && a.orow.packed && g_knobs.tensor_store != 0 &&
             pool->head_dim <= 256 && a.page_size <= 256 && page_bytes % 128 == 0 && a.orow.tok > 0 && a.orow.head > 0 &&
             a.orow.tok < (1LL << 40) && a.orow.head < (1LL << 40)) {
             const long long tokens = 0x7fffffffLL;      // full pages never reach past their sequence; no clipping needed
@@ -1493,27 +1912,18 @@ static int gather_common(const barqkv_pool_layout* pool, const void* k_pool, con
                              make_out_map(&map_v, v_out, pool->elem_bytes, pool->head_dim, a.heads, a.orow.head,
                                           a.orow.tok, tokens, a.page_size);
         }
-        if (g_knob_pdl) {
-            cudaLaunchConfig_t cfg = {};
-            cfg.gridDim = dim3((unsigned)grid);
-            cfg.blockDim = dim3(32);
-            cfg.dynamicSmemBytes = smem;
-            cfg.stream = st;
-            cudaLaunchAttribute attr[1];
-            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-            attr[0].val.programmaticStreamSerializationAllowed = 1;
-            cfg.attrs = attr;
-            cfg.numAttrs = 1;
-            const cudaError_t le = cudaLaunchKernelEx(&cfg, gather_bulk_kernel, a, map_k, map_v);
-            if (le != cudaSuccess) return fail_cuda("gather launch", le);
-        } else {
-            gather_bulk_kernel<<<(int)grid, 32, smem, st>>>(a, map_k, map_v);
-        }
+        if (opts.max_ctas > 0 && grid > opts.max_ctas) grid = opts.max_ctas;
+        if (opts.validate_only) return 0;
+        const bool dependent = (opts.after_own_kernel || stable) && g_knobs.pdl != 0 && a.work;
+        a.early = dependent ? 1 : 0;
+        const cudaError_t le = launch(gather_bulk_kernel, dim3((unsigned)grid), dim3(32), smem, st, dependent, a, map_k, map_v);
+        if (le != cudaSuccess) return fail_cuda("gather launch", le);
     } else {
         const size_t smem = (size_t)(n + 1) * 4;
-        long long grid = (long long)d->sms * (g_knob_vector_ctas_per_sm ? g_knob_vector_ctas_per_sm : 8);
+        long long grid = (long long)d->sms * (g_knobs.vector_ctas_per_sm ? g_knobs.vector_ctas_per_sm : 8);
         const long long want = (tiles_bound + 3) / 4;
         if (want < grid) grid = want < 1 ? 1 : want;
+        if (opts.validate_only) return 0;
         switch (vec) {
             case 16: gather_vector_kernel<uint4><<<(int)grid, kGatherThreads, smem, st>>>(a); break;
             case 8: gather_vector_kernel<uint2><<<(int)grid, kGatherThreads, smem, st>>>(a); break;
@@ -1581,11 +1991,91 @@ int barqkv_update(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,
                                       "the append, device int32[n]) so that it can run as append + gather");
     if (total_new_tokens) {
         if (int rc = barqkv_append(pool, k_pool, v_pool, table, seq_start, cu_new, n, tokens_per_entry, total_new_tokens,
-                                   k_new, v_new, new_rows, status, stream))
+                                   k_new, v_new, new_rows, status, work, 0, stream))
             return rc;
     }
+    // two kernels that share `work`: the gather must not start taking pages while the append still does
     return barqkv_gather(pool, k_pool, v_pool, table, seq_lens_after, cu_out, n, total_tokens_hint, k_out, v_out,
-                         out_rows, mode, status, work, stream);
+                         out_rows, mode & ~BARQKV_FLAG_DESC_STABLE, status, work, stream);
+}
+
+int barqkv_update_layers(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,
+                         int32_t layers, int64_t pool_layer_stride,
+                         const barqkv_block_table* table,
+                         const int32_t* seq_start, const int32_t* cu_new,
+                         int32_t n, int32_t tokens_per_entry, int32_t total_new_tokens,
+                         const void* k_new, const void* v_new, const barqkv_rows_layout* new_rows,
+                         int64_t new_layer_stride,
+                         const int32_t* cu_out, int64_t total_tokens_hint,
+                         void* const* k_out, void* const* v_out, int32_t num_out,
+                         const barqkv_rows_layout* out_rows,
+                         int32_t mode, int32_t* status, int32_t* work, const int32_t* seq_lens_after,
+                         barqkv_stream_t stream) {
+    if (layers <= 0 || layers > 65535) return fail(BARQKV_E_INVALID, "update_layers: bad layer count");
+    if (num_out <= 0 || !k_out || !v_out) return fail(BARQKV_E_INVALID, "update_layers: needs at least one output pair");
+    if (pool_layer_stride < 0 || new_layer_stride < 0) return fail(BARQKV_E_INVALID, "update_layers: negative layer stride");
+    if (n < 0 || total_new_tokens < 0) return fail(BARQKV_E_INVALID, "update_layers: negative batch size or token count");
+    if (n == 0) return 0;
+    if (int rc = check_pool(pool)) return rc;
+    if (!k_pool || !v_pool || !seq_start || !new_rows || (total_new_tokens && (!k_new || !v_new)))
+        return fail(BARQKV_E_INVALID, "update_layers: null pointer argument");
+    if (!cu_new && (tokens_per_entry < 0 || (long long)tokens_per_entry * n != total_new_tokens))
+        return fail(BARQKV_E_INVALID, "update_layers: without cu_new, total_new_tokens must equal n * tokens_per_entry");
+    if (new_rows->packed && !cu_new && tokens_per_entry > 1)
+        return fail(BARQKV_E_INVALID, "update_layers: packed rows with more than one token per entry need cu_new");
+    const long long e = pool->elem_bytes;
+    mode &= ~BARQKV_FLAG_DESC_STABLE;      // the first layer waits for whatever precedes it; the rest are chained here
+    const bool try_fused = total_new_tokens > 0 && total_new_tokens <= (long long)n * pool->page_size;
+    bool fused_ok = try_fused;
+    for (int l = 0; l < layers; ++l) {
+        unsigned char* kp = static_cast<unsigned char*>(k_pool) + (long long)l * pool_layer_stride * e;
+        unsigned char* vp = static_cast<unsigned char*>(v_pool) + (long long)l * pool_layer_stride * e;
+        const unsigned char* kn = k_new ? static_cast<const unsigned char*>(k_new) + (long long)l * new_layer_stride * e : nullptr;
+        const unsigned char* vn = v_new ? static_cast<const unsigned char*>(v_new) + (long long)l * new_layer_stride * e : nullptr;
+        void* ko = k_out[l % num_out];
+        void* vo = v_out[l % num_out];
+        if (fused_ok) {
+            // Layers alternate between the two counter pairs of `work`: layer l + 1 takes its first pages while
+            // layer l is still handing out its last ones.  From the second layer on the launch is a programmatic
+            // dependent of the layer before, whose batch description it shares.
+            const FusedRows fused = {kn, vn, new_rows, cu_new, tokens_per_entry};
+            LaunchOpts opts;
+            opts.after_own_kernel = l > 0;
+            const int rc = gather_common(pool, kp, vp, table, seq_start, cu_out, n, total_tokens_hint, ko, vo, out_rows, mode,
+                                         status, work ? work + 2 * (l & 1) : nullptr, stream, &fused, nullptr, opts);
+            if (rc == 0) continue;
+            if (rc != kNotFusable || l > 0) return rc;
+            fused_ok = false;
+        }
+        if (!seq_lens_after)
+            return fail(BARQKV_E_INVALID, "update_layers: this call cannot run as one launch per layer; pass seq_lens_after "
+                                          "(lengths after the append, device int32[n]) so that it can run as append + gather");
+        if (total_new_tokens) {
+            if (int rc = barqkv_append(pool, kp, vp, table, seq_start, cu_new, n, tokens_per_entry, total_new_tokens, kn, vn,
+                                       new_rows, status, work, 0, stream))
+                return rc;
+        }
+        if (int rc = barqkv_gather(pool, kp, vp, table, seq_lens_after, cu_out, n, total_tokens_hint, ko, vo, out_rows,
+                                   mode & ~BARQKV_FLAG_DESC_STABLE, status, work, stream))
+            return rc;
+    }
+    return 0;
+}
+
+int barqkv_gather_wait_selftest(const barqkv_pool_layout* pool, const void* k_pool, const void* v_pool,
+                                const barqkv_block_table* table,
+                                const int32_t* seq_lens, const int32_t* cu_out, int32_t n,
+                                void* k_out, void* v_out, const barqkv_rows_layout* out_rows,
+                                int64_t wait_cycles, int32_t* status, barqkv_stream_t stream) {
+    if (wait_cycles <= 0 || wait_cycles > kWaitCycles)
+        return fail(BARQKV_E_INVALID, "gather_wait_selftest: wait_cycles must be in 1..2e9");
+    if (!status) return fail(BARQKV_E_INVALID, "gather_wait_selftest: needs the status word");
+    LaunchOpts opts;
+    opts.wait_cycles = wait_cycles;
+    opts.extra_tx = 16;       // every stage waits for 16 bytes that no copy brings
+    opts.max_ctas = 1;
+    return gather_common(pool, k_pool, v_pool, table, seq_lens, cu_out, n, 0, k_out, v_out, out_rows, BARQKV_MODE_BULK,
+                         status, nullptr, stream, nullptr, nullptr, opts);
 }
 
 // --------------------------------------------------------------------------
@@ -1606,8 +2096,10 @@ static __device__ __align__(256) int32_t g_static_work[BARQKV_STATIC_WORK_SLOTS 
 
 // Device address of g_static_work per device.  In host code the array's name is
 // only a handle for the runtime, not an address a kernel can use, so it is
-// translated once per device with that device current.
-static int32_t* g_static_work_addr[64];
+// translated once per device with that device current.  Published with
+// release/acquire: two threads that make the first call together both look the
+// address up and store the same value.
+static std::atomic<int32_t*> g_static_work_addr[64];
 
 int barqkv_gather_noalloc(const barqkv_pool_layout* pool, const void* k_pool, const void* v_pool,
                           const barqkv_block_table* table,
@@ -1621,13 +2113,22 @@ int barqkv_gather_noalloc(const barqkv_pool_layout* pool, const void* k_pool, co
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return fail_cuda("gather_noalloc: cudaGetDevice", e);
     if (dev < 0 || dev >= 64) return fail(BARQKV_E_LIMIT, "gather_noalloc: device ordinal above 63");
-    if (!g_static_work_addr[dev]) {
+    int32_t* base = g_static_work_addr[dev].load(std::memory_order_acquire);
+    if (!base) {
         void* addr = nullptr;
         e = cudaGetSymbolAddress(&addr, g_static_work);
         if (e != cudaSuccess || !addr) return fail_cuda("gather_noalloc: cudaGetSymbolAddress", e);
-        g_static_work_addr[dev] = static_cast<int32_t*>(addr);
+        base = static_cast<int32_t*>(addr);
+        g_static_work_addr[dev].store(base, std::memory_order_release);
     }
-    int32_t* work = g_static_work_addr[dev] + (size_t)work_slot * kStaticWorkStride;
+    int32_t* work = base + (size_t)work_slot * kStaticWorkStride;
+    // Arguments are checked before anything is enqueued: a refused call leaves the slot as it was.
+    LaunchOpts check;
+    check.validate_only = true;
+    if (int rc = gather_common(pool, k_pool, v_pool, table, seq_lens, cu_out, n, total_tokens_hint, k_out, v_out, out_rows,
+                               mode, status, work, stream, nullptr, nullptr, check))
+        return rc;
+    if (n == 0) return 0;
     // The slot keeps whatever its previous user left; the counters must start at zero.
     e = cudaMemsetAsync(work, 0, 2 * sizeof(int32_t), static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return fail_cuda("gather_noalloc: cudaMemsetAsync", e);

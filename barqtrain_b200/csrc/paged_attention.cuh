@@ -339,8 +339,8 @@ bool make_pool_map(CUtensorMap* map, const void* base, const barqkv_pool_layout*
                                    (cuuint64_t)(pool->head_stride * e)};
     const cuuint32_t box[4] = {64u, (cuuint32_t)pool->page_size, 1u, 1u};
     const cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
-    const CUtensorMapL2promotion promo = g_knob_attn_promotion == 1   ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B
-                                         : g_knob_attn_promotion == 2 ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B
+    const CUtensorMapL2promotion promo = g_knobs.attn_promotion == 1   ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B
+                                         : g_knobs.attn_promotion == 2 ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B
                                                                       : CU_TENSOR_MAP_L2_PROMOTION_NONE;
     return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, const_cast<void*>(base), dims, strides, box, estr,
                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, promo,
@@ -355,9 +355,9 @@ int attn_splits(int n, int kv_heads, long long max_len, long long total_len, int
     const long long pages = (max_len + page_size - 1) / page_size;
     int sms = 148;
     if (DeviceInfo* d = device_info()) sms = d->sms;
-    const int cap = (g_knob_attn_split_tokens > 0 ? g_knob_attn_split_tokens : kAttnSplitTokens) / page_size;
+    const int cap = (g_knobs.attn_split_tokens > 0 ? g_knobs.attn_split_tokens : kAttnSplitTokens) / page_size;
     int sp = cap < 1 ? 1 : cap;
-    if (total_len > 0 && g_knob_attn_split_tokens <= 0) {
+    if (total_len > 0 && g_knobs.attn_split_tokens <= 0) {
         const int floor_pages = 64 / page_size > 1 ? 64 / page_size : 1;
         const long long slots = (long long)sms * (page_size <= 16 ? 6 : page_size <= 32 ? 4 : 2);   // resident one-warp CTAs
         const long long units = ((total_len + page_size - 1) / page_size + n) * kv_heads;           // (page, head) units, rounded up

@@ -238,6 +238,37 @@ class DecodeWorkload:
         self.graph.step()
         self.step_no += 2
 
+    def append_only_leg(self, steps: int, barrier, max_over_ranks, backend):
+        """Decode tokens appended per second with nothing but the append in the timed region: every step
+        appends one token per sequence in every layer - one launch per layer (what a model's forward pass
+        issues), and again with one launch for all layers - replayed from a CUDA graph."""
+        from barqtrain_b200 import DecodeStepGraph
+
+        out = {}
+        for name, what in (("per_layer", "append"), ("all_layers_one_launch", "append_layers")):
+            g = DecodeStepGraph(self.cache, self.slots, capacity_tokens=0, what=what)
+            g.k_in.copy_(self.new_k[1])
+            g.v_in.copy_(self.new_v[1])
+            g.step()
+            g.record()
+            for _ in range(3):
+                g.step()
+            half = max(steps // 2, 1)
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(half):
+                g.step()
+            e1.record()
+            barrier()
+            ms = max_over_ranks(e0.elapsed_time(e1))
+            out[name] = {"tokens_per_s": round(self.B * half / (ms * 1e-3), 1), "us_per_step": round(ms * 1e3 / half, 2),
+                         "steps": half, "launches_per_step": g.launches_per_replay,
+                         "gbs_per_gpu": round(self.step_bytes(0)[0] * half / (ms * 1e-3) / 1e9, 1)}
+        out["note"] = ("a token = its K and V rows in all %d layers; the append moves %.1f MiB per step per GPU, so "
+                       "these steps are bound by launches, not by bandwidth" % (self.L, self.step_bytes(0)[0] / 2 / 2**20))
+        return out
+
     def resident_step(self, events=None):
         if self.graph is not None:                          # inputs stay in the graph's resident buffers
             self.step_no += 1
@@ -263,6 +294,10 @@ class DecodeWorkload:
         return total
 
 
+def _median(xs):
+    return statistics.median(xs)
+
+
 def run_barqkv(args):
     import torch.distributed as dist
 
@@ -283,7 +318,11 @@ def run_barqkv(args):
     backend = _ffi.require_cuda_backend()
     K, W = args.steps, max(args.warmup, 3)
     e2e_steps = max(3, min(K, 10))
-    total_steps = W + K + 3 + e2e_steps + 8
+    # The K-step region is timed again and again until a second has gone by (at most 256 decode steps in
+    # all, the configuration's length), so that clock samples exist; the line reports the median region.
+    max_regions = max(1, min(12, 256 // max(K, 1)))
+    append_steps = 64
+    total_steps = W + K * max_regions + 3 + e2e_steps + 8 + append_steps + 8
     if args.tune:
         backend.set_tuning(**{k: int(v) for k, v in (kv.split("=") for kv in args.tune.split(","))})
     wl = DecodeWorkload(world, rank, device, total_steps, fused=not args.two_launches, heads=args.shard_heads)
@@ -308,28 +347,39 @@ def run_barqkv(args):
     for _ in range(W):
         wl.resident_step()
     barrier()
-    launches0 = backend.launches
     events = []
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    app_bytes = gat_bytes = 0
+    regions = []          # (ms, append bytes, gather bytes, launches) of every timed K-step region
     with ClockSampler(local) as clocks:
-        barrier()
-        start.record()
-        for _ in range(K):
-            total = wl.resident_step(events)
-            a, g = wl.step_bytes(total)
-            app_bytes += a
-            gat_bytes += g
-        stop.record()
-        barrier()
-    launches = backend.launches - launches0
-    if use_graph:
-        # kernel nodes replayed (a replay makes no library call) plus what the library launched itself in
-        # the region: the small table-scatter kernel of the steps in which a sequence enters a new page
-        launches += K * wl.graph.launches_per_replay
-    ms = max_over_ranks(start.elapsed_time(stop))
-    job_bytes = (app_bytes + gat_bytes) * world
-    value = job_bytes / (ms * 1e-3) / 1e9
+        spent = 0.0
+        while True:
+            launches0 = backend.launches
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            app_bytes = gat_bytes = 0
+            barrier()
+            start.record()
+            for _ in range(K):
+                total = wl.resident_step(events)
+                a, g = wl.step_bytes(total)
+                app_bytes += a
+                gat_bytes += g
+            stop.record()
+            barrier()
+            launches = backend.launches - launches0
+            if use_graph:
+                # kernel nodes replayed (a replay makes no library call) plus what the library launched itself in
+                # the region: the small table-scatter kernel of the steps in which a sequence enters a new page
+                launches += K * wl.graph.launches_per_replay
+            ms = max_over_ranks(start.elapsed_time(stop))
+            regions.append((ms, app_bytes, gat_bytes, launches))
+            spent += ms
+            if spent >= 1000.0 * args.min_seconds or len(regions) >= max_regions:
+                break
+    rates = [(a + g) * world / (ms * 1e-3) / 1e9 for ms, a, g, _ in regions]
+    value = _median(rates)
+    ms = _median([r[0] for r in regions])
+    app_bytes = _median([r[1] for r in regions])
+    gat_bytes = _median([r[2] for r in regions])
+    launches = sum(r[3] for r in regions)
     status = backend.read_status(device)
     if status:
         raise SystemExit(f"device guard fired during the timed region: status {status}")
@@ -343,13 +393,14 @@ def run_barqkv(args):
         gbytes = [(t + wl.B) * per_tok for _, _, t in events]
         avg_dur = sum(durs) / len(durs)
         avg_bytes = sum(gbytes) / len(gbytes)
-        how = f"event pairs around {len(events)} sampled launches inside the timed region"
+        how = f"event pairs around {len(events)} sampled launches inside the timed regions"
     else:
-        # graph replay: the timed region is nothing but these launches back to back, so its CUDA-event
+        # graph replay: a timed region is nothing but these launches back to back, so its CUDA-event
         # time divided by the launch count is the launch duration (kernel plus the gap to the next one)
-        avg_dur = ms * 1e-3 / (K * wl.L)
-        avg_bytes = (app_bytes + gat_bytes) / (K * wl.L)
-        how = f"timed region / {K * wl.L} back-to-back launches of the replayed graph"
+        n_launch = len(regions) * K * wl.L
+        avg_dur = sum(r[0] for r in regions) * 1e-3 / n_launch
+        avg_bytes = sum(r[1] + r[2] for r in regions) / n_launch
+        how = f"{len(regions)} timed regions / {n_launch} back-to-back launches of the replayed graph"
     achieved = avg_bytes / avg_dur / 1e9
     roofline = {"bound": "hbm", "kernel": "gather_bulk_kernel" + (" (append fused)" if wl.fused else " + append_rows_kernel"),
                 "how": how, "achieved": round(achieved, 1), "peak": peak,
@@ -361,8 +412,12 @@ def run_barqkv(args):
     if tpath.exists():
         try:
             t = json.loads(tpath.read_text())
-            # DRAM bytes per algorithmic byte measured by ncu on a smaller case, scaled to this launch
-            roofline["traffic"] = int(t["dram_bytes_per_algorithmic_byte"] * roofline["bytes_per_launch"])
+            # DRAM bytes per algorithmic byte measured by ncu on a smaller case with the same number of KV
+            # heads per GPU, scaled to this launch; null for a head count nobody captured
+            ratio = t.get("by_heads", {}).get(str(wl.H))
+            if ratio is not None:
+                roofline["traffic"] = int(ratio * roofline["bytes_per_launch"])
+                roofline["traffic_source"] = t.get("source")
         except Exception:  # noqa: BLE001
             pass
 
@@ -381,6 +436,9 @@ def run_barqkv(args):
     e2e_value = e2e_bytes * world / e2e_s / 1e9
     h2d = 2 * wl.host_k.numel() * wl.host_k.element_size()
 
+    # ---- the metric's second half: decode tokens appended per second, append only -------
+    append_only = wl.append_only_leg(append_steps, barrier, max_over_ranks, backend) if use_graph else None
+
     line = {
         "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
         "ms_per_step": round(ms / K, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
@@ -392,6 +450,11 @@ def run_barqkv(args):
                    "launch": ("one update() kernel per layer" if wl.fused else "append() + gather() per layer")
                    + (", replayed from a CUDA graph" if use_graph else ", called from Python"),
                    "l2": "inputs larger than L2: each step reads ~%.1f GB of pool per GPU" % (gat_bytes / K / 2 / 1e9)},
+        "timed_regions": {"count": len(regions), "steps_each": K, "ms_median": round(ms, 3),
+                          "ms_min": round(min(r[0] for r in regions), 3), "ms_max": round(max(r[0] for r in regions), 3),
+                          "value_min": round(min(rates), 1), "value_max": round(max(rates), 1),
+                          "note": "value and ms_per_step are the median region's; every region is exactly `steps` steps "
+                                  "between barriers, max over ranks"},
         "pct_of_nominal_8TBs": round(100 * value / world / NOMINAL_PEAK_GBS, 2),
         "pct_of_measured_copy": round(100 * value / world / peak, 2),
         "decode_tokens_per_s": round(wl.B * K / (ms * 1e-3), 1),
@@ -400,10 +463,23 @@ def run_barqkv(args):
         "roofline": roofline,
         "e2e": {"value": round(e2e_value, 1), "unit": UNIT, "h2d_bytes_per_step": h2d * world,
                 "d2h_bytes_per_step": 4 * world, "steps": e2e_steps,
-                "ms_per_step": round(e2e_s * 1e3 / e2e_steps, 4)},
+                "ms_per_step": round(e2e_s * 1e3 / e2e_steps, 4),
+                "note": "per step: the new K/V rows of all layers come from pinned host memory, the step runs, and "
+                        "the 4-byte device status word is read back and checked; the gathered K/V stay on the device "
+                        "on purpose - they are the attention operand, not a result the host consumes"},
         "gpu_launches": launches,
         "clocks": clocks.summary,
     }
+    if append_only is not None:
+        line["decode_append_tokens_per_s"] = append_only["per_layer"]["tokens_per_s"]
+        line["decode_append"] = append_only
+
+    # ---- the other configurations, short legs -----------------------------------------
+    if not args.no_legs and not args.shard_heads:
+        del wl
+        torch.cuda.empty_cache()
+        line["configs"] = run_legs(world, rank, local, device, barrier, max_over_ranks, backend, peak, peak_kind,
+                                   quick=args.quick_legs)
 
     # ---- CPU baseline beside it (rank 0, N = 1 only) ------------------------------
     if world == 1:
@@ -414,14 +490,69 @@ def run_barqkv(args):
         dist.destroy_process_group()
 
 
+def run_legs(world, rank, local, device, barrier, max_over_ranks, backend, peak, peak_kind, quick=False):
+    """Short legs of the other configurations (chunked prefill at page 16 and 32, the 70B-shaped gather,
+    continuous-batching churn), each through ``barqtrain_b200.benchmarks.workloads`` at the
+    configuration's full shape for this rank's KV-head shard; one entry per leg."""
+    from barqtrain_b200.benchmarks.workloads import WORKLOADS
+
+    plan = [
+        ("chunked-prefill-ps16", "prefill", dict(page_size=16), 48, 4),
+        ("chunked-prefill-ps32", "prefill", dict(page_size=32), 48, 4),
+        ("llama3-70b-gather", "gather70b", {}, 24, 3),
+        ("continuous-batching-churn", "churn", {}, 1000, 20),
+    ]
+    out = {}
+    for name, key, kwargs, steps, warmup in plan:
+        if quick:
+            steps, warmup = max(4, steps // 8), 3
+            if key != "churn":
+                kwargs = dict(kwargs, layers=8)
+        try:
+            with ClockSampler(local) as clocks:
+                res = WORKLOADS[key](world, rank, device, steps, warmup, sync=barrier, **kwargs)
+            ms = max_over_ranks(res["ms"])
+            value = res["bytes"] * world / (ms * 1e-3) / 1e9
+            entry = {"workload": res["config"], "value": round(value, 1), "unit": UNIT, "steps": steps, "warmup": warmup,
+                     "ms_per_step": round(ms / steps, 4), "seconds_timed": round(ms * 1e-3, 3),
+                     "frac_of_%s_copy" % peak_kind: round(value / world / peak, 4),
+                     "frac_of_nominal_8TBs": round(value / world / NOMINAL_PEAK_GBS, 4),
+                     "tokens_per_s": round(res["tokens"] / (ms * 1e-3), 1), "gpu_launches": res["launches"],
+                     "us_per_launch": round(ms * 1e3 / max(res["launches"], 1), 2), "clocks": clocks.summary}
+            if "extra" in res:
+                entry["extra"] = res["extra"]
+            status = backend.read_status(device)
+            if status:
+                entry["device_status"] = status
+        except Exception as exc:  # noqa: BLE001 - a leg that cannot run must not take the headline with it
+            entry = {"error": f"{type(exc).__name__}: {str(exc)[:200]}"}
+        out[name] = entry
+        torch.cuda.empty_cache()
+    return out
+
+
 # ---------------------------------------------------------------------------
 # the CPU arm: the oracle's port of the reference's CPU path
 # ---------------------------------------------------------------------------
 def cpu_baseline(budget_s: float = 15.0, want_native: bool = True, steps_max: int = 2000, warmup: int = 1):
     """Time the reference's CPU algorithm (per-token strided assignment loop for append,
     flattened view + ``.contiguous()`` for gather) on ONE layer of the workload, all 64
-    sequences at their prompt lengths, for whole decode steps until ``budget_s`` is used."""
-    from oracle.paged_kv_oracle import OracleLayer
+    sequences at their prompt lengths, for whole decode steps until ``budget_s`` is used.
+
+    The layer class is the reference's own ``BarqPagedKVCacheLayer`` when its byte-compiled CPU path is at
+    hand (``oracle/ref_python.py`` -> ``oracle/_ref``; ``kind: "reference"``), else the oracle's restatement
+    of it (``kind: "port"``).  Only the class's public methods are used, so both run the same script."""
+    from oracle import ref_python
+
+    kind, layer_cls = "port", None
+    try:
+        module = ref_python.load()
+        if module is not None:
+            kind, layer_cls = "reference", module.BarqPagedKVCacheLayer
+    except Exception:  # noqa: BLE001 - e.g. bytecode of another Python version: the port runs instead
+        layer_cls = None
+    if layer_cls is None:
+        from oracle.paged_kv_oracle import OracleLayer as layer_cls
 
     torch.set_num_threads(os.cpu_count() or 1)
     g, prompts = seeded_lengths()
@@ -429,12 +560,9 @@ def cpu_baseline(budget_s: float = 15.0, want_native: bool = True, steps_max: in
     dtype = torch.bfloat16
     layers = []
     for n in prompts:                                   # set-up (untimed): caches already holding the prompts
-        lay = OracleLayer(1, -(-(n + steps_max + warmup + 1) // ps) * ps, ps)
-        lay._allocate(torch.empty(1, H, 1, D, dtype=dtype))
-        flat = lay.keys.view(1, H, -1, D)
-        flat[0, :, :n] = torch.randn(H, n, D, generator=g).to(dtype)
-        lay.values.view(1, H, -1, D)[0, :, :n] = flat[0, :, :n]
-        lay.seq_lens[0] = n
+        lay = layer_cls(1, -(-(n + steps_max + warmup + 1) // ps) * ps, ps)
+        prompt = torch.randn(1, H, n, D, generator=g).to(dtype)
+        lay.append(prompt, prompt)
         layers.append(lay)
     k_new = torch.randn(B, 1, H, 1, D, generator=g).to(dtype)
     per_tok = 4 * H * D * 2
@@ -454,12 +582,14 @@ def cpu_baseline(budget_s: float = 15.0, want_native: bool = True, steps_max: in
     while True:
         one_step()
         steps += 1
-        moved += (B + sum(int(l.seq_lens[0]) for l in layers)) * per_tok
+        moved += (B + sum(lay.get_seq_length() for lay in layers)) * per_tok
         if time.perf_counter() - t0 > budget_s or steps >= steps_max:
             break
     dt = time.perf_counter() - t0
-    out = {"value": round(moved / dt / 1e9, 3), "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+    out = {"value": round(moved / dt / 1e9, 3), "unit": UNIT, "cores": torch.get_num_threads(), "kind": kind,
            "host_cpus": os.cpu_count(), "steps": steps, "ms_per_step": round(dt * 1e3 / steps, 3),
+           "what": ("the reference's own BarqPagedKVCacheLayer (python/barqtrain/kv_cache.py), CPU path, byte-compiled "
+                    "from its checkout" if kind == "reference" else "the oracle's restatement of the reference's CPU path"),
            "sample": f"1 of {CFG['layers']} layers, all {B} sequences, {steps} decode steps "
                      f"(append loop + view.contiguous() gather), {dt:.1f} s; GB/s is per-layer work / time, "
                      f"so it compares directly with the GPU figure",
@@ -602,7 +732,7 @@ def run_micro(args):
     dtype = torch.bfloat16
     gen = torch.Generator(device=device).manual_seed(7)
     g = torch.Generator().manual_seed(CFG["seed"])
-    if args.micro in ("gather", "update", "attention"):
+    if args.micro in ("gather", "update", "update-layers", "attention"):
         if args.lengths == "loguniform":          # the 70B-shaped gather configuration: 32 sequences in [1k, 32k]
             import math
             u = torch.rand(32, generator=g, dtype=torch.float64)
@@ -675,6 +805,25 @@ def run_micro(args):
                 for _ in range(args.reps):
                     cache.update(0, new, full, k1, k1, args.layout, out=out, mode=args.mode)
             return launch, args.reps, (full.total + B) * per_tok * args.reps
+        if args.micro == "update-layers":
+            # the decode step's launches: `layers` fused append + gather kernels issued by one native call
+            many = BlockTableKVCache(args.layers, H, D, page_size=ps, num_pages=pages, max_seqs=B,
+                                     max_blocks_per_seq=-(-(max(lens) + 64) // ps), dtype=dtype, device=device,
+                                     free_order=torch.randperm(pages, generator=g).tolist(), zero_pages=False)
+            mslots = [many.open(i) for i in range(B)]
+            fill = many.begin_append(mslots, lens)          # lengths only: the pools' contents do not matter for timing
+            many.end_append(fill)
+            new = many.begin_append(mslots, [1] * B)
+            many.end_append(new)
+            full = many.begin_gather(mslots)
+            outs = [(torch.empty(H, full.total, D, dtype=dtype, device=device),
+                     torch.empty(H, full.total, D, dtype=dtype, device=device)) for _ in range(2)]
+            k_all = torch.randn(args.layers, B, H, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
+
+            def launch():
+                for _ in range(args.reps):
+                    many.update_layers(new, full, k_all, k_all, outs, "HND", mode=args.mode)
+            return launch, args.layers * args.reps, (full.total + B) * per_tok * args.layers * args.reps
         if args.micro == "attention":
             total = sum(lens)
             k = torch.randn(total, H, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
@@ -692,13 +841,18 @@ def run_micro(args):
             return launch, args.reps, total * 2 * H * D * 2 * args.reps
         if args.micro == "append-prefill":
             total = args.chunk * B
-            k = torch.randn(total, H, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
-            v = torch.randn(total, H, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
+            # four source sets taken in turn, so that consecutive launches read different memory (1 GB at 8 heads)
+            srcs = [(torch.randn(total, H, D, generator=gen, device=device, dtype=torch.float32).to(dtype),
+                     torch.randn(total, H, D, generator=gen, device=device, dtype=torch.float32).to(dtype))
+                    for _ in range(4)]
+            if args.src_head_major:           # head-major sources: rows of a head adjacent in memory
+                srcs = [(k.transpose(0, 1).contiguous().transpose(0, 1), v.transpose(0, 1).contiguous().transpose(0, 1))
+                        for k, v in srcs]
             batch = cache.begin_append(slots, [args.chunk] * B)   # the same chunk lands on the same pages every launch
 
             def launch():
-                for _ in range(args.reps):
-                    cache.append(0, batch, k, v)
+                for i in range(args.reps):
+                    cache.append(0, batch, *srcs[i & 3])
             return launch, args.reps, total * per_tok * args.reps
         if args.micro == "append-layers":
             # one decode token per sequence for `layers` layers in ONE launch (pools of all layers are one tensor)
@@ -837,8 +991,8 @@ def run_reference(args):
                    "head_dim": CFG["head_dim"], "page_size": CFG["page_size"], "batch": CFG["batch"]},
         "cpu_baseline": base,
         "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "note": "reference's CPU PyTorch path (oracle port of _python_append + current_tensors().contiguous()) on the "
-                "host cores; each step is a bounded sample (one layer) of the workload",
+        "note": "the reference's CPU PyTorch path (_python_append + current_tensors().contiguous(); see cpu_baseline.kind "
+                "and .what) on the host cores; each step is a bounded sample (one layer) of the workload",
     }
     print(json.dumps(line), flush=True)
 
@@ -852,14 +1006,20 @@ def main():
                     help="reference: the reference's CPU path (default run) or CUDA kernel (--micro append-legacy); "
                          "torch: --micro gather with torch.index_select over the pages, for comparison")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="budget of the CPU baseline leg")
+    ap.add_argument("--min-seconds", type=float, default=1.0,
+                    help="repeat the timed K-step region until this much device time has been measured")
+    ap.add_argument("--no-legs", action="store_true", help="skip the short legs of the other configurations")
+    ap.add_argument("--quick-legs", action="store_true", help="legs with fewer layers and steps (smoke runs)")
     ap.add_argument("--eager", action="store_true",
                     help="call update() per layer from Python every step instead of replaying a CUDA graph")
     ap.add_argument("--two-launches", action="store_true",
                     help="per layer call append() then gather() instead of the single update() launch")
-    ap.add_argument("--micro", choices=["gather", "update", "attention", "append-prefill", "append-decode", "append-layers", "append-legacy"],
+    ap.add_argument("--micro", choices=["gather", "update", "update-layers", "attention", "append-prefill", "append-decode", "append-layers", "append-legacy"],
                     help="time one kernel alone on a one-layer case instead of the full step")
     ap.add_argument("--mode", default="auto", choices=["auto", "vector", "bulk"])
     ap.add_argument("--layout", default="HND", choices=["HND", "NHD"])
+    ap.add_argument("--src-head-major", action="store_true",
+                    help="micro append-prefill: new rows laid out [H, tokens, D] instead of [tokens, H, D]")
     ap.add_argument("--heads", type=int, default=8, help="KV heads on this GPU (micro cases)")
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--chunk", type=int, default=2048, help="tokens per sequence per append (append-prefill)")

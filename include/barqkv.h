@@ -4,7 +4,8 @@
  * C ABI of libbarqkv.so.  Every entry point takes raw device pointers, plain
  * integers and a CUDA stream; nothing here allocates device memory, takes a
  * lock, or synchronises with the device (barqkv_max_length, whose job is a
- * blocking read of the lengths, is the one exception).  All functions return 0 on success
+ * blocking read of the lengths, is the one exception), and the library keeps no
+ * mutable process-wide settings.  All functions return 0 on success
  * or a negative BARQKV_E_* code; barqkv_last_error() then holds a message for
  * the calling thread.  Work is enqueued on the given stream and runs
  * asynchronously; device-side guards (bad block-table entry, capacity) never
@@ -23,7 +24,7 @@
 extern "C" {
 #endif
 
-#define BARQKV_VERSION 101 /* major*100 + minor */
+#define BARQKV_VERSION 102 /* major*100 + minor */
 
 /* host-side return codes */
 #define BARQKV_OK 0
@@ -41,6 +42,20 @@ extern "C" {
 #define BARQKV_MODE_AUTO 0
 #define BARQKV_MODE_VECTOR 1  /* 16-byte ld/st through registers */
 #define BARQKV_MODE_BULK 2    /* cp.async.bulk global->shared->global, mbarrier pipelined */
+
+/*
+ * BARQKV_FLAG_DESC_STABLE (argument `flags` of the appends; OR-ed into `mode` of barqkv_gather and
+ * barqkv_update): the caller vouches that everything the call reads BESIDES the K/V payload - the block
+ * table, slots, seq_start / seq_lens, cu_new, cu_out - was completely written before the kernel that
+ * precedes this call in `stream` was enqueued, and stays unchanged until this call's kernel has run.
+ * True for the second and later layers of a step whose description was uploaded once before the first
+ * layer.  The kernel is then launched as a programmatic dependent of its predecessor: its prologue
+ * (page counts, first page hand-out, first block-table look-ups) overlaps the predecessor's tail and only
+ * its first copy waits for the predecessor to finish.  Consecutive flagged calls that pass `work` must
+ * alternate between two work buffers, because the later kernel starts taking pages while the earlier one
+ * may still be handing out its last.  Results are the same with and without the flag.
+ */
+#define BARQKV_FLAG_DESC_STABLE 0x100
 
 typedef void* barqkv_stream_t; /* a cudaStream_t */
 
@@ -99,19 +114,6 @@ typedef struct barqkv_rows_layout {
     int32_t reserved;
 } barqkv_rows_layout;
 
-/* tuning knobs for experiments (process-wide, not thread-safe); value 0 restores the default */
-#define BARQKV_KNOB_BULK_STAGES 1        /* ring stages of the bulk gather (3..32) */
-#define BARQKV_KNOB_BULK_CTAS_PER_SM 2   /* persistent one-warp CTAs per SM of the bulk gather */
-#define BARQKV_KNOB_VECTOR_CTAS_PER_SM 3 /* CTAs per SM of the vector gather */
-#define BARQKV_KNOB_INTERLEAVE 4         /* static shares only. 1: every gridDim-th group of 32 pages; 0: contiguous */
-#define BARQKV_KNOB_GROUP_TILES 5        /* pages handed out per atomic fetch by the bulk gather (1..32) */
-#define BARQKV_KNOB_STATIC_SHARES 6      /* 1: ignore `work` and split pages statically among CTAs */
-#define BARQKV_KNOB_STATIC_PERMILLE 8    /* thousandths of the pages split evenly among CTAs before the atomic hand-out (-1 = default) */
-#define BARQKV_KNOB_TENSOR_STORE 9       /* 0: token-major outputs use row copies only; default: tiled TMA store per full page */
-#define BARQKV_KNOB_ATTN_L2_PROMOTION 10 /* decode attention: L2 promotion of the page loads. 0 none, 1 128 B, 2 256 B (-1 = default) */
-#define BARQKV_KNOB_ATTN_SPLIT_TOKENS 11 /* decode attention: tokens per split before adapting to the batch (0 = default 512) */
-#define BARQKV_KNOB_PDL 7                /* 1: launch the bulk gather with programmatic stream serialization */
-
 int barqkv_version(void);
 const char* barqkv_last_error(void);
 
@@ -120,9 +122,6 @@ int barqkv_sm_count(void);
 
 /* Kernels this library has enqueued so far in this process (every entry point counts its launches). */
 int64_t barqkv_launch_count(void);
-
-/* Set a BARQKV_KNOB_* value.  No counterpart in the reference, which has no tunables. */
-int barqkv_set_tuning(int32_t knob, int32_t value);
 
 /*
  * Append new K/V rows through the block table.
@@ -135,13 +134,23 @@ int barqkv_set_tuning(int32_t knob, int32_t value);
  * cu_new is NULL) to its sequence, the first one landing at position
  * seq_start[i].  total_tokens = cu_new[n] (n*tokens_per_entry), known to the
  * host.  Pages must already be in the table; lengths are kept by the caller.
+ * work: device int32[2] scratch, zero before its first use, or NULL (same rules
+ * as for barqkv_gather: the kernel leaves it zero, launches that may overlap
+ * must not share it).  With it, appends that bring at least a page of tokens
+ * per entry on average (prefill chunks) move whole pages with the copy engine
+ * - one tiled TMA load of a [page_size][1 head][head_dim] box of the new rows
+ * (token-major sources) or one bulk copy (head-major sources) and one bulk
+ * store per page, head and K/V - when rows and strides are 16-byte aligned and
+ * the new rows are packed.  Everything else (decode, unaligned rows, NULL)
+ * takes the 16-byte-vector row kernel; results are identical.
+ * flags: 0 or BARQKV_FLAG_DESC_STABLE.
  */
 int barqkv_append(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,
                   const barqkv_block_table* table,
                   const int32_t* seq_start, const int32_t* cu_new,
                   int32_t n, int32_t tokens_per_entry, int32_t total_tokens,
                   const void* k_new, const void* v_new, const barqkv_rows_layout* new_rows,
-                  int32_t* status, barqkv_stream_t stream);
+                  int32_t* status, int32_t* work, int32_t flags, barqkv_stream_t stream);
 
 /*
  * barqkv_append for `layers` layers in ONE launch: layer l uses the pools at
@@ -158,7 +167,8 @@ int barqkv_append_layers(const barqkv_pool_layout* pool, void* k_pool, void* v_p
                          const int32_t* seq_start, const int32_t* cu_new,
                          int32_t n, int32_t tokens_per_entry, int32_t total_tokens,
                          const void* k_new, const void* v_new, const barqkv_rows_layout* new_rows,
-                         int64_t new_layer_stride, int32_t* status, barqkv_stream_t stream);
+                         int64_t new_layer_stride, int32_t* status, int32_t* work, int32_t flags,
+                         barqkv_stream_t stream);
 
 /*
  * Largest of seq_lens[0..n) (device int32), read back on `stream`: copies the n values to the host,
@@ -286,6 +296,50 @@ int barqkv_update(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,
                   barqkv_stream_t stream);
 
 /*
+ * barqkv_update for `layers` layers, one launch per layer, issued by one call: layer l uses the pools
+ * at k_pool / v_pool + l * pool_layer_stride, the new rows at k_new / v_new + l * new_layer_stride
+ * (strides in elements) and writes its gathered rows to k_out[l % num_out] / v_out[l % num_out] (host
+ * arrays of device pointers: two pairs let consecutive layers alternate buffers).  The batch
+ * description (seq_start, cu_new, cu_out, seq_lens_after) and the block table are shared by all
+ * layers and must not change while the launches run.
+ * Replaces `layers` calls of the reference layer's update() (python/barqtrain/kv_cache.py:135-142), each
+ * of which costs two kernel launches and two device synchronisations there
+ * (csrc/kernels/paged_kv_cache.cu:93,104-127, kv_cache.py:150-153).  Here the host pays one call, and
+ * from the second layer on each launch is a programmatic dependent of the one before: because it reads
+ * the same, unchanged description, its prologue (page counts, first hand-out, first block-table
+ * look-ups) runs while the previous layer's last copies drain, and only its first copy waits for that
+ * layer to finish.  work: device int32[4] scratch, zero before its first use (two counter pairs that
+ * consecutive layers alternate); the kernels leave it zero.  For callers that have every layer's new rows
+ * at hand (a recorded decode step, cache import); results equal `layers` calls of barqkv_update.
+ */
+int barqkv_update_layers(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,
+                         int32_t layers, int64_t pool_layer_stride,
+                         const barqkv_block_table* table,
+                         const int32_t* seq_start, const int32_t* cu_new,
+                         int32_t n, int32_t tokens_per_entry, int32_t total_new_tokens,
+                         const void* k_new, const void* v_new, const barqkv_rows_layout* new_rows,
+                         int64_t new_layer_stride,
+                         const int32_t* cu_out, int64_t total_tokens_hint,
+                         void* const* k_out, void* const* v_out, int32_t num_out,
+                         const barqkv_rows_layout* out_rows,
+                         int32_t mode, int32_t* status, int32_t* work, const int32_t* seq_lens_after,
+                         barqkv_stream_t stream);
+
+/*
+ * Self-test of the bounded waits (no counterpart in the reference, which has no device-side waits).
+ * Runs the bulk gather on the given small batch with ONE CTA whose ring stages each expect 16 bytes
+ * more than their copies bring, so the first wait can never be satisfied, and with every wait bounded
+ * by wait_cycles clock cycles (1 .. 2e9) instead of the default ~1 s.  The kernel must give up, let the
+ * copies it had already issued land, OR BARQKV_S_TIMEOUT into *status (required) and return; the
+ * context stays usable and nothing spins beyond the bound.  The output is left partly written.
+ */
+int barqkv_gather_wait_selftest(const barqkv_pool_layout* pool, const void* k_pool, const void* v_pool,
+                                const barqkv_block_table* table,
+                                const int32_t* seq_lens, const int32_t* cu_out, int32_t n,
+                                void* k_out, void* v_out, const barqkv_rows_layout* out_rows,
+                                int64_t wait_cycles, int32_t* status, barqkv_stream_t stream);
+
+/*
  * barqkv_gather for several layers in one launch: layer l reads the pools at k_pool / v_pool +
  * l * pool_layer_stride and writes its outputs at k_out / v_out + l * out_layer_stride (strides in
  * elements); everything else as in barqkv_gather, bulk path only (16-byte aligned rows and strides),
@@ -338,12 +392,19 @@ int barqkv_paged_decode_attention(const barqkv_pool_layout* pool, const void* k_
  * caller-owned `work` buffer.  Meant for callers such as a server that has
  * already given all free device memory to its own arena, or a plugin host that
  * forbids allocation inside an operator call.  This function and everything it
- * calls allocate nothing, on the host or on the device.
+ * calls make no allocation call of their own, on the host or on the device.
+ * One caveat: the array is part of the library's device code, so the CUDA
+ * runtime reserves its 4 KiB (with the rest of the code image) when it loads
+ * the library's module on a device - at the first call of ANY function of this
+ * library on that device, this one included, under CUDA's lazy loading.  A
+ * caller whose arena takes all remaining memory should make one call of this
+ * library before the arena is created.
  *
  * work_slot selects one of BARQKV_STATIC_WORK_SLOTS counter pairs; a value
  * outside [0, BARQKV_STATIC_WORK_SLOTS) is refused with BARQKV_E_LIMIT.  All
  * calls on a device share the array, and a slot still holds what its last
- * user left: each call first clears its slot on `stream`.  Two calls that can
+ * user left: each call first checks its arguments and then clears its slot on
+ * `stream` (a refused call enqueues nothing).  Two calls that can
  * be in flight on the GPU at the same time (different streams) must use
  * different slots, or they corrupt each other's page hand-out.
  *

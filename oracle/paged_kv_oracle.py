@@ -22,6 +22,8 @@ What is restated, with the reference lines each part follows:
   explicit block tables: one reference layer per (layer, sequence) with
   ``max_batch_size=1``.  Logical page ``j`` of a sequence is
   ``layer.keys[0, :, j]``; the gathered sequence is ``current_tensors()[.][0]``.
+* ``rope_rotate_keys``       - the K half of ``apply_rope_to_qk``  (ops.py:376-428),
+  pinned by ``tests/golden/rope_prefill.npz`` (the helper's own output).
 """
 
 from __future__ import annotations
@@ -206,3 +208,12 @@ def bits(t: torch.Tensor) -> torch.Tensor:
     """Reinterpret a floating tensor as same-width integers for bit-exact comparison."""
     width = {1: torch.uint8, 2: torch.int16, 4: torch.int32, 8: torch.int64}[t.element_size()]
     return t.contiguous().view(width)
+
+
+def rope_rotate_keys(k: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """Rotary embedding of ``k`` ``[..., T, D]`` with tables ``[T, D/2]``: the reference helper's
+    expressions (ops.py:409-427) - real half ``k1*cos - k2*sin``, imaginary half ``k1*sin + k2*cos``,
+    every product and sum rounded to the tensor's dtype as torch's CPU kernels round them."""
+    half = k.shape[-1] // 2
+    k1, k2 = k[..., :half], k[..., half:]
+    return torch.cat([k1 * cos - k2 * sin, k1 * sin + k2 * cos], dim=-1)

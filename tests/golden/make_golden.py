@@ -34,6 +34,7 @@ sys.dont_write_bytecode = True
 sys.path.insert(0, str(REF / "python"))
 
 from barqtrain.kv_cache import BarqPagedKVCacheLayer  # noqa: E402  (the reference)
+from barqtrain.ops import apply_rope_to_qk  # noqa: E402  (the reference)
 
 from tests import scenarios as S  # noqa: E402
 
@@ -123,8 +124,28 @@ def gen_overflow():
     np.savez_compressed(HERE / "legacy_overflow.npz", **out)
 
 
+def gen_rope():
+    """The reference's rotary helper on a seeded prefill, per dtype: its rotated K rows, plus the cos / sin
+    tables formed with the helper's own expressions - stored so that a test does not depend on the host's
+    libm - after checking that they reproduce the helper's output bit for bit."""
+    out = {}
+    for name in ("fp32", "fp16", "bf16"):
+        k, _v = S.rope_prefill(name)
+        _, k_rope = apply_rope_to_qk(k, k)
+        T, D = k.shape[2], k.shape[3]
+        cos, sin = S.rope_tables(T, D, k.dtype)
+        half = D // 2
+        again = torch.cat([k[..., :half] * cos - k[..., half:] * sin, k[..., :half] * sin + k[..., half:] * cos], dim=-1)
+        assert torch.equal(S.bits(again), S.bits(k_rope)), name
+        out[f"k_rope_{name}"] = npbits(k_rope)
+        out[f"cos_{name}"] = npbits(cos)
+        out[f"sin_{name}"] = npbits(sin)
+    np.savez_compressed(HERE / "rope_prefill.npz", **out)
+
+
 def main():
     gen_known_answer()
+    gen_rope()
     gen_small_paged("small_paged_fp32")
     gen_small_paged("small_paged_bf16", dtype=torch.bfloat16, kv_heads=2, head_dim=128,
                     prefill=(21, 64, 90), decode_steps=5, num_pages=40, seed=2001)

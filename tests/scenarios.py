@@ -130,6 +130,10 @@ def legacy_script(dtype_name: str, seed: int = 4321):
     app(2, 6)      # rows 0, 1 -> (20, 20, 14)
     ops.append(("reset",))
     app(1, 9)
+    ops.append(("repeat", 2))                      # beam expansion: row 0 twice, lengths (9, 9), batch capacity 2
+    app(2, 3)      # both copies grow on their own -> (12, 12)
+    ops.append(("select", torch.tensor([1, 1, 0])))  # reorder with a duplicate: batch capacity 3
+    app(3, 2)      # (14, 14, 14)
     return dict(max_batch_size=3, max_cache_len=22, page_size=4), ops
 
 
@@ -175,3 +179,25 @@ def ragged_lengths(g: torch.Generator, n: int, lo: int, hi: int, log_uniform: bo
         import math
         return [int(round(math.exp(math.log(lo) + float(x) * (math.log(hi) - math.log(lo))))) for x in u]
     return torch.randint(lo, hi + 1, (n,), generator=g).tolist()
+
+
+# --------------------------------------------------------------------------
+# Scenario 5: rotary embedding of a prefill's K rows, the reference helper's formula
+# (python/barqtrain/ops.py:376-428: positions 0..T-1, base 10000, halves convention)
+# --------------------------------------------------------------------------
+def rope_prefill(dtype_name: str, seed: int = 777):
+    """``k`` and ``v`` ``[B, H, T, D]`` of one prefill in the given dtype."""
+    dtype = DTYPES[dtype_name]
+    g = torch.Generator().manual_seed(seed)
+    B, H, T, D = 2, 3, 45, 64
+    return randn(g, (B, H, T, D), dtype), randn(g, (B, H, T, D), dtype)
+
+
+def rope_tables(T: int, D: int, dtype: torch.dtype):
+    """cos / sin ``[T, D/2]`` exactly as the reference helper forms them (ops.py:394-407)."""
+    positions = torch.arange(T, dtype=dtype)
+    half = D // 2
+    freqs = torch.arange(half, dtype=torch.float32)
+    freqs = 1.0 / torch.pow(10000.0, freqs / half)
+    angles = positions[:, None] * freqs[None, :]
+    return torch.cos(angles).to(dtype), torch.sin(angles).to(dtype)

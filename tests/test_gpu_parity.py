@@ -725,6 +725,99 @@ def test_full_size_layer_against_c_oracle(backend, shape):
     cache.check_device_status()
 
 
+@pytest.mark.parametrize("ps", [16, 32])
+def test_full_size_chunked_prefill_against_c_oracle(backend, ps):
+    """One layer of the chunked-prefill configuration at full size (16 sequences of 8192 tokens in four
+    2048-token chunks, 8 heads, head_dim 128, fp16, pool shuffled by a seeded permutation; page 16 and
+    32): every chunk goes through ``append`` - token-major rows for three chunks, a head-major source for
+    the last, so both page-sized copy paths run - and the whole pool and every gathered row equal the C
+    oracle's."""
+    from barqtrain_b200 import BlockTableKVCache
+    from oracle import c_oracle
+
+    B, chunk, chunks, H, D, dtype = 16, 2048, 4, 8, 128, torch.float16
+    pages = B * chunk * chunks // ps
+    cache = BlockTableKVCache(1, H, D, page_size=ps, num_pages=pages, max_seqs=B, max_blocks_per_seq=chunk * chunks // ps,
+                              dtype=dtype, device=DEV, seed=1237)
+    slots = [cache.open(i) for i in range(B)]
+    ref_k = torch.zeros(H, pages, ps, D, dtype=dtype)
+    ref_v = torch.zeros_like(ref_k)
+    gen = torch.Generator(device=DEV).manual_seed(9)
+    launches = backend.launches
+    for c in range(chunks):
+        total = B * chunk
+        if c < chunks - 1:
+            k = torch.randn(total, H, D, generator=gen, device=DEV, dtype=torch.float32).to(dtype)
+            v = torch.randn(total, H, D, generator=gen, device=DEV, dtype=torch.float32).to(dtype)
+        else:                                    # [H, total, D] in memory, handed over as [total, H, D]
+            k = torch.randn(H, total, D, generator=gen, device=DEV, dtype=torch.float32).to(dtype).transpose(0, 1)
+            v = torch.randn(H, total, D, generator=gen, device=DEV, dtype=torch.float32).to(dtype).transpose(0, 1)
+        batch = cache.begin_append(slots, [chunk] * B)
+        cache.append(0, batch, k, v)
+        start = torch.full((B,), c * chunk, dtype=torch.int32)
+        cu = torch.tensor(batch.cu, dtype=torch.int32)
+        assert c_oracle.append_paged(ref_k, ref_v, cache.table_host.clone(), None, start, cu, k.cpu().contiguous(),
+                                     v.cpu().contiguous()) == 0
+        cache.end_append(batch)
+    assert backend.launches <= launches + 2 * chunks        # per chunk: one append kernel (+ one table scatter)
+    cache.check_device_status()
+    assert torch.equal(S.bits(cache.pools[0, 0]), S.bits(ref_k)), "K pool differs"
+    assert torch.equal(S.bits(cache.pools[0, 1]), S.bits(ref_v)), "V pool differs"
+    gb = cache.begin_gather(slots)
+    want_k = torch.zeros(gb.total, H, D, dtype=dtype)
+    want_v = torch.zeros_like(want_k)
+    assert c_oracle.gather_paged(ref_k, ref_v, cache.table_host.clone(), None,
+                                 torch.full((B,), chunk * chunks, dtype=torch.int32),
+                                 torch.tensor(gb.cu[:-1], dtype=torch.int32), want_k, want_v) == 0
+    kn, vn = cache.gather(0, gb, "NHD")
+    assert torch.equal(S.bits(kn), S.bits(want_k)) and torch.equal(S.bits(vn), S.bits(want_v))
+    cache.check_device_status()
+
+
+def test_bounded_wait_gives_up_flags_and_leaves_the_context_usable(backend):
+    """``barqkv_gather_wait_selftest``: one CTA of the bulk gather whose ring stages expect bytes that never
+    arrive, every wait bounded by about a millisecond.  The kernel must return on its own, report
+    ``BARQKV_S_TIMEOUT`` through the status word, take no longer than a few bounds, and leave the device in
+    working order: the same gather run normally afterwards is bit-exact."""
+    import ctypes
+    import time
+
+    from barqtrain_b200 import BlockTableKVCache, _ffi
+
+    H, D, ps, dtype = 2, 128, 16, torch.bfloat16
+    lens = [100, 37, 260]
+    g = torch.Generator().manual_seed(77)
+    cache = BlockTableKVCache(1, H, D, page_size=ps, num_pages=40, max_seqs=3, max_blocks_per_seq=20, dtype=dtype,
+                              device=DEV, seed=2)
+    slots = [cache.open(i) for i in range(3)]
+    k = S.randn(g, (sum(lens), H, D), dtype).to(DEV)
+    v = S.randn(g, (sum(lens), H, D), dtype).to(DEV)
+    cache.append_step(slots, lens, [k], [v])
+    gb = cache.begin_gather(slots)
+    want_k, want_v = cache.gather(0, gb, "HND", mode="bulk")
+    torch.cuda.synchronize()
+    assert backend.read_status(DEV) == 0
+
+    out_k, out_v = torch.zeros_like(want_k), torch.zeros_like(want_v)
+    rows = _ffi.RowsLayout(0, D, gb.total * D, 1, 0)
+    status = backend.status_word(DEV)
+    cycles = 2_000_000                                       # about 1 ms at the SM clock
+    t0 = time.perf_counter()
+    rc = backend.lib.barqkv_gather_wait_selftest(ctypes.byref(cache._pool_layout), cache._k_ptr[0], cache._v_ptr[0],
+                                                 gb.table_ref, gb.p_first, gb.p_cu, gb.n, out_k.data_ptr(),
+                                                 out_v.data_ptr(), ctypes.byref(rows), cycles, status.data_ptr(), gb.stream)
+    assert rc == 0, backend.lib.barqkv_last_error()
+    torch.cuda.synchronize()                                 # returns: the kernel did not spin past its bound
+    elapsed = time.perf_counter() - t0
+    assert elapsed < 1.0, f"the give-up took {elapsed:.3f} s for a 1 ms bound"
+    assert backend.read_status(DEV) == _ffi.S_TIMEOUT        # reported, and cleared by the read
+    # the context still works and the data are untouched
+    got_k, got_v = cache.gather(0, gb, "HND", mode="bulk")
+    torch.cuda.synchronize()
+    assert torch.equal(S.bits(got_k), S.bits(want_k)) and torch.equal(S.bits(got_v), S.bits(want_v))
+    assert backend.read_status(DEV) == 0
+
+
 def test_continuous_batching_churn_at_full_width_reads_back_exactly(backend):
     """The churn configuration at full width (256 live sequences, 8 heads, head_dim 128, fp16, page 16;
     two layers, 150 steps, about 380 sequences finished, released and replaced): after all the page
@@ -736,6 +829,36 @@ def test_continuous_batching_churn_at_full_width_reads_back_exactly(backend):
     assert res["verified"] is True
     assert res["extra"]["sequences_released"] > 200
     assert res["extra"]["pages_peak"] >= res["extra"]["pages_resident"] > 0
+
+
+@pytest.mark.parametrize("dtype_name", ["fp32", "fp16", "bf16"])
+def test_rope_fused_into_append_against_the_reference_helper(backend, golden_dir, dtype_name):
+    """A prefill appended with ``rope=(cos, sin)`` leaves in the pages exactly the K rows the reference's
+    ``apply_rope_to_qk`` (ops.py:376-428) returns for it - compared with the helper's stored output bit for
+    bit, using the helper's own cos / sin tables - and the V rows unchanged."""
+    from barqtrain_b200 import BlockTableKVCache
+
+    gold = np.load(golden_dir / "rope_prefill.npz")
+    k, v = S.rope_prefill(dtype_name)                          # [B, H, T, D]
+    B, H, T, D = k.shape
+    cos = torch.from_numpy(gold[f"cos_{dtype_name}"]).view(k.dtype)       # [T, D/2]
+    sin = torch.from_numpy(gold[f"sin_{dtype_name}"]).view(k.dtype)
+    want_k = torch.from_numpy(gold[f"k_rope_{dtype_name}"]).view(k.dtype)  # [B, H, T, D]
+    ps = 16
+    cache = BlockTableKVCache(1, H, D, page_size=ps, num_pages=2 * B * (-(-T // ps)), max_seqs=B,
+                              max_blocks_per_seq=-(-T // ps), dtype=k.dtype, device=DEV, seed=3)
+    slots = [cache.open(i) for i in range(B)]
+    rows = lambda t: t.permute(0, 2, 1, 3).reshape(B * T, H, D).to(DEV)   # packed [B*T, H, D]
+    full = lambda t: torch.cat([t, t], dim=-1).repeat(B, 1).to(DEV)       # per packed token, halves duplicated
+    batch = cache.begin_append(slots, [T] * B)
+    cache.append(0, batch, rows(k), rows(v), rope=(full(cos), full(sin)))
+    cache.end_append(batch)
+    gk, gv = cache.gather(0, cache.begin_gather(slots), "HND")            # [H, B*T, D]
+    cache.check_device_status()
+    got_k = gk.view(H, B, T, D).permute(1, 0, 2, 3)
+    got_v = gv.view(H, B, T, D).permute(1, 0, 2, 3)
+    assert torch.equal(S.bits(got_k), S.bits(want_k))
+    assert torch.equal(S.bits(got_v), S.bits(v))
 
 
 @pytest.mark.parametrize("dtype,D", [(torch.bfloat16, 128), (torch.float16, 64), (torch.float32, 32)])

@@ -84,6 +84,7 @@ def test_library_exports_every_symbol_the_header_declares():
     assert backend is not None, "libbarqkv.so must be built (python -c 'import __graft_entry__ as g; g.build()')"
     for name in sorted(declared):
         assert hasattr(backend.lib, name), name
+    assert declared <= set(_ffi.EXPORTS), declared - set(_ffi.EXPORTS)     # and the loader insists on each of them
     assert backend.version == int(re.search(r"#define BARQKV_VERSION (\d+)", header).group(1))
     # struct mirrors have the C sizes
     import ctypes
@@ -106,7 +107,17 @@ def test_argument_errors_come_back_as_codes_with_messages():
     rc = backend.lib.barqkv_gather(ctypes.byref(pool), 1, 1, ctypes.byref(table), 1, 1, 9000, 0, 1, 1,
                                    ctypes.byref(rows), 0, None, None, None)
     assert rc == -3 and b"8192" in backend.lib.barqkv_last_error()
-    assert backend.lib.barqkv_set_tuning(99, 1) == -1
+    # the serving library has no tuning knobs: no mutable process-wide settings behind the ABI
+    assert not hasattr(backend.lib, "barqkv_set_tuning") and not backend.tunable
+    with pytest.raises(_ffi.BarqKVError, match="no tuning knobs"):
+        backend.set_tuning(stages=4)
+    # the no-allocation gather refuses a slot outside its built-in scratch before touching the device
+    rc = backend.lib.barqkv_gather_noalloc(ctypes.byref(pool), 1, 1, ctypes.byref(table), 1, 1, 1, 0, 1, 1,
+                                           ctypes.byref(rows), 0, None, _ffi.STATIC_WORK_SLOTS, None)
+    assert rc == -3 and b"work_slot" in backend.lib.barqkv_last_error()
+    rc = backend.lib.barqkv_gather_wait_selftest(ctypes.byref(pool), 1, 1, ctypes.byref(table), 1, 1, 1, 1, 1,
+                                                 ctypes.byref(rows), 0, None, None)
+    assert rc == -1 and b"wait_cycles" in backend.lib.barqkv_last_error()
     # decode-attention workspace: none while one split per sequence suffices, else counters + partial results
     ws = backend.lib.barqkv_paged_decode_workspace_bytes
     assert ws(64, 8, 64, 0, 16) == 0 and ws(0, 8, 4096, 0, 16) == 0

@@ -4,7 +4,7 @@ import numpy as np
 import pytest
 import torch
 
-from oracle.paged_kv_oracle import OracleLayer, OraclePagedCache
+from oracle.paged_kv_oracle import OracleLayer, OraclePagedCache, rope_rotate_keys
 from tests import scenarios as S
 
 
@@ -119,3 +119,34 @@ def test_argument_checks():
         layer.append(k.double(), k.double())                              # dtype change
     empty = OracleLayer(2, 8, 4)
     assert empty.get_seq_length() == 0
+
+
+@pytest.mark.parametrize("dtype_name", ["fp32", "fp16", "bf16"])
+def test_rope_restatement_against_the_reference_helper(golden_dir, dtype_name):
+    """``rope_rotate_keys`` equals the K output of the reference's ``apply_rope_to_qk`` (ops.py:376-428) on
+    the seeded prefill, with the helper's own cos / sin tables (stored beside the output)."""
+    gold = np.load(golden_dir / "rope_prefill.npz")
+    k, _ = S.rope_prefill(dtype_name)
+    view = S._INT_VIEW[k.element_size()]
+    cos = torch.from_numpy(gold[f"cos_{dtype_name}"]).view(k.dtype)
+    sin = torch.from_numpy(gold[f"sin_{dtype_name}"]).view(k.dtype)
+    assert cos.shape == (k.shape[2], k.shape[3] // 2) and view is not None
+    assert np.array_equal(_np(rope_rotate_keys(k, cos, sin)), gold[f"k_rope_{dtype_name}"])
+
+
+def test_byte_compiled_reference_runs_the_known_answer_case(golden_dir):
+    """``oracle/ref_python.py`` byte-compiles the reference's own CPU path into ``oracle/_ref``; where that
+    build exists it must be the code the golden files were made with (the benchmark's reference arm times it)."""
+    from oracle import ref_python
+
+    module = ref_python.load() if ref_python.built() else None
+    if module is None:
+        pytest.skip("no byte-compiled reference under oracle/_ref (no checkout on this machine)")
+    gold = np.load(golden_dir / "ref_known_answer.npz")
+    ctor, steps = S.ref_known_answer()
+    layer = module.BarqPagedKVCacheLayer(**ctor)
+    for i, (k, v) in enumerate(steps):
+        ks, vs = layer.update(k, v)
+        assert np.array_equal(_np(ks), gold[f"ret_k_{i}"]) and np.array_equal(_np(vs), gold[f"ret_v_{i}"])
+        assert np.array_equal(_np(layer.keys), gold[f"keys_{i}"])
+        assert layer.get_seq_length() == int(gold[f"seq_length_{i}"])
