@@ -53,7 +53,7 @@ def is_stale() -> bool:
     if not LIBRARY.exists():
         return True
     built = LIBRARY.stat().st_mtime
-    deps = [SOURCE, SOURCE.parent / "paged_attention.cuh", HEADER_DIR / "barqkv.h", HEADER_DIR / "barqkv_experimental.h"]
+    deps = [SOURCE, SOURCE.parent / "paged_attention.cuh", SOURCE.parent / "host_table.cuh", HEADER_DIR / "barqkv.h", HEADER_DIR / "barqkv_experimental.h"]
     return any(d.exists() and d.stat().st_mtime > built for d in deps)
 
 
@@ -62,9 +62,11 @@ def build_native(force: bool = False, verbose: bool = False, tuning: bool = Fals
     ``tuning=True`` builds the experiment variant (always) beside it."""
     if tuning:
         TUNING_LIBRARY.parent.mkdir(parents=True, exist_ok=True)
-        proc = subprocess.run(nvcc_command(output=TUNING_LIBRARY, tuning=True), capture_output=True, text=True)
+        scratch = TUNING_LIBRARY.with_name(f"{TUNING_LIBRARY.name}.{os.getpid()}.tmp")
+        proc = subprocess.run(nvcc_command(output=scratch, tuning=True), capture_output=True, text=True)
         if proc.returncode != 0:
             raise RuntimeError("nvcc failed:\n" + proc.stdout + proc.stderr)
+        os.replace(scratch, TUNING_LIBRARY)
         return TUNING_LIBRARY
     if not force and not is_stale():
         return LIBRARY

@@ -63,7 +63,10 @@ EXPORTS = ("barqkv_version", "barqkv_last_error", "barqkv_sm_count", "barqkv_lau
            "barqkv_max_length", "barqkv_table_scatter", "barqkv_copy_pages", "barqkv_append_legacy",
            "barqkv_gather", "barqkv_gather_layers", "barqkv_update", "barqkv_paged_decode_attention",
            "barqkv_paged_decode_workspace_bytes", "barqkv_update_layers", "barqkv_gather_wait_selftest",
-           "barqkv_gather_noalloc")
+           "barqkv_gather_noalloc", "barqkv_host_create", "barqkv_host_destroy", "barqkv_host_take", "barqkv_host_share",
+           "barqkv_host_give_back", "barqkv_host_holders", "barqkv_host_stats", "barqkv_host_free_list",
+           "barqkv_host_reserve", "barqkv_host_set_pages", "barqkv_host_release", "barqkv_host_pending_changes",
+           "barqkv_host_attach", "barqkv_host_begin", "barqkv_paged_decode_update")
 # experiment knobs: only a library built with -DBARQKV_TUNING exports barqkv_set_tuning (include/barqkv_experimental.h)
 KNOBS = {"stages": 1, "ctas": 2, "vctas": 3, "interleave": 4, "group": 5, "static": 6, "pdl": 7, "fixed": 8, "tensor_store": 9,
          "attn_promotion": 10, "attn_split": 11, "append_bulk": 12}
@@ -137,6 +140,10 @@ class CudaBackend:
         lib.barqkv_paged_decode_attention.argtypes = [P(PoolLayout), _ptr, _ptr, P(BlockTable), _ptr, _i32,
                                                       _ptr, _i64, _i64, _ptr, _i64, _i64, _i32, ctypes.c_float, _i32,
                                                       _i64, _i64, _ptr, _i64, _ptr, _ptr]
+        lib.barqkv_paged_decode_update.restype = _i32
+        lib.barqkv_paged_decode_update.argtypes = [P(PoolLayout), _ptr, _ptr, P(BlockTable), _ptr, _i32, _ptr, _ptr, _i64,
+                                                   _i64, _ptr, _i64, _i64, _ptr, _i64, _i64, _i32, ctypes.c_float, _i32,
+                                                   _i64, _i64, _ptr, _i64, _i32, _ptr, _ptr]
         lib.barqkv_update.restype = _i32
         lib.barqkv_update.argtypes = [P(PoolLayout), _ptr, _ptr, P(BlockTable), _ptr, _ptr, _i32, _i32, _i32,
                                       _ptr, _ptr, P(RowsLayout), _ptr, _i64, _ptr, _ptr, P(RowsLayout),
@@ -151,6 +158,20 @@ class CudaBackend:
         lib.barqkv_gather_noalloc.restype = _i32
         lib.barqkv_gather_noalloc.argtypes = [P(PoolLayout), _ptr, _ptr, P(BlockTable), _ptr, _ptr, _i32, _i64,
                                               _ptr, _ptr, P(RowsLayout), _i32, _ptr, _i32, _ptr]
+        lib.barqkv_host_create.restype = _ptr
+        lib.barqkv_host_create.argtypes = [_i32, _ptr, _i32, _i32, _i32, _ptr, _ptr, _ptr]
+        lib.barqkv_host_destroy.restype = None
+        lib.barqkv_host_destroy.argtypes = [_ptr]
+        for name, args in (("take", [_ptr, _i32, _ptr]), ("share", [_ptr, _ptr, _i32]), ("give_back", [_ptr, _ptr, _i32]),
+                           ("holders", [_ptr, _i32]), ("stats", [_ptr, _ptr]), ("free_list", [_ptr, _ptr, _i32]),
+                           ("reserve", [_ptr, _i32, _i64]), ("set_pages", [_ptr, _i32, _ptr, _i32]),
+                           ("release", [_ptr, _i32]), ("attach", [_ptr, _ptr, _ptr, _ptr, _i64, _ptr, _i64]),
+                           ("begin", [_ptr, _i32, _ptr, _ptr, _i32, _i32, _ptr, _ptr])):
+            fn = getattr(lib, "barqkv_host_" + name)
+            fn.restype = _i32
+            fn.argtypes = args
+        lib.barqkv_host_pending_changes.restype = _i64
+        lib.barqkv_host_pending_changes.argtypes = [_ptr]
         self.version = int(lib.barqkv_version())
         lib.barqkv_launch_count.restype = _i64
         self._status: Dict[int, "object"] = {}
@@ -171,6 +192,9 @@ class CudaBackend:
         if rc != 0:
             msg = self.lib.barqkv_last_error().decode("utf-8", "replace")
             raise BarqKVError(msg or f"barqkv call failed with code {rc}")
+
+    def last_error(self) -> str:
+        return self.lib.barqkv_last_error().decode("utf-8", "replace")
 
     @staticmethod
     def _stream(device) -> int:

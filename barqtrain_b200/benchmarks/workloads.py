@@ -264,16 +264,19 @@ def churn(world: int, rank: int, device, steps: int, warmup: int, layers: int = 
 
 
 def decode_attention(world: int, rank: int, device, steps: int, warmup: int, layers: int = 32, heads: int = 0,
-                     sync=lambda: None) -> Dict:
+                     eager: bool = False, sync=lambda: None) -> Dict:
     """The decode configuration (32 layers, 8 KV heads x 4 query heads, head_dim 128, bf16, page 16, 64
-    sequences uniform [512, 4096]) with attention reading the pages directly: a step is, per layer, the
-    append of one token per sequence and one attention call over the pages - no gather.  Bytes counted:
-    K and V read once (2*sum_len*H*D*e per layer) plus the append's 4*B*H*D*e."""
+    sequences uniform [512, 4096]) with attention reading the pages directly: a step is, per layer, ONE
+    launch that stores the step's token and attends over the pages - no separate append, no gather -
+    replayed from a CUDA graph (``eager``: append + attention called per layer from Python, two launches).
+    Bytes counted: K and V read once (2*sum_len*H*D*e per layer) plus the append's 4*B*H*D*e."""
+    from ..block_table import DecodeStepGraph
+
     H = heads or kv_head_shard(8, world, rank)[1]
     group, B, dtype = 4, 64, torch.bfloat16
     g = torch.Generator().manual_seed(1236)
     lens = torch.randint(512, 4097, (B,), generator=g).tolist()
-    total_steps = steps + max(warmup, 1)
+    total_steps = steps + max(warmup, 1) + 4
     pages = sum(-(-(n + total_steps) // 16) for n in lens)
     cache = BlockTableKVCache(layers, H, D, page_size=16, num_pages=pages, max_seqs=B,
                               max_blocks_per_seq=-(-(max(lens) + total_steps) // 16), dtype=dtype, device=device,
@@ -288,17 +291,32 @@ def decode_attention(world: int, rank: int, device, steps: int, warmup: int, lay
     del k
     new_rows = torch.randn(layers, B, H, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
     q = torch.randn(B, H * group, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
-    out = torch.empty_like(q)
     moved = {"bytes": 0}
+    if eager:
+        out = torch.empty_like(q)
 
-    def step():
-        new = cache.begin_append(slots, [1] * B)
-        cache.end_append(new)
-        full = cache.begin_gather(slots)
-        for layer in range(layers):
-            cache.append(layer, new, new_rows[layer], new_rows[layer])
-            cache.decode_attention(layer, full, q, out=out)
-        moved["bytes"] += (2 * full.total + 4 * B) * H * D * 2 * layers
+        def step():
+            new = cache.begin_append(slots, [1] * B)
+            cache.end_append(new)
+            full = cache.begin_gather(slots)
+            for layer in range(layers):
+                cache.append(layer, new, new_rows[layer], new_rows[layer])
+                cache.decode_attention(layer, full, q, out=out)
+            moved["bytes"] += (2 * full.total + 4 * B) * H * D * 2 * layers
+        per_layer = 2
+    else:
+        graph = DecodeStepGraph(cache, slots, capacity_tokens=sum(lens) + B * total_steps, what="attention",
+                                q_heads=H * group, max_len=max(lens) + total_steps)
+        graph.k_in.copy_(new_rows)
+        graph.v_in.copy_(new_rows)
+        graph.q_in.copy_(q)
+        graph.step()
+        graph.record()
+
+        def step():
+            total = graph.step()
+            moved["bytes"] += (2 * total + 4 * B) * H * D * 2 * layers
+        per_layer = 1
 
     for _ in range(max(warmup, 1)):
         step()
@@ -312,10 +330,12 @@ def decode_attention(world: int, rank: int, device, steps: int, warmup: int, lay
     sync()
     ms = e0.elapsed_time(e1)
     cache.check_device_status()
-    return {"bytes": moved["bytes"], "ms": ms, "tokens": B * steps, "launches": 3 * layers * steps,
+    return {"bytes": moved["bytes"], "ms": ms, "tokens": B * steps, "launches": per_layer * layers * steps,
             "config": {"workload": "llama3-8b-decode-attention-from-pages", "layers": layers, "kv_heads_per_gpu": H,
                        "query_heads_per_kv_head": group, "dtype": "bf16", "page_size": 16, "sequences": B,
-                       "step": "per layer: append 1 token/seq, then attention over the pages (no gather); bytes = K and V "
+                       "launch": "append + attention per layer, called from Python" if eager
+                       else "one launch per layer (append fused into attention), replayed from a CUDA graph",
+                       "step": "per layer: store 1 token/seq and attend over the pages (no gather); bytes = K and V "
                                "read once + appended rows",
                        "l2": "inputs larger than L2: each step reads ~%.1f GB of pool per GPU"
                              % (2 * sum(lens) * H * D * 2 * layers / 1e9)}}

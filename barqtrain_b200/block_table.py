@@ -36,109 +36,96 @@ class PagePoolExhausted(RuntimeError):
     """The free list cannot satisfy an allocation; nothing was changed."""
 
 
+E_INVALID, E_LIMIT, E_CAPACITY = -1, -3, -4
+
+
+def _i32(values) -> np.ndarray:
+    return np.ascontiguousarray(values, dtype=np.int32).reshape(-1)
+
+
 class PageAllocator:
-    """Host-side free list with resident/peak accounting.
+    """Host-side free list with resident/peak accounting (native: ``barqkv_host_*`` in ``libbarqkv.so``).
 
     ``order`` fixes the initial free list (e.g. a seeded permutation, so tests
     and benchmarks get fragmented but reproducible tables); pages are handed
-    out from its front and released pages go to its back.
+    out from its front and released pages go to its back.  A page may have
+    several holders (forked sequences share their full pages).
     """
 
-    def __init__(self, num_pages: int, order: Optional[Sequence[int]] = None, seed: Optional[int] = None):
-        if order is None:
-            if seed is None:
-                order = np.arange(num_pages)
-            else:
-                g = torch.Generator().manual_seed(seed)
-                order = torch.randperm(num_pages, generator=g).numpy()
-        ring = np.array(order, dtype=np.int32).reshape(-1)
-        if ring.size != num_pages or not np.array_equal(np.sort(ring), np.arange(num_pages, dtype=np.int32)):
-            raise ValueError("free-list order must be a permutation of range(num_pages)")
+    def __init__(self, num_pages: int, order: Optional[Sequence[int]] = None, seed: Optional[int] = None, *,
+                 _handle=None, _backend=None):
+        self.backend = _backend or _ffi.require_cuda_backend()
+        self._lib = self.backend.lib
         self.num_pages = num_pages
-        # a page is either free or held, so a ring of num_pages entries holds every possible free list
-        self._ring = ring
-        self._head = 0                       # ring index of the next page to hand out
-        self.pages_free = num_pages
-        self._refs = np.zeros(num_pages, dtype=np.int32)   # sequences holding each page (forks share full pages)
-        self._mark = np.zeros(num_pages, dtype=np.int32)   # scratch for spotting a page listed twice
-        self.pages_resident = 0
-        self.pages_peak = 0
-        self.alloc_calls = 0
-        self.release_calls = 0
+        if _handle is not None:                 # the free list of a BlockTableKVCache's native table
+            self._h, self._owns = _handle, False
+            return
+        self._h = _create_host_table(self.backend, num_pages, order, seed, 0, 0, 1, None, None, None)
+        self._owns = True
+
+    def __del__(self):
+        if getattr(self, "_owns", False) and self._h:
+            self._lib.barqkv_host_destroy(self._h)
+            self._h = None
+
+    def _stats(self) -> List[int]:
+        out = (ctypes.c_int64 * 6)()
+        self._lib.barqkv_host_stats(self._h, out)
+        return list(out)
+
+    pages_free = property(lambda self: self._stats()[0])
+    pages_resident = property(lambda self: self._stats()[1])
+    pages_peak = property(lambda self: self._stats()[2])
+    alloc_calls = property(lambda self: self._stats()[3])
+    release_calls = property(lambda self: self._stats()[4])
 
     def free_pages(self) -> List[int]:
         """The free list, front first."""
-        at = (self._head + np.arange(self.pages_free)) % max(self.num_pages, 1)
-        return self._ring[at].tolist()
+        out = np.empty(self.num_pages, dtype=np.int32)
+        count = self._lib.barqkv_host_free_list(self._h, out.ctypes.data, self.num_pages)
+        return out[:count].tolist()
 
     def take(self, count: int) -> np.ndarray:
         """``count`` pages from the front of the free list, as an int32 array."""
-        if count > self.pages_free:
-            raise PagePoolExhausted(f"need {count} pages, {self.pages_free} free of {self.num_pages}")
-        end = self._head + count
-        if end <= self.num_pages:
-            pages = self._ring[self._head:end].copy()
-        else:
-            pages = np.concatenate((self._ring[self._head:], self._ring[:end - self.num_pages]))
-        if count:
-            if self._refs[pages].any():
-                raise AssertionError(f"page {int(pages[np.argmax(self._refs[pages] != 0)])} handed out twice")
-            self._refs[pages] = 1
-            self._head = end % self.num_pages
-        self.pages_free -= count
-        self.pages_resident += count
-        self.pages_peak = max(self.pages_peak, self.pages_resident)
-        self.alloc_calls += 1
-        return pages
+        out = np.empty(max(count, 0), dtype=np.int32)
+        rc = self._lib.barqkv_host_take(self._h, count, out.ctypes.data)
+        if rc == E_LIMIT:
+            raise PagePoolExhausted(self.backend.last_error())
+        if rc:
+            raise AssertionError(self.backend.last_error())
+        return out
 
     def share(self, pages: Iterable[int]) -> None:
         """One more holder for pages that are already held (a forked sequence)."""
-        idx = np.asarray(pages, dtype=np.int64).reshape(-1)
-        if idx.size:
-            if (self._refs[idx] == 0).any():
-                raise AssertionError(f"page {int(idx[np.argmax(self._refs[idx] == 0)])} shared but not owned")
-            np.add.at(self._refs, idx, 1)
+        idx = _i32(list(pages) if not isinstance(pages, np.ndarray) else pages)
+        if idx.size and self._lib.barqkv_host_share(self._h, idx.ctypes.data, idx.size):
+            raise AssertionError(self.backend.last_error())
 
     def holders(self, page: int) -> int:
-        return int(self._refs[page])
+        return int(self._lib.barqkv_host_holders(self._h, int(page)))
 
     def give_back(self, pages: Iterable[int]) -> None:
         """Drop one holder of each page; pages nobody holds any more join the back of the free list."""
-        idx = np.asarray(pages, dtype=np.int64).reshape(-1)
-        self.release_calls += 1
-        if idx.size == 0:
-            return
-        order = np.arange(idx.size, dtype=np.int32)
-        self._mark[idx] = order
-        if (self._mark[idx] == order).all():
-            # no page listed twice: one vectorised decrement
-            held = self._refs[idx]
-            if held.min() < 1:
-                raise AssertionError(f"page {int(idx[np.argmin(held)])} released but not owned")
-            held -= 1
-            self._refs[idx] = held
-            freed = idx[held == 0]
-        else:
-            uniq, times = np.unique(idx, return_counts=True)
-            if (self._refs[uniq] < times).any():
-                bad = int(uniq[np.argmax(self._refs[uniq] < times)])
-                raise AssertionError(f"page {bad} released but not owned" if self._refs[bad] == 0
-                                     else f"page {bad} released twice")
-            self._refs[uniq] -= times.astype(np.int32)
-            # pages nobody holds any more, in the order they were given back
-            freed = np.asarray(list(dict.fromkeys(idx[self._refs[idx] == 0].tolist())), dtype=np.int64)
-        n = freed.size
-        if n:
-            tail = (self._head + self.pages_free) % self.num_pages
-            end = tail + n
-            if end <= self.num_pages:
-                self._ring[tail:end] = freed
-            else:
-                cut = self.num_pages - tail
-                self._ring[tail:] = freed[:cut]
-                self._ring[:end - self.num_pages] = freed[cut:]
-            self.pages_free += n
-            self.pages_resident -= n
+        idx = _i32(list(pages) if not isinstance(pages, np.ndarray) else pages)
+        if self._lib.barqkv_host_give_back(self._h, idx.ctypes.data if idx.size else None, idx.size):
+            raise AssertionError(self.backend.last_error())
+
+
+def _create_host_table(backend, num_pages, order, seed, max_seqs, max_blocks, page_size, table_ptr, lengths_ptr, count_ptr):
+    if order is None and seed is not None:
+        g = torch.Generator().manual_seed(seed)
+        order = torch.randperm(num_pages, generator=g).numpy()
+    order_ptr = None
+    if order is not None:
+        order = _i32(order)
+        if order.size != num_pages:
+            raise ValueError("free-list order must be a permutation of range(num_pages)")
+        order_ptr = order.ctypes.data
+    handle = backend.lib.barqkv_host_create(num_pages, order_ptr, max_seqs, max_blocks, page_size, table_ptr, lengths_ptr,
+                                            count_ptr)
+    if not handle:
+        raise ValueError(backend.last_error())
+    return handle
 
 
 @dataclass(frozen=True)
@@ -235,7 +222,6 @@ class BlockTableKVCache:
         self.max_seqs, self.max_blocks = max_seqs, max_blocks_per_seq
         self.dtype = dtype
         self.gather_mode = gather_mode
-        self.allocator = PageAllocator(num_pages, order=free_order, seed=seed)
 
         shape = (num_layers, 2, num_kv_heads, num_pages, page_size, head_dim)
         self.pools = (torch.zeros if zero_pages else torch.empty)(shape, dtype=dtype, device=self.device)
@@ -246,27 +232,36 @@ class BlockTableKVCache:
         self._k_ptr = [self.pools[l, 0].data_ptr() for l in range(num_layers)]
         self._v_ptr = [self.pools[l, 1].data_ptr() for l in range(num_layers)]
 
-        # block table: pinned host copy is authoritative, device copy follows
+        # block table: pinned host copy is authoritative, device copy follows.  The free list, the table rows and
+        # the per-step descriptions are kept by native code (barqkv_host_*); the arrays below are shared with it.
         self.table_host = torch.full((max_seqs, max_blocks_per_seq), -1, dtype=torch.int32).pin_memory()
         self.table_dev = torch.full((max_seqs, max_blocks_per_seq), -1, dtype=torch.int32, device=self.device)
         self._table_np = self.table_host.numpy()
-        self._table_changes: List[Tuple[np.ndarray, np.ndarray]] = []
-        self._pairs_dev: Optional[torch.Tensor] = None
         self._table = _ffi.BlockTable(self.table_dev.data_ptr(), None, max_seqs, max_blocks_per_seq, 0, 0)
-
         self.lengths = np.zeros(max_seqs, dtype=np.int64)      # tokens held, per slot
         self._page_count = np.zeros(max_seqs, dtype=np.int64)  # pages owned, per slot
+        self._host = _create_host_table(self.backend, num_pages, free_order, seed, max_seqs, max_blocks_per_seq, page_size,
+                                        self.table_host.data_ptr(), self.lengths.ctypes.data,
+                                        self._page_count.ctypes.data)
+        self.allocator = PageAllocator(num_pages, _handle=self._host, _backend=self.backend)
+        # A step's upload is its description (at most 5 * max_seqs + 2 words) followed by the table entries that
+        # changed (two words each); more entries than fit go in several uploads.
+        self._step_words = 5 * max_seqs + 2 + 2 * min(max(max_seqs * max_blocks_per_seq, 1024), 1 << 18)
+        self._step_dev = [torch.zeros(self._step_words, dtype=torch.int32, device=self.device) for _ in range(2)]
+        self._staging = torch.zeros(8 * self._step_words, dtype=torch.int32).pin_memory()
+        rc = self.backend.lib.barqkv_host_attach(self._host, self.table_dev.data_ptr(), self._step_dev[0].data_ptr(),
+                                                 self._step_dev[1].data_ptr(), self._step_words,
+                                                 self._staging.data_ptr(), self._staging.numel())
+        if rc:
+            self.backend._check(rc)
+        self._c_begin = self.backend.lib.barqkv_host_begin
+        self._info = (ctypes.c_int64 * 8)()
         self.pages_of = _PagesOf(self)                         # pages_of[slot] -> list of page ids, in order
         self._free_slots: List[int] = list(range(max_seqs - 1, -1, -1))
         self._slot_of: Dict[object, int] = {}
         self._fork_counter = 0
         self._attn_ws, self._attn_ws_bytes, self._attn_tickets = None, 0, 0
 
-        # staging ring for descriptors and table uploads (pinned; reuse guarded by events)
-        self._ring: List[Tuple[torch.Tensor, Optional[torch.cuda.Event]]] = []
-        self._ring_pos = 0
-        self._ring_words = 0
-        self._desc_dev: Dict[str, torch.Tensor] = {}
         self._desc_turn: Dict[str, int] = {}
         self._uploads = 0               # descriptions uploaded + table scatters enqueued so far
         self._tables: Dict[str, _ffi.BlockTable] = {}
@@ -293,33 +288,41 @@ class BlockTableKVCache:
     def slot(self, seq_id) -> int:
         return self._slot_of[seq_id]
 
+    def __del__(self):
+        host, backend = getattr(self, "_host", None), getattr(self, "backend", None)
+        if host and backend is not None:
+            try:
+                torch.cuda.synchronize(self.device)       # uploads out of the staging memory must have run
+            except Exception:  # noqa: BLE001 - interpreter or context already going down
+                pass
+            backend.lib.barqkv_host_destroy(host)
+            self._host = None
+
+    def _raise_host(self, rc: int):
+        msg = self.backend.last_error()
+        if rc == E_CAPACITY:
+            raise ValueError(msg)
+        if rc == E_LIMIT and msg.startswith("need "):
+            raise PagePoolExhausted(msg)
+        if rc == E_INVALID and msg.startswith("page "):
+            raise AssertionError(msg)
+        raise _ffi.BarqKVError(msg)
+
     def release(self, seq_id) -> None:
-        """Return a sequence's pages to the free list and free its slot (data stays in the pages)."""
+        """Return a sequence's pages to the free list and free its slot (data stays in the pages; the row is
+        cleared in the host table only - kernels never read entries beyond a sequence's length, so the device
+        copy keeps the stale ids until a new owner of the row overwrites them)."""
         slot = self._slot_of.pop(seq_id)
-        used = int(self._page_count[slot])
-        self.allocator.give_back(self._table_np[slot, :used])
-        self._page_count[slot] = 0
-        self._table_np[slot, :used] = -1      # host copy only: kernels never read entries beyond a sequence's
-        #                                         length, so the device copy may keep the stale ids until a new
-        #                                         owner of the row overwrites them
-        self.lengths[slot] = 0
+        rc = self.backend.lib.barqkv_host_release(self._host, slot)
+        if rc:
+            self._raise_host(rc)
         self._free_slots.append(slot)
 
     def reserve(self, slot: int, new_length: int) -> None:
         """Make sure the slot owns pages for ``new_length`` tokens."""
-        need = -(-new_length // self.page_size)
-        have = int(self._page_count[slot])
-        if need <= have:
-            return
-        if need > self.max_blocks:
-            raise ValueError(
-                f"paged KV cache capacity exceeded: requested {new_length}, "
-                f"max_cache_len={self.max_blocks * self.page_size}"
-            )
-        pages = self.allocator.take(need - have)
-        self._page_count[slot] = need
-        self._table_np[slot, have:need] = pages
-        self._note_table_change(slot, have, pages)
+        rc = self.backend.lib.barqkv_host_reserve(self._host, slot, int(new_length))
+        if rc:
+            self._raise_host(rc)
 
     # -- forks, crops, beam reordering: table edits plus at most one page copy per sequence --------
     def _copy_pages(self, pairs: List[Tuple[int, int]]) -> None:
@@ -334,11 +337,10 @@ class BlockTableKVCache:
             self.backend._check(rc)
 
     def _set_pages(self, slot: int, pages: List[int]) -> None:
-        old = int(self._page_count[slot])
-        self._page_count[slot] = len(pages)
-        row = list(pages) + [-1] * max(old - len(pages), 0)
-        self._table_np[slot, :len(row)] = row
-        self._note_table_change(slot, 0, row)
+        arr = _i32(pages)
+        rc = self.backend.lib.barqkv_host_set_pages(self._host, slot, arr.ctypes.data if arr.size else None, arr.size)
+        if rc:
+            self._raise_host(rc)
 
     def fork(self, seq_id, new_seq_id=None):
         """A new sequence with the same contents as ``seq_id`` (the block-table form of the reference's
@@ -415,117 +417,38 @@ class BlockTableKVCache:
                 out.append(sid)
         return out
 
-    # -- host -> device staging ---------------------------------------------------
-    def _stage(self, words: int):
-        """A pinned int32 staging buffer nobody is reading any more: (numpy view, host address)."""
-        if words > self._ring_words:
-            for _, event in self._ring:            # copies out of the old buffers must have run before they go
-                if event is not None:
-                    event.synchronize()
-            self._ring_words = max(2 * words, 1 << 16)
-            self._ring = [(torch.empty(self._ring_words, dtype=torch.int32).pin_memory(), None) for _ in range(8)]
-            self._ring_np = [buf.numpy() for buf, _ in self._ring]
-            self._ring_ptr = [buf.data_ptr() for buf, _ in self._ring]
-            self._ring_pos = 0
-        _, event = self._ring[self._ring_pos]
-        if event is not None:
-            event.synchronize()
-        return self._ring_np[self._ring_pos], self._ring_ptr[self._ring_pos]
-
-    def _stage_done(self, stream) -> None:
-        buf, event = self._ring[self._ring_pos]
-        if event is None:
-            event = torch.cuda.Event()
-        event.record(stream)
-        self._ring[self._ring_pos] = (buf, event)
-        self._ring_pos = (self._ring_pos + 1) % len(self._ring)
-
-    def _reserve_many(self, slots: np.ndarray, have: np.ndarray, need: np.ndarray, lengths: np.ndarray) -> None:
-        """Pages for several sequences at once: one trip to the free list, vectorised table edits."""
-        over = np.nonzero(need > self.max_blocks)[0]
-        if over.size:
-            raise ValueError(
-                f"paged KV cache capacity exceeded: requested {int(lengths[over[0]])}, "
-                f"max_cache_len={self.max_blocks * self.page_size}"
-            )
-        extra = need - have
-        total = int(extra.sum())
-        pages = self.allocator.take(total)
-        starts = np.cumsum(extra) - extra
-        rows = np.repeat(slots, extra)
-        cols = np.repeat(have - starts, extra) + np.arange(total, dtype=np.int64)
-        self._table_np[rows, cols] = pages
-        self._table_changes.append(((rows * self.max_blocks + cols).astype(np.int32), pages))
-        self._page_count[slots] = need
-
-    def _note_table_change(self, slot: int, first_col: int, values) -> None:
-        """Remember entries of the host table that the device copy does not have yet."""
-        values = np.asarray(values, dtype=np.int32)
-        at = slot * self.max_blocks + first_col + np.arange(values.size, dtype=np.int32)
-        self._table_changes.append((at, values))
-
-    def _flush_table(self) -> None:
-        """Send the changed block-table entries (index, value pairs) and scatter them into the device table."""
-        if not self._table_changes:
-            return
-        at = np.concatenate([c[0] for c in self._table_changes])
-        values = np.concatenate([c[1] for c in self._table_changes])
-        several = len(self._table_changes) > 1
-        self._table_changes = []
-        if several:
-            # an entry written twice since the last flush (a released slot claimed again) keeps its last
-            # value: the scatter kernel applies the pairs in no particular order
-            _, last = np.unique(at[::-1], return_index=True)
-            keep = np.sort(at.size - 1 - last)
-            at, values = at[keep], values[keep]
-        m = at.size
-        if self._pairs_dev is None or self._pairs_dev.numel() < 2 * m:
-            self._pairs_dev = torch.empty(max(2 * m, 4096), dtype=torch.int32, device=self.device)
-        host, host_ptr = self._stage(2 * m)
-        host[0:2 * m:2] = at
-        host[1:2 * m:2] = values
-        stream = torch.cuda.current_stream(self.device)
-        lib = self.backend.lib
-        rc = lib.barqkv_upload(self._pairs_dev.data_ptr(), host_ptr, 8 * m, stream.cuda_stream)
-        rc = rc or lib.barqkv_table_scatter(self.table_dev.data_ptr(), self.max_seqs * self.max_blocks,
-                                            self._pairs_dev.data_ptr(), m, stream.cuda_stream)
-        if rc:
-            self.backend._check(rc)
-        self._stage_done(stream)
-        self._uploads += 1
-
-    def _describe(self, kind: str, slots, first, counts) -> _Descriptor:
-        slots = np.array(slots, dtype=np.int64)            # a copy: the description keeps it
-        first = np.asarray(first, dtype=np.int64)
-        n = slots.size
-        cu = np.zeros(n + 1, dtype=np.int64)
-        np.cumsum(np.asarray(counts, dtype=np.int64), out=cu[1:])
-        words = 3 * n + 1
-        dev = self._desc_dev.get(kind)
-        if dev is None or dev.numel() < words:
-            dev = torch.empty(max(words, 3 * self.max_seqs + 1), dtype=torch.int32, device=self.device)
-            self._desc_dev[kind] = dev
-        host, host_ptr = self._stage(words)
-        host[:n] = slots
-        host[n:2 * n] = first
-        host[2 * n:words] = cu
-        # the device buffer is laid out for this n: [slots | first | cu]
+    # -- a step's host work: pages, table entries, description - one native call ------------------------
+    def _begin(self, kind: str, slots, counts) -> _Descriptor:
+        slots32 = _i32(slots)
+        n = slots32.size
+        code = 0 if kind == "append" else 1
+        counts32 = None
+        if code == 0:
+            counts32 = _i32(counts)
+            if counts32.shape != slots32.shape:
+                raise ValueError("slots and counts must have the same length")
         cur = torch.cuda.current_stream(self.device)
-        rc = self.backend.lib.barqkv_upload(dev.data_ptr(), host_ptr, 4 * words, cur.cuda_stream)
+        info = self._info
+        rc = self._c_begin(self._host, code, slots32.ctypes.data if n else None,
+                           counts32.ctypes.data if (n and counts32 is not None) else None, n, 0, cur.cuda_stream, info)
         if rc:
-            self.backend._check(rc)
-        self._stage_done(cur)
+            self._raise_host(rc)
         self._uploads += 1
+        # host copy of the description the native side just wrote: [slots | first | cu]
+        words = 3 * n + 1
+        host = np.frombuffer((ctypes.c_int32 * words).from_address(info[4]), dtype=np.int32).astype(np.int64)
+        first, cu = host[n:2 * n], host[2 * n:words]
         table = self._tables.get(kind)
         if table is None:
-            table = _ffi.BlockTable(self.table_dev.data_ptr(), None, self.max_seqs, self.max_blocks, 0, 0)
+            table = _ffi.BlockTable(self.table_dev.data_ptr(), self._step_dev[code].data_ptr(), self.max_seqs,
+                                    self.max_blocks, 0, 0)
             self._tables[kind] = table
-        table.slots = dev.data_ptr()
-        stream = cur.cuda_stream
         work = self.backend.work_words(self.device).data_ptr()      # the stream's hand-out counters
-        desc = _Descriptor(n, dev, int(cu[n]), first, cu, slots, ctypes.byref(table), stream, work)
-        desc.slots_np, desc.after_np = slots, first + (cu[1:] - cu[:-1])
-        desc.max_first = int(first.max()) if n else 0
+        slots64 = host[:n]
+        desc = _Descriptor(n, self._step_dev[code], int(info[0]), first, cu, slots64, ctypes.byref(table),
+                           cur.cuda_stream, work)
+        desc.slots_np, desc.after_np = slots64, first + (cu[1:] - cu[:-1])
+        desc.max_first = int(info[1])
         # The device buffer of a kind is rewritten by the next begin_* of that kind: an older description
         # would silently address the newer one's contents, so every use checks that it is still current.
         self._desc_turn[kind] = self._desc_turn.get(kind, 0) + 1
@@ -552,19 +475,7 @@ class BlockTableKVCache:
 
         Use the returned batch for every layer's ``append`` of this step, then ``end_append``.
         """
-        slots = np.asarray(slots, dtype=np.int64)
-        counts = np.asarray(counts, dtype=np.int64)
-        if slots.shape != counts.shape:
-            raise ValueError("slots and counts must have the same length")
-        first = self.lengths[slots]
-        after = first + counts
-        need = -(-after // self.page_size)
-        have = self._page_count[slots]
-        grow = np.nonzero(need > have)[0]                   # only sequences that cross into a new page
-        if grow.size:
-            self._reserve_many(slots[grow], have[grow], need[grow], after[grow])
-        self._flush_table()
-        return self._describe("append", slots, first, counts)
+        return self._begin("append", slots, counts)
 
     def append(self, layer: int, batch: _Descriptor, k_new: torch.Tensor, v_new: torch.Tensor,
                rope: Optional[Tuple[torch.Tensor, torch.Tensor]] = None) -> None:
@@ -665,10 +576,7 @@ class BlockTableKVCache:
 
     # -- gather -------------------------------------------------------------------
     def begin_gather(self, slots: Sequence[int]) -> _Descriptor:
-        slots = np.asarray(slots, dtype=np.int64)
-        lens = self.lengths[slots]
-        self._flush_table()
-        return self._describe("gather", slots, lens, lens)
+        return self._begin("gather", slots, None)
 
     def _output(self, layout: str, total: int, out, n: int = 0):
         """Output buffers, their row addressing and the views holding exactly ``total`` tokens.
@@ -921,12 +829,19 @@ class BlockTableKVCache:
 
     # -- attention straight from the pages (decode) ---------------------------------------
     def decode_attention(self, layer: int, full: _Descriptor, q: torch.Tensor, scale: Optional[float] = None,
-                         out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                         out: Optional[torch.Tensor] = None, new_rows: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
+                         max_len: Optional[int] = None, total_len: Optional[int] = None) -> torch.Tensor:
         """``softmax(q k^T * scale) v`` for one query token per sequence, reading K/V from the pages.
 
         ``full`` is a ``begin_gather`` description (lengths include the token appended this step);
         ``q`` is ``[n, num_q_heads, head_dim]`` in the cache dtype, ``num_q_heads`` a multiple (<= 8x) of
         the KV heads on this device.  Returns ``[n, num_q_heads, head_dim]``.  No gather is involved.
+
+        ``new_rows=(k_new, v_new)``, each ``[n, kv_heads, head_dim]``: the step's token has NOT been appended
+        yet (its page is reserved, the lengths already count it); the same launch stores the rows into the
+        pages and attends them - a decode layer in one launch (``decode_update``).  ``max_len`` /
+        ``total_len`` override the description's longest length and sum of lengths (they fix the launch
+        shape and the workspace size; a recorded CUDA graph passes bounds that hold for all its replays).
         """
         self._current(full)
         if q.dim() != 3 or q.shape[0] != full.n or q.shape[2] != self.head_dim or q.stride(2) != 1:
@@ -939,8 +854,10 @@ class BlockTableKVCache:
             raise ValueError("out must match q")
         if full.n == 0:
             return out
-        max_len = full.max_first
-        total_len = full.total          # the sum of the lengths: sizes the splits for small batches
+        if max_len is None:
+            max_len = full.max_first
+        if total_len is None:
+            total_len = full.total          # the sum of the lengths: sizes the splits for small batches
         need = int(self.backend.lib.barqkv_paged_decode_workspace_bytes(full.n, self.num_kv_heads, max_len, total_len,
                                                                         self.page_size))
         if need:
@@ -960,14 +877,38 @@ class BlockTableKVCache:
         ws_ptr = self._attn_ws.data_ptr() if need else None
         if scale is None:
             scale = self.head_dim ** -0.5
-        rc = self.backend.lib.barqkv_paged_decode_attention(
-            self._pool_ref, self._k_ptr[layer], self._v_ptr[layer], full.table_ref, full.p_first, full.n,
-            q.data_ptr(), q.stride(0), q.stride(1), out.data_ptr(), out.stride(0), out.stride(1), q.shape[1],
-            float(scale), 1 if self.dtype == torch.bfloat16 else 0, max_len, total_len, ws_ptr, need, self._status_ptr,
-            full.stream)
+        is_bf16 = 1 if self.dtype == torch.bfloat16 else 0
+        lib = self.backend.lib
+        if new_rows is None:
+            rc = lib.barqkv_paged_decode_attention(
+                self._pool_ref, self._k_ptr[layer], self._v_ptr[layer], full.table_ref, full.p_first, full.n,
+                q.data_ptr(), q.stride(0), q.stride(1), out.data_ptr(), out.stride(0), out.stride(1), q.shape[1],
+                float(scale), is_bf16, max_len, total_len, ws_ptr, need, self._status_ptr, full.stream)
+        else:
+            k_new, v_new = new_rows
+            want = (full.n, self.num_kv_heads, self.head_dim)
+            if tuple(k_new.shape) != want or v_new.shape != k_new.shape or k_new.dtype != self.dtype \
+                    or v_new.dtype != self.dtype or k_new.device != self.device or v_new.device != self.device:
+                raise ValueError(f"new rows must both be {want} in the cache dtype on the cache device")
+            if k_new.stride(2) != 1 or v_new.stride() != k_new.stride():
+                k_new, v_new = k_new.contiguous(), v_new.contiguous()
+            flag = _ffi.FLAG_DESC_STABLE if full.used_at == self._uploads else 0
+            full.used_at = self._uploads
+            rc = lib.barqkv_paged_decode_update(
+                self._pool_ref, self._k_ptr[layer], self._v_ptr[layer], full.table_ref, full.p_first, full.n,
+                k_new.data_ptr(), v_new.data_ptr(), k_new.stride(0), k_new.stride(1),
+                q.data_ptr(), q.stride(0), q.stride(1), out.data_ptr(), out.stride(0), out.stride(1), q.shape[1],
+                float(scale), is_bf16, max_len, total_len, ws_ptr, need, flag, self._status_ptr, full.stream)
         if rc:
             self.backend._check(rc)
         return out
+
+    def decode_update(self, layer: int, full: _Descriptor, k_new: torch.Tensor, v_new: torch.Tensor, q: torch.Tensor,
+                      scale: Optional[float] = None, out: Optional[torch.Tensor] = None, **bounds) -> torch.Tensor:
+        """A decode layer in one launch: store the step's K/V rows into the pages and attend over the pages,
+        new token included (``barqkv_paged_decode_update``).  Call ``begin_append`` / ``end_append`` /
+        ``begin_gather`` for the step first, as for ``update``; skip the layer's ``append``."""
+        return self.decode_attention(layer, full, q, scale=scale, out=out, new_rows=(k_new, v_new), **bounds)
 
     def gather_sequence(self, layer: int, seq_id, layout: str = "HND") -> Tuple[torch.Tensor, torch.Tensor]:
         """One sequence as contiguous ``[H, len, D]`` (or ``[len, H, D]``)."""
@@ -1009,12 +950,14 @@ class DecodeStepGraph:
     """
 
     def __init__(self, cache: BlockTableKVCache, slots: Sequence[int], capacity_tokens: int,
-                 mode: Optional[str] = None, what: str = "update"):
+                 mode: Optional[str] = None, what: str = "update", q_heads: int = 0, max_len: int = 0):
         """``what``: ``"update"`` (append + gather per layer, the default), ``"append"`` (the append alone, one
-        launch per layer) or ``"append_layers"`` (the append alone, one launch for all layers); the append-only
-        forms need no output buffers and ignore ``capacity_tokens``."""
-        if what not in ("update", "append", "append_layers"):
-            raise ValueError("what must be 'update', 'append' or 'append_layers'")
+        launch per layer), ``"append_layers"`` (the append alone, one launch for all layers) or ``"attention"``
+        (append fused into attention over the pages, one launch per layer, no gather: fill ``q_in``
+        ``[batch, q_heads, head_dim]``, read ``attn_out``; ``max_len`` bounds the longest sequence over all
+        replays and ``capacity_tokens`` the sum of the lengths).  Only ``"update"`` needs output buffers."""
+        if what not in ("update", "append", "append_layers", "attention"):
+            raise ValueError("what must be 'update', 'append', 'append_layers' or 'attention'")
         self.cache, self.slots, self.mode, self.what = cache, list(slots), mode, what
         c = cache
         B = len(self.slots)
@@ -1026,15 +969,24 @@ class DecodeStepGraph:
         self.bufs = [(torch.empty(c.num_kv_heads, self.capacity, c.head_dim, dtype=c.dtype, device=c.device),
                       torch.empty(c.num_kv_heads, self.capacity, c.head_dim, dtype=c.dtype, device=c.device))
                      for _ in range(2)] if what == "update" else []
+        self.q_in = self.attn_out = None
+        self.max_len = int(max_len)
+        if what == "attention":
+            if q_heads <= 0 or self.max_len <= 0 or self.capacity <= 0:
+                raise ValueError("what='attention' needs q_heads, max_len and capacity_tokens")
+            self.q_in = torch.zeros(B, q_heads, c.head_dim, dtype=c.dtype, device=c.device)
+            self.attn_out = torch.zeros_like(self.q_in)
         self.total = 0
         self.steps = 0
         self.launches_per_replay = 0
         self.graph: Optional[torch.cuda.CUDAGraph] = None
-        # One device buffer holds both descriptions of a step at fixed addresses:
+        # Both descriptions of a step live at the start of the cache's append step buffer, at fixed addresses:
         # [slots(n) | start(n) | cu_new(n+1) | lengths_after(n) | cu_out(n+1)], rewritten by one upload per step.
         n = B
         self._slots_np = np.asarray(self.slots, dtype=np.int64)
-        self._desc = torch.zeros(5 * n + 2, dtype=torch.int32, device=c.device)
+        self._slots32 = _i32(self.slots)
+        self._ones32 = np.ones(n, dtype=np.int32)
+        self._desc = c._step_dev[0]
         self._table = _ffi.BlockTable(c.table_dev.data_ptr(), self._desc.data_ptr(), c.max_seqs, c.max_blocks, 0, 0)
         base = self._desc.data_ptr()
         ones_cu = list(range(n + 1))
@@ -1056,39 +1008,35 @@ class DecodeStepGraph:
         if self.what == "append_layers":
             c.append_layers(self._new, self.k_in, self.v_in)
             return
+        if self.what == "attention":
+            # the launch shape and the workspace come from the bounds, so every replay fits the recording
+            self._full.n = len(self.slots)
+            for layer in range(c.num_layers):
+                c.decode_update(layer, self._full, self._k_rows[layer], self._v_rows[layer], self.q_in, out=self.attn_out,
+                                max_len=self.max_len, total_len=self.capacity)
+            return
         # one native call issues every layer's launch; from the second layer on each is a programmatic
         # dependent of the one before (its prologue overlaps that layer's tail)
         self.cache.update_layers(self._new, self._full, self.k_in, self.v_in, self.bufs, "HND", mode=self.mode,
                                  tokens_hint=self.capacity)
 
     def _describe_step(self) -> int:
-        """Host side of a step: pages for the new tokens, new lengths, one upload of both descriptions."""
-        c, sl, n = self.cache, self._slots_np, len(self.slots)
-        first = c.lengths[sl]
-        after = first + 1
-        total = int(after.sum())
-        if total > self.capacity and self.what == "update":
-            raise ValueError(f"decode graph capacity {self.capacity} tokens exceeded by {total}")
-        need = -(-after // c.page_size)
-        have = c._page_count[sl]
-        grow = np.nonzero(need > have)[0]
-        if grow.size:
-            c._reserve_many(sl[grow], have[grow], need[grow], after[grow])
-        c._flush_table()
-        c.lengths[sl] = after
-        words = 5 * n + 2
-        host, host_ptr = c._stage(words)
-        host[:n] = sl
-        host[n:2 * n] = first
-        host[2 * n:3 * n + 1] = np.arange(n + 1)
-        host[3 * n + 1:4 * n + 1] = after
-        host[4 * n + 1] = 0
-        np.cumsum(after, out=host[4 * n + 2:words])
-        rc = c.backend.lib.barqkv_upload(self._desc.data_ptr(), host_ptr, 4 * words, self.stream.cuda_stream)
+        """Host side of a step: pages for the new tokens, new lengths, one upload of both descriptions
+        (one native call: ``barqkv_host_begin`` with the decode-step layout)."""
+        c, n = self.cache, len(self.slots)
+        info = c._info
+        rc = c._c_begin(c._host, 0, self._slots32.ctypes.data, self._ones32.ctypes.data, n, 1, self.stream.cuda_stream, info)
         if rc:
-            c.backend._check(rc)
-        c._stage_done(self.stream)
+            c._raise_host(rc)
+        total = int(info[0])
+        if total > self.capacity and self.what in ("update", "attention"):
+            raise ValueError(f"decode graph capacity {self.capacity} tokens exceeded by {total}")
+        if self.what == "attention" and int(info[1]) + 1 > self.max_len:
+            raise ValueError(f"decode graph max_len {self.max_len} exceeded by a sequence of {int(info[1]) + 1} tokens")
+        c.lengths[self._slots_np] += 1
         c._uploads += 1
+        # any description made by begin_append meanwhile now points at this step's words
+        c._desc_turn["append"] = c._desc_turn.get("append", 0) + 1
         self._full.total = total
         return total
 

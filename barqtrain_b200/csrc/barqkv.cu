@@ -41,13 +41,16 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <cudaTypedefs.h>
+#include <algorithm>
 #include <atomic>
 #include <mutex>
 #include <initializer_list>
 #include <stdint.h>
 #include <stdio.h>
 #include <string.h>
+#include <new>
 #include <utility>
+#include <vector>
 
 #include "barqkv.h"
 #ifdef BARQKV_TUNING
@@ -2139,3 +2142,4 @@ int barqkv_gather_noalloc(const barqkv_pool_layout* pool, const void* k_pool, co
 }  // extern "C"
 
 #include "paged_attention.cuh"
+#include "host_table.cuh"

@@ -14,7 +14,11 @@
 //                         With several splits per sequence each warp leaves a partial (max, sum, output)
 //                         triple in the workspace and takes a ticket; the warp that takes a sequence's
 //                         last ticket combines the triples (they are still in L2) and writes the output,
-//                         so no second launch is needed.
+//                         so no second launch is needed.  Optionally the step's append is fused in: the
+//                         CTA that owns a sequence's last page takes the new K/V row from the caller's
+//                         buffers, patches it into the page's tile in shared memory (the pool still holds
+//                         whatever was in that slot) and writes it to the pool, so a decode layer is ONE
+//                         launch: no separate append, no gather.
 //
 // Restrictions (checked on the host): 2-byte elements (bf16 / fp16), head_dim 128, page_size 16, 32 or 64,
 // group <= 8.  Every wait is bounded; a guard failure skips the sequence and sets a status bit.
@@ -42,6 +46,16 @@ struct AttnArgs {
     int n, kv_heads, group, split_pages, splits, page_size;
     float scale_log2;                         // softmax scale * log2(e)
     int32_t* status;
+    // Fused append (null k_new = plain attention): the step's new K/V row of every (sequence, KV head) - the
+    // token at position len - 1 - comes from k_new / v_new instead of the pool; the CTA that owns the
+    // sequence's last page attends it and stores it into its page slot.
+    const unsigned char* k_new;
+    const unsigned char* v_new;
+    unsigned char* k_pool_w;
+    unsigned char* v_pool_w;
+    long long new_seq, new_head;              // byte strides of the new rows
+    long long pool_head, pool_page;           // byte strides of the pools
+    int early;                                // lengths, slots and table are older than the kernel before this one
 };
 
 __device__ __forceinline__ void tensor_load_4d(uint32_t dst_smem, const CUtensorMap* map, int c0, int c1, int c2, int c3,
@@ -108,16 +122,24 @@ paged_decode_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap map_k,
     const int lane = threadIdx.x;
     const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
 
-    pdl_let_successor_in();
-    pdl_wait_for_predecessor();
+    // Lengths, slots and block-table entries may be read before the kernel ahead of this one has finished
+    // when the caller vouches that they are older than it; the query, the new rows and the pools may not.
+    if (!a.early) {
+        pdl_wait_for_predecessor();
+        pdl_let_successor_in();
+    }
     // the length and the table row are independent loads: both are in flight before either is used
     const int len = a.seq_lens[seq];
     const int row = a.tb.slots ? a.tb.slots[seq] : seq;
     const int pages = (len + PS - 1) / PS;
     const int p0 = split * a.split_pages;
-    if (len <= 0 || p0 >= pages) return;
+    if (len <= 0 || p0 >= pages) {
+        if (a.early) { pdl_wait_for_predecessor(); pdl_let_successor_in(); }
+        return;
+    }
     const int p1 = min(pages, p0 + a.split_pages);
     if (row < 0 || row >= a.tb.rows || pages > a.tb.stride) {
+        if (a.early) { pdl_wait_for_predecessor(); pdl_let_successor_in(); }
         if (lane == 0) raise(a.status, BARQKV_S_BAD_SLOT);
         return;
     }
@@ -126,6 +148,20 @@ paged_decode_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap map_k,
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncwarp();
+
+    float acc[16][4];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;      // for row g (the c0/c1 half of the fragments)
+
+    // block-table entries of this split, 32 at a time, one per lane
+    int table_base = p0;
+    int my_page = (p0 + lane < p1) ? a.tb.table[(long long)row * a.tb.stride + p0 + lane] : -1;
+    bool bad = false, dead = false;
+    if (a.early) {
+        pdl_wait_for_predecessor();
+        pdl_let_successor_in();
+    }
 
     // Q as the A operand: rows = query heads of this KV head (lane/4), zero rows beyond the group.
     const int g = lane >> 2, tq = lane & 3;
@@ -139,15 +175,14 @@ paged_decode_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap map_k,
         }
     }
 
-    float acc[16][4];
-#pragma unroll
-    for (int i = 0; i < 16; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;      // for row g (the c0/c1 half of the fragments)
-
-    // block-table entries of this split, 32 at a time, one per lane
-    int table_base = p0;
-    int my_page = (p0 + lane < p1) ? a.tb.table[(long long)row * a.tb.stride + p0 + lane] : -1;
-    bool bad = false, dead = false;
+    // Fused append: this CTA owns the sequence's last page; lanes 0-15 carry the 16-byte chunks of the new K
+    // row, lanes 16-31 those of the new V row (loaded now, used when the page arrives).
+    const bool owns_new = a.k_new != nullptr && p1 == pages;
+    uint4 new_chunk = make_uint4(0u, 0u, 0u, 0u);
+    if (owns_new) {
+        const unsigned char* src = (lane < 16 ? a.k_new : a.v_new) + (long long)seq * a.new_seq + (long long)kvh * a.new_head;
+        new_chunk = *reinterpret_cast<const uint4*>(src + (lane & 15) * 16);
+    }
 
     auto issue = [&](int p) {                  // load page p of this split into stage (p - p0) % stages
         if (p - table_base >= 32) {
@@ -188,6 +223,18 @@ paged_decode_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap map_k,
 
         unsigned char* kt = s_attn + (size_t)st * kAttnStageBytes;
         unsigned char* vt = kt + kAttnPageBytes;
+        if (owns_new && p == pages - 1) {
+            // the step's own token: into the tile (the pool's slot still holds stale bytes) and into the pool
+            const int r = (len - 1) - p * PS;
+            const int j = lane & 15;
+            unsigned char* tile = lane < 16 ? kt : vt;
+            *reinterpret_cast<uint4*>(tile + (j >> 3) * kHalf + swz(r, j & 7)) = new_chunk;
+            const int phys = __shfl_sync(0xffffffffu, my_page, p - table_base);
+            unsigned char* dst = (lane < 16 ? a.k_pool_w : a.v_pool_w) + (long long)phys * a.pool_page +
+                                 (long long)kvh * a.pool_head + (long long)r * 256 + j * 16;
+            *reinterpret_cast<uint4*>(dst) = new_chunk;
+            __syncwarp();
+        }
 #pragma unroll 1
         for (int sb = 0; sb < PS / 16; ++sb) {                    // 16 tokens at a time
             const int valid = min(16, len - p * PS - sb * 16);    // rows of this block that hold tokens
@@ -397,14 +444,20 @@ int64_t barqkv_paged_decode_workspace_bytes(int32_t n, int32_t kv_heads, int64_t
     return attn_ticket_bytes(n, kv_heads) + (int64_t)n * kv_heads * splits * 8 * (128 + 2) * (int64_t)sizeof(float);
 }
 
-int barqkv_paged_decode_attention(const barqkv_pool_layout* pool, const void* k_pool, const void* v_pool,
-                                  const barqkv_block_table* table, const int32_t* seq_lens, int32_t n,
-                                  const void* q, int64_t q_seq_stride, int64_t q_head_stride,
-                                  void* out, int64_t out_seq_stride, int64_t out_head_stride,
-                                  int32_t num_q_heads, float softmax_scale, int32_t is_bf16, int64_t max_len,
-                                  int64_t total_len,
-                                  void* workspace, int64_t workspace_bytes, int32_t* status, barqkv_stream_t stream) {
+}  // extern "C"
+
+namespace {
+
+int attention_common(const barqkv_pool_layout* pool, const void* k_pool, const void* v_pool,
+                     const barqkv_block_table* table, const int32_t* seq_lens, int32_t n,
+                     const void* k_new, const void* v_new, int64_t new_seq_stride, int64_t new_head_stride,
+                     const void* q, int64_t q_seq_stride, int64_t q_head_stride,
+                     void* out, int64_t out_seq_stride, int64_t out_head_stride,
+                     int32_t num_q_heads, float softmax_scale, int32_t is_bf16, int64_t max_len,
+                     int64_t total_len,
+                     void* workspace, int64_t workspace_bytes, int32_t flags, int32_t* status, barqkv_stream_t stream) {
     if (int rc = check_pool(pool)) return rc;
+    if (flags & ~BARQKV_FLAG_DESC_STABLE) return fail(BARQKV_E_INVALID, "decode_attention: unknown flag");
     if (n < 0) return fail(BARQKV_E_INVALID, "decode_attention: negative batch size");
     if (n == 0) return 0;
     if (int rc = check_table(table, n)) return rc;
@@ -443,6 +496,20 @@ int barqkv_paged_decode_attention(const barqkv_pool_layout* pool, const void* k_
     a.splits = attn_splits(n, a.kv_heads, max_len, total_len, a.page_size, &a.split_pages);
     a.scale_log2 = softmax_scale * 1.4426950408889634f;
     a.status = status;
+    a.early = (flags & BARQKV_FLAG_DESC_STABLE) && g_knobs.pdl != 0 ? 1 : 0;
+    if (k_new || v_new) {
+        if (!k_new || !v_new) return fail(BARQKV_E_INVALID, "decode_update: needs both the new K rows and the new V rows");
+        if (!aligned(k_new, 16) || !aligned(v_new, 16) || !multiple(new_seq_stride * e, 16) || !multiple(new_head_stride * e, 16))
+            return fail(BARQKV_E_INVALID, "decode_update: new rows must be 16-byte aligned");
+        a.k_new = static_cast<const unsigned char*>(k_new);
+        a.v_new = static_cast<const unsigned char*>(v_new);
+        a.k_pool_w = static_cast<unsigned char*>(const_cast<void*>(k_pool));
+        a.v_pool_w = static_cast<unsigned char*>(const_cast<void*>(v_pool));
+        a.new_seq = new_seq_stride * e;
+        a.new_head = new_head_stride * e;
+        a.pool_head = pool->head_stride * e;
+        a.pool_page = pool->page_stride * e;
+    }
     if (a.splits > 1) {
         const int64_t need = barqkv_paged_decode_workspace_bytes(n, a.kv_heads, max_len, total_len, a.page_size);
         if (!workspace || workspace_bytes < need || !aligned(workspace, 16))
@@ -463,8 +530,7 @@ int barqkv_paged_decode_attention(const barqkv_pool_layout* pool, const void* k_
             const cudaError_t se = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (se != cudaSuccess) return se;
         }
-        kernel<<<grid, 32, smem, st>>>(a, map_k, map_v);
-        return cudaSuccess;
+        return ::launch(kernel, grid, dim3(32), smem, st, a.early != 0, a, map_k, map_v);
     };
     cudaError_t le;
     // + 1024 bytes of slack to align the tiles to the swizzle period
@@ -480,6 +546,36 @@ int barqkv_paged_decode_attention(const barqkv_pool_layout* pool, const void* k_
     if (ce != cudaSuccess) return fail_cuda("decode_attention launch", ce);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int barqkv_paged_decode_attention(const barqkv_pool_layout* pool, const void* k_pool, const void* v_pool,
+                                  const barqkv_block_table* table, const int32_t* seq_lens, int32_t n,
+                                  const void* q, int64_t q_seq_stride, int64_t q_head_stride,
+                                  void* out, int64_t out_seq_stride, int64_t out_head_stride,
+                                  int32_t num_q_heads, float softmax_scale, int32_t is_bf16, int64_t max_len,
+                                  int64_t total_len,
+                                  void* workspace, int64_t workspace_bytes, int32_t* status, barqkv_stream_t stream) {
+    return attention_common(pool, k_pool, v_pool, table, seq_lens, n, nullptr, nullptr, 0, 0, q, q_seq_stride, q_head_stride,
+                            out, out_seq_stride, out_head_stride, num_q_heads, softmax_scale, is_bf16, max_len, total_len,
+                            workspace, workspace_bytes, 0, status, stream);
+}
+
+int barqkv_paged_decode_update(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,
+                               const barqkv_block_table* table, const int32_t* seq_lens_after, int32_t n,
+                               const void* k_new, const void* v_new, int64_t new_seq_stride, int64_t new_head_stride,
+                               const void* q, int64_t q_seq_stride, int64_t q_head_stride,
+                               void* out, int64_t out_seq_stride, int64_t out_head_stride,
+                               int32_t num_q_heads, float softmax_scale, int32_t is_bf16, int64_t max_len,
+                               int64_t total_len, void* workspace, int64_t workspace_bytes, int32_t flags,
+                               int32_t* status, barqkv_stream_t stream) {
+    if (!k_new || !v_new) return fail(BARQKV_E_INVALID, "decode_update: null new rows");
+    return attention_common(pool, k_pool, v_pool, table, seq_lens_after, n, k_new, v_new, new_seq_stride, new_head_stride, q,
+                            q_seq_stride, q_head_stride, out, out_seq_stride, out_head_stride, num_q_heads, softmax_scale,
+                            is_bf16, max_len, total_len, workspace, workspace_bytes, flags, status, stream);
 }
 
 }  // extern "C"

@@ -6,11 +6,11 @@ from a pool, a batch row is a block-table row, and ``update`` is one fused appen
 layer that returns contiguous ``[batch, kv_heads, length, head_dim]`` K/V.
 
 With ``attention_from_pages=True`` and the attention function of this module selected
-(``use_paged_attention(model)``), single-token decode steps skip the gather altogether: ``update`` only
-appends and hands the attention function a tag, and the attention function reads K/V from the pages
-(``BlockTableKVCache.decode_attention``).  Prefill and multi-token steps keep using the gathered tensors
-with the stock SDPA path.  From-pages decoding ignores the attention mask: it is for batches without
-padding (every cached token of a row is attended).
+(``use_paged_attention(model)``), single-token decode steps skip the gather altogether: ``update`` hands
+the attention function a tag carrying the new rows, and the attention function stores them and reads K/V
+from the pages in one launch (``BlockTableKVCache.decode_update``).  Prefill and multi-token steps keep using the gathered tensors
+with the stock SDPA path.  From-pages decoding attends every cached token of a row, so it is for batches
+without padding: a decode step whose attention mask hides any position is refused with an error.
 """
 
 from __future__ import annotations
@@ -61,15 +61,21 @@ class BarqBlockTableLayer(CacheLayerMixin):
             return t.transpose(1, 2).reshape(batch * tokens, heads, dim)
 
         self.length += tokens
-        if owner.attention_from_pages and tokens == 1:
+        if self.length == tokens and tokens > 1:
+            # a prompt entering an empty cache: the gathered result would be the new rows themselves
             store.append(self.layer_idx, new, rows(key_states), rows(value_states))
+            return key_states, value_states
+        if owner.attention_from_pages and tokens == 1:
+            # nothing is launched here: the attention function stores these rows and attends in one kernel
             tag = key_states.new_empty(0)
-            tag._barq_paged = (owner, self.layer_idx)       # picked up by paged_attention_forward
+            tag._barq_paged = (owner, self.layer_idx, rows(key_states), rows(value_states))
             return tag, tag
-        longest = self.length
-        out = (torch.empty(batch, heads, longest, dim, dtype=key_states.dtype, device=key_states.device),
-               torch.empty(batch, heads, longest, dim, dtype=key_states.dtype, device=key_states.device))
-        return store.update(self.layer_idx, new, full, rows(key_states), rows(value_states), "BHSD", out=out)
+        # Gathered rows go into one of two cache-owned buffers of the full capacity (consecutive layers
+        # alternate), so a decode step allocates nothing; the views returned are cut to the current length.
+        k_buf, v_buf = owner._gather_buffers(self.layer_idx, key_states)
+        store.update(self.layer_idx, new, full, rows(key_states), rows(value_states), "BHSD",
+                     out=(k_buf[:batch], v_buf[:batch]))
+        return k_buf[:batch, :, :self.length], v_buf[:batch, :, :self.length]
 
     def get_seq_length(self) -> int:
         return self.length
@@ -103,6 +109,7 @@ class BarqBlockTableCache(Cache):
         self.slots = []
         self._new = self._full = None
         self._step_tokens = 0
+        self._bufs = []
 
     def _ensure_store(self, key_states: torch.Tensor) -> None:
         if self.store is not None:
@@ -115,6 +122,13 @@ class BarqBlockTableCache(Cache):
                                        num_pages=self.barqtrain_max_batch_size * blocks, max_seqs=self.barqtrain_max_batch_size,
                                        max_blocks_per_seq=blocks, dtype=key_states.dtype, device=key_states.device)
         self.slots = [self.store.open(row) for row in range(self.barqtrain_max_batch_size)]
+
+    def _gather_buffers(self, layer_idx: int, like: torch.Tensor):
+        if not self._bufs:
+            shape = (self.barqtrain_max_batch_size, like.shape[1], self.barqtrain_max_cache_len, like.shape[3])
+            self._bufs = [(torch.empty(shape, dtype=like.dtype, device=like.device),
+                           torch.empty(shape, dtype=like.dtype, device=like.device)) for _ in range(2)]
+        return self._bufs[layer_idx & 1]
 
     def _reset_store(self) -> None:
         if self.store is not None and any(int(self.store.lengths[s]) for s in self.slots):
@@ -148,9 +162,17 @@ def paged_attention_forward(module, query, key, value, attention_mask, dropout: 
 
         return sdpa_attention_forward(module, query, key, value, attention_mask, dropout=dropout, scaling=scaling,
                                       **kwargs)
-    owner, layer_idx = tag
+    owner, layer_idx, k_rows, v_rows = tag
+    if attention_mask is not None and layer_idx == 0:
+        # The kernel attends every cached token of a row.  transformers hands a mask to a one-token step only
+        # when something is hidden (padding), so this read of the mask runs once per step at most, and only then.
+        hidden = (~attention_mask).any() if attention_mask.dtype == torch.bool else (attention_mask != 0).any()
+        if bool(hidden):
+            raise ValueError("attention_from_pages=True cannot serve a padded batch: the attention mask hides cached "
+                             "positions, and attention over the pages attends all of them; use the gathered path "
+                             "(attention_from_pages=False) or batch sequences of equal length")
     q = query[:, :, 0, :]                                        # [batch, q_heads, head_dim]
-    out = owner.store.decode_attention(layer_idx, owner._full, q, scale=scaling)
+    out = owner.store.decode_update(layer_idx, owner._full, k_rows, v_rows, q, scale=scaling)
     return out.unsqueeze(1), None                                # [batch, 1, q_heads, head_dim]
 
 

@@ -20,6 +20,7 @@ new K/V rows coming from pinned host memory and the status word read back.
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import os
 import statistics
@@ -91,7 +92,7 @@ class ClockSampler:
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "20",
                  "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             time.sleep(0.3)
         except OSError:
@@ -477,6 +478,7 @@ def run_barqkv(args):
     # ---- the other configurations, short legs -----------------------------------------
     if not args.no_legs and not args.shard_heads:
         del wl
+        gc.collect()
         torch.cuda.empty_cache()
         line["configs"] = run_legs(world, rank, local, device, barrier, max_over_ranks, backend, peak, peak_kind,
                                    quick=args.quick_legs)
@@ -497,9 +499,11 @@ def run_legs(world, rank, local, device, barrier, max_over_ranks, backend, peak,
     from barqtrain_b200.benchmarks.workloads import WORKLOADS
 
     plan = [
-        ("chunked-prefill-ps16", "prefill", dict(page_size=16), 48, 4),
-        ("chunked-prefill-ps32", "prefill", dict(page_size=32), 48, 4),
-        ("llama3-70b-gather", "gather70b", {}, 24, 3),
+        # (name, workload, arguments, timed steps, warm-up steps): step counts sized for about a second of device
+        # time at one GPU; the churn configuration's 1000 steps are the configuration's own
+        ("chunked-prefill-ps16", "prefill", dict(page_size=16), 640, 8),
+        ("chunked-prefill-ps32", "prefill", dict(page_size=32), 640, 8),
+        ("llama3-70b-gather", "gather70b", {}, 44, 3),
         ("continuous-batching-churn", "churn", {}, 1000, 20),
     ]
     out = {}
@@ -527,6 +531,7 @@ def run_legs(world, rank, local, device, barrier, max_over_ranks, backend, peak,
         except Exception as exc:  # noqa: BLE001 - a leg that cannot run must not take the headline with it
             entry = {"error": f"{type(exc).__name__}: {str(exc)[:200]}"}
         out[name] = entry
+        gc.collect()                       # the workload's cache sits in reference cycles of its closures
         torch.cuda.empty_cache()
     return out
 
@@ -933,6 +938,8 @@ def run_extra(args):
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         init_nccl(dist, device)
     backend = _ffi.require_cuda_backend()
+    if args.tune:
+        backend.set_tuning(**{k: int(v) for k, v in (kv.split("=") for kv in args.tune.split(","))})
 
     def barrier():
         torch.cuda.synchronize(device)
@@ -943,6 +950,8 @@ def run_extra(args):
     kwargs = {"page_size": args.page_size, "all_layers": args.all_layers} if args.workload == "prefill" else {}
     if args.workload == "gather70b":
         kwargs["all_layers"] = args.all_layers
+    if args.workload == "decode-attn":
+        kwargs["eager"] = args.eager
     if args.layers_override:
         kwargs["layers"] = args.layers_override
     if args.shard_heads:
@@ -974,6 +983,22 @@ def run_extra(args):
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def run_generate(args):
+    """The reference's generation benchmark method (notebook cell 3: warm-up, resident snapshot with the peak
+    reset, measured runs, peak snapshot, overhead) on a seeded random-weight Llama, for the stock dynamic
+    cache, the drop-in paged cache and the block-table cache gathered and from the pages."""
+    from barqtrain_b200.benchmarks import inference
+
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(device)
+    rows = inference.run_table(device=device, batch=args.gen_batch, layers=args.layers_override or 16)
+    print(json.dumps({"workload": "generate", "model": "seeded random-weight Llama: 16 layers, hidden 1024, 8 query / 2 KV "
+                      "heads of 128, vocabulary 32000, bf16", "batch": args.gen_batch,
+                      "method": "warm-up runs, cuda_memory_snapshot(reset_peak=True), measured runs, peak snapshot; "
+                                "generation_overhead_mb = peak max_allocated - resident allocated",
+                      "rows": rows}), flush=True)
 
 
 def run_reference(args):
@@ -1008,6 +1033,7 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="budget of the CPU baseline leg")
     ap.add_argument("--min-seconds", type=float, default=1.0,
                     help="repeat the timed K-step region until this much device time has been measured")
+    ap.add_argument("--gen-batch", type=int, default=1, help="--workload generate: sequences per generate() call")
     ap.add_argument("--no-legs", action="store_true", help="skip the short legs of the other configurations")
     ap.add_argument("--quick-legs", action="store_true", help="legs with fewer layers and steps (smoke runs)")
     ap.add_argument("--eager", action="store_true",
@@ -1029,7 +1055,8 @@ def main():
     ap.add_argument("--reps", type=int, default=1, help="micro gather/append-prefill: launches per timed sample")
     ap.add_argument("--graph", action="store_true", help="micro cases: time a CUDA-graph replay of the launches")
     ap.add_argument("--tune", default="", help="gather knobs, e.g. stages=8,ctas=3,interleave=1 (micro cases)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "gather70b", "churn", "decode-attn"],
+    ap.add_argument("--workload", default="decode",
+                    choices=["decode", "prefill", "gather70b", "churn", "decode-attn", "generate"],
                     help="decode = the headline configuration; the others print the same line for their configuration")
     ap.add_argument("--all-layers", action="store_true",
                     help="--workload prefill / gather70b: all layers with one launch (all layers' rows / outputs at hand)")
@@ -1037,7 +1064,9 @@ def main():
                     help="--workload: KV heads on this GPU instead of 8/N (1 = an 8-GPU shard's work on one GPU)")
     ap.add_argument("--layers-override", type=int, default=0, help="fewer layers for a quick run of --workload")
     args = ap.parse_args()
-    if args.micro == "append-legacy":
+    if args.workload == "generate":
+        run_generate(args)
+    elif args.micro == "append-legacy":
         run_micro_legacy(args)
     elif args.micro:
         run_micro(args)

@@ -30,7 +30,8 @@ extern "C" {
 #define BARQKV_OK 0
 #define BARQKV_E_INVALID (-1) /* bad argument (null pointer, size, alignment) */
 #define BARQKV_E_LAUNCH (-2)  /* the CUDA runtime refused the launch */
-#define BARQKV_E_LIMIT (-3)   /* a size is beyond a documented maximum */
+#define BARQKV_E_LIMIT (-3)   /* a size is beyond a documented maximum, or the page pool is exhausted */
+#define BARQKV_E_CAPACITY (-4) /* a sequence would pass max_blocks * page_size tokens (the reference's ValueError, kv_cache.py:80-83) */
 
 /* bits a kernel may OR into *status (device int32, optional) */
 #define BARQKV_S_BAD_PAGE 1   /* block-table entry outside [0, num_pages): row skipped */
@@ -384,6 +385,28 @@ int barqkv_paged_decode_attention(const barqkv_pool_layout* pool, const void* k_
                                   void* workspace, int64_t workspace_bytes, int32_t* status, barqkv_stream_t stream);
 
 /*
+ * A decode layer in one launch: barqkv_append of the step's token (one new K/V row per sequence and KV
+ * head) fused into barqkv_paged_decode_attention.  What the reference does per layer and step - append
+ * (csrc/kernels/paged_kv_cache.cu:58-128), current_tensors (python/barqtrain/kv_cache.py:129-133), then an
+ * attention call over the returned views - with neither a separate append launch nor any gathered copy.
+ * seq_lens_after: lengths INCLUDING the new token (its position is length - 1; its page must already be
+ * in the table).  k_new / v_new: [n, kv_heads, 128] rows addressed by new_seq_stride / new_head_stride
+ * (elements), 16-byte aligned.  The CTA that owns a sequence's last page attends the new row from the
+ * caller's buffer and stores it into its page slot; on return (stream order) the pool holds the row, bit
+ * for bit what barqkv_append would have stored, and `out` equals append-then-attend.  Other arguments
+ * as for barqkv_paged_decode_attention.  flags: 0 or BARQKV_FLAG_DESC_STABLE (lengths, slots and table
+ * older than the preceding kernel; q, the new rows and the workspace are never read early).
+ */
+int barqkv_paged_decode_update(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,
+                               const barqkv_block_table* table, const int32_t* seq_lens_after, int32_t n,
+                               const void* k_new, const void* v_new, int64_t new_seq_stride, int64_t new_head_stride,
+                               const void* q, int64_t q_seq_stride, int64_t q_head_stride,
+                               void* out, int64_t out_seq_stride, int64_t out_head_stride,
+                               int32_t num_q_heads, float softmax_scale, int32_t is_bf16, int64_t max_len,
+                               int64_t total_len, void* workspace, int64_t workspace_bytes, int32_t flags,
+                               int32_t* status, barqkv_stream_t stream);
+
+/*
  * barqkv_gather for callers that cannot allocate device memory.
  * No counterpart in the reference (it never needs scratch memory).
  *
@@ -418,6 +441,94 @@ int barqkv_gather_noalloc(const barqkv_pool_layout* pool, const void* k_pool, co
                           int64_t total_tokens_hint,
                           void* k_out, void* v_out, const barqkv_rows_layout* out_rows,
                           int32_t mode, int32_t* status, int32_t work_slot, barqkv_stream_t stream);
+
+/*
+ * ---------------------------------------------------------------------------------------------
+ * Host-side bookkeeping of the block-table cache: the page free list, the block table's host copy
+ * and the per-step description.  Host code only; the library owns no device memory here - every
+ * buffer is the caller's.
+ * The reference needs none of this: it allocates every sequence's pages up front
+ * (lazy_initialization, python/barqtrain/kv_cache.py:53-73), addresses them arithmetically (:84-89)
+ * and can only release a whole layer (reset, :188-194).  These calls are what "allocation" and
+ * "sequence release" become with a shared page pool, kept native because at 256 live sequences the
+ * interpreted version of barqkv_host_begin costs more than the step's kernels.
+ * Not thread-safe: one thread drives one table.
+ * ---------------------------------------------------------------------------------------------
+ */
+typedef struct barqkv_host_table barqkv_host_table;
+
+/*
+ * free_order: the initial free list (a permutation of 0..num_pages-1; NULL = ascending); pages are
+ * handed out from its front, released pages queue at its back.  table_host: pinned int32
+ * [max_seqs, max_blocks], the authoritative block table, filled with -1 by the caller; lengths /
+ * page_count: int64 [max_seqs] each, zero-filled by the caller, tokens held and pages owned per
+ * slot.  The caller keeps all three alive, may read them at any time, and writes `lengths` itself
+ * when an append has been issued (the library only reads it, except that release zeroes a slot).
+ * Returns NULL on bad arguments (barqkv_last_error() says why).
+ */
+barqkv_host_table* barqkv_host_create(int32_t num_pages, const int32_t* free_order, int32_t max_seqs,
+                                      int32_t max_blocks, int32_t page_size, int32_t* table_host,
+                                      int64_t* lengths, int64_t* page_count);
+void barqkv_host_destroy(barqkv_host_table* table);
+
+/*
+ * The free list.  take: `count` pages from the front (BARQKV_E_LIMIT when fewer are free; nothing
+ * changes then).  share: one more holder for pages already held (a forked sequence shares its parent's
+ * full pages).  give_back: one holder fewer per listed page; pages nobody holds any more join the back
+ * of the list in the order first listed; the whole list is checked before anything changes
+ * (BARQKV_E_INVALID: a page released that is not held, or more often than it is held).
+ * stats: out = {free, resident, peak resident, take calls, give_back calls, num_pages}.
+ * free_list: copies up to `capacity` ids, front first; returns the number of free pages.
+ */
+int barqkv_host_take(barqkv_host_table* table, int32_t count, int32_t* out_pages);
+int barqkv_host_share(barqkv_host_table* table, const int32_t* pages, int32_t n);
+int barqkv_host_give_back(barqkv_host_table* table, const int32_t* pages, int32_t n);
+int32_t barqkv_host_holders(const barqkv_host_table* table, int32_t page);
+int barqkv_host_stats(const barqkv_host_table* table, int64_t out[6]);
+int32_t barqkv_host_free_list(const barqkv_host_table* table, int32_t* out, int32_t capacity);
+
+/*
+ * Table rows.  reserve: make the slot own pages for new_length tokens (BARQKV_E_CAPACITY beyond
+ * max_blocks * page_size, BARQKV_E_LIMIT when the pool cannot serve it).  set_pages: replace the
+ * slot's page list (fork, crop, beam reordering; holder counts are the caller's business through
+ * share / give_back).  release: give the slot's pages back, clear its row in the host table and zero
+ * its length.  Entries changed by any of these are remembered and sent to the device copy by the next
+ * barqkv_host_begin.
+ */
+int barqkv_host_reserve(barqkv_host_table* table, int32_t slot, int64_t new_length);
+int barqkv_host_set_pages(barqkv_host_table* table, int32_t slot, const int32_t* pages, int32_t n);
+int barqkv_host_release(barqkv_host_table* table, int32_t slot);
+int64_t barqkv_host_pending_changes(const barqkv_host_table* table);
+
+/*
+ * Device side of the table, all caller-owned: table_dev (int32 [max_seqs, max_blocks], the copy the
+ * kernels read), two step buffers of step_words int32 each (one for append descriptions, one for
+ * gather descriptions) and pinned staging memory of staging_words int32, used as a ring of 8 slots
+ * whose reuse is guarded by CUDA events.  May be called again with larger buffers.
+ */
+int barqkv_host_attach(barqkv_host_table* table, int32_t* table_dev, int32_t* step_dev_append, int32_t* step_dev_gather,
+                       int64_t step_words, int32_t* staging_host, int64_t staging_words);
+
+/*
+ * One step's host work in one call.  kind 0 (append): entry i will append counts[i] tokens to
+ * slots[i]; pages for them are reserved (all or nothing: BARQKV_E_CAPACITY / BARQKV_E_LIMIT leave
+ * everything as it was).  kind 1 (gather): the entries' current lengths.  Then every block-table
+ * entry changed since the last call and the description are written into a staging slot, sent with
+ * ONE cudaMemcpyAsync on `stream`, and the changed entries are applied to table_dev by a small
+ * kernel.  The description sits at the start of the kind's step buffer - an address that never
+ * changes, so a recorded CUDA graph can keep reading it - and the changed entries follow it.
+ * layout 0: the description is [slots n | first n | cu n+1] (first = start position for an append,
+ * length for a gather; cu = packed row offsets).  layout 1 (a decode step, one token per entry, kind
+ * 0): [slots n | start n | cu_new n+1 | lengths_after n | cu_out n+1], everything a fused append +
+ * gather of the step needs.  More changed entries than a staging slot holds (after bulk edits) go in
+ * several uploads.
+ * info: {total tokens, largest first, device address of the description, changed entries sent, host
+ * address of the description (readable until eight more calls have been made), pages taken, copies +
+ * kernels enqueued, words sent}.  When not even the description fits the attached buffers the call
+ * fails with BARQKV_E_LIMIT and info[7] holds the words needed.
+ */
+int barqkv_host_begin(barqkv_host_table* table, int32_t kind, const int32_t* slots, const int32_t* counts, int32_t n,
+                      int32_t layout, barqkv_stream_t stream, int64_t info[8]);
 
 #ifdef __cplusplus
 }

@@ -122,3 +122,111 @@ def test_decode_attention_workspace_survives_changing_batches():
         words = cache._attn_ws[: 4 * take * hkv].view(torch.int32)
         assert int(words.abs().sum()) == 0, "tickets left non-zero"
     assert backend.read_status(DEV) == 0
+
+
+@pytest.mark.parametrize("case", [
+    dict(dtype=torch.bfloat16, hkv=8, group=4, lens=(1, 15, 16, 17, 37, 500, 512, 513, 1500), ps=16),
+    dict(dtype=torch.float16, hkv=2, group=8, lens=(700, 33, 2100), ps=32),
+    dict(dtype=torch.bfloat16, hkv=1, group=4, lens=(64, 65, 1, 3000), ps=64),
+])
+def test_append_fused_into_decode_attention(case):
+    """``decode_update`` (one launch: store the step's rows and attend) against append-then-attend on a twin
+    cache: the pools end up bit-identical, the attention outputs are identical too (the same arithmetic on the
+    same values), and both stay within the fp32 reference's tolerance.  Two steps in a row, so the second
+    attends a token the first one stored."""
+    from barqtrain_b200 import BlockTableKVCache, _ffi
+
+    backend = _ffi.require_cuda_backend()
+    dtype, hkv, group, lens, ps = case["dtype"], case["hkv"], case["group"], list(case["lens"]), case["ps"]
+    D, n = 128, len(lens)
+    g = torch.Generator(device=DEV).manual_seed(12)
+    pages = sum(-(-(x + 2) // ps) for x in lens) + 2
+    order = torch.randperm(pages, generator=torch.Generator().manual_seed(3)).tolist()
+
+    def make():
+        c = BlockTableKVCache(1, hkv, D, page_size=ps, num_pages=pages, max_seqs=n, max_blocks_per_seq=-(-(max(lens) + 2) // ps),
+                              dtype=dtype, device=DEV, free_order=order, zero_pages=False)
+        c.pools.fill_(float("nan"))
+        return c, [c.open(i) for i in range(n)]
+
+    fused, fs = make()
+    plain, pl = make()
+    k = torch.randn(sum(lens), hkv, D, generator=g, device=DEV, dtype=torch.float32).to(dtype)
+    v = torch.randn(sum(lens), hkv, D, generator=g, device=DEV, dtype=torch.float32).to(dtype)
+    fused.append_step(fs, lens, [k], [v])
+    plain.append_step(pl, lens, [k], [v])
+    scale = D ** -0.5
+    for _ in range(2):
+        k1 = torch.randn(n, hkv, D, generator=g, device=DEV, dtype=torch.float32).to(dtype)
+        v1 = torch.randn(n, hkv, D, generator=g, device=DEV, dtype=torch.float32).to(dtype)
+        q = torch.randn(n, hkv * group, D, generator=g, device=DEV, dtype=torch.float32).to(dtype)
+        launches = backend.launches
+        new = fused.begin_append(fs, [1] * n)
+        fused.end_append(new)
+        full = fused.begin_gather(fs)
+        mid = backend.launches
+        got = fused.decode_update(0, full, k1, v1, q)
+        assert backend.launches == mid + 1 and mid - launches <= 2       # one kernel; the rest is table upkeep
+        new = plain.begin_append(pl, [1] * n)
+        plain.append(0, new, k1, v1)
+        plain.end_append(new)
+        full_p = plain.begin_gather(pl)
+        want = plain.decode_attention(0, full_p, q)
+        torch.cuda.synchronize()
+        used = torch.tensor(sorted(p for s_ in fs for p in fused.pages_of[s_]), device=DEV)
+        assert torch.equal(fused.pools[:, :, :, used].view(torch.int16), plain.pools[:, :, :, used].view(torch.int16))
+        assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+        _, ref = _reference(plain, 0, pl, q, scale)
+        assert torch.allclose(got.float(), ref, atol=ATOL, rtol=RTOL)
+    fused.check_device_status()
+    plain.check_device_status()
+
+
+def test_decode_graph_with_attention_replays_what_eager_steps_compute():
+    """``DecodeStepGraph(what="attention")``: one fused launch per layer recorded once and replayed; the pools and
+    the last layer's attention output must equal a twin cache stepped eagerly (append + attention per layer)."""
+    from barqtrain_b200 import BlockTableKVCache, DecodeStepGraph, _ffi
+
+    backend = _ffi.require_cuda_backend()
+    L, hkv, group, D, ps, dtype = 3, 2, 4, 128, 16, torch.bfloat16
+    lens = [30, 700, 15, 129]
+    n, steps = len(lens), 6
+    g = torch.Generator(device=DEV).manual_seed(21)
+    pages = sum(-(-(x + steps + 1) // ps) for x in lens)
+    order = torch.randperm(pages, generator=torch.Generator().manual_seed(4)).tolist()
+
+    def make():
+        c = BlockTableKVCache(L, hkv, D, page_size=ps, num_pages=pages, max_seqs=n,
+                              max_blocks_per_seq=-(-(max(lens) + steps + 1) // ps), dtype=dtype, device=DEV, free_order=order)
+        return c, [c.open(i) for i in range(n)]
+
+    a, sa = make()
+    b, sb = make()
+    for layer_rows in [[torch.randn(sum(lens), hkv, D, generator=g, device=DEV, dtype=torch.float32).to(dtype) for _ in range(L)]]:
+        a.append_step(sa, lens, layer_rows, layer_rows)
+        b.append_step(sb, lens, layer_rows, layer_rows)
+    graph = DecodeStepGraph(a, sa, capacity_tokens=sum(lens) + n * (steps + 1), what="attention", q_heads=hkv * group,
+                            max_len=max(lens) + steps + 1)
+    out_b = torch.empty(n, hkv * group, D, dtype=dtype, device=DEV)
+    for step in range(steps):
+        rows = torch.randn(L, n, hkv, D, generator=g, device=DEV, dtype=torch.float32).to(dtype)
+        q = torch.randn(n, hkv * group, D, generator=g, device=DEV, dtype=torch.float32).to(dtype)
+        graph.k_in.copy_(rows)
+        graph.v_in.copy_(rows.flip(0))
+        graph.q_in.copy_(q)
+        graph.step()
+        if step == 1:
+            graph.record()
+            assert graph.launches_per_replay == L
+        new = b.begin_append(sb, [1] * n)
+        b.end_append(new)
+        full = b.begin_gather(sb)
+        for layer in range(L):
+            b.append(layer, new, rows[layer], rows.flip(0)[layer])
+            b.decode_attention(layer, full, q, out=out_b, max_len=max(lens) + steps + 1, total_len=graph.capacity)
+        torch.cuda.synchronize()
+        assert torch.equal(a.pools.view(torch.int16), b.pools.view(torch.int16)), step
+        assert torch.equal(graph.attn_out.view(torch.int16), out_b.view(torch.int16)), step
+    assert graph.graph is not None
+    a.check_device_status()
+    assert backend.read_status(DEV) == 0

@@ -117,3 +117,33 @@ def test_block_table_cache_under_generate(from_pages):
     assert out.shape == (3, 53)
     model.config._attn_implementation = "sdpa"
     assert backend.read_status("cuda") == 0
+
+
+def test_generation_benchmark_table_has_the_reference_columns_and_paged_rows():
+    """``benchmarks.inference`` follows the reference's ``benchmark_generation`` (notebook cell 3): every row
+    carries the reference's columns; the paged set-ups report ``paged_kv_cache`` on the long profile; and the
+    block-table cache read from the pages adds no more generation overhead than the stock dynamic cache."""
+    from barqtrain_b200 import _ffi
+    from barqtrain_b200.benchmarks import inference
+
+    backend = _ffi.require_cuda_backend()
+    profile = {"profile": "memory_long", "prompt_tokens": 700, "new_tokens": 40, "warmup_runs": 1, "measure_runs": 1,
+               "paged_kv_min_cache_len": 0}
+    rows = inference.run_table(device="cuda", batch=2, layers=2, profiles=[profile])
+    by = {r["setup"]: r for r in rows}
+    assert set(by) == set(inference.SETUPS)
+    for r in rows:
+        for column in ("tokens_per_sec", "resident_vram_mb", "peak_vram_mb", "generation_overhead_mb", "paged_kv_cache"):
+            assert column in r
+        assert r["generated_tokens"] == 40 and r["tokens_per_sec"] > 0
+        assert r["peak_vram_mb"] >= r["resident_vram_mb"] > 0
+    assert by["hf_dynamic_cache"]["paged_kv_cache"] is False
+    assert all(by[s]["paged_kv_cache"] is True for s in inference.SETUPS[1:])
+    assert by["barq_block_table_from_pages"]["pages_peak"] == 2 * -(-740 // 16)
+    assert by["barq_block_table_from_pages"]["generation_overhead_mb"] <= by["hf_dynamic_cache"]["generation_overhead_mb"]
+    # short profile: the injection stays off below its minimum cache length, as in the reference
+    short = dict(inference.PROFILES[0], warmup_runs=1, measure_runs=1, new_tokens=8)
+    row = inference.benchmark_generation("barq_paged_kv_cache", inference.build_model(layers=2), torch.randint(
+        2, 32000, (1, 14)).to("cuda"), short)
+    assert row["paged_kv_cache"] is False
+    assert backend.read_status("cuda") == 0

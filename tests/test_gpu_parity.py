@@ -969,3 +969,115 @@ def test_all_layers_in_one_gather_launch(backend, layout):
         k1, v1 = cache.gather(layer, gb, layout)
         assert torch.equal(S.bits(k_all[layer]), S.bits(k1)) and torch.equal(S.bits(v_all[layer]), S.bits(v1))
     assert backend.read_status(DEV) == 0
+
+
+def test_crop_on_an_exhausted_pool_raises_and_changes_nothing(backend):
+    """``crop`` of a sequence that shares its last kept page needs one fresh page for its private copy; when the
+    pool has none the call must fail before anything was given back or edited."""
+    from barqtrain_b200 import BlockTableKVCache
+    from barqtrain_b200.block_table import PagePoolExhausted
+
+    H, D, ps, dtype = 2, 64, 16, torch.float16
+    g = torch.Generator().manual_seed(5)
+    cache = BlockTableKVCache(1, H, D, page_size=ps, num_pages=8, max_seqs=3, max_blocks_per_seq=6, dtype=dtype,
+                              device=DEV, seed=1)
+    a = cache.open("a")
+    k = S.randn(g, (64, H, D), dtype).to(DEV)
+    cache.append_step([a], [64], [k], [k])                      # 4 full pages
+    cache.fork("a", "b")                                        # shares all four
+    filler = cache.open("c")
+    cache.append_step([filler], [64], [k], [k])                 # the other 4 pages: the pool is empty
+    assert cache.allocator.pages_free == 0
+    before = (cache.pages_of[cache.slot("b")], int(cache.lengths[cache.slot("b")]),
+              [cache.allocator.holders(p) for p in range(8)])
+    with pytest.raises(PagePoolExhausted):
+        cache.crop("b", 40)                                     # keeps 3 pages, the third partly: needs a copy
+    after = (cache.pages_of[cache.slot("b")], int(cache.lengths[cache.slot("b")]),
+             [cache.allocator.holders(p) for p in range(8)])
+    assert after == before
+    cache.release("c")
+    cache.crop("b", 40)                                         # with room it goes through
+    assert int(cache.lengths[cache.slot("b")]) == 40 and len(cache.pages_of[cache.slot("b")]) == 3
+    gk, _ = cache.gather_sequence(0, "b", "NHD")
+    assert torch.equal(S.bits(gk), S.bits(k[:40]))
+    cache.check_device_status()
+
+
+def test_padded_output_of_a_batch_gathered_in_slices(backend, monkeypatch):
+    """Batches beyond one launch's scan limit are gathered in slices; with the padded ``[n, H, S, D]`` layout
+    every slice must land on its own batch rows (the limit is lowered here so that a small batch needs three)."""
+    from barqtrain_b200 import BlockTableKVCache, block_table
+
+    monkeypatch.setattr(block_table, "_GATHER_MAX_ENTRIES", 4)
+    H, D, ps, dtype = 2, 128, 16, torch.bfloat16
+    lens = [5, 33, 16, 1, 40, 17, 2, 31, 9, 20]
+    g = torch.Generator().manual_seed(6)
+    cache = BlockTableKVCache(1, H, D, page_size=ps, num_pages=40, max_seqs=len(lens), max_blocks_per_seq=4, dtype=dtype,
+                              device=DEV, seed=4)
+    slots = [cache.open(i) for i in range(len(lens))]
+    k = S.randn(g, (sum(lens), H, D), dtype).to(DEV)
+    v = S.randn(g, (sum(lens), H, D), dtype).to(DEV)
+    cache.append_step(slots, lens, [k], [v])
+    gb = cache.begin_gather(slots)
+    out = (torch.zeros(len(lens), H, max(lens), D, dtype=dtype, device=DEV),
+           torch.zeros(len(lens), H, max(lens), D, dtype=dtype, device=DEV))
+    cache.gather(0, gb, "BHSD", out=out)
+    at = 0
+    for i, n in enumerate(lens):
+        assert torch.equal(S.bits(out[0][i, :, :n]), S.bits(k[at:at + n].transpose(0, 1))), i
+        assert torch.equal(S.bits(out[1][i, :, :n]), S.bits(v[at:at + n].transpose(0, 1))), i
+        assert not out[0][i, :, n:].any()
+        at += n
+    kn, _ = cache.gather(0, gb, "NHD")                           # packed outputs go in slices too
+    assert torch.equal(S.bits(kn), S.bits(k))
+    cache.check_device_status()
+
+
+def test_a_description_overwritten_by_a_later_one_is_refused(backend):
+    from barqtrain_b200 import BlockTableKVCache
+
+    H, D, dtype = 1, 128, torch.bfloat16
+    cache = BlockTableKVCache(1, H, D, num_pages=8, max_seqs=2, max_blocks_per_seq=4, dtype=dtype, device=DEV)
+    a, b = cache.open(0), cache.open(1)
+    k = torch.zeros(3, H, D, dtype=dtype, device=DEV)
+    first = cache.begin_append([a], [3])
+    second = cache.begin_append([b], [3])                       # rewrites the device words `first` points to
+    with pytest.raises(RuntimeError, match="stale"):
+        cache.append(0, first, k, k)
+    cache.append(0, second, k, k)
+    cache.end_append(second)
+    cache.check_device_status()
+
+
+def test_table_changes_beyond_one_staging_slot_go_in_several_uploads(backend):
+    """``barqkv_host_begin`` sends the description and the changed block-table entries in one upload; when more
+    entries changed than the attached buffers hold beside the description, the rest travel in further uploads
+    ahead of it.  Re-attached here with room for four entries per upload."""
+    import ctypes
+
+    from barqtrain_b200 import BlockTableKVCache
+
+    H, D, ps, dtype = 1, 128, 16, torch.bfloat16
+    lens = [200, 150, 90]
+    g = torch.Generator().manual_seed(8)
+    cache = BlockTableKVCache(1, H, D, page_size=ps, num_pages=40, max_seqs=3, max_blocks_per_seq=16, dtype=dtype,
+                              device=DEV, seed=9)
+    slots = [cache.open(i) for i in range(3)]
+    n = len(slots)
+    small = 3 * n + 1 + 8                                        # the description and four (index, page) pairs
+    dev = [torch.zeros(small, dtype=torch.int32, device=DEV) for _ in range(2)]
+    staging = torch.zeros(8 * small, dtype=torch.int32).pin_memory()
+    assert backend.lib.barqkv_host_attach(cache._host, cache.table_dev.data_ptr(), dev[0].data_ptr(), dev[1].data_ptr(),
+                                          small, staging.data_ptr(), staging.numel()) == 0
+    cache._step_dev = dev
+    cache._tables.clear()
+    k = S.randn(g, (sum(lens), H, D), dtype).to(DEV)
+    batch = cache.begin_append(slots, lens)                      # 13 + 10 + 6 = 29 new table entries: 8 uploads
+    assert int(cache._info[3]) == 29 and int(cache._info[6]) == 8 + 8
+    cache.append(0, batch, k, k)
+    cache.end_append(batch)
+    torch.cuda.synchronize()
+    assert torch.equal(cache.table_dev.cpu(), cache.table_host)
+    gk, _ = cache.gather(0, cache.begin_gather(slots), "NHD")
+    assert torch.equal(S.bits(gk), S.bits(k))
+    cache.check_device_status()
