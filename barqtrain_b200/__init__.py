@@ -16,7 +16,8 @@ from .kv_cache import (
     maybe_prepare_paged_kv_generate_kwargs,
     paged_kv_supported_for_model,
 )
-from .block_table import BlockTableKVCache, DecodeStepGraph, PageAllocator, PagePoolExhausted, PoolStats
+from .block_table import (BlockTableKVCache, DecodeGraphs, DecodeStepGraph, PageAllocator, PagePoolExhausted,
+                          PoolStats)
 from .hf_block_cache import BarqBlockTableCache, use_paged_attention
 from ._ffi import load_cuda_backend
 
@@ -26,6 +27,7 @@ __all__ = [
     "BarqPagedKVCacheLayer",
     "BlockTableKVCache",
     "CudaMemorySnapshot",
+    "DecodeGraphs",
     "DecodeStepGraph",
     "PageAllocator",
     "PagePoolExhausted",

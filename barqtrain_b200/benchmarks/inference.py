@@ -93,6 +93,8 @@ def benchmark_generation(setup: str, model, input_ids: torch.Tensor, profile: Di
             # the stock path must not pick up an injected cache even if the model was patched earlier
             os.environ["BARQTRAIN_ENABLE_PAGED_KV"] = "0"
         elif setup.startswith("barq_block_table"):
+            if last_cache[0] is not None:              # the previous run's pool goes before this run's is made
+                last_cache[0].release_memory()
             cache = BarqBlockTableCache(model.config, max_batch_size=batch, max_cache_len=prompt_tokens + new_tokens,
                                         page_size=page_size, attention_from_pages=setup.endswith("from_pages"))
             kwargs.update(past_key_values=cache, use_cache=True)
@@ -103,6 +105,8 @@ def benchmark_generation(setup: str, model, input_ids: torch.Tensor, profile: Di
     with torch.inference_mode():
         for _ in range(profile["warmup_runs"]):
             run(min(16, profile["new_tokens"]))
+    if last_cache[0] is not None:
+        last_cache[0].release_memory()
     last_cache[0] = None
     _clear_memory()
     resident = cuda_memory_snapshot(reset_peak=True)

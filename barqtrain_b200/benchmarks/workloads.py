@@ -149,11 +149,13 @@ def gather_70b(world: int, rank: int, device, steps: int, warmup: int, layers: i
 
 
 def churn(world: int, rank: int, device, steps: int, warmup: int, layers: int = 32, verify: bool = False,
-          heads: int = 0, sync=lambda: None) -> Dict:
+          heads: int = 0, attend: bool = False, sync=lambda: None) -> Dict:
     """Continuous batching: 32 layers, 8 KV heads, head_dim 128, fp16, page 16; 256 live sequences with
     initial lengths uniform in [128, 2048]; every step appends one token to every live sequence in every
     layer, then each sequence finishes with seeded probability 0.01, returns its pages to the free list
-    and is replaced by a new sequence with a 512-token prefill."""
+    and is replaced by a new sequence with a 512-token prefill.  ``attend``: the decode step also attends
+    over the pages (4 query heads per KV head) - per layer one launch that stores the token and attends,
+    replayed from a CUDA graph whose batch rows are re-pointed at the replacements (``DecodeGraphs``)."""
     H = heads or kv_head_shard(8, world, rank)[1]
     dtype = torch.float16
     g = torch.Generator().manual_seed(1239)
@@ -168,13 +170,13 @@ def churn(world: int, rank: int, device, steps: int, warmup: int, layers: int = 
     gen = torch.Generator(device=device).manual_seed(1239 + rank)
     rows = torch.randn(max(max(lens0), 512) * 8, H, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
     ids = list(range(live))
-    slots = [cache.open(i) for i in ids]
+    slots = np.array([cache.open(i) for i in ids], dtype=np.int32)
     next_id = live
     # set-up: initial contents, in slices so that the packed source stays small
     origin = [None] * live            # per live sequence: (first row, count) of its prefill in `rows`
     decoded = np.zeros(live, dtype=np.int64)   # decode tokens appended since (each is rows[j])
     for lo in range(0, live, 8):
-        part, counts = slots[lo:lo + 8], lens0[lo:lo + 8]
+        part, counts = slots[lo:lo + 8].tolist(), lens0[lo:lo + 8]
         at = 0
         for j, c in zip(range(lo, lo + 8), counts):
             origin[j] = (at, c)
@@ -188,18 +190,34 @@ def churn(world: int, rank: int, device, steps: int, warmup: int, layers: int = 
     one_all = rows[:live].unsqueeze(0).repeat(layers, 1, 1, 1)
     prompt_all = rows[: 512 * 32].unsqueeze(0).repeat(layers, 1, 1, 1)
     finished = (torch.rand(total_steps, live, generator=g) < 0.01).numpy()
-    ones = np.ones(live, dtype=np.int64)
-    counters = {"tokens": 0, "host_s": 0.0, "released": 0, "launches": 0}
+    ones = np.ones(live, dtype=np.int32)
+    counters = {"tokens": 0, "host_s": 0.0, "released": 0, "launches": 0, "attended": 0}
+    graphs = None
+    if attend:
+        from ..block_table import DecodeGraphs
+
+        graphs = DecodeGraphs(cache, capacity_tokens=live * cap, what="attention", q_heads=4 * H, max_len=cap)
+        g0 = graphs.graph_for(slots.tolist())
+        g0.k_in.copy_(one_all)
+        g0.v_in.copy_(one_all)
+        g0.q_in.normal_(generator=gen)
 
     def step(i):
         nonlocal next_id
-        t0 = time.perf_counter()
-        batch = cache.begin_append(slots, ones)
-        counters["host_s"] += time.perf_counter() - t0
-        cache.append_layers(batch, one_all, one_all)           # all layers' rows of the step in one launch
-        cache.end_append(batch)
+        if attend:
+            t0 = time.perf_counter()
+            graph = graphs.step(slots.tolist())                # host work of the step is inside (native description)
+            counters["host_s"] += time.perf_counter() - t0
+            counters["attended"] += graph.total
+            counters["launches"] += layers
+        else:
+            t0 = time.perf_counter()
+            batch = cache.begin_append(slots, ones)
+            counters["host_s"] += time.perf_counter() - t0
+            cache.append_layers(batch, one_all, one_all)       # all layers' rows of the step in one launch
+            cache.end_append(batch)
+            counters["launches"] += 1
         counters["tokens"] += live
-        counters["launches"] += 1
         decoded[:] += 1
         gone = np.nonzero(finished[i])[0].tolist()
         if gone:
@@ -249,13 +267,15 @@ def churn(world: int, rank: int, device, steps: int, warmup: int, layers: int = 
                 if b - a != count + int(decoded[j]) or not torch.equal(kn[a:b], want) or not torch.equal(vn[a:b], want):
                     verified = False
     st = cache.stats()
-    return {"bytes": 4 * counters["tokens"] * H * D * 2 * layers, "ms": ms, "tokens": counters["tokens"],
-            "verified": verified,
+    return {"bytes": (4 * counters["tokens"] + 2 * counters["attended"]) * H * D * 2 * layers, "ms": ms,
+            "tokens": counters["tokens"], "verified": verified,
             "launches": counters["launches"],
             "config": {"workload": "continuous-batching-churn", "layers": layers, "kv_heads_per_gpu": H,
                        "dtype": "fp16", "page_size": 16, "live_sequences": live,
-                       "step": "append 1 token to 256 sequences in every layer (one launch for all layers); finished "
-                               "sequences (p=0.01) release their pages and are replaced by a 512-token prefill",
+                       "step": ("per layer, store 1 token of 256 sequences and attend over their pages (one launch per "
+                                "layer, CUDA graph)" if attend else "append 1 token to 256 sequences in every layer (one "
+                                "launch for all layers)") + "; finished sequences (p=0.01) release their pages and are "
+                               "replaced by a 512-token prefill",
                        "l2": "decode appends are 1 MB per launch (L2-resident, launch-bound); prefills stream"},
             "extra": {"sequences_released": counters["released"], "pages_total": st.pages_total,
                       "pages_resident": st.pages_resident, "pages_peak": st.pages_peak,

@@ -248,7 +248,9 @@ class BlockTableKVCache:
         # changed (two words each); more entries than fit go in several uploads.
         self._step_words = 5 * max_seqs + 2 + 2 * min(max(max_seqs * max_blocks_per_seq, 1024), 1 << 18)
         self._step_dev = [torch.zeros(self._step_words, dtype=torch.int32, device=self.device) for _ in range(2)]
-        self._staging = torch.zeros(8 * self._step_words, dtype=torch.int32).pin_memory()
+        # staging ring: up to 32 steps for small tables (the host may run that far ahead of the device), 4 MiB at most
+        ring = max(2, min(32, (1 << 20) // self._step_words))
+        self._staging = torch.zeros(ring * self._step_words, dtype=torch.int32).pin_memory()
         rc = self.backend.lib.barqkv_host_attach(self._host, self.table_dev.data_ptr(), self._step_dev[0].data_ptr(),
                                                  self._step_dev[1].data_ptr(), self._step_words,
                                                  self._staging.data_ptr(), self._staging.numel())
@@ -256,6 +258,8 @@ class BlockTableKVCache:
             self.backend._check(rc)
         self._c_begin = self.backend.lib.barqkv_host_begin
         self._info = (ctypes.c_int64 * 8)()
+        self._staging_np, self._staging_ptr = self._staging.numpy(), self._staging.data_ptr()
+        self._work_bases: Dict[int, int] = {}
         self.pages_of = _PagesOf(self)                         # pages_of[slot] -> list of page ids, in order
         self._free_slots: List[int] = list(range(max_seqs - 1, -1, -1))
         self._slot_of: Dict[object, int] = {}
@@ -419,41 +423,50 @@ class BlockTableKVCache:
 
     # -- a step's host work: pages, table entries, description - one native call ------------------------
     def _begin(self, kind: str, slots, counts) -> _Descriptor:
-        slots32 = _i32(slots)
+        slots32 = slots if (type(slots) is np.ndarray and slots.dtype == np.int32 and slots.ndim == 1
+                            and slots.flags.c_contiguous) else _i32(slots)
         n = slots32.size
         code = 0 if kind == "append" else 1
-        counts32 = None
+        counts_ptr = None
         if code == 0:
-            counts32 = _i32(counts)
-            if counts32.shape != slots32.shape:
+            counts32 = counts if (type(counts) is np.ndarray and counts.dtype == np.int32 and counts.ndim == 1
+                                  and counts.flags.c_contiguous) else _i32(counts)
+            if counts32.size != n:
                 raise ValueError("slots and counts must have the same length")
-        cur = torch.cuda.current_stream(self.device)
+            counts_ptr = counts32.ctypes.data if n else None
+        stream = torch.cuda.current_stream(self.device).cuda_stream
         info = self._info
-        rc = self._c_begin(self._host, code, slots32.ctypes.data if n else None,
-                           counts32.ctypes.data if (n and counts32 is not None) else None, n, 0, cur.cuda_stream, info)
+        rc = self._c_begin(self._host, code, slots32.ctypes.data if n else None, counts_ptr, n, 0, stream, info)
         if rc:
             self._raise_host(rc)
         self._uploads += 1
-        # host copy of the description the native side just wrote: [slots | first | cu]
-        words = 3 * n + 1
-        host = np.frombuffer((ctypes.c_int32 * words).from_address(info[4]), dtype=np.int32).astype(np.int64)
-        first, cu = host[n:2 * n], host[2 * n:words]
+        # host copy of the description the native side just wrote into the staging ring: [slots | first | cu]
+        at = (info[4] - self._staging_ptr) >> 2
+        host = self._staging_np[at:at + 3 * n + 1].copy()
+        first, cu = host[n:2 * n], host[2 * n:]
         table = self._tables.get(kind)
         if table is None:
             table = _ffi.BlockTable(self.table_dev.data_ptr(), self._step_dev[code].data_ptr(), self.max_seqs,
                                     self.max_blocks, 0, 0)
-            self._tables[kind] = table
-        work = self.backend.work_words(self.device).data_ptr()      # the stream's hand-out counters
-        slots64 = host[:n]
-        desc = _Descriptor(n, self._step_dev[code], int(info[0]), first, cu, slots64, ctypes.byref(table),
-                           cur.cuda_stream, work)
-        desc.slots_np, desc.after_np = slots64, first + (cu[1:] - cu[:-1])
-        desc.max_first = int(info[1])
+            self._tables[kind] = (table, ctypes.byref(table))
+            table = self._tables[kind]
+        desc = _Descriptor(n, self._step_dev[code], info[0], first, cu, host[:n], table[1], stream, self._work_base(stream))
+        desc.slots_np = host[:n]
+        desc.after_np = cu[1:] - cu[:-1]
+        desc.after_np += first
+        desc.max_first = info[1]
         # The device buffer of a kind is rewritten by the next begin_* of that kind: an older description
         # would silently address the newer one's contents, so every use checks that it is still current.
-        self._desc_turn[kind] = self._desc_turn.get(kind, 0) + 1
-        desc.kind, desc.generation = kind, self._desc_turn[kind]
+        turn = self._desc_turn.get(kind, 0) + 1
+        self._desc_turn[kind] = turn
+        desc.kind, desc.generation = kind, turn
         return desc
+
+    def _work_base(self, stream: int) -> int:
+        base = self._work_bases.get(stream)
+        if base is None:
+            base = self._work_bases[stream] = self.backend.work_words(self.device).data_ptr()
+        return base
 
     def _launch_terms(self, desc: _Descriptor) -> Tuple[int, int]:
         """(work pointer, flag) for the next kernel that uses ``desc``.  The flag says that nothing the kernel
@@ -999,6 +1012,20 @@ class DecodeStepGraph:
         self._full.p_first = base + 4 * (3 * n + 1)
         self._full.p_cu = base + 4 * (4 * n + 1)
 
+    def set_slots(self, slots: Sequence[int]) -> None:
+        """Continue with other sequences in the batch's rows (continuous batching: a finished sequence's row is
+        taken by its replacement).  The recorded launches read the slots from the step's description on the
+        device, so the graph stays valid as long as the batch size does; a different size needs another graph
+        (``DecodeGraphs`` keeps one per size)."""
+        slots = list(slots)
+        if len(slots) != len(self.slots):
+            raise ValueError(f"this graph was recorded for {len(self.slots)} sequences, not {len(slots)}")
+        self.slots = slots
+        self._slots_np = np.asarray(slots, dtype=np.int64)
+        self._slots32 = _i32(slots)
+        self._new.slots_np = self._full.slots_np = self._slots_np
+        self._new._slots = self._full._slots = slots
+
     def _launch_layers(self) -> None:
         c = self.cache
         if self.what == "append":
@@ -1076,3 +1103,30 @@ class DecodeStepGraph:
     def outputs(self, layer: int) -> Tuple[torch.Tensor, torch.Tensor]:
         k, v = self.bufs[layer & 1]
         return k[:, :self.total], v[:, :self.total]
+
+
+class DecodeGraphs:
+    """Decode steps of a batch whose membership and size change (continuous batching): one recorded
+    ``DecodeStepGraph`` per batch size, made and recorded the first time that size shows up (one eager step,
+    then the recording), replayed from then on with whatever slots the step names."""
+
+    def __init__(self, cache: BlockTableKVCache, capacity_tokens: int, **graph_options):
+        self.cache, self.capacity, self.options = cache, int(capacity_tokens), graph_options
+        self.graphs: Dict[int, DecodeStepGraph] = {}
+
+    def graph_for(self, slots: Sequence[int]) -> DecodeStepGraph:
+        graph = self.graphs.get(len(slots))
+        if graph is None:
+            graph = self.graphs[len(slots)] = DecodeStepGraph(self.cache, slots, self.capacity, **self.options)
+        else:
+            graph.set_slots(slots)
+        return graph
+
+    def step(self, slots: Sequence[int]) -> DecodeStepGraph:
+        """One decode step for ``slots``; returns the graph that ran it (its ``k_in`` / ``v_in`` / ``q_in`` must hold
+        the step's inputs before the call: fill them through ``graph_for(slots)``)."""
+        graph = self.graph_for(slots)
+        graph.step()
+        if graph.graph is None and graph.steps >= 1:
+            graph.record()
+        return graph

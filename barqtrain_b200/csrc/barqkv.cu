@@ -1172,6 +1172,7 @@ struct Knobs {
     int attn_promotion = -1;
     int attn_split_tokens = 0;
     int append_bulk = -1;        // -1: page-sized appends go through the copy engine; 0: always the row kernel
+    int attn_wide = -1;          // -1: decode attention updates its softmax state every 32 tokens; 0: every 16
 };
 #ifdef BARQKV_TUNING
 Knobs g_knobs;
@@ -1388,6 +1389,7 @@ int barqkv_set_tuning(int32_t knob, int32_t value) {
         case BARQKV_KNOB_ATTN_L2_PROMOTION: g_knobs.attn_promotion = value; return 0;
         case BARQKV_KNOB_ATTN_SPLIT_TOKENS: g_knobs.attn_split_tokens = value; return 0;
         case BARQKV_KNOB_APPEND_BULK: g_knobs.append_bulk = value; return 0;
+        case BARQKV_KNOB_ATTN_WIDE: g_knobs.attn_wide = value; return 0;
         default: return fail(BARQKV_E_INVALID, "set_tuning: unknown knob");
     }
 }
@@ -1820,7 +1822,8 @@ static int gather_common(const barqkv_pool_layout* pool, const void* k_pool, con
     a.status = status;
     a.interleave = g_knobs.interleave < 0 ? 0 : g_knobs.interleave;
     a.work = g_knobs.static_shares ? nullptr : work;
-    a.group_tiles = g_knobs.group_tiles ? g_knobs.group_tiles : (a.heads >= 8 ? 1 : 8 / a.heads);
+    // tiles per hand-out: about 4 (page, head) units, i.e. 32 KiB of K and V, per atomic fetch
+    a.group_tiles = g_knobs.group_tiles ? g_knobs.group_tiles : (a.heads >= 4 ? (a.heads >= 8 ? 1 : 2) : 4);
     if (a.group_tiles > kGroup) a.group_tiles = kGroup;
     if (a.group_tiles < 1) a.group_tiles = 1;
     a.static_permille = g_knobs.static_permille >= 0 ? g_knobs.static_permille : 0;

@@ -19,7 +19,7 @@
 
 namespace {
 
-constexpr int kHostRing = 8;           // staging slots in flight
+constexpr int kHostRing = 64;          // most staging slots in flight (the caller's staging memory decides how many)
 
 struct HostTable {
     int num_pages = 0, max_seqs = 0, max_blocks = 0, page_size = 0;
@@ -40,8 +40,9 @@ struct HostTable {
     int32_t* table_dev = nullptr;
     int32_t* step_dev[2] = {nullptr, nullptr};     // per kind (0 append, 1 gather): [pairs | slots | first | cu]
     long long step_words = 0;
-    int32_t* staging = nullptr;        // pinned, kHostRing slots of slot_words int32 each
+    int32_t* staging = nullptr;        // pinned, ring_slots slots of slot_words int32 each
     long long slot_words = 0;
+    int ring_slots = 0;
     int pos = 0;
     cudaEvent_t done[kHostRing] = {};
     bool pending[kHostRing] = {};
@@ -279,8 +280,8 @@ int barqkv_host_attach(barqkv_host_table* handle, int32_t* table_dev, int32_t* s
                        int64_t step_words, int32_t* staging_host, int64_t staging_words) {
     HostTable* h = reinterpret_cast<HostTable*>(handle);
     if (!h || !table_dev || !step_dev_append || !step_dev_gather || !staging_host || step_words <= 0 ||
-        staging_words < kHostRing)
-        return fail(BARQKV_E_INVALID, "host_attach: bad arguments");
+        staging_words < 2 * step_words)
+        return fail(BARQKV_E_INVALID, "host_attach: bad arguments (the staging memory must hold at least two steps)");
     // copies out of the old staging memory must have run before it is replaced
     for (int i = 0; i < kHostRing; ++i) {
         if (h->pending[i]) {
@@ -298,7 +299,10 @@ int barqkv_host_attach(barqkv_host_table* handle, int32_t* table_dev, int32_t* s
     h->step_dev[1] = step_dev_gather;
     h->step_words = step_words;
     h->staging = staging_host;
-    h->slot_words = staging_words / kHostRing;
+    // as many whole steps as the staging memory holds, at most kHostRing: the host may run that many steps
+    // ahead of the device before a slot's earlier upload has to be waited for
+    h->ring_slots = (int)(staging_words / step_words < kHostRing ? staging_words / step_words : kHostRing);
+    h->slot_words = step_words;
     h->pos = 0;
     h->attached = true;
     return 0;
@@ -453,7 +457,7 @@ int barqkv_host_begin(barqkv_host_table* handle, int32_t kind, const int32_t* sl
         e = cudaEventRecord(h->done[s_], st);
         if (e != cudaSuccess) return fail_cuda("host_begin: cudaEventRecord", e);
         h->pending[s_] = true;
-        h->pos = (s_ + 1) % kHostRing;
+        h->pos = (s_ + 1) % h->ring_slots;
         ++uploads;
         sent_words += words;
         if (here) {

@@ -27,11 +27,12 @@ namespace {
 
 constexpr int kAttnSplitTokens = 512;                 // tokens per split by default
 // Per page size: bytes of one head's page of K (or V), of a stage (K + V), and ring depth.
-template <int PS> struct AttnTile {
+template <int PS, bool WIDE> struct AttnTile {
     static constexpr int kHalf = PS * 128;            // one half tile: PS rows x 64 dims x 2 bytes
     static constexpr int kPage = 2 * kHalf;
     static constexpr int kStage = 2 * kPage;
-    static constexpr int kStages = PS <= 16 ? 4 : 3;
+    // 16-token pages attended two at a time keep three pages in flight beside the two in use
+    static constexpr int kStages = PS <= 16 ? (WIDE ? 5 : 4) : 3;
 };
 
 struct AttnArgs {
@@ -107,11 +108,11 @@ __device__ __forceinline__ uint32_t swz(int r, int chunk) {
     return (uint32_t)(((r >> 3) << 10) + ((r & 7) << 7) + (((chunk ^ (r & 7)) & 7) << 4));
 }
 
-template <bool BF16, int PS>
+template <bool BF16, int PS, bool WIDE>
 __global__ void __launch_bounds__(32)
 paged_decode_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v) {
     extern __shared__ unsigned char s_attn_raw[];
-    using Tile = AttnTile<PS>;
+    using Tile = AttnTile<PS, WIDE>;
     constexpr int kAttnStages = Tile::kStages;
     constexpr int kAttnStageBytes = Tile::kStage;
     constexpr int kAttnPageBytes = Tile::kPage;
@@ -205,11 +206,79 @@ paged_decode_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap map_k,
         }
     };
 
-    const int ahead = kAttnStages - 1;
-    for (int p = p0; p < min(p1, p0 + ahead); ++p) issue(p);
-
-    for (int p = p0; p < p1 && !dead; ++p) {
-        if (p + ahead < p1) issue(p + ahead);
+    // One 16-token block of a tile: scores (two n-tiles of 8 tokens) and, later, its share of P.V.
+    auto block_qk = [&](const unsigned char* kt, int r0, float (&s0)[4], float (&s1)[4]) {
+        const int tile = lane >> 3, r8 = lane & 7;
+        const int trow = r0 + (tile >> 1) * 8 + r8;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+            const uint32_t addr = smem_addr(kt + (ks >> 2) * kHalf) + swz(trow, (ks & 3) * 2 + (tile & 1));
+            uint32_t b0, b1, b2, b3;
+            ldmatrix_x4(addr, b0, b1, b2, b3);
+            mma_16816<BF16>(s0, qa[ks][0], 0u, qa[ks][1], 0u, b0, b1);
+            mma_16816<BF16>(s1, qa[ks][0], 0u, qa[ks][1], 0u, b2, b3);
+        }
+    };
+    auto block_pv = [&](const unsigned char* vt, int r0, uint32_t pa0, uint32_t pa2) {
+        const int tile = lane >> 3, r8 = lane & 7;
+        const int trow = r0 + (tile & 1) * 8 + r8;
+#pragma unroll
+        for (int nb = 0; nb < 8; ++nb) {
+            const uint32_t addr = smem_addr(vt + (nb >> 2) * kHalf) + swz(trow, (nb & 3) * 2 + (tile >> 1));
+            uint32_t b0, b1, b2, b3;
+            ldmatrix_x4_trans(addr, b0, b1, b2, b3);
+            mma_16816<BF16>(acc[2 * nb], pa0, 0u, pa2, 0u, b0, b1);
+            mma_16816<BF16>(acc[2 * nb + 1], pa0, 0u, pa2, 0u, b2, b3);
+        }
+    };
+    // rows past the sequence's end hold whatever the page held before: keep them out of P.V
+    auto clear_v_tail = [&](unsigned char* vt, int r0, int valid) {
+        for (int idx = lane; idx < (16 - valid) * 16; idx += 32) {
+            const int r = r0 + valid + (idx >> 4), c = idx & 15;
+            *reinterpret_cast<uint4*>(vt + (c >> 3) * kHalf + ((r >> 3) << 10) + ((r & 7) << 7) + ((c & 7) << 4)) =
+                make_uint4(0u, 0u, 0u, 0u);
+        }
+        __syncwarp();
+    };
+    // Up to 32 tokens at a time: block A (16 rows from r0a of tile A, valid_a of them hold tokens) and, when
+    // valid_b > 0, block B.  One running-maximum update, one rescale of the accumulators and one pass of
+    // exponentials serve both blocks, and their score products are independent instruction streams.
+    auto attend = [&](unsigned char* kta, unsigned char* vta, int r0a, int valid_a, unsigned char* ktb, unsigned char* vtb,
+                      int r0b, int valid_b) {
+        if (valid_a < 16) clear_v_tail(vta, r0a, valid_a);
+        if (valid_b > 0 && valid_b < 16) clear_v_tail(vtb, r0b, valid_b);
+        float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+        float s2[4] = {0.f, 0.f, 0.f, 0.f}, s3[4] = {0.f, 0.f, 0.f, 0.f};
+        block_qk(kta, r0a, s0, s1);
+        if (valid_b > 0) block_qk(ktb, r0b, s2, s3);
+        // online softmax for row g: this lane holds tokens tq*2, tq*2+1 (n-tile 0) and +8 (n-tile 1) of each block
+        const int t_first = tq * 2;
+        float x[8] = {s0[0] * a.scale_log2, s0[1] * a.scale_log2, s1[0] * a.scale_log2, s1[1] * a.scale_log2,
+                      s2[0] * a.scale_log2, s2[1] * a.scale_log2, s3[0] * a.scale_log2, s3[1] * a.scale_log2};
+        if (t_first >= valid_a) x[0] = -INFINITY;
+        if (t_first + 1 >= valid_a) x[1] = -INFINITY;
+        if (t_first + 8 >= valid_a) x[2] = -INFINITY;
+        if (t_first + 9 >= valid_a) x[3] = -INFINITY;
+        if (t_first >= valid_b) x[4] = -INFINITY;
+        if (t_first + 1 >= valid_b) x[5] = -INFINITY;
+        if (t_first + 8 >= valid_b) x[6] = -INFINITY;
+        if (t_first + 9 >= valid_b) x[7] = -INFINITY;
+        float mx = fmaxf(fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3])), fmaxf(fmaxf(x[4], x[5]), fmaxf(x[6], x[7])));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run, mx);              // finite: the first token of every block A reached is valid
+        const float alpha = exp2f(m_run - m_new);
+        float e[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) e[i] = exp2f(x[i] - m_new);
+        l_run = l_run * alpha + ((e[0] + e[1]) + (e[2] + e[3])) + ((e[4] + e[5]) + (e[6] + e[7]));
+        m_run = m_new;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) { acc[i][0] *= alpha; acc[i][1] *= alpha; }
+        block_pv(vta, r0a, pack2<BF16>(e[0], e[1]), pack2<BF16>(e[2], e[3]));
+        if (valid_b > 0) block_pv(vtb, r0b, pack2<BF16>(e[4], e[5]), pack2<BF16>(e[6], e[7]));
+    };
+    auto wait_page = [&](int p) {              // false (and `dead`) when the bounded wait ran out
         const int st = (p - p0) % kAttnStages;
         const uint32_t phase = (uint32_t)(((p - p0) / kAttnStages) & 1);
         const uint32_t bar = smem_addr(&s_bar[st]);
@@ -218,86 +287,61 @@ paged_decode_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap map_k,
             if (clock64() - t0 > kWaitCycles) { dead = true; break; }
         }
         dead = __any_sync(0xffffffffu, dead);
-        if (dead) break;
-        if (bad) continue;                     // keep draining the loads already issued, compute nothing
+        return !dead;
+    };
+    // The step's own token (fused append): into the tile - the pool's slot still holds stale bytes - and into the pool.
+    auto place_new_row = [&](int p, unsigned char* kt, unsigned char* vt) {
+        const int r = (len - 1) - p * PS;
+        const int j = lane & 15;
+        unsigned char* tile = lane < 16 ? kt : vt;
+        *reinterpret_cast<uint4*>(tile + (j >> 3) * kHalf + swz(r, j & 7)) = new_chunk;
+        const int phys = __shfl_sync(0xffffffffu, my_page, p - table_base);
+        unsigned char* dst = (lane < 16 ? a.k_pool_w : a.v_pool_w) + (long long)phys * a.pool_page +
+                             (long long)kvh * a.pool_head + (long long)r * 256 + j * 16;
+        *reinterpret_cast<uint4*>(dst) = new_chunk;
+        __syncwarp();
+    };
 
-        unsigned char* kt = s_attn + (size_t)st * kAttnStageBytes;
-        unsigned char* vt = kt + kAttnPageBytes;
-        if (owns_new && p == pages - 1) {
-            // the step's own token: into the tile (the pool's slot still holds stale bytes) and into the pool
-            const int r = (len - 1) - p * PS;
-            const int j = lane & 15;
-            unsigned char* tile = lane < 16 ? kt : vt;
-            *reinterpret_cast<uint4*>(tile + (j >> 3) * kHalf + swz(r, j & 7)) = new_chunk;
-            const int phys = __shfl_sync(0xffffffffu, my_page, p - table_base);
-            unsigned char* dst = (lane < 16 ? a.k_pool_w : a.v_pool_w) + (long long)phys * a.pool_page +
-                                 (long long)kvh * a.pool_head + (long long)r * 256 + j * 16;
-            *reinterpret_cast<uint4*>(dst) = new_chunk;
-            __syncwarp();
+    if (PS == 16 && WIDE) {
+        // Two pages per iteration.  While pages p and p + 1 are attended, p + 2 .. p + kStages - 1 are on their way;
+        // the two stages freed by the previous iteration are re-armed first.
+        constexpr int ahead = kAttnStages - 2;
+        for (int p = p0; p < min(p1, p0 + ahead); ++p) issue(p);
+        for (int p = p0; p < p1; p += 2) {
+            if (p + ahead < p1) issue(p + ahead);
+            if (p + ahead + 1 < p1) issue(p + ahead + 1);
+            const bool two = p + 1 < p1;
+            if (!wait_page(p)) break;
+            if (two && !wait_page(p + 1)) break;
+            if (bad) continue;                     // keep draining the loads already issued, compute nothing
+            unsigned char* kta = s_attn + (size_t)((p - p0) % kAttnStages) * kAttnStageBytes;
+            unsigned char* ktb = s_attn + (size_t)((p + 1 - p0) % kAttnStages) * kAttnStageBytes;
+            const int last = two ? p + 1 : p;
+            if (owns_new && last == pages - 1) place_new_row(last, two ? ktb : kta, (two ? ktb : kta) + kAttnPageBytes);
+            attend(kta, kta + kAttnPageBytes, 0, min(16, len - p * PS), ktb, ktb + kAttnPageBytes, 0,
+                   two ? min(16, len - (p + 1) * PS) : 0);
+            __syncwarp();      // every lane is done with both stages before lane 0 re-arms them
         }
+    } else {
+        constexpr int ahead = kAttnStages - 1;
+        for (int p = p0; p < min(p1, p0 + ahead); ++p) issue(p);
+        for (int p = p0; p < p1; ++p) {
+            if (p + ahead < p1) issue(p + ahead);
+            if (!wait_page(p)) break;
+            if (bad) continue;                     // keep draining the loads already issued, compute nothing
+            unsigned char* kt = s_attn + (size_t)((p - p0) % kAttnStages) * kAttnStageBytes;
+            unsigned char* vt = kt + kAttnPageBytes;
+            if (owns_new && p == pages - 1) place_new_row(p, kt, vt);
+            constexpr int kStep = WIDE ? 32 : 16;              // tokens per softmax update
 #pragma unroll 1
-        for (int sb = 0; sb < PS / 16; ++sb) {                    // 16 tokens at a time
-            const int valid = min(16, len - p * PS - sb * 16);    // rows of this block that hold tokens
-            if (valid <= 0) break;
-            const int r0 = sb * 16;
-            if (valid < 16) {
-                // rows past the sequence's end hold whatever the page held before: keep them out of P.V
-                for (int idx = lane; idx < (16 - valid) * 16; idx += 32) {
-                    const int r = r0 + valid + (idx >> 4), c = idx & 15;
-                    *reinterpret_cast<uint4*>(vt + (c >> 3) * kHalf + ((r >> 3) << 10) + ((r & 7) << 7) + ((c & 7) << 4)) =
-                        make_uint4(0u, 0u, 0u, 0u);
-                }
-                __syncwarp();
+            for (int r0 = 0; r0 < PS; r0 += kStep) {
+                const int valid_a = min(16, len - p * PS - r0);
+                if (valid_a <= 0) break;
+                const int valid_b = WIDE ? min(16, len - p * PS - r0 - 16) : 0;
+                attend(kt, vt, r0, valid_a, kt, vt, r0 + 16, valid_b);
             }
-
-            // S = Q K^T for the block's 16 tokens: two n-tiles of 8 tokens
-            float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
-            {
-                const int tile = lane >> 3, r8 = lane & 7;
-                const int trow = r0 + (tile >> 1) * 8 + r8;
-#pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {
-                    const uint32_t addr = smem_addr(kt + (ks >> 2) * kHalf) + swz(trow, (ks & 3) * 2 + (tile & 1));
-                    uint32_t b0, b1, b2, b3;
-                    ldmatrix_x4(addr, b0, b1, b2, b3);
-                    mma_16816<BF16>(s0, qa[ks][0], 0u, qa[ks][1], 0u, b0, b1);
-                    mma_16816<BF16>(s1, qa[ks][0], 0u, qa[ks][1], 0u, b2, b3);
-                }
-            }
-            // online softmax for row g: this lane holds tokens tq*2, tq*2+1 (tile 0) and +8 (tile 1)
-            float x[4] = {s0[0] * a.scale_log2, s0[1] * a.scale_log2, s1[0] * a.scale_log2, s1[1] * a.scale_log2};
-            const int t_first = tq * 2;
-            if (t_first >= valid) x[0] = -INFINITY;
-            if (t_first + 1 >= valid) x[1] = -INFINITY;
-            if (t_first + 8 >= valid) x[2] = -INFINITY;
-            if (t_first + 9 >= valid) x[3] = -INFINITY;
-            float mx = fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3]));
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-            const float m_new = fmaxf(m_run, mx);              // finite: the first token of every block reached is valid
-            const float alpha = exp2f(m_run - m_new);
-            const float e0 = exp2f(x[0] - m_new), e1 = exp2f(x[1] - m_new), e2 = exp2f(x[2] - m_new), e3 = exp2f(x[3] - m_new);
-            l_run = l_run * alpha + (e0 + e1 + e2 + e3);
-            m_run = m_new;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) { acc[i][0] *= alpha; acc[i][1] *= alpha; }
-            const uint32_t pa0 = pack2<BF16>(e0, e1), pa2 = pack2<BF16>(e2, e3);
-
-            // O += P V: sixteen n-tiles of 8 dims, two per ldmatrix
-            {
-                const int tile = lane >> 3, r8 = lane & 7;
-                const int trow = r0 + (tile & 1) * 8 + r8;
-#pragma unroll
-                for (int nb = 0; nb < 8; ++nb) {
-                    const uint32_t addr = smem_addr(vt + (nb >> 2) * kHalf) + swz(trow, (nb & 3) * 2 + (tile >> 1));
-                    uint32_t b0, b1, b2, b3;
-                    ldmatrix_x4_trans(addr, b0, b1, b2, b3);
-                    mma_16816<BF16>(acc[2 * nb], pa0, 0u, pa2, 0u, b0, b1);
-                    mma_16816<BF16>(acc[2 * nb + 1], pa0, 0u, pa2, 0u, b2, b3);
-                }
-            }
+            __syncwarp();      // every lane is done with this stage before lane 0 re-arms it
         }
-        __syncwarp();      // every lane is done with this stage before lane 0 re-arms it
     }
 
     const bool failed = dead || bad;
@@ -406,7 +450,8 @@ int attn_splits(int n, int kv_heads, long long max_len, long long total_len, int
     int sp = cap < 1 ? 1 : cap;
     if (total_len > 0 && g_knobs.attn_split_tokens <= 0) {
         const int floor_pages = 64 / page_size > 1 ? 64 / page_size : 1;
-        const long long slots = (long long)sms * (page_size <= 16 ? 6 : page_size <= 32 ? 4 : 2);   // resident one-warp CTAs
+        const long long slots = (long long)sms * (page_size <= 16 ? (g_knobs.attn_wide != 0 ? 5 : 6)
+                                                                   : page_size <= 32 ? 4 : 2);       // resident one-warp CTAs
         const long long units = ((total_len + page_size - 1) / page_size + n) * kv_heads;           // (page, head) units, rounded up
         const long long partial = (long long)n * kv_heads / 2;                                      // last splits are half full on average
         for (int waves = 1; waves <= 2; ++waves) {
@@ -534,12 +579,13 @@ int attention_common(const barqkv_pool_layout* pool, const void* k_pool, const v
     };
     cudaError_t le;
     // + 1024 bytes of slack to align the tiles to the swizzle period
-#define BARQKV_ATTN_LAUNCH(PS)                                                                                  \
-    le = is_bf16 ? launch(paged_decode_kernel<true, PS>, (size_t)AttnTile<PS>::kStages * AttnTile<PS>::kStage + 1024) \
-                 : launch(paged_decode_kernel<false, PS>, (size_t)AttnTile<PS>::kStages * AttnTile<PS>::kStage + 1024)
-    if (a.page_size == 16) { BARQKV_ATTN_LAUNCH(16); }
-    else if (a.page_size == 32) { BARQKV_ATTN_LAUNCH(32); }
-    else { BARQKV_ATTN_LAUNCH(64); }
+#define BARQKV_ATTN_LAUNCH(PS, W)                                                                                      \
+    le = is_bf16 ? launch(paged_decode_kernel<true, PS, W>, (size_t)AttnTile<PS, W>::kStages * AttnTile<PS, W>::kStage + 1024) \
+                 : launch(paged_decode_kernel<false, PS, W>, (size_t)AttnTile<PS, W>::kStages * AttnTile<PS, W>::kStage + 1024)
+    const bool wide = g_knobs.attn_wide != 0;
+    if (a.page_size == 16) { if (wide) { BARQKV_ATTN_LAUNCH(16, true); } else { BARQKV_ATTN_LAUNCH(16, false); } }
+    else if (a.page_size == 32) { if (wide) { BARQKV_ATTN_LAUNCH(32, true); } else { BARQKV_ATTN_LAUNCH(32, false); } }
+    else { if (wide) { BARQKV_ATTN_LAUNCH(64, true); } else { BARQKV_ATTN_LAUNCH(64, false); } }
 #undef BARQKV_ATTN_LAUNCH
     if (le != cudaSuccess) return fail_cuda("decode_attention: cudaFuncSetAttribute", le);
     cudaError_t ce = cudaGetLastError();

@@ -130,6 +130,12 @@ class BarqBlockTableCache(Cache):
                            torch.empty(shape, dtype=like.dtype, device=like.device)) for _ in range(2)]
         return self._bufs[layer_idx & 1]
 
+    def release_memory(self) -> None:
+        """Drop the page pool and the gather buffers now (the cache object sits in reference cycles with its
+        layers, so otherwise the memory would wait for the garbage collector)."""
+        self.store, self._bufs, self.slots = None, [], []
+        self._new = self._full = None
+
     def _reset_store(self) -> None:
         if self.store is not None and any(int(self.store.lengths[s]) for s in self.slots):
             for row in range(self.barqtrain_max_batch_size):

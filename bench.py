@@ -737,7 +737,7 @@ def run_micro(args):
     dtype = torch.bfloat16
     gen = torch.Generator(device=device).manual_seed(7)
     g = torch.Generator().manual_seed(CFG["seed"])
-    if args.micro in ("gather", "update", "update-layers", "attention"):
+    if args.micro in ("gather", "update", "update-layers", "attention", "decode-update"):
         if args.lengths == "loguniform":          # the 70B-shaped gather configuration: 32 sequences in [1k, 32k]
             import math
             u = torch.rand(32, generator=g, dtype=torch.float64)
@@ -829,6 +829,24 @@ def run_micro(args):
                 for _ in range(args.reps):
                     many.update_layers(new, full, k_all, k_all, outs, "HND", mode=args.mode)
             return launch, args.layers * args.reps, (full.total + B) * per_tok * args.layers * args.reps
+        if args.micro == "decode-update":
+            # a decode layer in one launch: the step's rows stored and attended by the same kernel
+            total = sum(lens)
+            k = torch.randn(total, H, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
+            if cache.lengths[slots[0]] == 0:
+                cache.append_step(slots, lens, [k], [k])
+            new = cache.begin_append(slots, [1] * B)     # every launch stores the same token again: same work each time
+            cache.end_append(new)
+            full = cache.begin_gather(slots)
+            q = torch.randn(B, H * args.group, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
+            out = torch.empty_like(q)
+            k1 = k[:B].contiguous()
+            cache.decode_update(0, full, k1, k1, q, out=out)       # sizes the workspace outside any capture
+
+            def launch():
+                for _ in range(args.reps):
+                    cache.decode_update(0, full, k1, k1, q, out=out)
+            return launch, args.reps, (full.total * 2 + 4 * B) * H * D * 2 * args.reps
         if args.micro == "attention":
             total = sum(lens)
             k = torch.randn(total, H, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
@@ -952,6 +970,8 @@ def run_extra(args):
         kwargs["all_layers"] = args.all_layers
     if args.workload == "decode-attn":
         kwargs["eager"] = args.eager
+    if args.workload == "churn":
+        kwargs["attend"] = args.attend
     if args.layers_override:
         kwargs["layers"] = args.layers_override
     if args.shard_heads:
@@ -993,8 +1013,9 @@ def run_generate(args):
 
     device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(device)
-    rows = inference.run_table(device=device, batch=args.gen_batch, layers=args.layers_override or 16)
-    print(json.dumps({"workload": "generate", "model": "seeded random-weight Llama: 16 layers, hidden 1024, 8 query / 2 KV "
+    layers = args.layers_override or 16
+    rows = inference.run_table(device=device, batch=args.gen_batch, layers=layers)
+    print(json.dumps({"workload": "generate", "model": f"seeded random-weight Llama: {layers} layers, hidden 1024, 8 query / 2 KV "
                       "heads of 128, vocabulary 32000, bf16", "batch": args.gen_batch,
                       "method": "warm-up runs, cuda_memory_snapshot(reset_peak=True), measured runs, peak snapshot; "
                                 "generation_overhead_mb = peak max_allocated - resident allocated",
@@ -1034,13 +1055,15 @@ def main():
     ap.add_argument("--min-seconds", type=float, default=1.0,
                     help="repeat the timed K-step region until this much device time has been measured")
     ap.add_argument("--gen-batch", type=int, default=1, help="--workload generate: sequences per generate() call")
+    ap.add_argument("--attend", action="store_true",
+                    help="--workload churn: every decode step also attends over the pages (graph of fused launches)")
     ap.add_argument("--no-legs", action="store_true", help="skip the short legs of the other configurations")
     ap.add_argument("--quick-legs", action="store_true", help="legs with fewer layers and steps (smoke runs)")
     ap.add_argument("--eager", action="store_true",
                     help="call update() per layer from Python every step instead of replaying a CUDA graph")
     ap.add_argument("--two-launches", action="store_true",
                     help="per layer call append() then gather() instead of the single update() launch")
-    ap.add_argument("--micro", choices=["gather", "update", "update-layers", "attention", "append-prefill", "append-decode", "append-layers", "append-legacy"],
+    ap.add_argument("--micro", choices=["gather", "update", "update-layers", "attention", "decode-update", "append-prefill", "append-decode", "append-layers", "append-legacy"],
                     help="time one kernel alone on a one-layer case instead of the full step")
     ap.add_argument("--mode", default="auto", choices=["auto", "vector", "bulk"])
     ap.add_argument("--layout", default="HND", choices=["HND", "NHD"])

@@ -503,8 +503,9 @@ int64_t barqkv_host_pending_changes(const barqkv_host_table* table);
 /*
  * Device side of the table, all caller-owned: table_dev (int32 [max_seqs, max_blocks], the copy the
  * kernels read), two step buffers of step_words int32 each (one for append descriptions, one for
- * gather descriptions) and pinned staging memory of staging_words int32, used as a ring of 8 slots
- * whose reuse is guarded by CUDA events.  May be called again with larger buffers.
+ * gather descriptions) and pinned staging memory of staging_words int32, used as a ring of
+ * staging_words / step_words slots (at least 2, at most 64) whose reuse is guarded by CUDA events: that
+ * is how many steps the host may run ahead of the device.  May be called again with larger buffers.
  */
 int barqkv_host_attach(barqkv_host_table* table, int32_t* table_dev, int32_t* step_dev_append, int32_t* step_dev_gather,
                        int64_t step_words, int32_t* staging_host, int64_t staging_words);
@@ -523,7 +524,7 @@ int barqkv_host_attach(barqkv_host_table* table, int32_t* table_dev, int32_t* st
  * gather of the step needs.  More changed entries than a staging slot holds (after bulk edits) go in
  * several uploads.
  * info: {total tokens, largest first, device address of the description, changed entries sent, host
- * address of the description (readable until eight more calls have been made), pages taken, copies +
+ * address of the description (readable until the staging ring comes round), pages taken, copies +
  * kernels enqueued, words sent}.  When not even the description fits the attached buffers the call
  * fails with BARQKV_E_LIMIT and info[7] holds the words needed.
  */

@@ -831,6 +831,20 @@ def test_continuous_batching_churn_at_full_width_reads_back_exactly(backend):
     assert res["extra"]["pages_peak"] >= res["extra"]["pages_resident"] > 0
 
 
+def test_continuous_batching_with_attention_from_a_graph_reads_back_exactly(backend):
+    """The churn configuration with every decode step run as recorded launches that store the token and attend
+    over the pages, the batch's rows re-pointed at the replacement sequences between replays
+    (``DecodeGraphs``): after 80 steps of releases and replacements every live sequence still gathers to
+    exactly the rows that were appended to it."""
+    from barqtrain_b200.benchmarks.workloads import churn
+
+    res = churn(1, 0, torch.device("cuda", 0), steps=80, warmup=2, layers=2, verify=True, attend=True,
+                sync=lambda: torch.cuda.synchronize())
+    assert res["verified"] is True
+    assert res["extra"]["sequences_released"] > 100
+    assert res["launches"] >= 80 * 2
+
+
 @pytest.mark.parametrize("dtype_name", ["fp32", "fp16", "bf16"])
 def test_rope_fused_into_append_against_the_reference_helper(backend, golden_dir, dtype_name):
     """A prefill appended with ``rope=(cos, sin)`` leaves in the pages exactly the K rows the reference's
@@ -1069,7 +1083,8 @@ def test_table_changes_beyond_one_staging_slot_go_in_several_uploads(backend):
     staging = torch.zeros(8 * small, dtype=torch.int32).pin_memory()
     assert backend.lib.barqkv_host_attach(cache._host, cache.table_dev.data_ptr(), dev[0].data_ptr(), dev[1].data_ptr(),
                                           small, staging.data_ptr(), staging.numel()) == 0
-    cache._step_dev = dev
+    cache._step_dev, cache._staging = dev, staging
+    cache._staging_np, cache._staging_ptr = staging.numpy(), staging.data_ptr()
     cache._tables.clear()
     k = S.randn(g, (sum(lens), H, D), dtype).to(DEV)
     batch = cache.begin_append(slots, lens)                      # 13 + 10 + 6 = 29 new table entries: 8 uploads

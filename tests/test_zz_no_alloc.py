@@ -72,9 +72,17 @@ def test_gather_noalloc_matches_gather_on_two_calls_in_a_row():
         assert torch.equal(got_v.view(view), want_v.view(view))
         return total
 
-    # first call on this device: performs the one-time address look-up of the built-in scratch
+    # First call on this device: performs the one-time address look-up of the built-in scratch.  The library's
+    # device code is loaded already (the appends above ran its kernels), so even this call must not take device
+    # memory: the array it uses came with the code image.  Output tensors are made before the reading.
+    warm = cache.gather(0, cache.begin_gather(slots), "HND", mode="bulk")
+    spare = [torch.full_like(warm[0], float("nan")) for _ in range(2)]
+    del warm, spare                                        # torch keeps the blocks cached for the calls below
+    torch.cuda.synchronize(dev)
+    free_before_first = torch.cuda.mem_get_info(dev)[0]
     assert both(slots, "HND", work_slot=3) == sum(lens)
     free_after_first = torch.cuda.mem_get_info(dev)[0]
+    assert free_after_first >= free_before_first - (1 << 20)
     # second call, same slot, a different and smaller batch in another layout: leftovers would corrupt it
     assert both([slots[4], slots[0], slots[2]], "NHD", work_slot=3) == 1290 + 700 + 1
     assert both(slots, "HND", work_slot=31) == sum(lens)
