@@ -1172,7 +1172,8 @@ struct Knobs {
     int attn_promotion = -1;
     int attn_split_tokens = 0;
     int append_bulk = -1;        // -1: page-sized appends go through the copy engine; 0: always the row kernel
-    int attn_wide = -1;          // -1: decode attention updates its softmax state every 32 tokens; 0: every 16
+    int attn_wide = -1;          // decode attention updates its softmax state every 32 tokens (1) or 16 (0);
+                                 // -1: 32 for pages of 32 and 64, 16 for pages of 16
 };
 #ifdef BARQKV_TUNING
 Knobs g_knobs;

@@ -450,7 +450,7 @@ int attn_splits(int n, int kv_heads, long long max_len, long long total_len, int
     int sp = cap < 1 ? 1 : cap;
     if (total_len > 0 && g_knobs.attn_split_tokens <= 0) {
         const int floor_pages = 64 / page_size > 1 ? 64 / page_size : 1;
-        const long long slots = (long long)sms * (page_size <= 16 ? (g_knobs.attn_wide != 0 ? 5 : 6)
+        const long long slots = (long long)sms * (page_size <= 16 ? (g_knobs.attn_wide > 0 ? 5 : 6)
                                                                    : page_size <= 32 ? 4 : 2);       // resident one-warp CTAs
         const long long units = ((total_len + page_size - 1) / page_size + n) * kv_heads;           // (page, head) units, rounded up
         const long long partial = (long long)n * kv_heads / 2;                                      // last splits are half full on average
@@ -500,7 +500,7 @@ int attention_common(const barqkv_pool_layout* pool, const void* k_pool, const v
                      void* out, int64_t out_seq_stride, int64_t out_head_stride,
                      int32_t num_q_heads, float softmax_scale, int32_t is_bf16, int64_t max_len,
                      int64_t total_len,
-                     void* workspace, int64_t workspace_bytes, int32_t flags, int32_t* status, barqkv_stream_t stream) {
+                     void* workspace, int64_t workspace_bytes, int32_t flags, int32_t* status, barqkv_stream_t stream_) {
     if (int rc = check_pool(pool)) return rc;
     if (flags & ~BARQKV_FLAG_DESC_STABLE) return fail(BARQKV_E_INVALID, "decode_attention: unknown flag");
     if (n < 0) return fail(BARQKV_E_INVALID, "decode_attention: negative batch size");
@@ -568,7 +568,7 @@ int attention_common(const barqkv_pool_layout* pool, const void* k_pool, const v
     if (!make_pool_map(&map_k, k_pool, pool) || !make_pool_map(&map_v, v_pool, pool))
         return fail(BARQKV_E_LAUNCH, "decode_attention: could not describe the pools to the copy engine");
 
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaStream_t st = static_cast<cudaStream_t>(stream_);
     const dim3 grid((unsigned)a.splits, (unsigned)a.kv_heads, (unsigned)n);
     auto launch = [&](auto kernel, size_t smem) -> cudaError_t {
         if (smem > 48 * 1024) {
@@ -582,7 +582,8 @@ int attention_common(const barqkv_pool_layout* pool, const void* k_pool, const v
 #define BARQKV_ATTN_LAUNCH(PS, W)                                                                                      \
     le = is_bf16 ? launch(paged_decode_kernel<true, PS, W>, (size_t)AttnTile<PS, W>::kStages * AttnTile<PS, W>::kStage + 1024) \
                  : launch(paged_decode_kernel<false, PS, W>, (size_t)AttnTile<PS, W>::kStages * AttnTile<PS, W>::kStage + 1024)
-    const bool wide = g_knobs.attn_wide != 0;
+    // 32-token softmax blocks pay for pages of 32 and 64; pages of 16 would need a fifth ring stage for them
+    const bool wide = g_knobs.attn_wide >= 0 ? g_knobs.attn_wide != 0 : a.page_size >= 32;
     if (a.page_size == 16) { if (wide) { BARQKV_ATTN_LAUNCH(16, true); } else { BARQKV_ATTN_LAUNCH(16, false); } }
     else if (a.page_size == 32) { if (wide) { BARQKV_ATTN_LAUNCH(32, true); } else { BARQKV_ATTN_LAUNCH(32, false); } }
     else { if (wide) { BARQKV_ATTN_LAUNCH(64, true); } else { BARQKV_ATTN_LAUNCH(64, false); } }

@@ -29,7 +29,7 @@ extern "C" {
 #define BARQKV_KNOB_ATTN_L2_PROMOTION 10 /* decode attention: L2 promotion of the page loads. 0 none, 1 128 B, 2 256 B (-1 = default) */
 #define BARQKV_KNOB_ATTN_SPLIT_TOKENS 11 /* decode attention: tokens per split before adapting to the batch (0 = default 512) */
 #define BARQKV_KNOB_APPEND_BULK 12       /* 0: appends always use the row kernel (-1 = default: copy engine for page-sized appends) */
-#define BARQKV_KNOB_ATTN_WIDE 13         /* 0: decode attention updates its softmax state every 16 tokens (-1 = default: every 32) */
+#define BARQKV_KNOB_ATTN_WIDE 13         /* decode attention updates its softmax state every 32 tokens (1) or 16 (0); -1 = default: 32 for pages of 32 / 64 */
 
 int barqkv_set_tuning(int32_t knob, int32_t value);
 
