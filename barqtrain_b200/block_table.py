@@ -292,7 +292,10 @@ class BlockTableKVCache:
     def slot(self, seq_id) -> int:
         return self._slot_of[seq_id]
 
-    def __del__(self):
+    def close(self) -> None:
+        """Give the pools and every other buffer back now.  The cache object sits in reference cycles (its page
+        views, its allocator), so without this its device memory waits for the garbage collector; after it the
+        object must not be used any more."""
         host, backend = getattr(self, "_host", None), getattr(self, "backend", None)
         if host and backend is not None:
             try:
@@ -301,6 +304,14 @@ class BlockTableKVCache:
                 pass
             backend.lib.barqkv_host_destroy(host)
             self._host = None
+            if getattr(self, "allocator", None) is not None:
+                self.allocator._h = None
+        self.pools = self.table_dev = self._attn_ws = None
+        self._step_dev, self._staging, self._staging_np = [], None, None
+        self._k_ptr, self._v_ptr = [], []
+
+    def __del__(self):
+        self.close()
 
     def _raise_host(self, rc: int):
         msg = self.backend.last_error()

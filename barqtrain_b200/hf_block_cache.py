@@ -133,6 +133,8 @@ class BarqBlockTableCache(Cache):
     def release_memory(self) -> None:
         """Drop the page pool and the gather buffers now (the cache object sits in reference cycles with its
         layers, so otherwise the memory would wait for the garbage collector)."""
+        if self.store is not None:
+            self.store.close()
         self.store, self._bufs, self.slots = None, [], []
         self._new = self._full = None
 

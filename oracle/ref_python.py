@@ -6,32 +6,33 @@ product package.
 The reference's CPU implementation of the path is pure Python: ``BarqPagedKVCacheLayer`` with
 ``_python_append`` and ``current_tensors`` in ``python/barqtrain/kv_cache.py`` (37-194), plus the loader
 it imports (``python/barqtrain/_ffi.py``).  ``build(reference_root)`` byte-compiles those two files
-*where they lie* in a reference checkout into ``oracle/_ref/barqtrain_ref_py/barqtrain/*.pyc`` - the
+*where they lie* in a reference checkout into ``oracle/_ref/barqtrain_ref_py_<tag>/*.code`` (marshalled
+code objects; not named ``.pyc``, which tools that copy a working tree tend to leave behind) - the
 Python counterpart of compiling a C reference into a shared object.  No reference source is copied and
 the output directory is not under version control; it travels with the working tree to machines that
-have no checkout, which must run the same Python minor version that compiled it (the file name carries
+have no checkout, which must run the same Python minor version that compiled it (the folder name carries
 it).
 
-``load()`` imports ``barqtrain.kv_cache`` from those files with the reference's native backend
-disabled (``BARQTRAIN_AUTO_BUILD=0``, so ``append`` takes ``_python_append``, kv_cache.py:75-91), or
-returns ``None`` when they are not there.  The package is loaded as a bare namespace: the reference's
-``barqtrain/__init__.py``, which pulls in its training stack, is not part of the path and is not
-compiled.
+``load()`` executes those code objects as the modules ``barqtrain._ffi`` and ``barqtrain.kv_cache`` with the
+reference's native backend disabled (``BARQTRAIN_AUTO_BUILD=0``, so ``append`` takes ``_python_append``,
+kv_cache.py:75-91), or returns ``None`` when they are not there.  ``barqtrain`` itself is a bare namespace
+module: the reference's ``barqtrain/__init__.py``, which pulls in its training stack, is not part of the
+path and is not compiled.
 """
 
 from __future__ import annotations
 
-import importlib
+import marshal
 import os
-import py_compile
 import sys
+import types
 from pathlib import Path
 from typing import Optional
 
 _HERE = Path(__file__).resolve().parent
 _TAG = f"py{sys.version_info.major}{sys.version_info.minor}"
 _OUT_DIR = _HERE / "_ref" / f"barqtrain_ref_py_{_TAG}"
-_FILES = ("kv_cache.py", "_ffi.py")
+_FILES = ("_ffi.py", "kv_cache.py")            # in import order
 _MODULE = None
 
 
@@ -44,8 +45,12 @@ def default_reference_root() -> Optional[Path]:
     return beside if (beside / "python" / "barqtrain" / "kv_cache.py").exists() else None
 
 
+def _out(name: str) -> Path:
+    return _OUT_DIR / (Path(name).stem + ".code")
+
+
 def built() -> bool:
-    return all((_OUT_DIR / "barqtrain" / (Path(f).stem + ".pyc")).exists() for f in _FILES)
+    return all(_out(f).exists() for f in _FILES)
 
 
 def build(reference_root=None, force: bool = False) -> Optional[Path]:
@@ -54,15 +59,13 @@ def build(reference_root=None, force: bool = False) -> Optional[Path]:
     root = Path(reference_root) if reference_root else default_reference_root()
     if root is None or not (root / "python" / "barqtrain" / "kv_cache.py").exists():
         return _OUT_DIR if built() else None
-    pkg = _OUT_DIR / "barqtrain"
-    pkg.mkdir(parents=True, exist_ok=True)
+    _OUT_DIR.mkdir(parents=True, exist_ok=True)
     for name in _FILES:
         src = root / "python" / "barqtrain" / name
-        out = pkg / (Path(name).stem + ".pyc")
+        out = _out(name)
         if force or not out.exists() or out.stat().st_mtime < src.stat().st_mtime:
-            # unchecked-hash pyc: valid wherever the file goes, whatever the source's timestamp was
-            py_compile.compile(str(src), cfile=str(out), dfile=f"<reference>/python/barqtrain/{name}", doraise=True,
-                               invalidation_mode=py_compile.PycInvalidationMode.UNCHECKED_HASH)
+            code = compile(src.read_bytes(), f"<reference>/python/barqtrain/{name}", "exec", dont_inherit=True)
+            out.write_bytes(marshal.dumps(code))
     return _OUT_DIR
 
 
@@ -73,12 +76,21 @@ def load():
         return _MODULE
     if not built():
         return None
-    if "barqtrain" in sys.modules and not str(getattr(sys.modules["barqtrain"], "__path__", "")).count(str(_OUT_DIR)):
+    if "barqtrain" in sys.modules and not getattr(sys.modules["barqtrain"], "_barq_reference_bytecode", False):
         raise RuntimeError("another `barqtrain` package is already imported in this process")
     os.environ["BARQTRAIN_AUTO_BUILD"] = "0"         # no native build: append takes the reference's CPU loop
-    sys.path.insert(0, str(_OUT_DIR))
-    try:
-        _MODULE = importlib.import_module("barqtrain.kv_cache")
-    finally:
-        sys.path.remove(str(_OUT_DIR))
+    package = types.ModuleType("barqtrain")
+    package.__path__ = []                            # a package with nothing to find on disk
+    package._barq_reference_bytecode = True
+    sys.modules["barqtrain"] = package
+    module = None
+    for name in _FILES:
+        stem = Path(name).stem
+        module = types.ModuleType(f"barqtrain.{stem}")
+        module.__file__ = str(_out(name))
+        module.__package__ = "barqtrain"
+        sys.modules[module.__name__] = module
+        setattr(package, stem, module)
+        exec(marshal.loads(_out(name).read_bytes()), module.__dict__)
+    _MODULE = module
     return _MODULE
