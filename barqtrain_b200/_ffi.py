@@ -69,7 +69,7 @@ EXPORTS = ("barqkv_version", "barqkv_last_error", "barqkv_sm_count", "barqkv_lau
            "barqkv_host_attach", "barqkv_host_begin", "barqkv_paged_decode_update")
 # experiment knobs: only a library built with -DBARQKV_TUNING exports barqkv_set_tuning (include/barqkv_experimental.h)
 KNOBS = {"stages": 1, "ctas": 2, "vctas": 3, "interleave": 4, "group": 5, "static": 6, "pdl": 7, "fixed": 8, "tensor_store": 9,
-         "attn_promotion": 10, "attn_split": 11, "append_bulk": 12, "attn_wide": 13}
+         "attn_promotion": 10, "attn_split": 11, "append_bulk": 12, "attn_wide": 13, "layer_overlap": 14}
 STATIC_WORK_SLOTS = 32
 
 
@@ -233,7 +233,7 @@ class CudaBackend:
             raise BarqKVError("device-side guard: " + ", ".join(names))
 
     def work_words(self, device):
-        """Device int32[4] scratch of the bulk kernels' page hand-out, one per (device, current stream)."""
+        """Device int32[8] scratch of the bulk kernels' page hand-out (four counter pairs), one per (device, current stream)."""
         import torch
 
         device = torch.device(device)
@@ -241,21 +241,21 @@ class CudaBackend:
         key = (index, self._stream(torch.device("cuda", index)))
         words = self._work.get(key)
         if words is None:
-            # two counter pairs: single launches use the first, barqkv_update_layers alternates between both
-            words = torch.zeros(4, dtype=torch.int32, device=torch.device("cuda", index))
+            # four counter pairs: single launches alternate between the first two, barqkv_update_layers uses all
+            words = torch.zeros(8, dtype=torch.int32, device=torch.device("cuda", index))
             self._work[key] = words
         return words
 
     def take_work(self, index: int, stream: int) -> int:
-        """Address of the counter pair the next bulk launch on ``stream`` should use.  The stream's four
-        words hold two pairs handed out in turn, so that two launches adjacent in the stream never share
+        """Address of the counter pair the next bulk launch on ``stream`` should use.  The first four of
+        the stream's words hold two pairs handed out in turn, so that two launches adjacent in the stream never share
         one (a launch flagged ``FLAG_DESC_STABLE`` takes its first pages while its predecessor still runs)."""
         import torch
 
         key = (index, stream)
         words = self._work.get(key)
         if words is None:
-            words = torch.zeros(4, dtype=torch.int32, device=torch.device("cuda", index))
+            words = torch.zeros(8, dtype=torch.int32, device=torch.device("cuda", index))
             self._work[key] = words
         turn = self._work_turn.get(key, 0)
         self._work_turn[key] = turn ^ 1

@@ -22,6 +22,7 @@ All device work goes through ``libbarqkv.so``; there is no CPU path.
 from __future__ import annotations
 
 import ctypes
+import gc
 from dataclasses import dataclass
 
 import numpy as np
@@ -200,6 +201,27 @@ class _Descriptor:
         return self._slots
 
 
+# Native host tables whose owner is gone.  Destroying one waits for its last uploads and frees pinned memory -
+# neither is allowed while a stream of this thread records a CUDA graph, and the garbage collector may well run
+# a cache's finaliser in the middle of a recording - so the handles wait here until no recording is under way.
+_PENDING_DESTROY: list = []
+
+
+def _destroy_pending() -> None:
+    try:
+        if torch.cuda.is_available() and torch.cuda.is_current_stream_capturing():
+            return
+    except Exception:  # noqa: BLE001 - interpreter or context already going down
+        return
+    while _PENDING_DESTROY:
+        backend, host, device = _PENDING_DESTROY.pop()
+        try:
+            torch.cuda.synchronize(device)                # uploads out of the staging memory must have run
+        except Exception:  # noqa: BLE001
+            pass
+        backend.lib.barqkv_host_destroy(host)
+
+
 class BlockTableKVCache:
     """Paged K/V for ``num_layers`` layers over a shared block table.
 
@@ -240,6 +262,7 @@ class BlockTableKVCache:
         self._table = _ffi.BlockTable(self.table_dev.data_ptr(), None, max_seqs, max_blocks_per_seq, 0, 0)
         self.lengths = np.zeros(max_seqs, dtype=np.int64)      # tokens held, per slot
         self._page_count = np.zeros(max_seqs, dtype=np.int64)  # pages owned, per slot
+        _destroy_pending()
         self._host = _create_host_table(self.backend, num_pages, free_order, seed, max_seqs, max_blocks_per_seq, page_size,
                                         self.table_host.data_ptr(), self.lengths.ctypes.data,
                                         self._page_count.ctypes.data)
@@ -298,14 +321,11 @@ class BlockTableKVCache:
         object must not be used any more."""
         host, backend = getattr(self, "_host", None), getattr(self, "backend", None)
         if host and backend is not None:
-            try:
-                torch.cuda.synchronize(self.device)       # uploads out of the staging memory must have run
-            except Exception:  # noqa: BLE001 - interpreter or context already going down
-                pass
-            backend.lib.barqkv_host_destroy(host)
             self._host = None
             if getattr(self, "allocator", None) is not None:
                 self.allocator._h = None
+            _PENDING_DESTROY.append((backend, host, self.device))
+            _destroy_pending()
         self.pools = self.table_dev = self._attn_ws = None
         self._step_dev, self._staging, self._staging_np = [], None, None
         self._k_ptr, self._v_ptr = [], []
@@ -1101,6 +1121,8 @@ class DecodeStepGraph:
         c = self.cache
         if self.steps == 0:
             raise RuntimeError("run one eager step() before record(): the first launch sets kernel attributes")
+        gc.collect()                                     # finalisers of dead caches run now, not inside the recording
+        _destroy_pending()
         torch.cuda.synchronize(c.device)
         self._new.used_at = self._full.used_at = -1      # the first recorded launch waits for whatever precedes a replay
         with torch.cuda.stream(self.stream):

@@ -1172,6 +1172,7 @@ struct Knobs {
     int attn_promotion = -1;
     int attn_split_tokens = 0;
     int append_bulk = -1;        // -1: page-sized appends go through the copy engine; 0: always the row kernel
+    int layer_overlap = 1;       // update_layers issues odd layers on a second stream (0: one stream, one chain)
     int attn_wide = -1;          // decode attention updates its softmax state every 32 tokens (1) or 16 (0);
                                  // -1: 32 for pages of 32 and 64, 16 for pages of 16
 };
@@ -1186,6 +1187,12 @@ struct DeviceInfo {
     int smem_optin = 0;
     std::atomic<bool> bulk_attr_set{false};     // cudaFuncSetAttribute done for the bulk gather / bulk append
     std::atomic<bool> append_attr_set{false};
+    // Second stream of barqkv_update_layers (odd layers), with the events that fork it from and join it to the
+    // caller's stream.  Made by the first call that is not being captured into a graph; `lane_mu` serialises
+    // the callers that issue through it.
+    std::mutex lane_mu;
+    cudaStream_t lane = nullptr;
+    cudaEvent_t lane_fork = nullptr, lane_join = nullptr;
 };
 DeviceInfo g_dev[64];
 std::once_flag g_dev_once[64];
@@ -1203,6 +1210,32 @@ DeviceInfo* device_info() {
         d->sms = sms;
     });
     return d->sms > 0 ? d : nullptr;
+}
+
+// The device's second stream for barqkv_update_layers, or null when it does not exist yet and `caller` is
+// being captured (streams and events are not created in the middle of a capture).  Call with lane_mu held.
+bool second_stream(DeviceInfo* d, cudaStream_t caller) {
+    if (d->lane) return true;
+    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(caller, &capturing) != cudaSuccess || capturing != cudaStreamCaptureStatusNone) {
+        cudaGetLastError();
+        return false;
+    }
+    cudaStream_t st = nullptr;
+    cudaEvent_t fork = nullptr, join = nullptr;
+    if (cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&fork, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&join, cudaEventDisableTiming) != cudaSuccess) {
+        cudaGetLastError();
+        if (join) cudaEventDestroy(join);
+        if (fork) cudaEventDestroy(fork);
+        if (st) cudaStreamDestroy(st);
+        return false;
+    }
+    d->lane_fork = fork;
+    d->lane_join = join;
+    d->lane = st;
+    return true;
 }
 
 inline bool aligned(const void* p, int a) { return (reinterpret_cast<uintptr_t>(p) % (uintptr_t)a) == 0; }
@@ -1391,6 +1424,7 @@ int barqkv_set_tuning(int32_t knob, int32_t value) {
         case BARQKV_KNOB_ATTN_SPLIT_TOKENS: g_knobs.attn_split_tokens = value; return 0;
         case BARQKV_KNOB_APPEND_BULK: g_knobs.append_bulk = value; return 0;
         case BARQKV_KNOB_ATTN_WIDE: g_knobs.attn_wide = value; return 0;
+        case BARQKV_KNOB_LAYER_OVERLAP: g_knobs.layer_overlap = value; return 0;
         default: return fail(BARQKV_E_INVALID, "set_tuning: unknown knob");
     }
 }
@@ -2034,6 +2068,39 @@ int barqkv_update_layers(const barqkv_pool_layout* pool, void* k_pool, void* v_p
     mode &= ~BARQKV_FLAG_DESC_STABLE;      // the first layer waits for whatever precedes it; the rest are chained here
     const bool try_fused = total_new_tokens > 0 && total_new_tokens <= (long long)n * pool->page_size;
     bool fused_ok = try_fused;
+
+    // Two layers next to one another touch nothing in common when they write to different outputs: each reads
+    // and writes its own layer's pools.  Even layers are then issued on the caller's stream and odd layers on a
+    // second stream forked from it, each stream a chain of programmatic dependents (layer l behind layer l - 2,
+    // the layer whose output buffer it may reuse), and the two chains run side by side: the first blocks of one
+    // layer take the SMs that the last blocks of the layer before leave, so no layer pays for an empty machine
+    // at its start or its end.  An even and an odd layer share an output only if num_out is odd and smaller than
+    // `layers`; such calls, and calls whose outputs are not all distinct, keep to one stream.
+    cudaStream_t main_stream = static_cast<cudaStream_t>(stream);
+    DeviceInfo* dev = device_info();
+    bool overlap = try_fused && layers >= 2 && work && dev && g_knobs.layer_overlap != 0 && g_knobs.pdl != 0 &&
+                   (num_out % 2 == 0 || num_out >= layers) && num_out <= 1024;
+    for (int i = 0; overlap && i < num_out; ++i)
+        for (int j = 0; j < i; ++j)
+            if (k_out[i] == k_out[j] || v_out[i] == v_out[j] || k_out[i] == v_out[j] || v_out[i] == k_out[j]) overlap = false;
+    std::unique_lock<std::mutex> lane_lock;
+    if (overlap) {
+        lane_lock = std::unique_lock<std::mutex>(dev->lane_mu);
+        overlap = second_stream(dev, main_stream) &&
+                  cudaEventRecord(dev->lane_fork, main_stream) == cudaSuccess &&
+                  cudaStreamWaitEvent(dev->lane, dev->lane_fork, 0) == cudaSuccess;
+        if (!overlap) {
+            cudaGetLastError();
+            lane_lock.unlock();
+        }
+    }
+    // whatever happens below, the second stream is joined back before the call returns
+    auto done = [&](int rc) {
+        if (overlap && (cudaEventRecord(dev->lane_join, dev->lane) != cudaSuccess ||
+                        cudaStreamWaitEvent(main_stream, dev->lane_join, 0) != cudaSuccess) && rc == 0)
+            rc = fail(BARQKV_E_LAUNCH, "update_layers: could not join the second stream");
+        return rc;
+    };
     for (int l = 0; l < layers; ++l) {
         unsigned char* kp = static_cast<unsigned char*>(k_pool) + (long long)l * pool_layer_stride * e;
         unsigned char* vp = static_cast<unsigned char*>(v_pool) + (long long)l * pool_layer_stride * e;
@@ -2042,31 +2109,34 @@ int barqkv_update_layers(const barqkv_pool_layout* pool, void* k_pool, void* v_p
         void* ko = k_out[l % num_out];
         void* vo = v_out[l % num_out];
         if (fused_ok) {
-            // Layers alternate between the two counter pairs of `work`: layer l + 1 takes its first pages while
-            // layer l is still handing out its last ones.  From the second layer on the launch is a programmatic
-            // dependent of the layer before, whose batch description it shares.
+            // Launches that may be on the device together never share a counter pair of `work`: a layer takes its
+            // first pages while the layer before it in its stream is still handing out its last ones, and the two
+            // streams use different pairs.  Within a stream each launch is a programmatic dependent of the one
+            // before, whose batch description it shares.
             const FusedRows fused = {kn, vn, new_rows, cu_new, tokens_per_entry};
             LaunchOpts opts;
-            opts.after_own_kernel = l > 0;
+            opts.after_own_kernel = overlap ? l >= 2 : l > 0;
+            int32_t* pair = !work ? nullptr : work + 2 * (overlap ? (l & 3) : (l & 1));
             const int rc = gather_common(pool, kp, vp, table, seq_start, cu_out, n, total_tokens_hint, ko, vo, out_rows, mode,
-                                         status, work ? work + 2 * (l & 1) : nullptr, stream, &fused, nullptr, opts);
+                                         status, pair, overlap && (l & 1) ? static_cast<barqkv_stream_t>(dev->lane) : stream,
+                                         &fused, nullptr, opts);
             if (rc == 0) continue;
-            if (rc != kNotFusable || l > 0) return rc;
+            if (rc != kNotFusable || l > 0) return done(rc);
             fused_ok = false;
         }
         if (!seq_lens_after)
-            return fail(BARQKV_E_INVALID, "update_layers: this call cannot run as one launch per layer; pass seq_lens_after "
-                                          "(lengths after the append, device int32[n]) so that it can run as append + gather");
+            return done(fail(BARQKV_E_INVALID, "update_layers: this call cannot run as one launch per layer; pass seq_lens_after "
+                                               "(lengths after the append, device int32[n]) so that it can run as append + gather"));
         if (total_new_tokens) {
             if (int rc = barqkv_append(pool, kp, vp, table, seq_start, cu_new, n, tokens_per_entry, total_new_tokens, kn, vn,
                                        new_rows, status, work, 0, stream))
-                return rc;
+                return done(rc);
         }
         if (int rc = barqkv_gather(pool, kp, vp, table, seq_lens_after, cu_out, n, total_tokens_hint, ko, vo, out_rows,
                                    mode & ~BARQKV_FLAG_DESC_STABLE, status, work, stream))
-            return rc;
+            return done(rc);
     }
-    return 0;
+    return done(0);
 }
 
 int barqkv_gather_wait_selftest(const barqkv_pool_layout* pool, const void* k_pool, const void* v_pool,

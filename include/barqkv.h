@@ -24,7 +24,7 @@
 extern "C" {
 #endif
 
-#define BARQKV_VERSION 102 /* major*100 + minor */
+#define BARQKV_VERSION 103 /* major*100 + minor */
 
 /* host-side return codes */
 #define BARQKV_OK 0
@@ -306,12 +306,19 @@ int barqkv_update(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,
  * Replaces `layers` calls of the reference layer's update() (python/barqtrain/kv_cache.py:135-142), each
  * of which costs two kernel launches and two device synchronisations there
  * (csrc/kernels/paged_kv_cache.cu:93,104-127, kv_cache.py:150-153).  Here the host pays one call, and
- * from the second layer on each launch is a programmatic dependent of the one before: because it reads
- * the same, unchanged description, its prologue (page counts, first hand-out, first block-table
- * look-ups) runs while the previous layer's last copies drain, and only its first copy waits for that
- * layer to finish.  work: device int32[4] scratch, zero before its first use (two counter pairs that
- * consecutive layers alternate); the kernels leave it zero.  For callers that have every layer's new rows
- * at hand (a recorded decode step, cache import); results equal `layers` calls of barqkv_update.
+ * the launches are chained as programmatic dependents: because a layer reads the same, unchanged
+ * description as the one before, its prologue (page counts, first hand-out, first block-table look-ups)
+ * runs while the earlier layer's last copies drain, and only its first copy waits for that layer to finish.
+ * Layers next to one another are independent when they write to different outputs (each touches its own
+ * layer's pools only).  With an even num_out (or num_out >= layers) and pairwise distinct, non-overlapping
+ * outputs, even layers are therefore issued on `stream` and odd layers on a second, library-owned stream
+ * that is forked from `stream` at the start of the call and joined back to it before the call returns
+ * (events only; also inside a stream capture): layer l is ordered behind layer l - 2, the layer whose
+ * output it overwrites, and runs beside layer l - 1.  Work issued to `stream` after the call is ordered
+ * behind every layer.  Other calls keep all layers on `stream`, each behind the one before.
+ * work: device int32[8] scratch, zero before its first use (four counter pairs, so that launches that can be
+ * on the device together never share one); the kernels leave it zero.  For callers that have every layer's
+ * new rows at hand (a recorded decode step, cache import); results equal `layers` calls of barqkv_update.
  */
 int barqkv_update_layers(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,
                          int32_t layers, int64_t pool_layer_stride,

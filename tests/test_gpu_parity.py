@@ -368,6 +368,57 @@ def test_all_layers_in_one_launch_equals_per_layer_appends(backend):
     one.check_device_status()
 
 
+@pytest.mark.parametrize("num_out", [1, 2, 3, 4, 6])
+def test_update_of_all_layers_in_one_call_for_any_number_of_outputs(backend, num_out):
+    """``update_layers``: with an even number of outputs (or one per layer) odd layers run on the library's
+    second stream beside the even ones; with an odd number, or a single pair, all stay on one stream.  Whatever
+    the schedule, the pools and the outputs of the last ``num_out`` layers must equal per-layer ``update``
+    calls on a twin cache, and work queued on the caller's stream afterwards must see every layer done."""
+    from barqtrain_b200 import BlockTableKVCache
+
+    L, H, D, ps, dtype = 6, 2, 128, 16, torch.float16
+    lens = [500, 31, 16, 1200, 257, 64, 900]
+    n = len(lens)
+    g = torch.Generator().manual_seed(num_out)
+    pages = sum(-(-(x + 8) // ps) for x in lens)
+    order = torch.randperm(pages, generator=g).tolist()
+
+    def make():
+        c = BlockTableKVCache(L, H, D, page_size=ps, num_pages=pages, max_seqs=n, max_blocks_per_seq=-(-(max(lens) + 8) // ps),
+                              dtype=dtype, device=DEV, free_order=order)
+        return c, [c.open(i) for i in range(n)]
+
+    fast, fs = make()
+    slow, ss = make()
+    k0 = [S.randn(g, (sum(lens), H, D), dtype).to(DEV) for _ in range(L)]
+    fast.append_step(fs, lens, k0, k0[::-1])
+    slow.append_step(ss, lens, k0, k0[::-1])
+    cap = sum(lens) + 8 * n
+    outs = [(torch.zeros(H, cap, D, dtype=dtype, device=DEV), torch.zeros(H, cap, D, dtype=dtype, device=DEV))
+            for _ in range(num_out)]
+    for step in range(5):
+        k = S.randn(g, (L, n, H, D), dtype).to(DEV)
+        v = S.randn(g, (L, n, H, D), dtype).to(DEV)
+        new = fast.begin_append(fs, [1] * n)
+        fast.end_append(new)
+        full = fast.begin_gather(fs)
+        before = backend.launches
+        fast.update_layers(new, full, k, v, outs, "HND", tokens_hint=cap)
+        assert backend.launches - before == L
+        # copies queued behind the call on the same stream: they must read finished outputs
+        snap = [(ko.clone(), vo.clone()) for ko, vo in outs]
+        slow.append_step(ss, [1] * n, list(k.unbind(0)), list(v.unbind(0)))
+        gb = slow.begin_gather(ss)
+        for layer in range(L - min(num_out, L), L):
+            want_k, want_v = slow.gather(layer, gb, "HND")
+            got_k, got_v = snap[layer % num_out]
+            assert torch.equal(S.bits_dev(got_k[:, :gb.total]), S.bits_dev(want_k)), (step, layer)
+            assert torch.equal(S.bits_dev(got_v[:, :gb.total]), S.bits_dev(want_v)), (step, layer)
+        assert torch.equal(S.bits_dev(fast.pools), S.bits_dev(slow.pools)), step
+    fast.check_device_status()
+    assert backend.read_status(DEV) == 0
+
+
 @pytest.mark.parametrize("H", [8, 1])
 def test_decode_step_graph_replays_what_eager_steps_compute(backend, H):
     """A decode step recorded into a CUDA graph: every replay must leave the same pools and gathered
