@@ -1173,6 +1173,7 @@ struct Knobs {
     int attn_split_tokens = 0;
     int append_bulk = -1;        // -1: page-sized appends go through the copy engine; 0: always the row kernel
     int layer_overlap = 1;       // update_layers issues odd layers on a second stream (0: one stream, one chain)
+    int attn_page_box = 1;       // decode attention loads a head's page with one copy instruction (0: two half-page boxes)
     int attn_wide = -1;          // decode attention updates its softmax state every 32 tokens (1) or 16 (0);
                                  // -1: 32 for pages of 32 and 64, 16 for pages of 16
 };
@@ -1425,6 +1426,7 @@ int barqkv_set_tuning(int32_t knob, int32_t value) {
         case BARQKV_KNOB_APPEND_BULK: g_knobs.append_bulk = value; return 0;
         case BARQKV_KNOB_ATTN_WIDE: g_knobs.attn_wide = value; return 0;
         case BARQKV_KNOB_LAYER_OVERLAP: g_knobs.layer_overlap = value; return 0;
+        case BARQKV_KNOB_ATTN_PAGE_BOX: g_knobs.attn_page_box = value; return 0;
         default: return fail(BARQKV_E_INVALID, "set_tuning: unknown knob");
     }
 }

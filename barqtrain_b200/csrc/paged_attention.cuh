@@ -6,8 +6,9 @@
 // form the rows of one 16-row MMA tile.
 //
 //   paged_decode_kernel   one warp per (sequence, KV head, split of the sequence's pages).  Pages travel
-//                         through a ring of stages with tiled TMA loads (4-D tensor map over the pool,
-//                         128-byte swizzle, mbarrier completion; no multicast); Q.K^T and P.V run on
+//                         through a ring of stages with tiled TMA loads (one box per page of K and of V
+//                         from a 5-D tensor map over the pool, 128-byte swizzle, mbarrier completion; no
+//                         multicast); Q.K^T and P.V run on
 //                         mma.sync m16n8k16 with ldmatrix from the swizzled tiles; softmax is kept
 //                         online in fp32 (base-2 exponent).  Memory-bound: the tensor-core work is
 //                         ~6 warp instructions per token, the limit is reading 512 B per token and head.
@@ -57,6 +58,7 @@ struct AttnArgs {
     long long new_seq, new_head;              // byte strides of the new rows
     long long pool_head, pool_page;           // byte strides of the pools
     int early;                                // lengths, slots and table are older than the kernel before this one
+    int page_box;                             // the maps are 5-d and one box is a head's whole page (else 4-d, half a page)
 };
 
 __device__ __forceinline__ void tensor_load_4d(uint32_t dst_smem, const CUtensorMap* map, int c0, int c1, int c2, int c3,
@@ -64,6 +66,14 @@ __device__ __forceinline__ void tensor_load_4d(uint32_t dst_smem, const CUtensor
     asm volatile(
         "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
         ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
+        : "memory");
+}
+
+__device__ __forceinline__ void tensor_load_5d(uint32_t dst_smem, const CUtensorMap* map, int c0, int c1, int c2, int c3, int c4,
+                                               uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
+        ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(bar)
         : "memory");
 }
 
@@ -199,7 +209,12 @@ paged_decode_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap map_k,
             if (ok) mbar_arrive_expect(bar, kAttnStageBytes); else mbar_arrive(bar);
         }
         __syncwarp();
-        if (ok && lane < 4) {
+        if (ok && a.page_box) {
+            // lanes 0 and 1: the head's page of K, of V (both halves of every row in one box)
+            if (lane < 2)
+                tensor_load_5d(smem_addr(s_attn + (size_t)st * kAttnStageBytes + lane * kAttnPageBytes), lane ? &map_v : &map_k,
+                               0, 0, 0, phys, kvh, bar);
+        } else if (ok && lane < 4) {
             // lanes 0..3: K dims 0-63, K dims 64-127, V dims 0-63, V dims 64-127 (one half tile each)
             const uint32_t dst = smem_addr(s_attn + (size_t)st * kAttnStageBytes + lane * kHalf);
             tensor_load_4d(dst, lane < 2 ? &map_k : &map_v, (lane & 1) * 64, 0, phys, kvh, bar);
@@ -419,6 +434,30 @@ paged_decode_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap map_k,
     }
 }
 
+// 5-D map over one layer's K (or V) pool: (64 dims, row in page, half of the row, page, head); box = one
+// head's page, which lands in shared memory as [half][row][64 dims] - what two boxes of the 4-D map below
+// leave there - from ONE copy instruction.  An instruction costs the issuing warp, and the copy engine, about
+// 100 cycles for a 2 KiB box and 140 for a 4 KiB one (measured with a warp that does nothing but issue them),
+// so four boxes per 16-token page cap an SM near 39 KB/us - below its share of the memory bandwidth - and two
+// boxes do not.  (The half's stride, 128 bytes, is smaller than the row's, 256: the dimensions are listed in
+// the order shared memory wants, not by stride.  If the driver refuses the map the 4-D one is used.)
+bool make_page_map(CUtensorMap* map, const void* base, const barqkv_pool_layout* pool) {
+    PFN_cuTensorMapEncodeTiled enc = tensor_map_encoder();
+    if (!enc) return false;
+    const long long e = pool->elem_bytes;
+    const cuuint64_t dims[5] = {64u, (cuuint64_t)pool->page_size, 2u, (cuuint64_t)pool->num_pages, (cuuint64_t)pool->num_heads};
+    const cuuint64_t strides[4] = {(cuuint64_t)(pool->head_dim * e), 128u, (cuuint64_t)(pool->page_stride * e),
+                                   (cuuint64_t)(pool->head_stride * e)};
+    const cuuint32_t box[5] = {64u, (cuuint32_t)pool->page_size, 2u, 1u, 1u};
+    const cuuint32_t estr[5] = {1u, 1u, 1u, 1u, 1u};
+    const CUtensorMapL2promotion promo = g_knobs.attn_promotion == 1   ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B
+                                         : g_knobs.attn_promotion == 2 ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B
+                                                                      : CU_TENSOR_MAP_L2_PROMOTION_NONE;
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 5, const_cast<void*>(base), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, promo,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 // 4-D map over one layer's K (or V) pool: (dim, row in page, page, head); box = 64 dims x 16 rows.
 bool make_pool_map(CUtensorMap* map, const void* base, const barqkv_pool_layout* pool) {
     PFN_cuTensorMapEncodeTiled enc = tensor_map_encoder();
@@ -565,7 +604,8 @@ int attention_common(const barqkv_pool_layout* pool, const void* k_pool, const v
         a.ws_ml = a.ws_o + (size_t)n * a.kv_heads * a.splits * 8 * 128;
     }
     CUtensorMap map_k, map_v;
-    if (!make_pool_map(&map_k, k_pool, pool) || !make_pool_map(&map_v, v_pool, pool))
+    a.page_box = g_knobs.attn_page_box != 0 && make_page_map(&map_k, k_pool, pool) && make_page_map(&map_v, v_pool, pool);
+    if (!a.page_box && (!make_pool_map(&map_k, k_pool, pool) || !make_pool_map(&map_v, v_pool, pool)))
         return fail(BARQKV_E_LAUNCH, "decode_attention: could not describe the pools to the copy engine");
 
     cudaStream_t st = static_cast<cudaStream_t>(stream_);

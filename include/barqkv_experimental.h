@@ -31,6 +31,7 @@ extern "C" {
 #define BARQKV_KNOB_APPEND_BULK 12       /* 0: appends always use the row kernel (-1 = default: copy engine for page-sized appends) */
 #define BARQKV_KNOB_ATTN_WIDE 13         /* decode attention updates its softmax state every 32 tokens (1) or 16 (0); -1 = default: 32 for pages of 32 / 64 */
 #define BARQKV_KNOB_LAYER_OVERLAP 14     /* 0: barqkv_update_layers keeps every layer on the caller's stream (default 1: odd layers on a second stream) */
+#define BARQKV_KNOB_ATTN_PAGE_BOX 15     /* 0: decode attention loads half a page per copy instruction (default 1: a whole page) */
 
 int barqkv_set_tuning(int32_t knob, int32_t value);
 

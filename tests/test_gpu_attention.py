@@ -13,6 +13,11 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 ATOL, RTOL = 8e-3, 2e-2
 
+# A launch that fills the GPU's resident warps several times over (44 sequences, 103k tokens, 8 KV heads):
+# lengths on both sides of every page and split boundary (16 and 512 tokens) and a bulk of long sequences.
+LARGE_LENS = (1, 15, 16, 17, 127, 128, 129, 511, 512, 513, 639, 640, 641, 1023, 1024, 1025, 2047, 2048, 2049, 4095,
+              4096, 4097) + tuple(2500 + 97 * i for i in range(22))
+
 
 def _reference(cache, layer, slots, q, scale):
     gb = cache.begin_gather(slots)
@@ -36,6 +41,8 @@ def _reference(cache, layer, slots, q, scale):
     dict(dtype=torch.float16, hkv=1, group=4, lens=(3000, 16, 1024), seed=4),
     dict(dtype=torch.bfloat16, hkv=2, group=4, lens=(1, 31, 32, 33, 47, 48, 49, 1000, 2100), seed=5, ps=32),
     dict(dtype=torch.float16, hkv=2, group=2, lens=(63, 64, 65, 17, 700), seed=6, ps=64),
+    dict(dtype=torch.bfloat16, hkv=8, group=4, lens=LARGE_LENS, seed=7),
+    dict(dtype=torch.float16, hkv=8, group=2, lens=LARGE_LENS, seed=8),
 ])
 def test_decode_attention_matches_fp32_reference(case):
     from barqtrain_b200 import BlockTableKVCache, _ffi
@@ -128,6 +135,7 @@ def test_decode_attention_workspace_survives_changing_batches():
     dict(dtype=torch.bfloat16, hkv=8, group=4, lens=(1, 15, 16, 17, 37, 500, 512, 513, 1500), ps=16),
     dict(dtype=torch.float16, hkv=2, group=8, lens=(700, 33, 2100), ps=32),
     dict(dtype=torch.bfloat16, hkv=1, group=4, lens=(64, 65, 1, 3000), ps=64),
+    dict(dtype=torch.bfloat16, hkv=8, group=4, lens=LARGE_LENS, ps=16),
 ])
 def test_append_fused_into_decode_attention(case):
     """``decode_update`` (one launch: store the step's rows and attend) against append-then-attend on a twin
