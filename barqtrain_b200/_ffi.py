@@ -34,6 +34,7 @@ S_BAD_PAGE, S_CAPACITY, S_TIMEOUT, S_BAD_SLOT = 1, 2, 4, 8
 MODE_AUTO, MODE_VECTOR, MODE_BULK = 0, 1, 2
 MODES = {"auto": MODE_AUTO, "vector": MODE_VECTOR, "bulk": MODE_BULK}
 FLAG_DESC_STABLE = 0x100
+FLAG_ONE_STREAM = 0x200       # barqkv_update_layers: no second stream
 
 _i32, _i64, _ptr = ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p
 

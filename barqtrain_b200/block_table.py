@@ -824,11 +824,13 @@ class BlockTableKVCache:
 
     def update_layers(self, new: _Descriptor, full: _Descriptor, k_all: torch.Tensor, v_all: torch.Tensor,
                       outs: Sequence[Tuple[torch.Tensor, torch.Tensor]], layout: str = "HND",
-                      mode: Optional[str] = None, tokens_hint: Optional[int] = None) -> None:
+                      mode: Optional[str] = None, tokens_hint: Optional[int] = None, one_stream: bool = False) -> None:
         """``update`` of every layer with one native call (``barqkv_update_layers``): ``k_all`` / ``v_all`` are
         ``[num_layers, new_tokens, kv_heads, head_dim]``; layer ``l`` writes its gathered rows to
         ``outs[l % len(outs)]`` (pairs of fixed-capacity buffers as ``update`` takes them).  For callers that
-        hold every layer's new rows before the first launch - a recorded decode step."""
+        hold every layer's new rows before the first launch - a recorded decode step.  With an even number of
+        distinct output pairs the library runs odd layers on a second stream of its own beside the even ones
+        (joined back before the call returns); ``one_stream=True`` keeps every layer on the caller's stream."""
         self._current(new), self._current(full)
         if full.n != new.n or not np.array_equal(full.slots_np, new.slots_np):
             raise ValueError("update_layers: the append and gather descriptions must list the same slots")
@@ -863,7 +865,8 @@ class BlockTableKVCache:
         rc = self.backend.lib.barqkv_update_layers(
             self._pool_ref, self._k_ptr[0], self._v_ptr[0], L, self.pools.stride(0), new.table_ref, new.p_first, new.p_cu,
             new.n, 0, new.total, k_all.data_ptr(), v_all.data_ptr(), new_ref, strides[0], full.p_cu,
-            tokens_hint or full.total, k_ptrs, v_ptrs, len(outs), out_ref, _ffi.MODES[mode or self.gather_mode],
+            tokens_hint or full.total, k_ptrs, v_ptrs, len(outs), out_ref,
+            _ffi.MODES[mode or self.gather_mode] | (_ffi.FLAG_ONE_STREAM if one_stream else 0),
             self._status_ptr, full.work, full.p_first, full.stream)
         # the layers alternated between the stream's two counter pairs starting with the first: the next
         # launch on this stream takes the pair the last layer did not use
@@ -994,7 +997,8 @@ class DecodeStepGraph:
     """
 
     def __init__(self, cache: BlockTableKVCache, slots: Sequence[int], capacity_tokens: int,
-                 mode: Optional[str] = None, what: str = "update", q_heads: int = 0, max_len: int = 0):
+                 mode: Optional[str] = None, what: str = "update", q_heads: int = 0, max_len: int = 0,
+                 one_stream: bool = False):
         """``what``: ``"update"`` (append + gather per layer, the default), ``"append"`` (the append alone, one
         launch per layer), ``"append_layers"`` (the append alone, one launch for all layers) or ``"attention"``
         (append fused into attention over the pages, one launch per layer, no gather: fill ``q_in``
@@ -1002,6 +1006,9 @@ class DecodeStepGraph:
         replays and ``capacity_tokens`` the sum of the lengths).  Only ``"update"`` needs output buffers."""
         if what not in ("update", "append", "append_layers", "attention"):
             raise ValueError("what must be 'update', 'append', 'append_layers' or 'attention'")
+        # "update" only: keep every layer's launch on one stream (see ``update_layers``); takes effect at the
+        # next eager step or ``record()``
+        self.one_stream = one_stream
         self.cache, self.slots, self.mode, self.what = cache, list(slots), mode, what
         c = cache
         B = len(self.slots)
@@ -1076,7 +1083,7 @@ class DecodeStepGraph:
         # one native call issues every layer's launch; from the second layer on each is a programmatic
         # dependent of the one before (its prologue overlaps that layer's tail)
         self.cache.update_layers(self._new, self._full, self.k_in, self.v_in, self.bufs, "HND", mode=self.mode,
-                                 tokens_hint=self.capacity)
+                                 tokens_hint=self.capacity, one_stream=self.one_stream)
 
     def _describe_step(self) -> int:
         """Host side of a step: pages for the new tokens, new lengths, one upload of both descriptions

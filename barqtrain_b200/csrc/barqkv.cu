@@ -2067,7 +2067,8 @@ int barqkv_update_layers(const barqkv_pool_layout* pool, void* k_pool, void* v_p
     if (new_rows->packed && !cu_new && tokens_per_entry > 1)
         return fail(BARQKV_E_INVALID, "update_layers: packed rows with more than one token per entry need cu_new");
     const long long e = pool->elem_bytes;
-    mode &= ~BARQKV_FLAG_DESC_STABLE;      // the first layer waits for whatever precedes it; the rest are chained here
+    const bool one_stream = (mode & BARQKV_FLAG_ONE_STREAM) != 0;
+    mode &= ~(BARQKV_FLAG_DESC_STABLE | BARQKV_FLAG_ONE_STREAM);   // the first layer waits for whatever precedes it; the rest are chained here
     const bool try_fused = total_new_tokens > 0 && total_new_tokens <= (long long)n * pool->page_size;
     bool fused_ok = try_fused;
 
@@ -2080,7 +2081,7 @@ int barqkv_update_layers(const barqkv_pool_layout* pool, void* k_pool, void* v_p
     // `layers`; such calls, and calls whose outputs are not all distinct, keep to one stream.
     cudaStream_t main_stream = static_cast<cudaStream_t>(stream);
     DeviceInfo* dev = device_info();
-    bool overlap = try_fused && layers >= 2 && work && dev && g_knobs.layer_overlap != 0 && g_knobs.pdl != 0 &&
+    bool overlap = !one_stream && try_fused && layers >= 2 && work && dev && g_knobs.layer_overlap != 0 && g_knobs.pdl != 0 &&
                    (num_out % 2 == 0 || num_out >= layers) && num_out <= 1024;
     for (int i = 0; overlap && i < num_out; ++i)
         for (int j = 0; j < i; ++j)

@@ -24,7 +24,7 @@
 extern "C" {
 #endif
 
-#define BARQKV_VERSION 103 /* major*100 + minor */
+#define BARQKV_VERSION 104 /* major*100 + minor */
 
 /* host-side return codes */
 #define BARQKV_OK 0
@@ -57,6 +57,10 @@ extern "C" {
  * may still be handing out its last.  Results are the same with and without the flag.
  */
 #define BARQKV_FLAG_DESC_STABLE 0x100
+/* barqkv_update_layers only: keep every layer on the caller's stream, each launch behind the one before
+ * (no second stream).  For callers whose stream has a priority or a capture the second stream should not
+ * take part in, and for measuring what the overlap of neighbouring layers is worth. */
+#define BARQKV_FLAG_ONE_STREAM 0x200
 
 typedef void* barqkv_stream_t; /* a cudaStream_t */
 
@@ -315,7 +319,8 @@ int barqkv_update(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,
  * that is forked from `stream` at the start of the call and joined back to it before the call returns
  * (events only; also inside a stream capture): layer l is ordered behind layer l - 2, the layer whose
  * output it overwrites, and runs beside layer l - 1.  Work issued to `stream` after the call is ordered
- * behind every layer.  Other calls keep all layers on `stream`, each behind the one before.
+ * behind every layer.  Other calls, and calls whose `mode` carries BARQKV_FLAG_ONE_STREAM, keep all layers on
+ * `stream`, each behind the one before.
  * work: device int32[8] scratch, zero before its first use (four counter pairs, so that launches that can be
  * on the device together never share one); the kernels leave it zero.  For callers that have every layer's
  * new rows at hand (a recorded decode step, cache import); results equal `layers` calls of barqkv_update.

@@ -403,7 +403,7 @@ def test_update_of_all_layers_in_one_call_for_any_number_of_outputs(backend, num
         fast.end_append(new)
         full = fast.begin_gather(fs)
         before = backend.launches
-        fast.update_layers(new, full, k, v, outs, "HND", tokens_hint=cap)
+        fast.update_layers(new, full, k, v, outs, "HND", tokens_hint=cap, one_stream=step % 2 == 1)
         assert backend.launches - before == L
         # copies queued behind the call on the same stream: they must read finished outputs
         snap = [(ko.clone(), vo.clone()) for ko, vo in outs]
