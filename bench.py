@@ -471,15 +471,13 @@ def run_barqkv(args):
         "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
         "ms_per_step": round(ms / K, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": CFG["name"], "layers": wl.L, "kv_heads": CFG["kv_heads"], "kv_heads_per_gpu": wl.H,
-                   "head_dim": wl.D, "page_size": wl.ps, "batch": wl.B, "prompt_lengths": "uniform[512,4096] seeded",
-                   "sum_len_tokens": wl.sum_len(), "sharding": f"kv-head x{world}",
-                   "step": "per layer: append 1 token/seq, gather all sequences to [H,sum_len,D]",
-                   "launch": ("one update() kernel per layer" if wl.fused else "append() + gather() per layer")
-                   + (", odd layers on a second stream so that neighbouring layers overlap at their ends (a layer is "
-                      "ordered behind the layer two before it, whose output buffer it reuses), replayed from a CUDA graph"
-                      if use_graph else ", called from Python"),
-                   "l2": "inputs larger than L2: each step reads ~%.1f GB of pool per GPU" % (gat_bytes / K / 2 / 1e9)},
+        "config": decode_config(world),
+        "run": {"kv_heads_per_gpu": wl.H, "sum_len_tokens": wl.sum_len(),
+                "pool_gb_read_per_step_per_gpu": round(gat_bytes / K / 2 / 1e9, 1),
+                "launch": ("one update() kernel per layer" if wl.fused else "append() + gather() per layer")
+                + (", odd layers on a second stream so that neighbouring layers overlap at their ends (a layer is "
+                   "ordered behind the layer two before it, whose output buffer it reuses), replayed from a CUDA graph"
+                   if use_graph else ", called from Python")},
         "timed_regions": {"count": len(regions), "steps_each": K, "ms_median": round(ms, 3),
                           "ms_min": round(min(r[0] for r in regions), 3), "ms_max": round(max(r[0] for r in regions), 3),
                           "value_min": round(min(rates), 1), "value_max": round(max(rates), 1),
@@ -1052,6 +1050,16 @@ def run_generate(args):
                       "rows": rows}), flush=True)
 
 
+def decode_config(world: int) -> dict:
+    """The workload of the default run, in the same words on both arms' lines."""
+    return {"workload": CFG["name"], "layers": CFG["layers"], "kv_heads": CFG["kv_heads"], "head_dim": CFG["head_dim"],
+            "page_size": CFG["page_size"], "batch": CFG["batch"], "prompt_lengths": "uniform[512,4096] seeded",
+            "sharding": f"kv-head x{world}",
+            "step": "per layer: append 1 token/seq, gather all sequences to [H,sum_len,D]",
+            "l2": "inputs larger than L2: a step reads every layer's pages of all sequences once (~21 GB over 32 layers "
+                  "at 8 KV heads)"}
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -1063,8 +1071,7 @@ def run_reference(args):
         "steps": base["steps"], "warmup": W, "ms_per_step": base["ms_per_step"], "higher_is_better": True,
         "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": CFG["name"], "layers": CFG["layers"], "kv_heads": CFG["kv_heads"],
-                   "head_dim": CFG["head_dim"], "page_size": CFG["page_size"], "batch": CFG["batch"]},
+        "config": decode_config(args.gpus),
         "cpu_baseline": base,
         "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "the reference's CPU PyTorch path (_python_append + current_tensors().contiguous(); see cpu_baseline.kind "

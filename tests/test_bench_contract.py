@@ -21,6 +21,9 @@ def test_reference_arm_prints_the_contract_line():
     assert line["unit"] == "GB/s" and line["higher_is_better"] is True and line["value"] > 0
     assert line["steps"] == 2 and line["warmup"] == 1 and line["n_gpus"] == 1 and line["vs_baseline"] is None
     assert line["config"]["workload"] == "llama3-8b-decode"
+    import bench
+
+    assert line["config"] == bench.decode_config(1)          # the words the GPU arm's line uses too
     base = line["cpu_baseline"]
     from oracle import ref_python
 
