@@ -868,8 +868,9 @@ class BlockTableKVCache:
             tokens_hint or full.total, k_ptrs, v_ptrs, len(outs), out_ref,
             _ffi.MODES[mode or self.gather_mode] | (_ffi.FLAG_ONE_STREAM if one_stream else 0),
             self._status_ptr, full.work, full.p_first, full.stream)
-        # the layers alternated between the stream's two counter pairs starting with the first: the next
-        # launch on this stream takes the pair the last layer did not use
+        # on one stream the layers alternated between the first two counter pairs starting with the first, so the
+        # next launch on this stream takes the pair the last layer did not use (after a call that used the second
+        # stream every layer is complete before the next launch starts, and either pair will do)
         self.backend._work_turn[(self.device.index, full.stream)] = (L & 1)
         if rc:
             self.backend._check(rc)
