@@ -2082,7 +2082,7 @@ int barqkv_update_layers(const barqkv_pool_layout* pool, void* k_pool, void* v_p
     cudaStream_t main_stream = static_cast<cudaStream_t>(stream);
     DeviceInfo* dev = device_info();
     bool overlap = !one_stream && try_fused && layers >= 2 && work && dev && g_knobs.layer_overlap != 0 && g_knobs.pdl != 0 &&
-                   (num_out % 2 == 0 || num_out >= layers) && num_out <= 1024;
+                   (num_out % 2 == 0 || num_out >= layers) && num_out <= 128;
     for (int i = 0; overlap && i < num_out; ++i)
         for (int j = 0; j < i; ++j)
             if (k_out[i] == k_out[j] || v_out[i] == v_out[j] || k_out[i] == v_out[j] || v_out[i] == k_out[j]) overlap = false;
