@@ -287,7 +287,7 @@ class BlockTableKVCache:
         self._free_slots: List[int] = list(range(max_seqs - 1, -1, -1))
         self._slot_of: Dict[object, int] = {}
         self._fork_counter = 0
-        self._attn_ws, self._attn_ws_bytes, self._attn_tickets = None, 0, 0
+        self._attn_ws, self._attn_ws_bytes = None, 0
 
         self._desc_turn: Dict[str, int] = {}
         self._uploads = 0               # descriptions uploaded + table scatters enqueued so far
@@ -908,20 +908,12 @@ class BlockTableKVCache:
             total_len = full.total          # the sum of the lengths: sizes the splits for small batches
         need = int(self.backend.lib.barqkv_paged_decode_workspace_bytes(full.n, self.num_kv_heads, max_len, total_len,
                                                                         self.page_size))
-        if need:
-            # the front of the workspace holds one ticket per (sequence, KV head) that must be zero on entry;
-            # calls leave their own tickets zero, but a smaller batch's partial results may lie where a
-            # larger batch's tickets go
-            tickets = 4 * full.n * self.num_kv_heads
-            # allocated and zero-filled on the stream the kernel will run on (the description's), so the
-            # fill is ordered before the launch and a freed workspace is not reused under a running kernel
+        if need > self._attn_ws_bytes:
+            # allocated on the stream the kernels will run on (the description's), so that the workspace it
+            # replaces is not reused under a kernel that still runs there
             with torch.cuda.stream(torch.cuda.ExternalStream(full.stream, device=self.device)):
-                if need > self._attn_ws_bytes:
-                    self._attn_ws = torch.zeros(need, dtype=torch.uint8, device=self.device)
-                    self._attn_ws_bytes = need
-                elif tickets > self._attn_tickets:
-                    self._attn_ws[:tickets].zero_()
-            self._attn_tickets = tickets
+                self._attn_ws = torch.empty(need, dtype=torch.uint8, device=self.device)
+            self._attn_ws_bytes = need
         ws_ptr = self._attn_ws.data_ptr() if need else None
         if scale is None:
             scale = self.head_dim ** -0.5

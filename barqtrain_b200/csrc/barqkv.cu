@@ -1173,7 +1173,10 @@ struct Knobs {
     int attn_split_tokens = 0;
     int append_bulk = -1;        // -1: page-sized appends go through the copy engine; 0: always the row kernel
     int layer_overlap = 1;       // update_layers issues odd layers on a second stream (0: one stream, one chain)
-    int attn_page_box = 1;       // decode attention loads a head's page with one copy instruction (0: two half-page boxes)
+    int attn_page_box = 2;       // decode attention loads a head's page of K and of V with one copy instruction where the pools allow it
+                                 // (1: one instruction for K, one for V; 0: two half-page boxes each)
+    int attn_probe = 0;          // timing probes (results are wrong): 1 = decode attention loads pages without attending them, 2 = writes no result
+    int attn_compact = 1;        // decode attention: the grid lists only splits that have pages (0: one CTA per possible split)
     int attn_wide = -1;          // decode attention updates its softmax state every 32 tokens (1) or 16 (0);
                                  // -1: 32 for pages of 32 and 64, 16 for pages of 16
 };
@@ -1427,6 +1430,8 @@ int barqkv_set_tuning(int32_t knob, int32_t value) {
         case BARQKV_KNOB_ATTN_WIDE: g_knobs.attn_wide = value; return 0;
         case BARQKV_KNOB_LAYER_OVERLAP: g_knobs.layer_overlap = value; return 0;
         case BARQKV_KNOB_ATTN_PAGE_BOX: g_knobs.attn_page_box = value; return 0;
+        case BARQKV_KNOB_ATTN_COMPACT: g_knobs.attn_compact = value; return 0;
+        case BARQKV_KNOB_ATTN_PROBE: g_knobs.attn_probe = value; return 0;
         default: return fail(BARQKV_E_INVALID, "set_tuning: unknown knob");
     }
 }

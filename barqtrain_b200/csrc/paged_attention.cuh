@@ -13,13 +13,15 @@
 //                         online in fp32 (base-2 exponent).  Memory-bound: the tensor-core work is
 //                         ~6 warp instructions per token, the limit is reading 512 B per token and head.
 //                         With several splits per sequence each warp leaves a partial (max, sum, output)
-//                         triple in the workspace and takes a ticket; the warp that takes a sequence's
-//                         last ticket combines the triples (they are still in L2) and writes the output,
-//                         so no second launch is needed.  Optionally the step's append is fused in: the
+//                         triple in the workspace and is gone; paged_decode_merge_kernel, a small kernel
+//                         launched behind it as a programmatic dependent, combines the triples (they are
+//                         still in L2) and writes the output.  (Combining inside the launch - a fence, a
+//                         counter per sequence, the last split to arrive does it - kept every split's
+//                         place on the SM for microseconds with no page in flight and cost a tenth of the
+//                         bandwidth.)  Optionally the step's append is fused in: the
 //                         CTA that owns a sequence's last page takes the new K/V row from the caller's
 //                         buffers, patches it into the page's tile in shared memory (the pool still holds
-//                         whatever was in that slot) and writes it to the pool, so a decode layer is ONE
-//                         launch: no separate append, no gather.
+//                         whatever was in that slot) and writes it to the pool: no separate append, no gather.
 //
 // Restrictions (checked on the host): 2-byte elements (bf16 / fp16), head_dim 128, page_size 16, 32 or 64,
 // group <= 8.  Every wait is bounded; a guard failure skips the sequence and sets a status bit.
@@ -27,6 +29,8 @@
 namespace {
 
 constexpr int kAttnSplitTokens = 512;                 // tokens per split by default
+constexpr int kAttnMaxSplits = 64;                    // most splits of one sequence (bounds the workspace)
+constexpr int kAttnCompactSeqs = 256;                 // largest batch whose splits are listed without gaps (8 sequences per lane)
 // Per page size: bytes of one head's page of K (or V), of a stage (K + V), and ring depth.
 template <int PS, bool WIDE> struct AttnTile {
     static constexpr int kHalf = PS * 128;            // one half tile: PS rows x 64 dims x 2 bytes
@@ -44,8 +48,9 @@ struct AttnArgs {
     long long q_seq, q_head, o_seq, o_head;   // byte strides
     float* ws_o;                              // [n][kv_heads][splits][8][128] partial outputs
     float* ws_ml;                             // [n][kv_heads][splits][8][2]   (running max, running sum)
-    int32_t* tickets;                         // [n][kv_heads] splits that have left their partials; zero between calls
     int n, kv_heads, group, split_pages, splits, page_size;
+    int probe;                                // timing probes of the tuning build: 1 = pages are loaded but not attended, 2 = no result is written
+    int compact;                              // grid x counts the splits that have pages, one sequence after another (n <= kAttnCompactSeqs)
     float scale_log2;                         // softmax scale * log2(e)
     int32_t* status;
     // Fused append (null k_new = plain attention): the step's new K/V row of every (sequence, KV head) - the
@@ -58,7 +63,7 @@ struct AttnArgs {
     long long new_seq, new_head;              // byte strides of the new rows
     long long pool_head, pool_page;           // byte strides of the pools
     int early;                                // lengths, slots and table are older than the kernel before this one
-    int page_box;                             // the maps are 5-d and one box is a head's whole page (else 4-d, half a page)
+    int page_box;                             // 2: one 5-d box is a head's page of K and of V; 1: of K or of V; 0: 4-d maps, half a page per box
 };
 
 __device__ __forceinline__ void tensor_load_4d(uint32_t dst_smem, const CUtensorMap* map, int c0, int c1, int c2, int c3,
@@ -131,7 +136,8 @@ paged_decode_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap map_k,
     // the 128-byte swizzle pattern repeats every 1024 bytes of shared-memory address: align the tiles to it
     unsigned char* s_attn = s_attn_raw + ((1024u - (smem_addr(s_attn_raw) & 1023u)) & 1023u);
     const int lane = threadIdx.x;
-    const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
+    const int kvh = blockIdx.y;
+    int split = blockIdx.x, seq = blockIdx.z;
 
     // Lengths, slots and block-table entries may be read before the kernel ahead of this one has finished
     // when the caller vouches that they are older than it; the query, the new rows and the pools may not.
@@ -139,16 +145,63 @@ paged_decode_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap map_k,
         pdl_wait_for_predecessor();
         pdl_let_successor_in();
     }
-    // the length and the table row are independent loads: both are in flight before either is used
-    const int len = a.seq_lens[seq];
-    const int row = a.tb.slots ? a.tb.slots[seq] : seq;
+    int len, row;
+    if (a.compact) {
+        // blockIdx.x counts splits that have pages, sequence after sequence, so that only the few CTAs beyond
+        // the batch's real count (the grid is sized from the caller's bounds) find nothing to do - a CTA that
+        // starts only to leave again holds up the one behind it.  Every lane reads the lengths and slots of up
+        // to kAttnCompactSeqs / 32 sequences (all loads in flight together); a running sum of the sequences'
+        // split counts finds the one this CTA's split belongs to.
+        int my_len[kAttnCompactSeqs / 32], my_row[kAttnCompactSeqs / 32];
+#pragma unroll
+        for (int c = 0; c < kAttnCompactSeqs / 32; ++c) {
+            const int i = c * 32 + lane;
+            my_len[c] = i < a.n ? a.seq_lens[i] : 0;
+            my_row[c] = i < a.n ? (a.tb.slots ? a.tb.slots[i] : i) : 0;
+        }
+        const int item = blockIdx.x;
+        int before = 0;
+        seq = -1;
+        len = row = 0;
+#pragma unroll
+        for (int c = 0; c < kAttnCompactSeqs / 32; ++c) {
+            if (seq < 0 && c * 32 < a.n) {
+                const int pg = (max(my_len[c], 0) + PS - 1) / PS;
+                const int count = min(a.splits, (pg + a.split_pages - 1) / a.split_pages);
+                int upto = count;                                   // inclusive running sum over the lanes
+#pragma unroll
+                for (int d = 1; d < 32; d <<= 1) {
+                    const int t = __shfl_up_sync(0xffffffffu, upto, d);
+                    if (lane >= d) upto += t;
+                }
+                const unsigned holds = __ballot_sync(0xffffffffu, before + upto > item);
+                if (holds) {
+                    const int src = __ffs(holds) - 1;
+                    seq = c * 32 + src;
+                    len = __shfl_sync(0xffffffffu, my_len[c], src);
+                    row = __shfl_sync(0xffffffffu, my_row[c], src);
+                    split = item - before - __shfl_sync(0xffffffffu, upto - count, src);
+                }
+                before += __shfl_sync(0xffffffffu, upto, 31);
+            }
+        }
+        if (seq < 0) {
+            if (a.early) { pdl_wait_for_predecessor(); pdl_let_successor_in(); }
+            return;
+        }
+    } else {
+        // the length and the table row are independent loads: both are in flight before either is used
+        len = a.seq_lens[seq];
+        row = a.tb.slots ? a.tb.slots[seq] : seq;
+    }
     const int pages = (len + PS - 1) / PS;
-    const int p0 = split * a.split_pages;
+    const int sp = a.split_pages;
+    const int p0 = split * sp;
     if (len <= 0 || p0 >= pages) {
         if (a.early) { pdl_wait_for_predecessor(); pdl_let_successor_in(); }
         return;
     }
-    const int p1 = min(pages, p0 + a.split_pages);
+    const int p1 = min(pages, p0 + sp);
     if (row < 0 || row >= a.tb.rows || pages > a.tb.stride) {
         if (a.early) { pdl_wait_for_predecessor(); pdl_let_successor_in(); }
         if (lane == 0) raise(a.status, BARQKV_S_BAD_SLOT);
@@ -209,7 +262,11 @@ paged_decode_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap map_k,
             if (ok) mbar_arrive_expect(bar, kAttnStageBytes); else mbar_arrive(bar);
         }
         __syncwarp();
-        if (ok && a.page_box) {
+        if (ok && a.page_box == 2) {
+            // lane 0: the head's page of K and, one pool further on, of V, in one box
+            if (lane == 0)
+                tensor_load_5d(smem_addr(s_attn + (size_t)st * kAttnStageBytes), &map_k, 0, 0, 0, kvh * a.tb.num_pages + phys, 0, bar);
+        } else if (ok && a.page_box) {
             // lanes 0 and 1: the head's page of K, of V (both halves of every row in one box)
             if (lane < 2)
                 tensor_load_5d(smem_addr(s_attn + (size_t)st * kAttnStageBytes + lane * kAttnPageBytes), lane ? &map_v : &map_k,
@@ -353,12 +410,18 @@ paged_decode_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap map_k,
                 const int valid_a = min(16, len - p * PS - r0);
                 if (valid_a <= 0) break;
                 const int valid_b = WIDE ? min(16, len - p * PS - r0 - 16) : 0;
+    #ifdef BARQKV_TUNING
+                if (a.probe & 1) continue;
+#endif
                 attend(kt, vt, r0, valid_a, kt, vt, r0 + 16, valid_b);
             }
             __syncwarp();      // every lane is done with this stage before lane 0 re-arms it
         }
     }
 
+#ifdef BARQKV_TUNING
+    if (a.probe & 2) return;
+#endif
     const bool failed = dead || bad;
     if (failed && lane == 0) raise(a.status, dead ? BARQKV_S_TIMEOUT : BARQKV_S_BAD_PAGE);
 
@@ -375,62 +438,80 @@ paged_decode_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap map_k,
         return;
     }
 
-    const long long item0 = (((long long)seq * a.kv_heads + kvh) * a.splits) * 8;
+    // Several splits per sequence: this one leaves its (maximum, sum, output) in the workspace and goes away -
+    // no fence, no counter, nothing that would keep its place on the SM busy with no page in flight.
+    // paged_decode_merge_kernel, launched behind this kernel, combines them.
     if (!failed && g < a.group) {
-        const long long item = item0 + (long long)split * 8 + g;
+        const long long item = ((((long long)seq * a.kv_heads + kvh) * a.splits) + split) * 8 + g;
         float* wo = a.ws_o + item * 128;
 #pragma unroll
         for (int i = 0; i < 16; ++i) __stcg(reinterpret_cast<float2*>(wo + i * 8 + tq * 2), make_float2(acc[i][0], acc[i][1]));
         if (tq == 0) __stcg(reinterpret_cast<float2*>(a.ws_ml + item * 2), make_float2(m_run, l_tot));
     }
-    // Every split of the sequence that has pages takes one ticket once its partial is visible; the
-    // last one to arrive combines them.  A split that failed a guard still takes its ticket, so the
-    // counter returns to zero whatever happens (the status word says that the output is not valid).
-    const int used = min(a.splits, (pages + a.split_pages - 1) / a.split_pages);
-    int32_t* ticket = a.tickets + (long long)seq * a.kv_heads + kvh;
-    __syncwarp();                 // the lanes' stores are ordered before lane 0's fence (cumulativity)
-    int last = 0;
-    if (lane == 0) {
-        __threadfence();
-        last = atomicAdd(ticket, 1) == used - 1;
-        if (last) {
-            __threadfence();
-            *ticket = 0;
-        }
-    }
-    last = __shfl_sync(0xffffffffu, last, 0);
-    if (!last) return;
+}
 
-    // Eight lanes per query head, sixteen output dims per lane; the partials were written by other
-    // SMs, so they are read from L2.  All loads of a pass are independent of one another.
-    const int sub = lane & 7;
-    for (int r = lane >> 3; r < a.group; r += 4) {
+// Combines the partial results of a launch of paged_decode_kernel whose splits left them in the workspace and
+// went away without waiting for one another.  One CTA per (sequence, KV head), 128 threads per part: a warp per
+// query head (two rounds for more than four), four output dims per thread, one pass over the splits with a
+// running maximum.  For up to eight splits that is all (no shared memory, every CTA of the grid resident at
+// once); for more, PARTS parts take every PARTS-th split each and part 0 folds their results, which meet in
+// shared memory.  Launched as a programmatic dependent of the attention kernel, and lets its own successor in
+// at once: both are in place, their prologues done, when the last split finishes.
+template <bool BF16, int PARTS>
+__global__ void __launch_bounds__(128 * PARTS)
+paged_decode_merge_kernel(const AttnArgs a) {
+    __shared__ float4 s_num[PARTS > 1 ? PARTS - 1 : 1][128];
+    __shared__ float2 s_ml[PARTS > 1 ? PARTS - 1 : 1][128];
+    pdl_let_successor_in();
+    const int seq = blockIdx.x / a.kv_heads, kvh = blockIdx.x % a.kv_heads;
+    // the lengths are older than the kernel before this one: it read them itself before it let this one in
+    const int len = a.seq_lens[seq];
+    const int row = a.tb.slots ? a.tb.slots[seq] : seq;
+    const int pages = (len + a.page_size - 1) / a.page_size;
+    const int used = min(a.splits, (pages + a.split_pages - 1) / a.split_pages);
+    pdl_wait_for_predecessor();
+    if (row < 0 || row >= a.tb.rows || pages > a.tb.stride) return;      // the attention kernel skipped this sequence
+    const long long item0 = (((long long)seq * a.kv_heads + kvh) * a.splits) * 8;
+    const int t = threadIdx.x & 127, part = threadIdx.x >> 7;
+    const int d0 = (t & 31) * 4;
+    if (used <= 0) return;
+    for (int r0 = 0; r0 < a.group; r0 += 4) {                    // the same trip count for every thread of the CTA
+        const int r = r0 + (t >> 5);
+        const bool row = r < a.group;
         const float* ml = a.ws_ml + (item0 + r) * 2;
-        const float* po = a.ws_o + (item0 + r) * 128 + sub * 16;
-        float m = -INFINITY;
+        const float* po = a.ws_o + (item0 + r) * 128 + d0;
+        float m = -INFINITY, den = 0.f;
+        float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
+        auto fold = [&](float m_in, float den_in, const float4& o) {
+            const float m_new = fmaxf(m, m_in);
+            const float keep = m == -INFINITY ? 0.f : exp2f(m - m_new), wgt = m_in == -INFINITY ? 0.f : exp2f(m_in - m_new);
+            m = m_new;
+            den = den * keep + wgt * den_in;
+            num.x = num.x * keep + wgt * o.x;
+            num.y = num.y * keep + wgt * o.y;
+            num.z = num.z * keep + wgt * o.z;
+            num.w = num.w * keep + wgt * o.w;
+        };
 #pragma unroll 8
-        for (int s = 0; s < used; ++s) m = fmaxf(m, __ldcg(ml + (long long)s * 16));
-        float num[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) num[i] = 0.f;
-        float den = 0.f;
-#pragma unroll 2
-        for (int s = 0; s < used; ++s) {
+        for (int s = part; s < used && row; s += PARTS) {
             const float2 x = __ldcg(reinterpret_cast<const float2*>(ml + (long long)s * 16));
-            const float4* o4 = reinterpret_cast<const float4*>(po + (long long)s * 1024);
-            const float4 o0 = __ldcg(o4), o1 = __ldcg(o4 + 1), o2 = __ldcg(o4 + 2), o3 = __ldcg(o4 + 3);
-            const float w = exp2f(x.x - m);
-            num[0] += w * o0.x; num[1] += w * o0.y; num[2] += w * o0.z; num[3] += w * o0.w;
-            num[4] += w * o1.x; num[5] += w * o1.y; num[6] += w * o1.z; num[7] += w * o1.w;
-            num[8] += w * o2.x; num[9] += w * o2.y; num[10] += w * o2.z; num[11] += w * o2.w;
-            num[12] += w * o3.x; num[13] += w * o3.y; num[14] += w * o3.z; num[15] += w * o3.w;
-            den += w * x.y;
+            const float4 o = __ldcg(reinterpret_cast<const float4*>(po + (long long)s * 1024));
+            fold(x.x, x.y, o);
         }
-        const float inv = 1.f / den;
-        unsigned char* orow = a.out + (long long)seq * a.o_seq + (long long)(kvh * a.group + r) * a.o_head + sub * 32;
+        if (PARTS > 1) {
+            if (part > 0) { s_num[part - 1][t] = num; s_ml[part - 1][t] = make_float2(m, den); }
+            __syncthreads();
+            if (part == 0) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
-            *reinterpret_cast<uint32_t*>(orow + i * 4) = pack2<BF16>(num[2 * i] * inv, num[2 * i + 1] * inv);
+                for (int k = 0; k < PARTS - 1; ++k) fold(s_ml[k][t].x, s_ml[k][t].y, s_num[k][t]);
+            }
+            __syncthreads();                                      // read before the next round overwrites
+        }
+        if (part > 0 || !row) continue;
+        const float inv = 1.f / den;
+        unsigned char* orow = a.out + (long long)seq * a.o_seq + (long long)(kvh * a.group + r) * a.o_head + d0 * 2;
+        *reinterpret_cast<uint32_t*>(orow) = pack2<BF16>(num.x * inv, num.y * inv);
+        *reinterpret_cast<uint32_t*>(orow + 4) = pack2<BF16>(num.z * inv, num.w * inv);
     }
 }
 
@@ -458,6 +539,26 @@ bool make_page_map(CUtensorMap* map, const void* base, const barqkv_pool_layout*
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// The same when the V pool lies a fixed distance behind the K pool (one allocation holds both) and a pool's heads
+// are adjacent: (64 dims, row in page, half of the row, head * pages + page, K or V); the box is a head's page
+// of K AND of V, so a ring stage is filled by one copy instruction instead of two.
+bool make_kv_page_map(CUtensorMap* map, const void* k_base, const void* v_base, const barqkv_pool_layout* pool) {
+    PFN_cuTensorMapEncodeTiled enc = tensor_map_encoder();
+    if (!enc) return false;
+    const long long e = pool->elem_bytes;
+    const long long apart = static_cast<const unsigned char*>(v_base) - static_cast<const unsigned char*>(k_base);
+    if (apart <= 0 || apart % 16 || apart >= (1LL << 40)) return false;
+    if (pool->head_stride != (long long)pool->num_pages * pool->page_stride) return false;
+    if ((long long)pool->num_pages * pool->num_heads * pool->page_stride * e > apart) return false;     // the pools overlap
+    const cuuint64_t dims[5] = {64u, (cuuint64_t)pool->page_size, 2u, (cuuint64_t)pool->num_pages * (cuuint64_t)pool->num_heads, 2u};
+    const cuuint64_t strides[4] = {(cuuint64_t)(pool->head_dim * e), 128u, (cuuint64_t)(pool->page_stride * e), (cuuint64_t)apart};
+    const cuuint32_t box[5] = {64u, (cuuint32_t)pool->page_size, 2u, 1u, 2u};
+    const cuuint32_t estr[5] = {1u, 1u, 1u, 1u, 1u};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 5, const_cast<void*>(k_base), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 // 4-D map over one layer's K (or V) pool: (dim, row in page, page, head); box = 64 dims x 16 rows.
 bool make_pool_map(CUtensorMap* map, const void* base, const barqkv_pool_layout* pool) {
     PFN_cuTensorMapEncodeTiled enc = tensor_map_encoder();
@@ -481,7 +582,8 @@ bool make_pool_map(CUtensorMap* map, const void* base, const barqkv_pool_layout*
 // several times over.  When it does not (few sequences, a single KV head per GPU) the split is sized so
 // that the CTAs with work fill the resident slots once or twice: from the caller's total of the lengths
 // when it is given, else from the longest length alone by halving.  Never more than 64 splits per sequence.
-int attn_splits(int n, int kv_heads, long long max_len, long long total_len, int page_size, int* split_pages) {
+int attn_splits(int n, int kv_heads, long long max_len, long long total_len, int page_size, int* split_pages,
+                long long* live_bound = nullptr) {
     const long long pages = (max_len + page_size - 1) / page_size;
     int sms = 148;
     if (DeviceInfo* d = device_info()) sms = d->sms;
@@ -506,14 +608,23 @@ int attn_splits(int n, int kv_heads, long long max_len, long long total_len, int
         const long long per_cta = (long long)n * kv_heads * pages / (8LL * sms);
         while (sp * page_size > 64 && sp > per_cta) sp >>= 1;
     }
-    while ((pages + sp - 1) / sp > 64) sp *= 2;
+    while ((pages + sp - 1) / sp > kAttnMaxSplits) sp *= 2;
     *split_pages = sp;
-    const long long splits = (pages + sp - 1) / sp;
-    return splits < 1 ? 1 : (int)splits;
+    long long splits = (pages + sp - 1) / sp;
+    if (splits < 1) splits = 1;
+    if (live_bound) {
+        // splits with pages: every sequence at most `splits`; all together at most (pages of the batch) / sp + n
+        long long bound = (long long)n * splits;
+        if (total_len > 0) {
+            const long long batch_pages = (total_len + page_size - 1) / page_size + n;
+            const long long by_total = batch_pages / sp + n;
+            if (by_total < bound) bound = by_total;
+        }
+        *live_bound = bound;
+    }
+    return (int)splits;
 }
 
-// The tickets sit at the front of the workspace, padded so that the partial outputs stay 16-byte aligned.
-int64_t attn_ticket_bytes(int n, int kv_heads) { return (((int64_t)n * kv_heads * 4) + 15) / 16 * 16; }
 
 }  // namespace
 
@@ -525,7 +636,7 @@ int64_t barqkv_paged_decode_workspace_bytes(int32_t n, int32_t kv_heads, int64_t
     int sp;
     const int splits = attn_splits(n, kv_heads, max_len, total_len, page_size, &sp);
     if (splits == 1) return 0;
-    return attn_ticket_bytes(n, kv_heads) + (int64_t)n * kv_heads * splits * 8 * (128 + 2) * (int64_t)sizeof(float);
+    return (int64_t)n * kv_heads * splits * 8 * (128 + 2) * (int64_t)sizeof(float);
 }
 
 }  // extern "C"
@@ -552,7 +663,8 @@ int attention_common(const barqkv_pool_layout* pool, const void* k_pool, const v
         return fail(BARQKV_E_LIMIT, "decode_attention: supports 2-byte elements, head_dim 128, page_size 16, 32 or 64");
     if (num_q_heads <= 0 || num_q_heads % pool->num_heads || num_q_heads / pool->num_heads > 8)
         return fail(BARQKV_E_LIMIT, "decode_attention: query heads must be 1..8 times the KV heads");
-    if (n > 65535 || pool->num_heads > 65535) return fail(BARQKV_E_LIMIT, "decode_attention: more than 65535 sequences or heads");
+    if (n > 65535 || pool->num_heads > 65535 || (long long)n * pool->num_heads > 0x7fffffffLL)
+        return fail(BARQKV_E_LIMIT, "decode_attention: more than 65535 sequences or heads");
     if (max_len <= 0) return fail(BARQKV_E_INVALID, "decode_attention: max_len (upper bound of the lengths) must be positive");
     const long long e = 2;
     if (!aligned(q, 4) || !aligned(out, 4) || !multiple(q_seq_stride * e, 4) || !multiple(q_head_stride * e, 4) ||
@@ -577,7 +689,10 @@ int attention_common(const barqkv_pool_layout* pool, const void* k_pool, const v
     a.kv_heads = pool->num_heads;
     a.group = num_q_heads / pool->num_heads;
     a.page_size = pool->page_size;
-    a.splits = attn_splits(n, a.kv_heads, max_len, total_len, a.page_size, &a.split_pages);
+    long long live_bound = 0;
+    a.splits = attn_splits(n, a.kv_heads, max_len, total_len, a.page_size, &a.split_pages, &live_bound);
+    a.probe = g_knobs.attn_probe;
+    a.compact = n <= kAttnCompactSeqs && a.splits > 1 && g_knobs.attn_compact != 0 ? 1 : 0;
     a.scale_log2 = softmax_scale * 1.4426950408889634f;
     a.status = status;
     a.early = (flags & BARQKV_FLAG_DESC_STABLE) && g_knobs.pdl != 0 ? 1 : 0;
@@ -599,17 +714,22 @@ int attention_common(const barqkv_pool_layout* pool, const void* k_pool, const v
         if (!workspace || workspace_bytes < need || !aligned(workspace, 16))
             return fail(BARQKV_E_INVALID, "decode_attention: workspace missing or smaller than "
                                           "barqkv_paged_decode_workspace_bytes(n, kv_heads, max_len, total_len, page_size)");
-        a.tickets = static_cast<int32_t*>(workspace);
-        a.ws_o = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + attn_ticket_bytes(n, a.kv_heads));
+        a.ws_o = static_cast<float*>(workspace);
         a.ws_ml = a.ws_o + (size_t)n * a.kv_heads * a.splits * 8 * 128;
     }
     CUtensorMap map_k, map_v;
-    a.page_box = g_knobs.attn_page_box != 0 && make_page_map(&map_k, k_pool, pool) && make_page_map(&map_v, v_pool, pool);
+    if (g_knobs.attn_page_box == 2 && make_kv_page_map(&map_k, k_pool, v_pool, pool)) {
+        a.page_box = 2;
+        map_v = map_k;
+    } else {
+        a.page_box = g_knobs.attn_page_box != 0 && make_page_map(&map_k, k_pool, pool) && make_page_map(&map_v, v_pool, pool);
+    }
     if (!a.page_box && (!make_pool_map(&map_k, k_pool, pool) || !make_pool_map(&map_v, v_pool, pool)))
         return fail(BARQKV_E_LAUNCH, "decode_attention: could not describe the pools to the copy engine");
 
     cudaStream_t st = static_cast<cudaStream_t>(stream_);
-    const dim3 grid((unsigned)a.splits, (unsigned)a.kv_heads, (unsigned)n);
+    const dim3 grid = a.compact ? dim3((unsigned)live_bound, (unsigned)a.kv_heads, 1u)
+                                : dim3((unsigned)a.splits, (unsigned)a.kv_heads, (unsigned)n);
     auto launch = [&](auto kernel, size_t smem) -> cudaError_t {
         if (smem > 48 * 1024) {
             const cudaError_t se = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -632,6 +752,17 @@ int attention_common(const barqkv_pool_layout* pool, const void* k_pool, const v
     cudaError_t ce = cudaGetLastError();
     if (ce != cudaSuccess) return fail_cuda("decode_attention launch", ce);
     g_launches.fetch_add(1, std::memory_order_relaxed);
+    if (a.splits > 1) {
+        const dim3 mgrid((unsigned)((long long)n * a.kv_heads));
+        if (a.splits > 8)
+            le = is_bf16 ? ::launch(paged_decode_merge_kernel<true, 4>, mgrid, dim3(512), 0, st, g_knobs.pdl != 0, a)
+                         : ::launch(paged_decode_merge_kernel<false, 4>, mgrid, dim3(512), 0, st, g_knobs.pdl != 0, a);
+        else
+            le = is_bf16 ? ::launch(paged_decode_merge_kernel<true, 1>, mgrid, dim3(128), 0, st, g_knobs.pdl != 0, a)
+                         : ::launch(paged_decode_merge_kernel<false, 1>, mgrid, dim3(128), 0, st, g_knobs.pdl != 0, a);
+        if (le != cudaSuccess) return fail_cuda("decode_attention merge launch", le);
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+    }
     return 0;
 }
 

@@ -24,7 +24,7 @@
 extern "C" {
 #endif
 
-#define BARQKV_VERSION 104 /* major*100 + minor */
+#define BARQKV_VERSION 105 /* major*100 + minor */
 
 /* host-side return codes */
 #define BARQKV_OK 0
@@ -378,12 +378,10 @@ int barqkv_gather_layers(const barqkv_pool_layout* pool, const void* k_pool, con
  * the host's sum of the lengths, or 0 when it is not known.  The two fix how many splits a sequence's
  * pages are cut into (with the sum the splits are sized to fill the GPU's resident CTAs once or twice
  * when the batch is small); pass the same values to both functions.  workspace: 16-byte aligned device
- * scratch of barqkv_paged_decode_workspace_bytes(...) bytes (0 when one split suffices).
- * Its first 4 * n * kv_heads bytes are per-sequence tickets (the split that finishes last combines the
- * partial results inside the same launch): they must be zero on entry and every call leaves them zero,
- * so a workspace that is zero-filled once serves any number of calls with the same n and kv_heads; zero
- * the front again before a call with a larger n * kv_heads.  Calls that may overlap on the device need
- * separate workspaces.
+ * scratch of barqkv_paged_decode_workspace_bytes(...) bytes (0 when one split suffices); its contents on
+ * entry do not matter.  With more than one split the call enqueues two kernels: the attention kernel, whose
+ * splits leave their partial results in the workspace, and a small one behind it (a programmatic dependent)
+ * that combines them into `out`.  Calls that may overlap on the device need separate workspaces.
  * Limits: head_dim 128, page_size 16, 32 or 64, 2-byte elements, at most 8 query heads per KV head.
  */
 int64_t barqkv_paged_decode_workspace_bytes(int32_t n, int32_t kv_heads, int64_t max_len, int64_t total_len,
@@ -397,8 +395,8 @@ int barqkv_paged_decode_attention(const barqkv_pool_layout* pool, const void* k_
                                   void* workspace, int64_t workspace_bytes, int32_t* status, barqkv_stream_t stream);
 
 /*
- * A decode layer in one launch: barqkv_append of the step's token (one new K/V row per sequence and KV
- * head) fused into barqkv_paged_decode_attention.  What the reference does per layer and step - append
+ * A decode layer in one call: barqkv_append of the step's token (one new K/V row per sequence and KV
+ * head) fused into barqkv_paged_decode_attention (the same kernels, the same count).  What the reference does per layer and step - append
  * (csrc/kernels/paged_kv_cache.cu:58-128), current_tensors (python/barqtrain/kv_cache.py:129-133), then an
  * attention call over the returned views - with neither a separate append launch nor any gathered copy.
  * seq_lens_after: lengths INCLUDING the new token (its position is length - 1; its page must already be

@@ -31,7 +31,9 @@ extern "C" {
 #define BARQKV_KNOB_APPEND_BULK 12       /* 0: appends always use the row kernel (-1 = default: copy engine for page-sized appends) */
 #define BARQKV_KNOB_ATTN_WIDE 13         /* decode attention updates its softmax state every 32 tokens (1) or 16 (0); -1 = default: 32 for pages of 32 / 64 */
 #define BARQKV_KNOB_LAYER_OVERLAP 14     /* 0: barqkv_update_layers keeps every layer on the caller's stream (default 1: odd layers on a second stream) */
-#define BARQKV_KNOB_ATTN_PAGE_BOX 15     /* 0: decode attention loads half a page per copy instruction (default 1: a whole page) */
+#define BARQKV_KNOB_ATTN_PAGE_BOX 15     /* decode attention, pages per copy instruction. 0: half of K or V; 1: K or V; 2 (default): K and V where the pools allow it */
+#define BARQKV_KNOB_ATTN_COMPACT 16      /* 0: decode attention launches one CTA per possible split of every sequence (default 1: only splits that can have pages, batches of up to 256) */
+#define BARQKV_KNOB_ATTN_PROBE 17        /* timing probes, results are wrong. 1: decode attention loads pages but does not attend them; 2: writes no result; 3: both */
 
 int barqkv_set_tuning(int32_t knob, int32_t value);
 

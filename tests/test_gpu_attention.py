@@ -101,8 +101,8 @@ def test_decode_attention_argument_limits():
 
 def test_decode_attention_workspace_survives_changing_batches():
     """Sequences long enough for several splits, attended in batches of changing size through the one
-    workspace the cache keeps: the per-sequence tickets at its front must be zero again after every
-    call, and a larger batch after a smaller one must not trip over the smaller one's partial results."""
+    workspace the cache keeps: its contents on entry must not matter, so a larger batch after a smaller one
+    must not trip over the smaller one's partial results (the workspace is filled with NaNs to start with)."""
     from barqtrain_b200 import BlockTableKVCache, _ffi
 
     backend = _ffi.require_cuda_backend()
@@ -120,14 +120,15 @@ def test_decode_attention_workspace_survives_changing_batches():
     cache.append(0, batch, k, v)
     cache.end_append(batch)
     scale = D ** -0.5
-    for take in (n, 2, n, n, 5, 1, 9, n):
+    for i, take in enumerate((n, 2, n, n, 5, 1, 9, n)):
         part = slots[:take]
         q = torch.randn(take, hkv * group, D, generator=g, device=DEV, dtype=torch.float32).to(dtype)
         gb, want = _reference(cache, 0, part, q, scale)
         got = cache.decode_attention(0, gb, q)
         assert bool(((got.float() - want).abs() <= ATOL + RTOL * want.abs()).all()), f"batch of {take}"
-        words = cache._attn_ws[: 4 * take * hkv].view(torch.int32)
-        assert int(words.abs().sum()) == 0, "tickets left non-zero"
+        if i == 0:
+            assert cache._attn_ws is not None
+            cache._attn_ws.view(torch.float32).fill_(float("nan"))
     assert backend.read_status(DEV) == 0
 
 
@@ -174,7 +175,9 @@ def test_append_fused_into_decode_attention(case):
         full = fused.begin_gather(fs)
         mid = backend.launches
         got = fused.decode_update(0, full, k1, v1, q)
-        assert backend.launches == mid + 1 and mid - launches <= 2       # one kernel; the rest is table upkeep
+        # the attention kernel, plus the small kernel that combines the splits' partial results when sequences
+        # are long enough to be split; the rest is table upkeep
+        assert backend.launches - mid in (1, 2) and mid - launches <= 2
         new = plain.begin_append(pl, [1] * n)
         plain.append(0, new, k1, v1)
         plain.end_append(new)
@@ -225,7 +228,7 @@ def test_decode_graph_with_attention_replays_what_eager_steps_compute():
         graph.step()
         if step == 1:
             graph.record()
-            assert graph.launches_per_replay == L
+            assert graph.launches_per_replay in (L, 2 * L)       # per layer: attention (+ the combining kernel)
         new = b.begin_append(sb, [1] * n)
         b.end_append(new)
         full = b.begin_gather(sb)
