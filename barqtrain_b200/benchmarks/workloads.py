@@ -154,7 +154,7 @@ def churn(world: int, rank: int, device, steps: int, warmup: int, layers: int = 
     initial lengths uniform in [128, 2048]; every step appends one token to every live sequence in every
     layer, then each sequence finishes with seeded probability 0.01, returns its pages to the free list
     and is replaced by a new sequence with a 512-token prefill.  ``attend``: the decode step also attends
-    over the pages (4 query heads per KV head) - per layer one launch that stores the token and attends,
+    over the pages (4 query heads per KV head) - per layer one call that stores the token and attends,
     replayed from a CUDA graph whose batch rows are re-pointed at the replacements (``DecodeGraphs``)."""
     H = heads or kv_head_shard(8, world, rank)[1]
     dtype = torch.float16
@@ -272,7 +272,7 @@ def churn(world: int, rank: int, device, steps: int, warmup: int, layers: int = 
             "launches": counters["launches"],
             "config": {"workload": "continuous-batching-churn", "layers": layers, "kv_heads_per_gpu": H,
                        "dtype": "fp16", "page_size": 16, "live_sequences": live,
-                       "step": ("per layer, store 1 token of 256 sequences and attend over their pages (one launch per "
+                       "step": ("per layer, store 1 token of 256 sequences and attend over their pages (one call per "
                                 "layer, CUDA graph)" if attend else "append 1 token to 256 sequences in every layer (one "
                                 "launch for all layers)") + "; finished sequences (p=0.01) release their pages and are "
                                "replaced by a 512-token prefill",
@@ -287,8 +287,9 @@ def decode_attention(world: int, rank: int, device, steps: int, warmup: int, lay
                      eager: bool = False, sync=lambda: None) -> Dict:
     """The decode configuration (32 layers, 8 KV heads x 4 query heads, head_dim 128, bf16, page 16, 64
     sequences uniform [512, 4096]) with attention reading the pages directly: a step is, per layer, ONE
-    launch that stores the step's token and attends over the pages - no separate append, no gather -
-    replayed from a CUDA graph (``eager``: append + attention called per layer from Python, two launches).
+    call that stores the step's token and attends over the pages - no separate append, no gather; the
+    attention kernel and the small kernel that combines its splits' partial results - replayed from a CUDA
+    graph (``eager``: append + attention called per layer from Python).
     Bytes counted: K and V read once (2*sum_len*H*D*e per layer) plus the append's 4*B*H*D*e."""
     from ..block_table import DecodeStepGraph
 
@@ -323,7 +324,6 @@ def decode_attention(world: int, rank: int, device, steps: int, warmup: int, lay
                 cache.append(layer, new, new_rows[layer], new_rows[layer])
                 cache.decode_attention(layer, full, q, out=out)
             moved["bytes"] += (2 * full.total + 4 * B) * H * D * 2 * layers
-        per_layer = 2
     else:
         graph = DecodeStepGraph(cache, slots, capacity_tokens=sum(lens) + B * total_steps, what="attention",
                                 q_heads=H * group, max_len=max(lens) + total_steps)
@@ -336,12 +336,18 @@ def decode_attention(world: int, rank: int, device, steps: int, warmup: int, lay
         def step():
             total = graph.step()
             moved["bytes"] += (2 * total + 4 * B) * H * D * 2 * layers
-        per_layer = 1
 
     for _ in range(max(warmup, 1)):
         step()
     sync()
     moved["bytes"] = 0
+    # kernels per step, by the library's own count: eager steps count as they go, a replay runs what was recorded
+    before = cache.backend.launches
+    if eager:
+        step()
+        sync()
+        moved["bytes"] = 0
+    per_step = cache.backend.launches - before if eager else graph.launches_per_replay
     e0, e1 = _events()
     e0.record()
     for _ in range(steps):
@@ -350,11 +356,12 @@ def decode_attention(world: int, rank: int, device, steps: int, warmup: int, lay
     sync()
     ms = e0.elapsed_time(e1)
     cache.check_device_status()
-    return {"bytes": moved["bytes"], "ms": ms, "tokens": B * steps, "launches": per_layer * layers * steps,
+    return {"bytes": moved["bytes"], "ms": ms, "tokens": B * steps, "launches": per_step * steps,
             "config": {"workload": "llama3-8b-decode-attention-from-pages", "layers": layers, "kv_heads_per_gpu": H,
                        "query_heads_per_kv_head": group, "dtype": "bf16", "page_size": 16, "sequences": B,
                        "launch": "append + attention per layer, called from Python" if eager
-                       else "one launch per layer (append fused into attention), replayed from a CUDA graph",
+                       else "one call per layer (append fused into attention; the attention kernel and the kernel that "
+                            "combines its splits), replayed from a CUDA graph",
                        "step": "per layer: store 1 token/seq and attend over the pages (no gather); bytes = K and V "
                                "read once + appended rows",
                        "l2": "inputs larger than L2: each step reads ~%.1f GB of pool per GPU"

@@ -887,7 +887,7 @@ class BlockTableKVCache:
 
         ``new_rows=(k_new, v_new)``, each ``[n, kv_heads, head_dim]``: the step's token has NOT been appended
         yet (its page is reserved, the lengths already count it); the same launch stores the rows into the
-        pages and attends them - a decode layer in one launch (``decode_update``).  ``max_len`` /
+        pages and attends them - a decode layer in one call (``decode_update``).  ``max_len`` /
         ``total_len`` override the description's longest length and sum of lengths (they fix the launch
         shape and the workspace size; a recorded CUDA graph passes bounds that hold for all its replays).
         """
@@ -945,7 +945,7 @@ class BlockTableKVCache:
 
     def decode_update(self, layer: int, full: _Descriptor, k_new: torch.Tensor, v_new: torch.Tensor, q: torch.Tensor,
                       scale: Optional[float] = None, out: Optional[torch.Tensor] = None, **bounds) -> torch.Tensor:
-        """A decode layer in one launch: store the step's K/V rows into the pages and attend over the pages,
+        """A decode layer in one call: store the step's K/V rows into the pages and attend over the pages,
         new token included (``barqkv_paged_decode_update``).  Call ``begin_append`` / ``end_append`` /
         ``begin_gather`` for the step first, as for ``update``; skip the layer's ``append``."""
         return self.decode_attention(layer, full, q, scale=scale, out=out, new_rows=(k_new, v_new), **bounds)
@@ -994,7 +994,7 @@ class DecodeStepGraph:
                  one_stream: bool = False):
         """``what``: ``"update"`` (append + gather per layer, the default), ``"append"`` (the append alone, one
         launch per layer), ``"append_layers"`` (the append alone, one launch for all layers) or ``"attention"``
-        (append fused into attention over the pages, one launch per layer, no gather: fill ``q_in``
+        (append fused into attention over the pages, one call per layer, no gather: fill ``q_in``
         ``[batch, q_heads, head_dim]``, read ``attn_out``; ``max_len`` bounds the longest sequence over all
         replays and ``capacity_tokens`` the sum of the lengths).  Only ``"update"`` needs output buffers."""
         if what not in ("update", "append", "append_layers", "attention"):

@@ -8,7 +8,7 @@ layer that returns contiguous ``[batch, kv_heads, length, head_dim]`` K/V.
 With ``attention_from_pages=True`` and the attention function of this module selected
 (``use_paged_attention(model)``), single-token decode steps skip the gather altogether: ``update`` hands
 the attention function a tag carrying the new rows, and the attention function stores them and reads K/V
-from the pages in one launch (``BlockTableKVCache.decode_update``).  Prefill and multi-token steps keep using the gathered tensors
+from the pages in one call (``BlockTableKVCache.decode_update``).  Prefill and multi-token steps keep using the gathered tensors
 with the stock SDPA path.  From-pages decoding attends every cached token of a row, so it is for batches
 without padding: a decode step whose attention mask hides any position is refused with an error.
 """

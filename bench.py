@@ -858,7 +858,7 @@ def run_micro(args):
                     many.update_layers(new, full, k_all, k_all, outs, "HND", mode=args.mode)
             return launch, args.layers * args.reps, (full.total + B) * per_tok * args.layers * args.reps
         if args.micro == "decode-update":
-            # a decode layer in one launch: the step's rows stored and attended by the same kernel
+            # a decode layer in one call: the step's rows stored and attended by the same kernel
             total = sum(lens)
             k = torch.randn(total, H, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
             if cache.lengths[slots[0]] == 0:
@@ -941,8 +941,10 @@ def run_micro(args):
                 launch()
             torch.cuda.synchronize(device)
             graph = torch.cuda.CUDAGraph()
+            counted = backend.launches
             with torch.cuda.graph(graph, stream=side):
                 launch()
+            kernels = backend.launches - counted
             graph.replay()
             torch.cuda.synchronize(device)
             evs = [timed(graph.replay) for _ in range(args.steps)]
@@ -951,14 +953,19 @@ def run_micro(args):
         for _ in range(args.warmup):
             launch()
         torch.cuda.synchronize(device)
+        counted = backend.launches
         evs = [timed(launch) for _ in range(args.steps)]
+        kernels = (backend.launches - counted) // max(args.steps, 1)
     args.warmup = 0
     torch.cuda.synchronize(device)
     times = sorted(e0.elapsed_time(e1) * 1e-3 for e0, e1 in evs[args.warmup:])
     med = times[len(times) // 2]
     peak, kind = measured_peak()
     status = backend.read_status(device)
+    # `launches_per_sample` counts calls of the library; `kernels_per_sample` what they enqueued (a decode
+    # attention call is two kernels when sequences are split; --impl torch / reference are not counted)
     print(json.dumps({"micro": args.micro, "impl": args.impl, "tune": args.tune, "graph": bool(args.graph), "launches_per_sample": reps,
+                      "kernels_per_sample": kernels,
                       "us_per_launch": round(med * 1e6 / reps, 2), "mode": args.mode, "layout": args.layout, "heads": H, "page_size": ps,
                       "sequences": B, "tokens": sum(lens) if args.micro == "gather" else None,
                       "bytes_per_launch": nbytes, "us_median": round(med * 1e6, 2), "us_min": round(times[0] * 1e6, 2),

@@ -139,7 +139,7 @@ def test_decode_attention_workspace_survives_changing_batches():
     dict(dtype=torch.bfloat16, hkv=8, group=4, lens=LARGE_LENS, ps=16),
 ])
 def test_append_fused_into_decode_attention(case):
-    """``decode_update`` (one launch: store the step's rows and attend) against append-then-attend on a twin
+    """``decode_update`` (one call: store the step's rows and attend) against append-then-attend on a twin
     cache: the pools end up bit-identical, the attention outputs are identical too (the same arithmetic on the
     same values), and both stay within the fp32 reference's tolerance.  Two steps in a row, so the second
     attends a token the first one stored."""
