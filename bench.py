@@ -522,7 +522,7 @@ def run_barqkv(args):
 
 def run_legs(world, rank, local, device, barrier, max_over_ranks, backend, peak, peak_kind, quick=False):
     """Short legs of the other configurations (chunked prefill at page 16 and 32, the 70B-shaped gather,
-    continuous-batching churn), each through ``barqtrain_b200.benchmarks.workloads`` at the
+    continuous-batching churn, the decode configuration with attention from the pages), each through ``barqtrain_b200.benchmarks.workloads`` at the
     configuration's full shape for this rank's KV-head shard; one entry per leg."""
     from barqtrain_b200.benchmarks.workloads import WORKLOADS
 
@@ -533,12 +533,14 @@ def run_legs(world, rank, local, device, barrier, max_over_ranks, backend, peak,
         ("chunked-prefill-ps32", "prefill", dict(page_size=32), 640, 8),
         ("llama3-70b-gather", "gather70b", {}, 44, 3),
         ("continuous-batching-churn", "churn", {}, 1000, 20),
+        # the decode configuration once more with attention reading the pages instead of the gather (K/V read once)
+        ("decode-attention-from-pages", "decode-attn", {}, 200, 5),
     ]
     out = {}
     for name, key, kwargs, steps, warmup in plan:
         if quick:
             steps, warmup = max(4, steps // 8), 3
-            if key != "churn":
+            if key not in ("churn", "decode-attn"):
                 kwargs = dict(kwargs, layers=8)
         try:
             with ClockSampler(local) as clocks:
