@@ -43,6 +43,11 @@ def _reference(cache, layer, slots, q, scale):
     dict(dtype=torch.float16, hkv=2, group=2, lens=(63, 64, 65, 17, 700), seed=6, ps=64),
     dict(dtype=torch.bfloat16, hkv=8, group=4, lens=LARGE_LENS, seed=7),
     dict(dtype=torch.float16, hkv=8, group=2, lens=LARGE_LENS, seed=8),
+    # one long sequence in a small batch: 40 splits, combined by the four-part form of the combining kernel,
+    # eight query heads per KV head (two rounds of four warps)
+    dict(dtype=torch.bfloat16, hkv=1, group=8, lens=(20000, 700, 5), seed=9),
+    # more than 256 sequences: the grid has one CTA per possible split instead of the gap-free list
+    dict(dtype=torch.float16, hkv=2, group=4, lens=tuple(300 + 3 * i for i in range(300)), seed=10),
 ])
 def test_decode_attention_matches_fp32_reference(case):
     from barqtrain_b200 import BlockTableKVCache, _ffi
@@ -81,6 +86,43 @@ def test_decode_attention_matches_fp32_reference(case):
     gb, want = _reference(cache, 1, [slots[i] for i in order], q2, scale)
     got = cache.decode_attention(1, gb, q2)
     assert bool(((got.float() - want).abs() <= ATOL + RTOL * want.abs()).all())
+    assert backend.read_status(DEV) == 0
+
+
+def test_decode_attention_with_pools_in_separate_allocations():
+    """The C entry point with a V pool that does not lie behind the K pool in one allocation (here: before it),
+    so a ring stage is filled by one copy per pool instead of one for both: same result as the cache's own call."""
+    from barqtrain_b200 import BlockTableKVCache, _ffi
+
+    backend = _ffi.require_cuda_backend()
+    dtype, hkv, group, D, ps = torch.bfloat16, 2, 4, 128, 16
+    lens = [1500, 40, 700, 2049]
+    n = len(lens)
+    g = torch.Generator(device=DEV).manual_seed(31)
+    cache = BlockTableKVCache(1, hkv, D, page_size=ps, num_pages=sum(-(-x // ps) for x in lens) + 2, max_seqs=n,
+                              max_blocks_per_seq=-(-max(lens) // ps), dtype=dtype, device=DEV, seed=31)
+    slots = [cache.open(i) for i in range(n)]
+    k = torch.randn(sum(lens), hkv, D, generator=g, device=DEV, dtype=torch.float32).to(dtype)
+    v = torch.randn(sum(lens), hkv, D, generator=g, device=DEV, dtype=torch.float32).to(dtype)
+    cache.append_step(slots, lens, [k], [v])
+    q = torch.randn(n, hkv * group, D, generator=g, device=DEV, dtype=torch.float32).to(dtype)
+    full = cache.begin_gather(slots)
+    want = cache.decode_attention(0, full, q).clone()
+    both = torch.empty(2, *cache.pools[0, 0].shape, dtype=dtype, device=DEV)      # V first, K behind it
+    both[0].copy_(cache.pools[0, 1])
+    both[1].copy_(cache.pools[0, 0])
+    got = torch.empty_like(q)
+    lib = backend.lib
+    need = int(lib.barqkv_paged_decode_workspace_bytes(n, hkv, full.max_first, full.total, ps))
+    ws = torch.empty(max(need, 16), dtype=torch.uint8, device=DEV)
+    stream = full.stream
+    rc = lib.barqkv_paged_decode_attention(
+        cache._pool_ref, both[1].data_ptr(), both[0].data_ptr(), full.table_ref, full.p_first, n,
+        q.data_ptr(), q.stride(0), q.stride(1), got.data_ptr(), got.stride(0), got.stride(1), hkv * group,
+        float(D ** -0.5), 1, full.max_first, full.total, ws.data_ptr() if need else None, need, None, stream)
+    assert rc == 0, backend.last_error()
+    torch.cuda.synchronize()
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
     assert backend.read_status(DEV) == 0
 
 
