@@ -153,7 +153,9 @@ def churn(world: int, rank: int, device, steps: int, warmup: int, layers: int = 
     """Continuous batching: 32 layers, 8 KV heads, head_dim 128, fp16, page 16; 256 live sequences with
     initial lengths uniform in [128, 2048]; every step appends one token to every live sequence in every
     layer, then each sequence finishes with seeded probability 0.01, returns its pages to the free list
-    and is replaced by a new sequence with a 512-token prefill.  ``attend``: the decode step also attends
+    and is replaced by a new sequence with a 512-token prefill.  The replacements' prompts travel in the next
+    step's launch, beside the other sequences' decode tokens - one ragged batch per step, as a server that
+    mixes prefill chunks and decode tokens forms it.  ``attend``: the decode step also attends
     over the pages (4 query heads per KV head) - per layer one call that stores the token and attends,
     replayed from a CUDA graph whose batch rows are re-pointed at the replacements (``DecodeGraphs``)."""
     H = heads or kv_head_shard(8, world, rank)[1]
@@ -168,18 +170,20 @@ def churn(world: int, rank: int, device, steps: int, warmup: int, layers: int = 
                               max_blocks_per_seq=-(-cap // 16), dtype=dtype, device=device,
                               free_order=torch.randperm(pages, generator=g).tolist(), zero_pages=False)
     gen = torch.Generator(device=device).manual_seed(1239 + rank)
-    rows = torch.randn(max(max(lens0), 512) * 8, H, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
+    rows = torch.randn(max(max(lens0), 512 * 4) * 8 + live, H, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
     ids = list(range(live))
     slots = np.array([cache.open(i) for i in ids], dtype=np.int32)
     next_id = live
     # set-up: initial contents, in slices so that the packed source stays small
     origin = [None] * live            # per live sequence: (first row, count) of its prefill in `rows`
-    decoded = np.zeros(live, dtype=np.int64)   # decode tokens appended since (each is rows[j])
+    decoded = np.zeros(live, dtype=np.int64)   # decode tokens appended since (each is rows[j]; `attend` only)
+    history = [[] for _ in range(live)]        # per live sequence: (first row, count) of every append (``verify``)
     for lo in range(0, live, 8):
         part, counts = slots[lo:lo + 8].tolist(), lens0[lo:lo + 8]
         at = 0
         for j, c in zip(range(lo, lo + 8), counts):
             origin[j] = (at, c)
+            history[j].append((at, c))
             at += c
         batch = cache.begin_append(part, counts)
         for layer in range(layers):
@@ -187,8 +191,12 @@ def churn(world: int, rank: int, device, steps: int, warmup: int, layers: int = 
         cache.end_append(batch)
     # the step's new rows, [layers, live, H, D], and the replacement prompts' rows, [layers, 32 * 512, H, D]: every
     # layer has rows of its own (layer l holds the shared rows, so that the read-back check stays simple)
-    one_all = rows[:live].unsqueeze(0).repeat(layers, 1, 1, 1)
-    prompt_all = rows[: 512 * 32].unsqueeze(0).repeat(layers, 1, 1, 1)
+    one_all = rows[:live].unsqueeze(0).repeat(layers, 1, 1, 1) if attend else None
+    prompt_all = rows[: 512 * 32].unsqueeze(0).repeat(layers, 1, 1, 1) if attend else None
+    # a mixed step's packed rows, [layers, up to 32 prompts + live tokens, H, D]: entry j of the batch takes the
+    # rows from its offset in the step's running count
+    mixed_all = None if attend else rows[: 512 * 32 + live].unsqueeze(0).repeat(layers, 1, 1, 1)
+    fresh_at: list = []               # batch positions whose sequence was opened after the last launch
     finished = (torch.rand(total_steps, live, generator=g) < 0.01).numpy()
     ones = np.ones(live, dtype=np.int32)
     counters = {"tokens": 0, "host_s": 0.0, "released": 0, "launches": 0, "attended": 0}
@@ -203,7 +211,7 @@ def churn(world: int, rank: int, device, steps: int, warmup: int, layers: int = 
         g0.q_in.normal_(generator=gen)
 
     def step(i):
-        nonlocal next_id
+        nonlocal next_id, fresh_at
         if attend:
             t0 = time.perf_counter()
             graph = graphs.step(slots.tolist())                # host work of the step is inside (native description)
@@ -212,15 +220,40 @@ def churn(world: int, rank: int, device, steps: int, warmup: int, layers: int = 
             counters["launches"] += layers
         else:
             t0 = time.perf_counter()
-            batch = cache.begin_append(slots, ones)
+            counts = ones
+            if fresh_at:
+                counts = ones.copy()
+                counts[fresh_at] = 512
+            batch = cache.begin_append(slots, counts)
             counters["host_s"] += time.perf_counter() - t0
-            cache.append_layers(batch, one_all, one_all)       # all layers' rows of the step in one launch
+            total = live + 511 * len(fresh_at)
+            mixed = mixed_all[:, :total]
+            cache.append_layers(batch, mixed, mixed)           # all layers' rows of the step in one launch
             cache.end_append(batch)
             counters["launches"] += 1
+            counters["tokens"] += total - live                 # the prompts; the decode tokens are counted below
+            if verify:
+                at = 0
+                for j in range(live):
+                    history[j].append((at, int(counts[j])))
+                    at += int(counts[j])
+            fresh_at = []
         counters["tokens"] += live
         decoded[:] += 1
         gone = np.nonzero(finished[i])[0].tolist()
-        if gone:
+        if gone and not attend:
+            t0 = time.perf_counter()
+            for j in gone[:32]:        # a step's packed rows hold 32 prompts; more than 32 of 256 finishing in one
+                #                        step at p = 0.01 has probability < 1e-30, the rest would wait a step
+                cache.release(ids[j])
+                ids[j] = next_id
+                next_id += 1
+                slots[j] = cache.open(ids[j])
+                history[j] = []
+                fresh_at.append(j)
+            counters["host_s"] += time.perf_counter() - t0
+            counters["released"] += len(fresh_at)
+        elif gone:
             t0 = time.perf_counter()
             fresh = []
             for j in gone[:32]:        # the packed prefill source holds 32 prompts; more than 32 of 256 finishing in
@@ -261,10 +294,15 @@ def churn(world: int, rank: int, device, steps: int, warmup: int, layers: int = 
         for layer in sorted({0, layers - 1}):
             kn, vn = cache.gather(layer, gb, "NHD")
             for j in range(live):
-                first, count = origin[j]
-                want = torch.cat([rows[first:first + count], rows[j:j + 1].expand(int(decoded[j]), -1, -1)])
+                if attend:
+                    first, count = origin[j]
+                    want = torch.cat([rows[first:first + count], rows[j:j + 1].expand(int(decoded[j]), -1, -1)])
+                else:
+                    index = np.concatenate([np.arange(first, first + count) for first, count in history[j]] or
+                                           [np.zeros(0, dtype=np.int64)])
+                    want = rows[torch.from_numpy(index).to(device)]
                 a, b = gb.cu[j], gb.cu[j + 1]
-                if b - a != count + int(decoded[j]) or not torch.equal(kn[a:b], want) or not torch.equal(vn[a:b], want):
+                if b - a != want.shape[0] or not torch.equal(kn[a:b], want) or not torch.equal(vn[a:b], want):
                     verified = False
     st = cache.stats()
     return {"bytes": (4 * counters["tokens"] + 2 * counters["attended"]) * H * D * 2 * layers, "ms": ms,
@@ -273,10 +311,12 @@ def churn(world: int, rank: int, device, steps: int, warmup: int, layers: int = 
             "config": {"workload": "continuous-batching-churn", "layers": layers, "kv_heads_per_gpu": H,
                        "dtype": "fp16", "page_size": 16, "live_sequences": live,
                        "step": ("per layer, store 1 token of 256 sequences and attend over their pages (one call per "
-                                "layer, CUDA graph)" if attend else "append 1 token to 256 sequences in every layer (one "
-                                "launch for all layers)") + "; finished sequences (p=0.01) release their pages and are "
-                               "replaced by a 512-token prefill",
-                       "l2": "decode appends are 1 MB per launch (L2-resident, launch-bound); prefills stream"},
+                                "layer, CUDA graph); finished sequences (p=0.01) release their pages and are replaced "
+                                "by a 512-token prefill" if attend else
+                                "one ragged launch for all layers: 1 token for each of 256 sequences, and the 512-token "
+                                "prompt of every sequence that replaced one that finished (p=0.01) and released its "
+                                "pages the step before"),
+                       "l2": "a step's decode rows are 2 MB per layer (L2-resident); the prompts stream"},
             "extra": {"sequences_released": counters["released"], "pages_total": st.pages_total,
                       "pages_resident": st.pages_resident, "pages_peak": st.pages_peak,
                       "bytes_peak": st.bytes_peak,
