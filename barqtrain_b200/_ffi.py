@@ -70,7 +70,7 @@ EXPORTS = ("barqkv_version", "barqkv_last_error", "barqkv_sm_count", "barqkv_lau
            "barqkv_host_attach", "barqkv_host_begin", "barqkv_paged_decode_update")
 # experiment knobs: only a library built with -DBARQKV_TUNING exports barqkv_set_tuning (include/barqkv_experimental.h)
 KNOBS = {"stages": 1, "ctas": 2, "vctas": 3, "interleave": 4, "group": 5, "static": 6, "pdl": 7, "fixed": 8, "tensor_store": 9,
-         "attn_promotion": 10, "attn_split": 11, "append_bulk": 12, "attn_wide": 13, "layer_overlap": 14, "attn_page_box": 15, "attn_compact": 16, "attn_probe": 17}
+         "attn_promotion": 10, "attn_split": 11, "append_bulk": 12, "attn_wide": 13, "layer_overlap": 14, "attn_page_box": 15, "attn_compact": 16, "attn_probe": 17, "zero_ahead": 18}
 STATIC_WORK_SLOTS = 32
 
 

@@ -137,6 +137,8 @@ struct GatherArgs {
     int stages;            // bulk kernel only
     int interleave;        // 1: CTAs take every gridDim-th group of tiles instead of one contiguous share
     int32_t* work;         // bulk kernel: [0] next group to hand out, [1] CTAs finished; null = static shares
+    int32_t* zero_ahead;   // bulk kernel: another counter pair, cleared once the kernel before this one has finished
+    int rearm;             // bulk kernel: the last CTA to finish clears `work` (else a later launch's zero_ahead does)
     int group_tiles;       // bulk kernel, dynamic hand-out: (sequence, page) tiles per group
     int static_permille;   // bulk kernel, dynamic hand-out: thousandths of the tiles split evenly up front
     int first_group;       // bulk kernel, dynamic hand-out: tiles of every CTA's first group (fetched before the scan)
@@ -700,8 +702,20 @@ gather_bulk_kernel(const GatherArgs a, const __grid_constant__ CUtensorMap out_m
     // Everything up to the first copy reads only the batch description and the block table.  When the
     // caller vouches that those are older than the kernel before this one (a.early), that part runs
     // while that kernel is still draining; otherwise it starts after it.
+    // In a chain of launches that alternate between two counter pairs nobody counts finished CTAs: the launch that
+    // uses one pair clears the other - last used by the launch before it, which has finished when the wait below
+    // returns, and next used by the launch after it, which cannot start its prologue before every CTA of this
+    // launch, the clearing one included, has let it in.
+    auto clear_other_pair = [&]() {
+        if (a.zero_ahead && blockIdx.x == 0 && lane == 0) {
+            a.zero_ahead[0] = 0;
+            a.zero_ahead[1] = 0;
+            __threadfence();
+        }
+    };
     if (!a.early) {
         pdl_wait_for_predecessor();
+        clear_other_pair();
         pdl_let_successor_in();
     }
     // The first group's size comes from the host's bound of the tile count, so its fetch can travel
@@ -788,6 +802,7 @@ gather_bulk_kernel(const GatherArgs a, const __grid_constant__ CUtensorMap out_m
     if (a.early) {
         if (more) stage_group();
         pdl_wait_for_predecessor();     // from here on the pools, the new rows and the outputs are touched
+        clear_other_pair();
         pdl_let_successor_in();
     }
 
@@ -910,7 +925,7 @@ gather_bulk_kernel(const GatherArgs a, const __grid_constant__ CUtensorMap out_m
         }
         if (lane == 0) raise(a.status, BARQKV_S_TIMEOUT);
     }
-    if (dynamic && lane == 0) {
+    if (dynamic && a.rearm && lane == 0) {
         // The last CTA to finish re-arms the counters for the next launch.
         __threadfence();
         const int finished = atomicAdd(a.work + 1, 1);
@@ -1175,6 +1190,8 @@ struct Knobs {
     int layer_overlap = 1;       // update_layers issues odd layers on a second stream (0: one stream, one chain)
     int attn_page_box = 2;       // decode attention loads a head's page of K and of V with one copy instruction where the pools allow it
                                  // (1: one instruction for K, one for V; 0: two half-page boxes each)
+    int zero_ahead = 1;          // update_layers: a launch clears the counter pair of its neighbours in the chain instead of
+                                 // every launch counting its finished CTAs to clear its own (0: every launch re-arms itself)
     int attn_probe = 0;          // timing probes (results are wrong): 1 = decode attention loads pages without attending them, 2 = writes no result
     int attn_compact = 1;        // decode attention: the grid lists only splits that have pages (0: one CTA per possible split)
     int attn_wide = -1;          // decode attention updates its softmax state every 32 tokens (1) or 16 (0);
@@ -1432,6 +1449,7 @@ int barqkv_set_tuning(int32_t knob, int32_t value) {
         case BARQKV_KNOB_ATTN_PAGE_BOX: g_knobs.attn_page_box = value; return 0;
         case BARQKV_KNOB_ATTN_COMPACT: g_knobs.attn_compact = value; return 0;
         case BARQKV_KNOB_ATTN_PROBE: g_knobs.attn_probe = value; return 0;
+        case BARQKV_KNOB_ZERO_AHEAD: g_knobs.zero_ahead = value; return 0;
         default: return fail(BARQKV_E_INVALID, "set_tuning: unknown knob");
     }
 }
@@ -1817,6 +1835,9 @@ struct LaunchOpts {
     int extra_tx = 0;                // self-test: make every stage wait for bytes that never come
     int max_ctas = 0;                // self-test: cap of the grid (0 = none)
     bool validate_only = false;      // check the arguments, enqueue nothing
+    int32_t* zero_ahead = nullptr;   // chained launches: the counter pair of the launch before and after this one, which
+                                     // this launch clears; with it and rearm = false nobody counts finished CTAs
+    bool rearm = true;               // the launch leaves its own counter pair zero
 };
 
 static int gather_common(const barqkv_pool_layout* pool, const void* k_pool, const void* v_pool,
@@ -1864,6 +1885,8 @@ static int gather_common(const barqkv_pool_layout* pool, const void* k_pool, con
     a.status = status;
     a.interleave = g_knobs.interleave < 0 ? 0 : g_knobs.interleave;
     a.work = g_knobs.static_shares ? nullptr : work;
+    a.zero_ahead = a.work ? opts.zero_ahead : nullptr;
+    a.rearm = opts.rearm || !a.zero_ahead ? 1 : 0;
     // tiles per hand-out: about 4 (page, head) units, i.e. 32 KiB of K and V, per atomic fetch
     a.group_tiles = g_knobs.group_tiles ? g_knobs.group_tiles : (a.heads >= 4 ? (a.heads >= 8 ? 1 : 2) : 4);
     if (a.group_tiles > kGroup) a.group_tiles = kGroup;
@@ -2103,7 +2126,13 @@ int barqkv_update_layers(const barqkv_pool_layout* pool, void* k_pool, void* v_p
         }
     }
     // whatever happens below, the second stream is joined back before the call returns
+    bool chained_pairs = false;      // some launch left clearing its counter pair to its successor
     auto done = [&](int rc) {
+        if (rc != 0 && chained_pairs) {
+            // the chain broke off: the successor that would have cleared the last launch's pair never came
+            if (overlap) cudaMemsetAsync(work, 0, 8 * sizeof(int32_t), dev->lane);
+            cudaMemsetAsync(work, 0, 8 * sizeof(int32_t), main_stream);
+        }
         if (overlap && (cudaEventRecord(dev->lane_join, dev->lane) != cudaSuccess ||
                         cudaStreamWaitEvent(main_stream, dev->lane_join, 0) != cudaSuccess) && rc == 0)
             rc = fail(BARQKV_E_LAUNCH, "update_layers: could not join the second stream");
@@ -2125,6 +2154,13 @@ int barqkv_update_layers(const barqkv_pool_layout* pool, void* k_pool, void* v_p
             LaunchOpts opts;
             opts.after_own_kernel = overlap ? l >= 2 : l > 0;
             int32_t* pair = !work ? nullptr : work + 2 * (overlap ? (l & 3) : (l & 1));
+            if (work && g_knobs.zero_ahead != 0) {
+                // a chain alternates between two pairs; each launch clears the one it does not use, and only the
+                // chain's last launch counts its finished CTAs to clear its own
+                opts.zero_ahead = work + 2 * (overlap ? ((l + 2) & 3) : ((l + 1) & 1));
+                opts.rearm = l + (overlap ? 2 : 1) >= layers;
+                chained_pairs = true;
+            }
             const int rc = gather_common(pool, kp, vp, table, seq_start, cu_out, n, total_tokens_hint, ko, vo, out_rows, mode,
                                          status, pair, overlap && (l & 1) ? static_cast<barqkv_stream_t>(dev->lane) : stream,
                                          &fused, nullptr, opts);

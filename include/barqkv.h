@@ -322,7 +322,8 @@ int barqkv_update(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,
  * behind every layer.  Other calls, and calls whose `mode` carries BARQKV_FLAG_ONE_STREAM, keep all layers on
  * `stream`, each behind the one before.
  * work: device int32[8] scratch, zero before its first use (four counter pairs, so that launches that can be
- * on the device together never share one); the kernels leave it zero.  For callers that have every layer's
+ * on the device together never share one); zero again when the call's last kernels have run (inside the call
+ * a launch clears the pair of its neighbours in its stream's chain, only the last launch of a chain its own).  For callers that have every layer's
  * new rows at hand (a recorded decode step, cache import); results equal `layers` calls of barqkv_update.
  */
 int barqkv_update_layers(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,

@@ -34,6 +34,7 @@ extern "C" {
 #define BARQKV_KNOB_ATTN_PAGE_BOX 15     /* decode attention, pages per copy instruction. 0: half of K or V; 1: K or V; 2 (default): K and V where the pools allow it */
 #define BARQKV_KNOB_ATTN_COMPACT 16      /* 0: decode attention launches one CTA per possible split of every sequence (default 1: only splits that can have pages, batches of up to 256) */
 #define BARQKV_KNOB_ATTN_PROBE 17        /* timing probes, results are wrong. 1: decode attention loads pages but does not attend them; 2: writes no result; 3: both */
+#define BARQKV_KNOB_ZERO_AHEAD 18         /* 0: every launch of barqkv_update_layers counts its finished CTAs and clears its own counter pair (default 1: a launch clears the pair of its neighbours in the chain) */
 
 int barqkv_set_tuning(int32_t knob, int32_t value);
 
