@@ -228,7 +228,7 @@ class CudaBackend:
         bits = self.read_status(device)
         if bits:
             names = [n for b, n in ((S_BAD_PAGE, "block-table entry out of range"),
-                                    (S_CAPACITY, "paged KV cache capacity exceeded"),
+                                    (S_CAPACITY, "paged KV cache capacity exceeded, or decode attention given a sum of lengths below the real one"),
                                     (S_TIMEOUT, "bulk-copy wait timed out"),
                                     (S_BAD_SLOT, "sequence slot out of range")) if bits & b]
             raise BarqKVError("device-side guard: " + ", ".join(names))

@@ -160,12 +160,15 @@ paged_decode_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap map_k,
             my_row[c] = i < a.n ? (a.tb.slots ? a.tb.slots[i] : i) : 0;
         }
         const int item = blockIdx.x;
+        // the first CTA adds the counts up to the end: the grid was sized from the caller's sum of the lengths,
+        // and a batch with more splits than that would lose some without a trace
+        const bool count_all = blockIdx.x == 0 && blockIdx.y == 0;
         int before = 0;
         seq = -1;
         len = row = 0;
 #pragma unroll
         for (int c = 0; c < kAttnCompactSeqs / 32; ++c) {
-            if (seq < 0 && c * 32 < a.n) {
+            if ((seq < 0 || count_all) && c * 32 < a.n) {
                 const int pg = (max(my_len[c], 0) + PS - 1) / PS;
                 const int count = min(a.splits, (pg + a.split_pages - 1) / a.split_pages);
                 int upto = count;                                   // inclusive running sum over the lanes
@@ -174,7 +177,7 @@ paged_decode_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap map_k,
                     const int t = __shfl_up_sync(0xffffffffu, upto, d);
                     if (lane >= d) upto += t;
                 }
-                const unsigned holds = __ballot_sync(0xffffffffu, before + upto > item);
+                const unsigned holds = seq < 0 ? __ballot_sync(0xffffffffu, before + upto > item) : 0u;
                 if (holds) {
                     const int src = __ffs(holds) - 1;
                     seq = c * 32 + src;
@@ -185,6 +188,7 @@ paged_decode_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap map_k,
                 before += __shfl_sync(0xffffffffu, upto, 31);
             }
         }
+        if (count_all && lane == 0 && before > (int)gridDim.x) raise(a.status, BARQKV_S_CAPACITY);
         if (seq < 0) {
             if (a.early) { pdl_wait_for_predecessor(); pdl_let_successor_in(); }
             return;

@@ -35,7 +35,8 @@ extern "C" {
 
 /* bits a kernel may OR into *status (device int32, optional) */
 #define BARQKV_S_BAD_PAGE 1   /* block-table entry outside [0, num_pages): row skipped */
-#define BARQKV_S_CAPACITY 2   /* reference-layout append would pass the cache capacity: nothing written */
+#define BARQKV_S_CAPACITY 2   /* reference-layout append would pass the cache capacity: nothing written; decode attention: the
+                                 lengths add up to more than the total_len the call was given, some pages were not attended */
 #define BARQKV_S_TIMEOUT 4    /* a bounded wait on a bulk copy gave up: remaining pages skipped */
 #define BARQKV_S_BAD_SLOT 8   /* sequence slot outside the block table: sequence skipped */
 
@@ -376,7 +377,8 @@ int barqkv_gather_layers(const barqkv_pool_layout* pool, const void* k_pool, con
  * q / out: [n, num_q_heads, 128] in the pool's 2-byte type (is_bf16 selects bf16 or fp16), strides in
  * elements; query head j uses KV head j / (num_q_heads / kv_heads).  seq_lens: lengths including the
  * current token (append first).  max_len: an upper bound of the lengths known to the host; total_len:
- * the host's sum of the lengths, or 0 when it is not known.  The two fix how many splits a sequence's
+ * the host's sum of the lengths or an upper bound of it, or 0 when it is not known (a sum smaller than the real
+ * one sets BARQKV_S_CAPACITY for batches of up to 256 sequences, whose launch is sized from it).  The two fix how many splits a sequence's
  * pages are cut into (with the sum the splits are sized to fill the GPU's resident CTAs once or twice
  * when the batch is small); pass the same values to both functions.  workspace: 16-byte aligned device
  * scratch of barqkv_paged_decode_workspace_bytes(...) bytes (0 when one split suffices); its contents on

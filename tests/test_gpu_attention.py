@@ -126,6 +126,31 @@ def test_decode_attention_with_pools_in_separate_allocations():
     assert backend.read_status(DEV) == 0
 
 
+def test_decode_attention_flags_an_understated_sum_of_lengths():
+    """The launch of a small batch is sized from the caller's sum of the lengths; a sum smaller than the real one
+    must not lose pages silently: the status word says so (and a correct sum clears the matter)."""
+    from barqtrain_b200 import BlockTableKVCache, _ffi
+
+    backend = _ffi.require_cuda_backend()
+    dtype, hkv, group, D, ps = torch.bfloat16, 2, 4, 128, 16
+    lens = [1500, 2100, 900]
+    n = len(lens)
+    g = torch.Generator(device=DEV).manual_seed(41)
+    cache = BlockTableKVCache(1, hkv, D, page_size=ps, num_pages=sum(-(-x // ps) for x in lens) + 2, max_seqs=n,
+                              max_blocks_per_seq=-(-max(lens) // ps), dtype=dtype, device=DEV, seed=41)
+    slots = [cache.open(i) for i in range(n)]
+    k = torch.randn(sum(lens), hkv, D, generator=g, device=DEV, dtype=torch.float32).to(dtype)
+    cache.append_step(slots, lens, [k], [k])
+    q = torch.randn(n, hkv * group, D, generator=g, device=DEV, dtype=torch.float32).to(dtype)
+    gb, want = _reference(cache, 0, slots, q, D ** -0.5)
+    assert backend.read_status(DEV) == 0
+    cache.decode_attention(0, gb, q, total_len=600)
+    assert backend.read_status(DEV) == _ffi.S_CAPACITY
+    got = cache.decode_attention(0, gb, q, total_len=sum(lens) + 100)        # an upper bound is fine
+    assert bool(((got.float() - want).abs() <= ATOL + RTOL * want.abs()).all())
+    assert backend.read_status(DEV) == 0
+
+
 def test_decode_attention_argument_limits():
     from barqtrain_b200 import BlockTableKVCache, _ffi
 
