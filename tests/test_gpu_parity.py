@@ -415,6 +415,53 @@ def test_update_of_all_layers_in_one_call_for_any_number_of_outputs(backend, num
             assert torch.equal(S.bits_dev(got_k[:, :gb.total]), S.bits_dev(want_k)), (step, layer)
             assert torch.equal(S.bits_dev(got_v[:, :gb.total]), S.bits_dev(want_v)), (step, layer)
         assert torch.equal(S.bits_dev(fast.pools), S.bits_dev(slow.pools)), step
+        # inside the call a launch leaves its hand-out counters to its neighbour to clear; after it all are zero
+        assert int(backend.work_words(DEV).abs().sum()) == 0, step
+    fast.check_device_status()
+    assert backend.read_status(DEV) == 0
+
+
+@pytest.mark.parametrize("L", [1, 2, 3, 5])
+def test_update_of_all_layers_leaves_the_counters_zero_for_any_number_of_layers(backend, L):
+    """``update_layers`` chains its launches: each clears the hand-out counters of its neighbours and only the
+    last launch of a chain its own.  For chains of every length, on one stream and on two, the counters must be
+    zero after the call and the next call (same buffer) must gather the right rows."""
+    from barqtrain_b200 import BlockTableKVCache
+
+    H, D, ps, dtype = 2, 128, 16, torch.bfloat16
+    lens = [700, 31, 1200, 64]
+    n = len(lens)
+    g = torch.Generator().manual_seed(50 + L)
+    pages = sum(-(-(x + 8) // ps) for x in lens)
+    order = torch.randperm(pages, generator=g).tolist()
+
+    def make():
+        c = BlockTableKVCache(L, H, D, page_size=ps, num_pages=pages, max_seqs=n, max_blocks_per_seq=-(-(max(lens) + 8) // ps),
+                              dtype=dtype, device=DEV, free_order=order)
+        return c, [c.open(i) for i in range(n)]
+
+    fast, fs = make()
+    slow, ss = make()
+    k0 = [S.randn(g, (sum(lens), H, D), dtype).to(DEV) for _ in range(L)]
+    fast.append_step(fs, lens, k0, k0)
+    slow.append_step(ss, lens, k0, k0)
+    cap = sum(lens) + 8 * n
+    outs = [(torch.zeros(H, cap, D, dtype=dtype, device=DEV), torch.zeros(H, cap, D, dtype=dtype, device=DEV))
+            for _ in range(L)]
+    for step in range(6):
+        k = S.randn(g, (L, n, H, D), dtype).to(DEV)
+        new = fast.begin_append(fs, [1] * n)
+        fast.end_append(new)
+        full = fast.begin_gather(fs)
+        fast.update_layers(new, full, k, k, outs, "HND", tokens_hint=cap, one_stream=step % 3 == 2)
+        torch.cuda.synchronize()
+        assert int(backend.work_words(DEV).abs().sum()) == 0, step
+        slow.append_step(ss, [1] * n, list(k.unbind(0)), list(k.unbind(0)))
+        gb = slow.begin_gather(ss)
+        for layer in range(L):
+            want_k, want_v = slow.gather(layer, gb, "HND")
+            assert torch.equal(S.bits_dev(outs[layer][0][:, :gb.total]), S.bits_dev(want_k)), (step, layer)
+            assert torch.equal(S.bits_dev(outs[layer][1][:, :gb.total]), S.bits_dev(want_v)), (step, layer)
     fast.check_device_status()
     assert backend.read_status(DEV) == 0
 
