@@ -60,7 +60,7 @@ class RowsLayout(ctypes.Structure):
 
 
 EXPORTS = ("barqkv_version", "barqkv_last_error", "barqkv_sm_count", "barqkv_launch_count",
-           "barqkv_append", "barqkv_append_layers", "barqkv_append_rope", "barqkv_upload",
+           "barqkv_append", "barqkv_append_layers", "barqkv_append_each_layer", "barqkv_append_rope", "barqkv_upload",
            "barqkv_max_length", "barqkv_table_scatter", "barqkv_copy_pages", "barqkv_append_legacy",
            "barqkv_gather", "barqkv_gather_layers", "barqkv_update", "barqkv_paged_decode_attention",
            "barqkv_paged_decode_workspace_bytes", "barqkv_update_layers", "barqkv_gather_wait_selftest",
@@ -126,6 +126,9 @@ class CudaBackend:
         lib.barqkv_append_layers.restype = _i32
         lib.barqkv_append_layers.argtypes = [P(PoolLayout), _ptr, _ptr, _i32, _i64, P(BlockTable), _ptr, _ptr,
                                              _i32, _i32, _i32, _ptr, _ptr, P(RowsLayout), _i64, _ptr, _ptr, _i32, _ptr]
+        lib.barqkv_append_each_layer.restype = _i32
+        lib.barqkv_append_each_layer.argtypes = [P(PoolLayout), _ptr, _ptr, _i32, _i64, P(BlockTable), _ptr, _ptr,
+                                                 _i32, _i32, _i32, _ptr, _ptr, P(RowsLayout), _ptr, _ptr, _i32, _ptr]
         lib.barqkv_append_rope.restype = _i32
         lib.barqkv_append_rope.argtypes = [P(PoolLayout), _ptr, _ptr, P(BlockTable), _ptr, _ptr, _i32, _i32, _i32,
                                            _ptr, _ptr, P(RowsLayout), _ptr, _ptr, _i64, _i32, _ptr, _ptr]

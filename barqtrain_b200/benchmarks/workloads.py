@@ -27,10 +27,13 @@ def _events():
 
 
 def chunked_prefill(world: int, rank: int, device, steps: int, warmup: int, page_size: int = 16,
-                    layers: int = 32, all_layers: bool = False, heads: int = 0, sync=lambda: None) -> Dict:
+                    layers: int = 32, all_layers: bool = False, heads: int = 0, calls_per_layer: bool = False,
+                    sync=lambda: None) -> Dict:
     """32 layers, 8 KV heads, head_dim 128, fp16; 16 sequences of 8192 tokens appended in 2048-token
     chunks into a pool shuffled by a seeded permutation.  A step appends one chunk of every sequence
-    in every layer; after four chunks the sequences are released and re-opened."""
+    in every layer; after four chunks the sequences are released and re-opened.  One launch per layer, issued
+    by one native call for the step (``calls_per_layer``: by one call from Python per layer, as a model's forward
+    pass would; ``all_layers``: one launch for all layers)."""
     H = heads or kv_head_shard(8, world, rank)[1]
     B, chunk, chunks = 16, 2048, 4
     dtype = torch.float16
@@ -46,6 +49,7 @@ def chunked_prefill(world: int, rank: int, device, steps: int, warmup: int, page
     for layer in range(layers):
         k_all[layer] = torch.randn(B * chunk, H, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
         v_all[layer] = torch.randn(B * chunk, H, D, generator=gen, device=device, dtype=torch.float32).to(dtype)
+    k_rows, v_rows = list(k_all.unbind(0)), list(v_all.unbind(0))
     state = {"ids": list(range(B)), "slots": [cache.open(i) for i in range(B)], "done": 0, "next": B}
 
     def step():
@@ -59,9 +63,11 @@ def chunked_prefill(world: int, rank: int, device, steps: int, warmup: int, page
         batch = cache.begin_append(state["slots"], [chunk] * B)
         if all_layers:
             cache.append_layers(batch, k_all, v_all)
-        else:
+        elif calls_per_layer:
             for layer in range(layers):
                 cache.append(layer, batch, k_all[layer], v_all[layer])
+        else:
+            cache.append_each_layer(batch, k_rows, v_rows)
         cache.end_append(batch)
         state["done"] += 1
 
@@ -80,7 +86,9 @@ def chunked_prefill(world: int, rank: int, device, steps: int, warmup: int, page
     return {"bytes": per_step * steps, "ms": ms, "tokens": B * chunk * steps,
             "launches": (1 if all_layers else layers) * steps,
             "config": {"workload": "chunked-prefill",
-                       "launch": "all layers per launch" if all_layers else "one per layer",
+                       "launch": "all layers per launch" if all_layers else
+                                 "one per layer, one call from Python each" if calls_per_layer else
+                                 "one per layer, all issued by one native call",
                        "layers": layers, "kv_heads_per_gpu": H, "dtype": "fp16",
                        "page_size": page_size, "sequences": B, "chunk_tokens": chunk,
                        "step": "append one 2048-token chunk of 16 sequences in every layer",

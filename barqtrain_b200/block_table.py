@@ -611,11 +611,50 @@ class BlockTableKVCache:
     def end_append(self, batch: _Descriptor) -> None:
         self.lengths[batch.slots_np] = batch.after_np
 
+    def append_each_layer(self, batch: _Descriptor, k_layers, v_layers) -> None:
+        """Every layer's append of a step from one native call, one launch per layer: ``k_layers[l]`` /
+        ``v_layers[l]`` are layer ``l``'s packed rows ``[total_tokens, kv_heads, head_dim]``, separate tensors of
+        one shape, dtype and stride pattern (``barqkv_append_each_layer``).  Same result as ``append`` layer by
+        layer, without the host's share of every call between the launches; layers whose tensors differ in their
+        strides are appended one by one."""
+        total = self._current(batch).total
+        if total == 0:
+            return
+        if len(k_layers) != self.num_layers or len(v_layers) != self.num_layers:
+            raise ValueError(f"need the rows of all {self.num_layers} layers")
+        first = k_layers[0]
+        want = (total, self.num_kv_heads, self.head_dim)
+        strides = first.stride()
+        same = strides[2] == 1
+        for k, v in zip(k_layers, v_layers):
+            if tuple(k.shape) != want or v.shape != k.shape or k.dtype != self.dtype or v.dtype != self.dtype \
+                    or k.device != self.device or v.device != self.device:
+                raise ValueError(f"every layer's new rows must be {want} in the cache dtype on the cache device")
+            same = same and k.stride() == strides and v.stride() == strides
+        if not same:
+            for layer in range(self.num_layers):
+                self.append(layer, batch, k_layers[layer], v_layers[layer])
+            return
+        rows_ref = self._rows.get(strides)
+        if rows_ref is None:
+            rows_ref = self._rows[strides] = self._rows_ref(0, strides[0], strides[1])
+        pointers = ctypes.c_void_p * self.num_layers
+        k_ptrs = pointers(*[k.data_ptr() for k in k_layers])
+        v_ptrs = pointers(*[v.data_ptr() for v in v_layers])
+        batch.used_at = self._uploads
+        # the first launch waits for whatever precedes it (a launch of this cache that still hands out pages from
+        # the first counter pair, say); the chain behind it is the library's
+        rc = self.backend.lib.barqkv_append_each_layer(
+            self._pool_ref, self._k_ptr[0], self._v_ptr[0], self.num_layers, self.pools.stride(0), batch.table_ref,
+            batch.p_first, batch.p_cu, batch.n, 0, total, k_ptrs, v_ptrs, rows_ref, self._status_ptr,
+            self._work_base(batch.stream), 0, batch.stream)
+        if rc:
+            self.backend._check(rc)
+
     def append_step(self, slots: Sequence[int], counts: Sequence[int], k_layers, v_layers) -> None:
         """All layers of one step: ``k_layers[l]`` / ``v_layers[l]`` are that layer's packed rows."""
         batch = self.begin_append(slots, counts)
-        for layer in range(self.num_layers):
-            self.append(layer, batch, k_layers[layer], v_layers[layer])
+        self.append_each_layer(batch, k_layers, v_layers)
         self.end_append(batch)
 
     # -- gather -------------------------------------------------------------------

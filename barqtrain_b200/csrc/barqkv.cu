@@ -953,6 +953,8 @@ gather_bulk_kernel(const GatherArgs a, const __grid_constant__ CUtensorMap out_m
 struct AppendBulkArgs {
     int stages;
     int32_t* work;          // [0] next tile to hand out, [1] CTAs finished
+    int32_t* zero_ahead;    // another counter pair, cleared once the kernel before this one has finished (chained launches)
+    int rearm;              // the last CTA to finish clears `work` (else a later launch's zero_ahead does)
     int group_tiles, first_group;
     int tensor_load;        // 1: tiled TMA loads (token-major source); 0: plain bulk copies (rows adjacent)
     int layers;
@@ -991,8 +993,17 @@ append_bulk_kernel(const AppendArgs a, const AppendBulkArgs x, const __grid_cons
         for (int s = 0; s < S; ++s) mbar_init(smem_addr(&s_bar[s]), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    // chained launches alternate between two counter pairs and clear each other's (see gather_bulk_kernel)
+    auto clear_other_pair = [&]() {
+        if (x.zero_ahead && blockIdx.x == 0 && lane == 0) {
+            x.zero_ahead[0] = 0;
+            x.zero_ahead[1] = 0;
+            __threadfence();
+        }
+    };
     if (!a.early) {
         pdl_wait_for_predecessor();
+        clear_other_pair();
         pdl_let_successor_in();
     }
     int early_first = 0;
@@ -1077,6 +1088,7 @@ append_bulk_kernel(const AppendArgs a, const AppendBulkArgs x, const __grid_cons
     if (a.early) {
         if (more) stage_group();
         pdl_wait_for_predecessor();     // from here on the new rows are read and the pools written
+        clear_other_pair();
         pdl_let_successor_in();
     }
 
@@ -1157,7 +1169,7 @@ append_bulk_kernel(const AppendArgs a, const AppendBulkArgs x, const __grid_cons
         }
         if (lane == 0) raise(a.status, BARQKV_S_TIMEOUT);
     }
-    if (lane == 0) {
+    if (x.rearm && lane == 0) {
         __threadfence();
         const int finished = atomicAdd(x.work + 1, 1);
         if (finished == (int)gridDim.x - 1) {
@@ -1461,7 +1473,9 @@ static int append_common(const barqkv_pool_layout* pool, void* k_pool, void* v_p
                          int32_t n, int32_t tokens_per_entry, int32_t total_tokens,
                          const void* k_new, const void* v_new, const barqkv_rows_layout* new_rows,
                          int32_t* status, int32_t* work, int32_t flags, barqkv_stream_t stream,
-                         int32_t layers, int64_t pool_layer_stride, int64_t new_layer_stride) {
+                         int32_t layers, int64_t pool_layer_stride, int64_t new_layer_stride,
+                         int32_t* zero_ahead = nullptr, bool rearm = true, bool* used_counters = nullptr) {
+    if (used_counters) *used_counters = false;
     if (int rc = check_pool(pool)) return rc;
     if (flags & ~BARQKV_FLAG_DESC_STABLE) return fail(BARQKV_E_INVALID, "append: unknown flag");
     if (layers <= 0 || layers > 65535) return fail(BARQKV_E_INVALID, "append: layers must be in 1..65535");
@@ -1534,6 +1548,8 @@ static int append_common(const barqkv_pool_layout* pool, void* k_pool, void* v_p
             AppendBulkArgs x;
             memset(&x, 0, sizeof(x));
             x.work = work;
+            x.zero_ahead = zero_ahead;
+            x.rearm = rearm || !zero_ahead ? 1 : 0;
             x.tensor_load = tensor_load ? 1 : 0;
             x.layers = layers;
             x.wait_cycles = kWaitCycles;
@@ -1572,6 +1588,7 @@ static int append_common(const barqkv_pool_layout* pool, void* k_pool, void* v_p
                                             map_k, map_v);
                     if (ce == cudaSuccess) ce = cudaGetLastError();
                     if (ce == cudaSuccess) g_launches.fetch_add(1, std::memory_order_relaxed);
+                    if (ce == cudaSuccess && used_counters) *used_counters = true;
                     return ce == cudaSuccess ? 0 : fail_cuda("append launch", ce);
                 }
             }
@@ -1606,6 +1623,46 @@ int barqkv_append_layers(const barqkv_pool_layout* pool, void* k_pool, void* v_p
                          int64_t new_layer_stride, int32_t* status, int32_t* work, int32_t flags, barqkv_stream_t stream) {
     return append_common(pool, k_pool, v_pool, table, seq_start, cu_new, n, tokens_per_entry, total_tokens, k_new, v_new,
                          new_rows, status, work, flags, stream, layers, pool_layer_stride, new_layer_stride);
+}
+
+int barqkv_append_each_layer(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,
+                             int32_t layers, int64_t pool_layer_stride,
+                             const barqkv_block_table* table,
+                             const int32_t* seq_start, const int32_t* cu_new,
+                             int32_t n, int32_t tokens_per_entry, int32_t total_tokens,
+                             const void* const* k_new, const void* const* v_new, const barqkv_rows_layout* new_rows,
+                             int32_t* status, int32_t* work, int32_t flags, barqkv_stream_t stream) {
+    if (layers <= 0 || layers > 65535) return fail(BARQKV_E_INVALID, "append_each_layer: bad layer count");
+    if (pool_layer_stride < 0) return fail(BARQKV_E_INVALID, "append_each_layer: negative layer stride");
+    if (!k_new || !v_new || !pool || !k_pool || !v_pool) return fail(BARQKV_E_INVALID, "append_each_layer: null pointer argument");
+    if (flags & ~BARQKV_FLAG_DESC_STABLE) return fail(BARQKV_E_INVALID, "append_each_layer: unknown flag");
+    const long long e = pool->elem_bytes;
+    const bool chained = work && g_knobs.zero_ahead != 0;
+    bool pending = false;       // the launch before left its counters for its successor to clear
+    int rc = 0;
+    for (int l = 0; l < layers; ++l) {
+        // One launch per layer.  From the second on each is a programmatic dependent of the one before, whose
+        // batch description it shares; the launches alternate between the two counter pairs of `work`, clear
+        // each other's, and only the last one counts its finished CTAs to clear its own.
+        unsigned char* kp = static_cast<unsigned char*>(k_pool) + (long long)l * pool_layer_stride * e;
+        unsigned char* vp = static_cast<unsigned char*>(v_pool) + (long long)l * pool_layer_stride * e;
+        const bool last = l == layers - 1;
+        bool counters = false;
+        rc = append_common(pool, kp, vp, table, seq_start, cu_new, n, tokens_per_entry, total_tokens, k_new[l], v_new[l],
+                           new_rows, status, work ? work + 2 * (l & 1) : nullptr, l > 0 ? BARQKV_FLAG_DESC_STABLE : flags,
+                           stream, 1, 0, 0, chained ? work + 2 * ((l + 1) & 1) : nullptr, last, &counters);
+        if (rc) break;
+        if (counters) {
+            pending = chained && !last;                            // and it cleared its predecessor's pair
+        } else if (pending) {
+            // this layer's rows took the kernel without counters (another alignment): nobody cleared for the one before
+            cudaMemsetAsync(work, 0, 4 * sizeof(int32_t), static_cast<cudaStream_t>(stream));
+            pending = false;
+        }
+    }
+    // an error broke the chain off: the launch that left its counters to a successor has none
+    if (pending) cudaMemsetAsync(work, 0, 4 * sizeof(int32_t), static_cast<cudaStream_t>(stream));
+    return rc;
 }
 
 int barqkv_append_rope(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,

@@ -1002,7 +1002,8 @@ def run_extra(args):
             dist.barrier()
         torch.cuda.synchronize(device)
 
-    kwargs = {"page_size": args.page_size, "all_layers": args.all_layers} if args.workload == "prefill" else {}
+    kwargs = {"page_size": args.page_size, "all_layers": args.all_layers,
+              "calls_per_layer": args.eager} if args.workload == "prefill" else {}
     if args.workload == "gather70b":
         kwargs["all_layers"] = args.all_layers
     if args.workload == "decode-attn":

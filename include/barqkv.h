@@ -24,7 +24,7 @@
 extern "C" {
 #endif
 
-#define BARQKV_VERSION 105 /* major*100 + minor */
+#define BARQKV_VERSION 106 /* major*100 + minor */
 
 /* host-side return codes */
 #define BARQKV_OK 0
@@ -157,6 +157,28 @@ int barqkv_append(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,
                   int32_t n, int32_t tokens_per_entry, int32_t total_tokens,
                   const void* k_new, const void* v_new, const barqkv_rows_layout* new_rows,
                   int32_t* status, int32_t* work, int32_t flags, barqkv_stream_t stream);
+
+/*
+ * barqkv_append for `layers` layers from one call, one launch per layer: layer l uses the pools at
+ * k_pool/v_pool + l*pool_layer_stride elements and the new rows at k_new[l] / v_new[l] (host arrays of
+ * `layers` device pointers; every layer's rows share `new_rows`); the block table, positions and counts are
+ * shared.  Equals `layers` calls of barqkv_append - what the reference does with one paged_kv_append_ per
+ * BarqPagedKVCacheLayer (python/barqtrain/kv_cache.py:207-219) - without their host cost between launches: from
+ * the second on every launch is a programmatic dependent of the one before, and for page-sized appends the
+ * launches alternate between the two counter pairs of `work`, clear each other's, and only the last counts its
+ * finished blocks to clear its own.  work: device int32[4], zero before its first use and again when the
+ * call's kernels have run, or NULL.  flags: 0 or BARQKV_FLAG_DESC_STABLE for the first layer's launch.  For
+ * callers that hold a step's rows of every layer in separate buffers (a chunk of a transferred or restored
+ * cache, a prefill whose rows were kept per layer); with one buffer for all layers barqkv_append_layers
+ * needs a single launch.
+ */
+int barqkv_append_each_layer(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,
+                             int32_t layers, int64_t pool_layer_stride,
+                             const barqkv_block_table* table,
+                             const int32_t* seq_start, const int32_t* cu_new,
+                             int32_t n, int32_t tokens_per_entry, int32_t total_tokens,
+                             const void* const* k_new, const void* const* v_new, const barqkv_rows_layout* new_rows,
+                             int32_t* status, int32_t* work, int32_t flags, barqkv_stream_t stream);
 
 /*
  * barqkv_append for `layers` layers in ONE launch: layer l uses the pools at

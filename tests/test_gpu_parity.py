@@ -421,6 +421,55 @@ def test_update_of_all_layers_in_one_call_for_any_number_of_outputs(backend, num
     assert backend.read_status(DEV) == 0
 
 
+@pytest.mark.parametrize("L,odd_one", [(1, None), (2, None), (4, 2), (5, 0), (5, 4), (3, 1)])
+def test_append_of_every_layer_from_one_call(backend, L, odd_one):
+    """``append_each_layer`` (one native call, one chained launch per layer) against ``append`` layer by layer on a
+    twin cache: page-sized chunks (the launches hand pages out through counters that they clear for one another)
+    and single tokens, with one layer's rows at an address that is not 16-byte aligned (that layer takes the
+    kernel without counters in the middle of the chain).  Same pools, counters zero after every call."""
+    from barqtrain_b200 import BlockTableKVCache
+
+    H, D, ps, dtype = 2, 128, 16, torch.float16
+    counts_per_step = ([700, 48, 1200, 16], [64, 17, 33, 512], [1, 1, 1, 1])
+    n = 4
+    g = torch.Generator().manual_seed(70 + L)
+    pages = sum(-(-sum(c[i] for c in counts_per_step) // ps) + 1 for i in range(n))
+    order = torch.randperm(pages, generator=g).tolist()
+
+    def make():
+        c = BlockTableKVCache(L, H, D, page_size=ps, num_pages=pages, max_seqs=n, max_blocks_per_seq=pages, dtype=dtype,
+                              device=DEV, free_order=order)
+        return c, [c.open(i) for i in range(n)]
+
+    fast, fs = make()
+    slow, ss = make()
+    for counts in counts_per_step:
+        total = sum(counts)
+        rows_k, rows_v = [], []
+        for layer in range(L):
+            if layer == odd_one:      # same shape and strides, but the rows start 6 bytes into a 16-byte line
+                flat = S.randn(g, (2 * total * H * D + 3,), dtype).to(DEV)
+                rows_k.append(flat[3:3 + total * H * D].view(total, H, D))
+                rows_v.append(flat[3 + total * H * D:].view(total, H, D))
+            else:
+                rows_k.append(S.randn(g, (total, H, D), dtype).to(DEV))
+                rows_v.append(S.randn(g, (total, H, D), dtype).to(DEV))
+        batch = fast.begin_append(fs, counts)
+        before = backend.launches
+        fast.append_each_layer(batch, rows_k, rows_v)
+        assert backend.launches - before == L
+        fast.end_append(batch)
+        torch.cuda.synchronize()
+        assert int(backend.work_words(DEV).abs().sum()) == 0, counts
+        batch = slow.begin_append(ss, counts)
+        for layer in range(L):
+            slow.append(layer, batch, rows_k[layer], rows_v[layer])
+        slow.end_append(batch)
+        assert torch.equal(S.bits_dev(fast.pools), S.bits_dev(slow.pools)), counts
+    fast.check_device_status()
+    assert backend.read_status(DEV) == 0
+
+
 @pytest.mark.parametrize("L", [1, 2, 3, 5])
 def test_update_of_all_layers_leaves_the_counters_zero_for_any_number_of_layers(backend, L):
     """``update_layers`` chains its launches: each clears the hand-out counters of its neighbours and only the
