@@ -97,11 +97,12 @@ def chunked_prefill(world: int, rank: int, device, steps: int, warmup: int, page
 
 
 def gather_70b(world: int, rank: int, device, steps: int, warmup: int, layers: int = 80, heads: int = 0,
-               all_layers: bool = False, sync=lambda: None) -> Dict:
+               all_layers: bool = False, calls_per_layer: bool = False, sync=lambda: None) -> Dict:
     """80 layers, 8 KV heads sharded by head, head_dim 128, bf16, page 16; 32 sequences with seeded
     lengths log-uniform in [1k, 32k]; fragmented block tables.  A step gathers every sequence to
     contiguous ``[H, sum_len, D]`` K and V in every layer: one launch per layer into two alternating
-    outputs, or (``all_layers``) one launch for all layers into ``[layers, H, sum_len, D]``."""
+    outputs, the step's launches issued by one native call (``calls_per_layer``: by one call from Python per
+    layer), or (``all_layers``) one launch for all layers into ``[layers, H, sum_len, D]``."""
     H = heads or kv_head_shard(8, world, rank)[1]
     dtype = torch.bfloat16
     g = torch.Generator().manual_seed(1238)
@@ -132,8 +133,11 @@ def gather_70b(world: int, rank: int, device, steps: int, warmup: int, layers: i
                 for _ in range(2)]
 
         def step():
-            for layer in range(layers):
-                cache.gather(layer, gb, "HND", out=outs[layer & 1])
+            if calls_per_layer:
+                for layer in range(layers):
+                    cache.gather(layer, gb, "HND", out=outs[layer & 1])
+            else:
+                cache.gather_each_layer(gb, outs, "HND")
 
     for _ in range(max(warmup, 1)):
         step()
@@ -148,7 +152,9 @@ def gather_70b(world: int, rank: int, device, steps: int, warmup: int, layers: i
     cache.check_device_status()
     per_step = 4 * total * H * D * 2 * layers
     return {"bytes": per_step * steps, "ms": ms, "tokens": total * steps, "launches": (1 if all_layers else layers) * steps,
-            "config": {"workload": "llama3-70b-gather", "launch": "all layers per launch" if all_layers else "one per layer",
+            "config": {"workload": "llama3-70b-gather", "launch": "all layers per launch" if all_layers else
+                       "one per layer, one call from Python each" if calls_per_layer else
+                       "one per layer, all issued by one native call (neighbouring layers overlap at their ends)",
                        "layers": layers, "kv_heads_per_gpu": H, "dtype": "bf16",
                        "page_size": 16, "sequences": 32, "sum_len_tokens": total,
                        "lengths": "log-uniform [1024, 32768] seeded",

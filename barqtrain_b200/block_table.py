@@ -914,6 +914,35 @@ class BlockTableKVCache:
         if rc:
             self.backend._check(rc)
 
+    def gather_each_layer(self, full: _Descriptor, outs: Sequence[Tuple[torch.Tensor, torch.Tensor]], layout: str = "HND",
+                          mode: Optional[str] = None, tokens_hint: Optional[int] = None, one_stream: bool = False) -> None:
+        """``gather`` of every layer with one native call, one launch per layer (``barqkv_update_layers`` with
+        nothing to append): layer ``l`` writes to ``outs[l % len(outs)]``.  The launches are chained and, with an
+        even number of distinct output pairs, neighbouring layers run side by side on two streams, as in
+        ``update_layers``; work queued on the caller's stream afterwards sees every layer done."""
+        self._current(full)
+        L = self.num_layers
+        if full.n > _GATHER_MAX_ENTRIES or full.total == 0:
+            for layer in range(L):
+                self.gather(layer, full, layout, out=outs[layer % len(outs)], mode=mode)
+            return
+        out_ref = None
+        k_ptrs, v_ptrs = (ctypes.c_void_p * len(outs))(), (ctypes.c_void_p * len(outs))()
+        for i, out in enumerate(outs):
+            k_out, v_out, ref, _ = self._output(layout, full.total, out, full.n)
+            if out_ref is not None and ref is not out_ref:
+                raise ValueError("gather_each_layer: all output pairs must have the same shape")
+            out_ref = ref
+            k_ptrs[i], v_ptrs[i] = k_out.data_ptr(), v_out.data_ptr()
+        rc = self.backend.lib.barqkv_update_layers(
+            self._pool_ref, self._k_ptr[0], self._v_ptr[0], L, self.pools.stride(0), full.table_ref, full.p_first, None,
+            full.n, 0, 0, None, None, None, 0, full.p_cu, tokens_hint or full.total, k_ptrs, v_ptrs, len(outs), out_ref,
+            _ffi.MODES[mode or self.gather_mode] | (_ffi.FLAG_ONE_STREAM if one_stream else 0),
+            self._status_ptr, full.work, full.p_first, full.stream)
+        self.backend._work_turn[(self.device.index, full.stream)] = (L & 1)
+        if rc:
+            self.backend._check(rc)
+
     # -- attention straight from the pages (decode) ---------------------------------------
     def decode_attention(self, layer: int, full: _Descriptor, q: torch.Tensor, scale: Optional[float] = None,
                          out: Optional[torch.Tensor] = None, new_rows: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,

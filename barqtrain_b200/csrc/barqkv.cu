@@ -2145,16 +2145,18 @@ int barqkv_update_layers(const barqkv_pool_layout* pool, void* k_pool, void* v_p
     if (n < 0 || total_new_tokens < 0) return fail(BARQKV_E_INVALID, "update_layers: negative batch size or token count");
     if (n == 0) return 0;
     if (int rc = check_pool(pool)) return rc;
-    if (!k_pool || !v_pool || !seq_start || !new_rows || (total_new_tokens && (!k_new || !v_new)))
+    if (!k_pool || !v_pool || !seq_start || (total_new_tokens && (!k_new || !v_new || !new_rows)))
         return fail(BARQKV_E_INVALID, "update_layers: null pointer argument");
     if (!cu_new && (tokens_per_entry < 0 || (long long)tokens_per_entry * n != total_new_tokens))
         return fail(BARQKV_E_INVALID, "update_layers: without cu_new, total_new_tokens must equal n * tokens_per_entry");
-    if (new_rows->packed && !cu_new && tokens_per_entry > 1)
+    if (total_new_tokens && new_rows->packed && !cu_new && tokens_per_entry > 1)
         return fail(BARQKV_E_INVALID, "update_layers: packed rows with more than one token per entry need cu_new");
     const long long e = pool->elem_bytes;
     const bool one_stream = (mode & BARQKV_FLAG_ONE_STREAM) != 0;
     mode &= ~(BARQKV_FLAG_DESC_STABLE | BARQKV_FLAG_ONE_STREAM);   // the first layer waits for whatever precedes it; the rest are chained here
-    const bool try_fused = total_new_tokens > 0 && total_new_tokens <= (long long)n * pool->page_size;
+    // nothing to append: the same chain of launches, each a plain gather (seq_start then holds the lengths)
+    const bool only_gather = total_new_tokens == 0;
+    const bool try_fused = only_gather || total_new_tokens <= (long long)n * pool->page_size;
     bool fused_ok = try_fused;
 
     // Two layers next to one another touch nothing in common when they write to different outputs: each reads
@@ -2171,6 +2173,12 @@ int barqkv_update_layers(const barqkv_pool_layout* pool, void* k_pool, void* v_p
     for (int i = 0; overlap && i < num_out; ++i)
         for (int j = 0; j < i; ++j)
             if (k_out[i] == k_out[j] || v_out[i] == v_out[j] || k_out[i] == v_out[j] || v_out[i] == k_out[j]) overlap = false;
+    // Launches may leave their counters to their successor only if every layer takes the same kernel: the one
+    // with counters needs 16-byte aligned rows, so the layers' pools and outputs must agree in that.
+    bool same_kernel = layers == 1 || multiple(pool_layer_stride * e, 16);
+    for (int i = 1; same_kernel && i < num_out; ++i)
+        same_kernel = aligned(k_out[i], 16) == aligned(k_out[0], 16) && aligned(v_out[i], 16) == aligned(v_out[0], 16);
+    if (total_new_tokens) same_kernel = same_kernel && multiple(new_layer_stride * e, 16);
     std::unique_lock<std::mutex> lane_lock;
     if (overlap) {
         lane_lock = std::unique_lock<std::mutex>(dev->lane_mu);
@@ -2211,16 +2219,17 @@ int barqkv_update_layers(const barqkv_pool_layout* pool, void* k_pool, void* v_p
             LaunchOpts opts;
             opts.after_own_kernel = overlap ? l >= 2 : l > 0;
             int32_t* pair = !work ? nullptr : work + 2 * (overlap ? (l & 3) : (l & 1));
-            if (work && g_knobs.zero_ahead != 0) {
+            if (work && g_knobs.zero_ahead != 0 && same_kernel) {
                 // a chain alternates between two pairs; each launch clears the one it does not use, and only the
                 // chain's last launch counts its finished CTAs to clear its own
                 opts.zero_ahead = work + 2 * (overlap ? ((l + 2) & 3) : ((l + 1) & 1));
                 opts.rearm = l + (overlap ? 2 : 1) >= layers;
                 chained_pairs = true;
             }
-            const int rc = gather_common(pool, kp, vp, table, seq_start, cu_out, n, total_tokens_hint, ko, vo, out_rows, mode,
-                                         status, pair, overlap && (l & 1) ? static_cast<barqkv_stream_t>(dev->lane) : stream,
-                                         &fused, nullptr, opts);
+            const int rc = gather_common(pool, kp, vp, table, only_gather && seq_lens_after ? seq_lens_after : seq_start, cu_out, n,
+                                         total_tokens_hint, ko, vo, out_rows, mode, status, pair,
+                                         overlap && (l & 1) ? static_cast<barqkv_stream_t>(dev->lane) : stream,
+                                         only_gather ? nullptr : &fused, nullptr, opts);
             if (rc == 0) continue;
             if (rc != kNotFusable || l > 0) return done(rc);
             fused_ok = false;

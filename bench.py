@@ -1006,6 +1006,7 @@ def run_extra(args):
               "calls_per_layer": args.eager} if args.workload == "prefill" else {}
     if args.workload == "gather70b":
         kwargs["all_layers"] = args.all_layers
+        kwargs["calls_per_layer"] = args.eager
     if args.workload == "decode-attn":
         kwargs["eager"] = args.eager
     if args.workload == "churn":

@@ -344,6 +344,8 @@ int barqkv_update(const barqkv_pool_layout* pool, void* k_pool, void* v_pool,
  * output it overwrites, and runs beside layer l - 1.  Work issued to `stream` after the call is ordered
  * behind every layer.  Other calls, and calls whose `mode` carries BARQKV_FLAG_ONE_STREAM, keep all layers on
  * `stream`, each behind the one before.
+ * With total_new_tokens == 0 (k_new, v_new and new_rows may then be NULL; seq_start holds the lengths) the call
+ * is barqkv_gather for every layer, chained the same way.
  * work: device int32[8] scratch, zero before its first use (four counter pairs, so that launches that can be
  * on the device together never share one); zero again when the call's last kernels have run (inside the call
  * a launch clears the pair of its neighbours in its stream's chain, only the last launch of a chain its own).  For callers that have every layer's

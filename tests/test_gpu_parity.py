@@ -421,6 +421,44 @@ def test_update_of_all_layers_in_one_call_for_any_number_of_outputs(backend, num
     assert backend.read_status(DEV) == 0
 
 
+@pytest.mark.parametrize("L,num_out", [(1, 1), (2, 2), (3, 2), (5, 2), (4, 4), (5, 3)])
+def test_gather_of_every_layer_from_one_call(backend, L, num_out):
+    """``gather_each_layer`` (one native call, one chained launch per layer, neighbouring layers on two streams
+    when the outputs allow it) against ``gather`` layer by layer: the last ``num_out`` layers' outputs, read by
+    work queued behind the call, and counters that are zero again after it."""
+    from barqtrain_b200 import BlockTableKVCache
+
+    H, D, ps, dtype = 2, 128, 16, torch.bfloat16
+    lens = [700, 31, 1200, 64, 16]
+    n = len(lens)
+    g = torch.Generator().manual_seed(90 + L)
+    pages = sum(-(-x // ps) for x in lens) + 1
+    cache = BlockTableKVCache(L, H, D, page_size=ps, num_pages=pages, max_seqs=n, max_blocks_per_seq=-(-max(lens) // ps),
+                              dtype=dtype, device=DEV, free_order=torch.randperm(pages, generator=g).tolist())
+    slots = [cache.open(i) for i in range(n)]
+    rows = [S.randn(g, (sum(lens), H, D), dtype).to(DEV) for _ in range(L)]
+    cache.append_step(slots, lens, rows, rows[::-1])
+    gb = cache.begin_gather(slots)
+    outs = [(torch.zeros(H, gb.total, D, dtype=dtype, device=DEV), torch.zeros(H, gb.total, D, dtype=dtype, device=DEV))
+            for _ in range(num_out)]
+    for turn in range(4):
+        before = backend.launches
+        cache.gather_each_layer(gb, outs, "HND", one_stream=turn == 3)
+        assert backend.launches - before == L
+        snap = [(ko.clone(), vo.clone()) for ko, vo in outs]
+        torch.cuda.synchronize()
+        assert int(backend.work_words(DEV).abs().sum()) == 0, turn
+        for layer in range(L - min(num_out, L), L):
+            want_k, want_v = cache.gather(layer, gb, "HND")
+            assert torch.equal(S.bits_dev(snap[layer % num_out][0]), S.bits_dev(want_k)), (turn, layer)
+            assert torch.equal(S.bits_dev(snap[layer % num_out][1]), S.bits_dev(want_v)), (turn, layer)
+        for ko, vo in outs:
+            ko.zero_()
+            vo.zero_()
+    cache.check_device_status()
+    assert backend.read_status(DEV) == 0
+
+
 @pytest.mark.parametrize("L,odd_one", [(1, None), (2, None), (4, 2), (5, 0), (5, 4), (3, 1)])
 def test_append_of_every_layer_from_one_call(backend, L, odd_one):
     """``append_each_layer`` (one native call, one chained launch per layer) against ``append`` layer by layer on a
