@@ -2,10 +2,11 @@
  * barqkv - paged KV-cache append and gather for NVIDIA B200 (sm_100a).
  *
  * C ABI of libbarqkv.so.  Every entry point takes raw device pointers, plain
- * integers and a CUDA stream; nothing here allocates device memory, takes a
- * lock, or synchronises with the device (barqkv_max_length, whose job is a
- * blocking read of the lengths, is the one exception), and the library keeps no
- * mutable process-wide settings.  All functions return 0 on success
+ * integers and a CUDA stream; nothing here allocates device memory or
+ * synchronises with the device (barqkv_max_length, whose job is a blocking read
+ * of the lengths, is the one exception), the only lock is the one that guards
+ * the second stream of barqkv_update_layers, and the library keeps no mutable
+ * process-wide settings.  All functions return 0 on success
  * or a negative BARQKV_E_* code; barqkv_last_error() then holds a message for
  * the calling thread.  Work is enqueued on the given stream and runs
  * asynchronously; device-side guards (bad block-table entry, capacity) never
