@@ -648,6 +648,9 @@ class BlockTableKVCache:
             self._pool_ref, self._k_ptr[0], self._v_ptr[0], self.num_layers, self.pools.stride(0), batch.table_ref,
             batch.p_first, batch.p_cu, batch.n, 0, total, k_ptrs, v_ptrs, rows_ref, self._status_ptr,
             self._work_base(batch.stream), 0, batch.stream)
+        # the launches alternated between the stream's two counter pairs starting with the first: the next launch on
+        # this stream takes the pair the last layer did not use
+        self.backend._work_turn[(self.device.index, batch.stream)] = self.num_layers & 1
         if rc:
             self.backend._check(rc)
 
